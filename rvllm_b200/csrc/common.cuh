@@ -1,0 +1,86 @@
+// Shared helpers of the hand-written sm_100a kernels: dtype-generic loads and stores that
+// compute in float, warp and block reductions, and the launch-status convention.
+//
+// Every exported launcher returns 0 on success or a negative code for sizes it refuses
+// (never a wrong result); a CUDA launch error is returned as the positive cudaError_t.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define RV_OK 0
+#define RV_ERR_BAD_SIZE (-1)
+#define RV_ERR_BAD_DTYPE (-2)
+#define RV_ERR_ALIGNMENT (-3)
+#define RV_ERR_UNSUPPORTED (-4)
+
+#define RV_DTYPE_F32 0
+#define RV_DTYPE_BF16 1
+
+#define RV_EXPORT extern "C" __attribute__((visibility("default")))
+
+static inline int rv_launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? RV_OK : (int)e;
+}
+
+__device__ __forceinline__ float rv_to_float(float v) { return v; }
+__device__ __forceinline__ float rv_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T rv_from_float(float v);
+template <> __device__ __forceinline__ float rv_from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 rv_from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// A vector parameter (norm weight, bias) may be stored in either type, whatever the
+// activations are: a tensor that the checkpoint holds in 32 bits stays in 32 bits.
+__device__ __forceinline__ float rv_load_param(const void* p, int dtype, int i) {
+    return dtype == RV_DTYPE_F32 ? ((const float*)p)[i]
+                                 : __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+
+__device__ __forceinline__ float rv_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float rv_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block; every thread gets the result.  `scratch` holds 33 floats.
+__device__ __forceinline__ float rv_block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = rv_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = rv_warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__device__ __forceinline__ float rv_block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = rv_warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : -INFINITY;
+        t = rv_warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}

@@ -1,0 +1,196 @@
+// Row-wise kernels of the dense decoder: embedding gather, RMSNorm, rotary position
+// encoding fused with the q/k/v bias and the paged cache write, and SiLU-gated product.
+// All arithmetic is in float; storage is float or bfloat16.  Any row width is accepted.
+//
+// Formulas (paths inside the reference project):
+//   gather   kernels/embedding_gather_f16.cu:12-39          (row copy, out-of-range id -> zeros)
+//   rmsnorm  kernels/fused_rmsnorm_fp8_quant.cu:61-84        (x * rsqrt(mean(x^2) + eps) * gamma)
+//   rotary   v3/crates/rvllm-fused/src/reference.rs:177-203  (pairs i, i + head_dim/2)
+//   cache    v3/kernels/fused_rope_cache_fp8kv.cu:63-80      (slot < 0 is a padded row: skipped)
+//   silu     kernels/fused_silu_fp8_quant.cu:52-56           (row = gate | up; g / (1 + e^-g) * u)
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding / row gather
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                   T* __restrict__ out, int width, int rows_in_table) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < rows_in_table;
+    const T* src = table + (size_t)(ok ? id : 0) * width;
+    T* dst = out + (size_t)t * width;
+    const bool vec = ((width * sizeof(T)) % 16 == 0) &&
+                     ((reinterpret_cast<uintptr_t>(table) | reinterpret_cast<uintptr_t>(out)) % 16 == 0);
+    if (vec) {
+        const int n16 = width * sizeof(T) / 16;
+        const uint4* s = reinterpret_cast<const uint4*>(src);
+        uint4* d = reinterpret_cast<uint4*>(dst);
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) d[i] = ok ? s[i] : make_uint4(0, 0, 0, 0);
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = ok ? src[i] : rv_from_float<T>(0.f);
+    }
+}
+
+RV_EXPORT int rv_gather_rows(const void* table, const int* ids, void* out, int n_rows, int width,
+                             int rows_in_table, int dtype, cudaStream_t stream) {
+    if (n_rows < 0 || width <= 0 || rows_in_table <= 0) return RV_ERR_BAD_SIZE;
+    if (n_rows == 0) return RV_OK;
+    const int threads = width >= 2048 ? 256 : 128;
+    if (dtype == RV_DTYPE_F32)
+        gather_rows_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)table, ids, (float*)out, width, rows_in_table);
+    else if (dtype == RV_DTYPE_BF16)
+        gather_rows_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out, width, rows_in_table);
+    else
+        return RV_ERR_BAD_DTYPE;
+    return rv_launch_status();
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One block per row.  The row is read twice (the second read hits L1/L2); the sum of squares,
+// the reciprocal root and the product with gamma are formed in float and rounded once.
+template <typename T>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, const void* __restrict__ gamma, int gamma_dtype,
+                               T* __restrict__ out, int width, float eps) {
+    __shared__ float scratch[33];
+    const T* row = x + (size_t)blockIdx.x * width;
+    T* dst = out + (size_t)blockIdx.x * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = rv_to_float(row[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = rv_block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = rv_to_float(row[i]);
+        dst[i] = rv_from_float<T>(v * r * rv_load_param(gamma, gamma_dtype, i));
+    }
+}
+
+RV_EXPORT int rv_rmsnorm(const void* x, const void* gamma, int gamma_dtype, void* out, int n_rows,
+                         int width, float eps, int dtype, cudaStream_t stream) {
+    if (n_rows < 0 || width <= 0) return RV_ERR_BAD_SIZE;
+    if (n_rows == 0) return RV_OK;
+    int threads = 32;
+    while (threads < 1024 && threads * 4 < width) threads <<= 1;
+    if (dtype == RV_DTYPE_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)x, gamma, gamma_dtype, (float*)out, width, eps);
+    else if (dtype == RV_DTYPE_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>((const __nv_bfloat16*)x, gamma, gamma_dtype, (__nv_bfloat16*)out, width, eps);
+    else
+        return RV_ERR_BAD_DTYPE;
+    return rv_launch_status();
+}
+
+// ------------------------------------------------------------------ rotary + bias + cache write
+// qkv row layout: [q (nh*hd) | k (nkv*hd) | v (nkv*hd)].  Grid (T, nh + 2*nkv): one block per
+// (token, head).  q heads: add bias, rotate, write to q_out [T, nh*hd].  k heads: add bias,
+// rotate, write into the page of the token's slot.  v heads: add bias, write into the page.
+// Cache layer layout: [num_pages, 2 (k, v), nkv, page_size, hd].
+// cos/sin: float [table_rows, hd/2]; null pointers mean "no rotation".  With write_kv = 0 the
+// rows hold q alone (row_stride = nh*hd) and nothing is written to the cache.
+template <typename T>
+__global__ void rope_cache_write_kernel(const T* __restrict__ qkv, const void* __restrict__ bias, int bias_dtype,
+                                        const int* __restrict__ positions, const float* __restrict__ cos_t,
+                                        const float* __restrict__ sin_t, const int* __restrict__ slot_mapping,
+                                        T* __restrict__ cache, T* __restrict__ q_out, int nh, int nkv, int hd,
+                                        int page_size, int write_kv, int table_rows, int row_stride) {
+    const int t = blockIdx.x;
+    const int head = blockIdx.y;
+    const int half = hd >> 1;
+    const T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
+    const int col0 = head * hd;
+    int pos = positions[t];
+    if (pos < 0) pos = 0;
+    if (pos >= table_rows) pos = table_rows - 1;   // the host refuses such positions; never read outside
+    const bool is_q = head < nh;
+    const bool is_k = !is_q && head < nh + nkv;
+    T* dst;
+    if (is_q) {
+        dst = q_out + (size_t)t * nh * hd + (size_t)head * hd;
+    } else {
+        if (!write_kv) return;
+        const int slot = slot_mapping[t];
+        if (slot < 0) return;
+        const int kvh = is_k ? head - nh : head - nh - nkv;
+        const int page = slot / page_size, off = slot - page * page_size;
+        dst = cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * hd;
+    }
+    if (is_q || is_k) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float a = rv_to_float(src[i]);
+            float b = rv_to_float(src[i + half]);
+            if (bias) {
+                a += rv_load_param(bias, bias_dtype, col0 + i);
+                b += rv_load_param(bias, bias_dtype, col0 + i + half);
+            }
+            float c = 1.f, s = 0.f;
+            if (cos_t) {
+                c = cos_t[(size_t)pos * half + i];
+                s = sin_t[(size_t)pos * half + i];
+            }
+            dst[i] = rv_from_float<T>(a * c - b * s);
+            dst[i + half] = rv_from_float<T>(a * s + b * c);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+            float a = rv_to_float(src[i]);
+            if (bias) a += rv_load_param(bias, bias_dtype, col0 + i);
+            dst[i] = rv_from_float<T>(a);
+        }
+    }
+}
+
+RV_EXPORT int rv_rope_cache_write(const void* qkv, const void* bias, int bias_dtype, const int* positions,
+                                  const float* cos_t, const float* sin_t, const int* slot_mapping,
+                                  void* cache, void* q_out, int n_tokens, int nh, int nkv, int hd,
+                                  int page_size, int write_kv, int table_rows, int row_stride,
+                                  int dtype, cudaStream_t stream) {
+    if (n_tokens < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || (hd & 1) || page_size <= 0 || table_rows <= 0)
+        return RV_ERR_BAD_SIZE;
+    if ((cos_t == nullptr) != (sin_t == nullptr)) return RV_ERR_BAD_SIZE;
+    if (row_stride < (write_kv ? nh + 2 * nkv : nh) * hd) return RV_ERR_BAD_SIZE;
+    if (n_tokens == 0) return RV_OK;
+    const dim3 grid(n_tokens, write_kv ? nh + 2 * nkv : nh);
+    const int threads = hd / 2 >= 128 ? 128 : (hd / 2 >= 64 ? 64 : 32);
+    if (dtype == RV_DTYPE_F32)
+        rope_cache_write_kernel<float><<<grid, threads, 0, stream>>>(
+            (const float*)qkv, bias, bias_dtype, positions, cos_t, sin_t, slot_mapping, (float*)cache,
+            (float*)q_out, nh, nkv, hd, page_size, write_kv, table_rows, row_stride);
+    else if (dtype == RV_DTYPE_BF16)
+        rope_cache_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+            (const __nv_bfloat16*)qkv, bias, bias_dtype, positions, cos_t, sin_t, slot_mapping,
+            (__nv_bfloat16*)cache, (__nv_bfloat16*)q_out, nh, nkv, hd, page_size, write_kv, table_rows, row_stride);
+    else
+        return RV_ERR_BAD_DTYPE;
+    return rv_launch_status();
+}
+
+// ------------------------------------------------------------------ SiLU(gate) * up
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const size_t row = idx / inter;
+        const int col = (int)(idx - row * inter);
+        const float g = rv_to_float(gate_up[row * 2 * inter + col]);
+        const float u = rv_to_float(gate_up[row * 2 * inter + inter + col]);
+        out[idx] = rv_from_float<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+RV_EXPORT int rv_silu_mul(const void* gate_up, void* out, int n_rows, int inter, int dtype, cudaStream_t stream) {
+    if (n_rows < 0 || inter <= 0) return RV_ERR_BAD_SIZE;
+    if (n_rows == 0) return RV_OK;
+    const size_t total = (size_t)n_rows * inter;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == RV_DTYPE_F32)
+        silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    else if (dtype == RV_DTYPE_BF16)
+        silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+    else
+        return RV_ERR_BAD_DTYPE;
+    return rv_launch_status();
+}

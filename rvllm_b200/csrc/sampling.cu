@@ -1,0 +1,201 @@
+// Sampling over float logits [R, V]: greedy (lowest index wins ties, NaN never wins) and
+// seeded temperature sampling with optional top-k / top-p, one block per row.
+//
+// Parameters per row as the reference's SamplingParams {temperature, top_k, top_p, seed}
+// (v3/crates/rvllm-sampling/src/params.rs:7-28): temperature 0 means greedy.  The reference
+// ships only an argmax kernel (kernels/argmax.cu:66-117; tie rule of its oracle,
+// v3/crates/rvllm-fused/src/reference.rs:131-146); the rest is defined here:
+//   p = softmax(logits / T) in float with the maximum subtracted;
+//   top-k keeps the tokens at least as likely as the k-th most likely one;
+//   top-p keeps the most likely tokens up to the first whose cumulated mass reaches top_p
+//   (tokens exactly as likely as the last kept one stay in);
+//   the draw is the first token, in vocabulary order, whose cumulated kept mass exceeds
+//   u * (kept mass), with u = Philox4x32-10(key = seed, counter = index of the output token).
+// The uniform depends on (seed, output index) only, never on the batch a row is sampled in.
+#include "common.cuh"
+
+#define SAMPLE_THREADS 1024
+
+__device__ __forceinline__ uint32_t order_key(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+        const uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
+        c[0] = n0; c[1] = lo1; c[2] = n2; c[3] = lo0;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+}
+
+// Block-wide (value, index) arg-max: larger value wins, then lower index.
+__device__ __forceinline__ void argmax_combine(float& v, int& i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+
+__device__ int block_argmax(const float* row, int V, float* s_val, int* s_idx) {
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || (v == best && i < idx)) { best = v; idx = i; }   // NaN compares false
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        argmax_combine(best, idx, ov, oi);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) { s_val[warp] = best; s_idx[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        best = lane < nw ? s_val[lane] : -INFINITY;
+        idx = lane < nw ? s_idx[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            argmax_combine(best, idx, ov, oi);
+        }
+        if (lane == 0) { s_val[0] = best; s_idx[0] = idx == 0x7fffffff ? 0 : idx; }
+    }
+    __syncthreads();
+    return s_idx[0];
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const unsigned long long* __restrict__ seeds, const long long* __restrict__ draw_index,
+              int* __restrict__ out, int V) {
+    __shared__ float s_val[33];
+    __shared__ int s_idx[33];
+    __shared__ float s_scan[SAMPLE_THREADS / 32 + 1];
+    __shared__ int s_result;
+    __shared__ float s_incl[SAMPLE_THREADS];
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * V;
+    const float T = temperature ? temperature[r] : 0.f;
+    const int best = block_argmax(row, V, s_val, s_idx);
+    if (!(T > 0.f)) {
+        if (threadIdx.x == 0) out[r] = best;
+        return;
+    }
+    const float m = s_val[0];
+    const float inv_t = 1.0f / T;
+    __syncthreads();
+
+    // mass of everything
+    float part = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) part += expf((row[i] - m) * inv_t);
+    const float total = rv_block_sum(part, s_val);
+
+    // threshold key: keep tokens whose order key is >= tau
+    uint32_t tau = 0;
+    const int k = top_k ? top_k[r] : 0;
+    const float pp = top_p ? top_p[r] : 1.0f;
+    const bool use_k = k > 0 && k < V;
+    const bool use_p = pp < 1.0f;
+    if (use_k || use_p) {
+        uint32_t tau_k = 0, tau_p = 0;
+        for (int bit = 31; bit >= 0; --bit) {
+            const uint32_t ck = tau_k | (1u << bit), cp = tau_p | (1u << bit);
+            float cnt = 0.f, mass = 0.f;
+            for (int i = threadIdx.x; i < V; i += blockDim.x) {
+                const float v = row[i];
+                const uint32_t key = order_key(v);
+                if (use_k && key >= ck) cnt += 1.f;
+                if (use_p && key >= cp) mass += expf((v - m) * inv_t);
+            }
+            if (use_k) { cnt = rv_block_sum(cnt, s_val); if (cnt >= (float)k) tau_k = ck; }
+            if (use_p) { mass = rv_block_sum(mass, s_val); if (mass >= pp * total) tau_p = cp; }
+        }
+        tau = tau_k > tau_p ? tau_k : tau_p;
+    }
+
+    // inverse CDF in vocabulary order: thread t owns the contiguous chunk [t*C, (t+1)*C)
+    const int C = (V + blockDim.x - 1) / blockDim.x;
+    const int lo = threadIdx.x * C;
+    const int hi = min(V, lo + C);
+    float local = 0.f;
+    int last_kept = -1;
+    for (int i = lo; i < hi; ++i) {
+        const float v = row[i];
+        if (order_key(v) >= tau && !(v != v)) { local += expf((v - m) * inv_t); last_kept = i; }
+    }
+    // exclusive scan of `local` over the block
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+    }
+    if (threadIdx.x == 0) s_result = -1;
+    __syncthreads();
+    if (lane == 31) s_scan[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        float w = lane < nw ? s_scan[lane] : 0.f;
+        float wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float n = __shfl_up_sync(0xffffffffu, wi, o);
+            if (lane >= o) wi += n;
+        }
+        if (lane < nw) s_scan[lane] = wi - w;          // exclusive prefix of the warp
+    }
+    __syncthreads();
+    // inclusive prefixes in shared memory, so that neighbouring chunks tile [0, kept mass)
+    // without gaps or overlaps whatever the rounding
+    s_incl[threadIdx.x] = s_scan[warp] + incl;
+    __syncthreads();
+    const float excl = threadIdx.x > 0 ? s_incl[threadIdx.x - 1] : 0.f;
+    const float upto = s_incl[threadIdx.x];
+    const float kept_total = s_incl[blockDim.x - 1];
+
+    uint32_t c[4] = {(uint32_t)(draw_index[r] & 0xffffffffll), (uint32_t)((unsigned long long)draw_index[r] >> 32), 0u, 0u};
+    philox4x32_10(c, (uint32_t)(seeds[r] & 0xffffffffull), (uint32_t)(seeds[r] >> 32));
+    const float u = (float)(c[0] >> 8) * (1.0f / 16777216.0f);
+    const float target = u * kept_total;
+
+    if (upto > excl && excl <= target && target < upto) {
+        float run = excl;
+        int pick = last_kept;
+        for (int i = lo; i < hi; ++i) {
+            const float v = row[i];
+            if (order_key(v) >= tau && !(v != v)) {
+                run += expf((v - m) * inv_t);
+                if (run > target) { pick = i; break; }
+            }
+        }
+        atomicMax(&s_result, pick);   // at most one thread matches; max is only a tie guard
+    }
+    __syncthreads();
+    if (s_result < 0) {
+        // rounding put the target at or beyond the kept mass: take the last kept token
+        atomicMax(&s_result, last_kept);
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[r] = s_result >= 0 ? s_result : best;
+}
+
+// temperature, top_k, top_p may be null (greedy / disabled).  seeds and draw_index are read
+// only for rows with temperature > 0.
+RV_EXPORT int rv_sample(const float* logits, const float* temperature, const int* top_k, const float* top_p,
+                        const unsigned long long* seeds, const long long* draw_index, int* out,
+                        int n_rows, int vocab, cudaStream_t stream) {
+    if (n_rows < 0 || vocab <= 0) return RV_ERR_BAD_SIZE;
+    if (n_rows == 0) return RV_OK;
+    if (temperature && (!seeds || !draw_index)) return RV_ERR_BAD_SIZE;
+    sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, temperature, top_k, top_p, seeds, draw_index, out, vocab);
+    return rv_launch_status();
+}

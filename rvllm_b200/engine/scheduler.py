@@ -1,0 +1,231 @@
+"""Continuous batching above the step function.
+
+The reference's scheduler is a skeleton: a step is either one prefill of every queued prompt
+whole or one decode of every running request, with no token budget, no page accounting and no
+stop on EOS (v3/crates/rvllm-runtime/src/scheduler.rs:37-128, sched_state.rs:9-54); its spec
+adds one chunk per step and watermark pre-emption (v3/specs/07-scheduler.md:37-41,74-78).
+This scheduler does what the spec sketches:
+
+* every step, running requests go first (oldest first): a decoding request brings one token, a
+  partly prefilled one its next portion; then waiting requests are admitted in arrival order
+  while request slots, the token budget (`max_num_batched_tokens`) and free pages last;
+* a prompt's portion is min(what is left, the budget left, `max_prefill_chunk`); with
+  chunking off a prompt is admitted only whole;
+* when a running request needs a page and none is free, the most recently admitted running
+  request is pre-empted: its pages are given back, it returns to the front of the waiting
+  queue and is computed again from its first token (prompt and the tokens it has produced)
+  when pages allow - its sampled tokens are kept, so its output does not change;
+* a request that could never fit (its prompt plus `max_tokens` need more pages than exist) is
+  refused when it is added, with `KvExhausted`;
+* a request finishes when it has produced `max_tokens` ("length"), a stop or EOS token
+  ("stop"), or has reached `max_model_len` ("length"); its pages and slot are freed at once.
+
+Same arrivals and seeds give the same sequence of batches.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+
+from ..cache import CacheManager
+from ..errors import KvExhausted, SchedulerError
+from ..sampling.params import SamplingParams
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+@dataclass
+class Request:
+    req_id: Hashable
+    prompt: List[int]
+    params: SamplingParams
+    seed: int = 0
+    output: List[int] = field(default_factory=list)
+    num_computed: int = 0          # tokens of prompt + output that are in the cache
+    state: str = WAITING
+    finish_reason: Optional[str] = None
+    arrival: int = 0
+    num_preemptions: int = 0
+
+    @property
+    def all_tokens(self) -> List[int]:
+        return self.prompt + self.output
+
+    @property
+    def remaining(self) -> int:
+        return len(self.prompt) + len(self.output) - self.num_computed
+
+
+@dataclass
+class ScheduledEntry:
+    request: Request
+    start: int                     # index of the first token of the portion in prompt + output
+    num_tokens: int
+    samples: bool                  # True when the portion ends the known tokens: its last row is sampled
+
+
+@dataclass
+class ScheduledBatch:
+    entries: List[ScheduledEntry]
+    preempted: List[Request]
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(e.num_tokens for e in self.entries)
+
+    @property
+    def is_decode_only(self) -> bool:
+        return bool(self.entries) and all(e.num_tokens == 1 and e.samples for e in self.entries)
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, max_num_seqs: int, max_num_batched_tokens: int,
+                 max_model_len: int, max_prefill_chunk: Optional[int] = None,
+                 enable_chunked_prefill: bool = True, eos_token_ids: Sequence[int] = ()):
+        self.cache = cache
+        self.max_num_seqs = max_num_seqs
+        self.max_num_batched_tokens = max_num_batched_tokens
+        self.max_model_len = max_model_len
+        self.max_prefill_chunk = max_prefill_chunk
+        self.enable_chunked_prefill = enable_chunked_prefill
+        self.eos_token_ids = tuple(eos_token_ids)
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []
+        self._arrivals = 0
+
+    # ---- admission ---------------------------------------------------------------------------
+    def add_request(self, req: Request) -> None:
+        if not req.prompt:
+            raise SchedulerError(f"request {req.req_id!r} has an empty prompt")
+        if len(req.prompt) >= self.max_model_len:
+            raise SchedulerError(f"request {req.req_id!r}: a prompt of {len(req.prompt)} tokens leaves no room "
+                                 f"under max_model_len {self.max_model_len}")
+        if not self.enable_chunked_prefill and len(req.prompt) > self.max_num_batched_tokens:
+            raise SchedulerError(f"request {req.req_id!r}: a prompt of {len(req.prompt)} tokens exceeds "
+                                 f"max_num_batched_tokens {self.max_num_batched_tokens} and chunking is off")
+        longest = min(len(req.prompt) + req.params.max_tokens, self.max_model_len)
+        need = self.cache.blocks_for(longest)
+        if need > self.cache.num_pages:
+            raise KvExhausted(need, self.cache.num_pages, f"request {req.req_id!r} can never fit: "
+                              f"{longest} tokens need {need} pages of {self.cache.page_size}")
+        req.arrival = self._arrivals
+        self._arrivals += 1
+        req.state = WAITING
+        self.waiting.append(req)
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ---- one scheduling decision --------------------------------------------------------------
+    def _portion(self, req: Request, budget: int) -> int:
+        n = min(req.remaining, budget)
+        if req.remaining > 1 and self.max_prefill_chunk is not None:
+            n = min(n, self.max_prefill_chunk)
+        return n
+
+    def _preempt(self, req: Request, preempted: List[Request]) -> None:
+        self.cache.free(req.req_id)
+        self.running.remove(req)
+        req.num_computed = 0
+        req.state = WAITING
+        req.num_preemptions += 1
+        self.waiting.appendleft(req)
+        preempted.append(req)
+
+    def schedule(self) -> ScheduledBatch:
+        budget = self.max_num_batched_tokens
+        entries: List[ScheduledEntry] = []
+        preempted: List[Request] = []
+        reserved = [0] * len(self.cache.groups)
+
+        # running requests: decoding ones first, then partly prefilled ones, each oldest first
+        order = sorted(self.running, key=lambda r: (r.remaining > 1, r.arrival))
+        scheduled_ids = set()
+        for req in order:
+            if req not in self.running or budget <= 0:
+                continue
+            n = self._portion(req, budget)
+            while not self.cache.can_append(req.req_id, n, reserved):
+                victim = max((r for r in self.running if r.req_id not in scheduled_ids),
+                             key=lambda r: r.arrival, default=None)
+                if victim is None:
+                    break
+                self._preempt(victim, preempted)
+                if victim is req:
+                    break
+            if req not in self.running or not self.cache.can_append(req.req_id, n, reserved):
+                continue
+            need = self.cache.pages_needed(req.req_id, n)
+            reserved = [a + b for a, b in zip(reserved, need)]
+            entries.append(ScheduledEntry(req, req.num_computed, n, n == req.remaining))
+            scheduled_ids.add(req.req_id)
+            budget -= n
+
+        # admissions, in arrival order (pre-empted requests wait at the front)
+        while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs:
+            req = self.waiting[0]
+            if req in preempted:
+                break                       # do not re-admit in the step that evicted it
+            n = self._portion(req, budget)
+            if not self.enable_chunked_prefill and n < req.remaining:
+                break
+            if not self.cache.can_append(None, n, reserved):
+                break
+            self.waiting.popleft()
+            self.cache.admit(req.req_id)
+            req.state = RUNNING
+            self.running.append(req)
+            need = self.cache.pages_needed(req.req_id, n)
+            reserved = [a + b for a, b in zip(reserved, need)]
+            entries.append(ScheduledEntry(req, 0, n, n == req.remaining))
+            scheduled_ids.add(req.req_id)
+            budget -= n
+
+        if not entries and self.has_unfinished():
+            # nothing runs and the head of the queue cannot start: it never will
+            head = self.waiting[0] if self.waiting else self.running[0]
+            need = self.cache.blocks_for(min(head.remaining, self.max_num_batched_tokens))
+            raise KvExhausted(need, min(self.cache.num_free_pages() or [0]),
+                              f"request {head.req_id!r} cannot be scheduled and nothing is running")
+        return ScheduledBatch(entries, preempted)
+
+    # ---- after the step ------------------------------------------------------------------------
+    def update(self, batch: ScheduledBatch, sampled: Dict[Hashable, int]) -> List[Request]:
+        """Account the step's tokens and the tokens sampled at the ends of portions; returns the
+        requests that finished."""
+        finished = []
+        for e in batch.entries:
+            req = e.request
+            req.num_computed += e.num_tokens
+            if not e.samples:
+                continue
+            tok = int(sampled[req.req_id])
+            req.output.append(tok)
+            reason = None
+            stops = set(req.params.stop_token_ids)
+            if not req.params.ignore_eos:
+                stops.update(self.eos_token_ids)
+            if tok in stops:
+                reason = "stop"
+            elif len(req.output) >= req.params.max_tokens:
+                reason = "length"
+            elif len(req.prompt) + len(req.output) >= self.max_model_len:
+                reason = "length"
+            if reason is not None:
+                req.state, req.finish_reason = FINISHED, reason
+                self.running.remove(req)
+                self.cache.free(req.req_id)
+                finished.append(req)
+        return finished
+
+    def abort(self, req_id: Hashable) -> None:
+        for req in list(self.running):
+            if req.req_id == req_id:
+                self.running.remove(req)
+                self.cache.free(req_id)
+                req.state, req.finish_reason = FINISHED, "abort"
+        for req in list(self.waiting):
+            if req.req_id == req_id:
+                self.waiting.remove(req)
+                req.state, req.finish_reason = FINISHED, "abort"

@@ -1,0 +1,210 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A batch holds, in any order, whole prompts, portions of prompts cut anywhere and single
+decoded tokens.  The step reserves cache room for exactly the tokens it is given, packs the
+batch's metadata into one pinned buffer that goes to the device in one copy, runs the model
+over these tokens against the cache that earlier steps left, and returns float32 logits at
+the wanted places.
+
+The reference runs a step either as all-decode or as all-prefill of equal-length prompts
+(v3/crates/rvllm-runtime/src/layer_exec.rs:32-39,367-372; scheduler.rs:1-6) and fills its
+metadata with separate synchronous copies (bring_up.rs:698-708); its packed layout
+(v3/crates/rvllm-metadata/src/layout.rs:19-55: token ids, positions, context lengths, block
+tables, slot mapping, sequence starts; padding rows have slot -1, pack.rs:79-86) is what the
+buffer here follows, extended per cache group.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager
+from ..errors import KvExhausted, SchedulerError
+from ..kernels.library import AttentionMeta
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places (indices into `tokens`)
+    whose logits are wanted."""
+    req_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepContext:
+    """What the parts see of a step."""
+    __slots__ = ("kernels", "num_tokens", "num_seqs", "token_ids", "positions", "token_seq", "cu_seqlens",
+                 "state_slots", "logit_rows", "attention", "q_lens", "ctx_lens", "req_ids", "extras")
+
+    def __init__(self):
+        self.extras = {}
+
+
+class ModelRunner:
+    def __init__(self, model, cache: CacheManager, kernels, max_model_len: int, device):
+        self.model, self.cache, self.kernels = model, cache, kernels
+        self.max_model_len = max_model_len
+        self.device = torch.device(device)
+        self.max_blocks = cache.blocks_for(max_model_len)
+        # a small ring of pinned staging buffers: a buffer is rewritten only after the copy that
+        # last read it has finished, so the host never waits for the step it has just launched
+        self._ring: List[Optional[torch.Tensor]] = [None, None, None]
+        self._ring_events: List[Optional[object]] = [None, None, None]
+        self._ring_next = 0
+        self._dev: Optional[torch.Tensor] = None
+        self.steps_run = 0
+
+    # ---- metadata buffers --------------------------------------------------------------------
+    def _buffers(self, n_ints: int):
+        i = self._ring_next
+        self._ring_next = (i + 1) % len(self._ring)
+        if self._ring_events[i] is not None:
+            self._ring_events[i].synchronize()
+        size = max(n_ints, 1 << 16)
+        if self._ring[i] is None or self._ring[i].numel() < n_ints:
+            self._ring[i] = torch.empty((size,), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        if self._dev is None or self._dev.numel() < n_ints:
+            self._dev = torch.empty((size,), dtype=torch.int32, device=self.device)
+        return i, self._ring[i], self._dev
+
+    # ---- one step ----------------------------------------------------------------------------
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        vocab = self.model.spec.vocab_size
+        seen = set()
+        for e in entries:
+            if e.req_id in seen:
+                raise SchedulerError(f"request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            if len(e.tokens) == 0:
+                raise SchedulerError(f"request {e.req_id!r} brings no tokens to the step")
+            bad = [t for t in e.tokens if not 0 <= int(t) < vocab]
+            if bad:
+                raise SchedulerError(f"request {e.req_id!r}: token id {bad[0]} is outside the vocabulary of {vocab}")
+            have = self.cache.num_tokens(e.req_id) if self.cache.has(e.req_id) else 0
+            if have + len(e.tokens) > self.max_model_len:
+                raise SchedulerError(f"request {e.req_id!r}: {have} + {len(e.tokens)} tokens exceed max_model_len {self.max_model_len}")
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise SchedulerError(f"request {e.req_id!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
+
+    def reserve(self, entries: Sequence[StepEntry]) -> List[int]:
+        """Admit unknown requests and take the pages of the whole batch, or nothing."""
+        total = [0] * len(self.cache.groups)
+        for e in entries:
+            need = self.cache.pages_needed(e.req_id if self.cache.has(e.req_id) else None, len(e.tokens))
+            total = [a + b for a, b in zip(total, need)]
+        free = self.cache.num_free_pages()
+        for need, have in zip(total, free):
+            if need > have:
+                raise KvExhausted(need, have, "the step's tokens do not fit the free pages")
+        new = sum(1 for e in entries if not self.cache.has(e.req_id))
+        if new > self.cache.slots.num_free:
+            raise SchedulerError(f"{new} new requests but only {self.cache.slots.num_free} request slots are free")
+        starts = []
+        for e in entries:
+            if not self.cache.has(e.req_id):
+                self.cache.admit(e.req_id)
+            starts.append(self.cache.append(e.req_id, len(e.tokens)))
+        return starts
+
+    def pack(self, entries: Sequence[StepEntry], starts: List[int]) -> StepContext:
+        cache = self.cache
+        B = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        T = sum(q_lens)
+        ctx_lens = [s + n for s, n in zip(starts, q_lens)]
+        R = sum(len(e.want) for e in entries)
+        G = len(cache.groups)
+        MB = max(1, cache.blocks_for(max(ctx_lens)))
+        n_ints = 3 * T + (B + 1) + 2 * B + R + G * (T + B * MB) + 16
+        ring_i, host, dev = self._buffers(n_ints)
+        h = host.numpy()
+        off = 0
+
+        def take(n):
+            nonlocal off
+            a = off
+            off += n
+            return a
+
+        o_tok, o_pos, o_seq = take(T), take(T), take(T)
+        o_cu, o_ctx, o_state, o_rows = take(B + 1), take(B), take(B), take(R)
+        cu = 0
+        rows: List[int] = []
+        h[o_cu] = 0
+        for i, e in enumerate(entries):
+            n = q_lens[i]
+            h[o_tok + cu:o_tok + cu + n] = np.asarray(e.tokens, dtype=np.int32)
+            h[o_pos + cu:o_pos + cu + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
+            h[o_seq + cu:o_seq + cu + n] = i
+            rows.extend(cu + w for w in e.want)
+            cu += n
+            h[o_cu + i + 1] = cu
+            h[o_ctx + i] = ctx_lens[i]
+            h[o_state + i] = cache.state_slot(e.req_id)
+        if R:
+            h[o_rows:o_rows + R] = np.asarray(rows, dtype=np.int32)
+        group_offsets = []
+        ps = cache.page_size
+        for gi in range(G):
+            o_slot, o_bt = take(T), take(B * MB)
+            h[o_bt:o_bt + B * MB] = -1
+            cu = 0
+            for i, e in enumerate(entries):
+                table = cache.block_table(e.req_id, gi)
+                nb = len(table)
+                tb = np.asarray(table, dtype=np.int32)
+                h[o_bt + i * MB:o_bt + i * MB + nb] = tb
+                pos = np.arange(starts[i], starts[i] + q_lens[i])
+                h[o_slot + cu:o_slot + cu + q_lens[i]] = tb[pos // ps] * ps + pos % ps
+                cu += q_lens[i]
+            group_offsets.append((o_slot, o_bt))
+        dev[:off].copy_(host[:off], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = self._ring_events[ring_i] or torch.cuda.Event()
+            ev.record()
+            self._ring_events[ring_i] = ev
+
+        ctx = StepContext()
+        ctx.kernels = self.kernels
+        ctx.num_tokens, ctx.num_seqs = T, B
+        ctx.token_ids = dev[o_tok:o_tok + T]
+        ctx.positions = dev[o_pos:o_pos + T]
+        ctx.token_seq = dev[o_seq:o_seq + T]
+        ctx.cu_seqlens = dev[o_cu:o_cu + B + 1]
+        dev_ctx = dev[o_ctx:o_ctx + B]
+        ctx.state_slots = dev[o_state:o_state + B]
+        ctx.logit_rows = dev[o_rows:o_rows + R]
+        ctx.q_lens, ctx.ctx_lens = q_lens, ctx_lens
+        ctx.req_ids = [e.req_id for e in entries]
+        ctx.attention = []
+        for (o_slot, o_bt) in group_offsets:
+            ctx.attention.append(AttentionMeta(
+                block_tables=dev[o_bt:o_bt + B * MB].view(B, MB), cu_seqlens=ctx.cu_seqlens, ctx_lens=dev_ctx,
+                token_seq=ctx.token_seq, slot_mapping=dev[o_slot:o_slot + T], num_seqs=B,
+                max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), page_size=ps))
+        return ctx
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the batch.  Returns float32 logits [wanted places, vocab] in the order of the
+        entries and of each entry's `want` (None if nothing is wanted)."""
+        if not entries:
+            return None
+        self.validate(entries)
+        starts = self.reserve(entries)
+        ctx = self.pack(entries, starts)
+        hidden = self.model.forward(ctx, self.cache)
+        logits = self.model.compute_logits(hidden, ctx) if ctx.logit_rows.numel() else None
+        for e in entries:
+            self.cache.release_passed(e.req_id)
+        self.steps_run += 1
+        return logits
+
+    def finish(self, req_id: Hashable) -> None:
+        """Give back everything the request holds."""
+        if self.cache.has(req_id):
+            self.cache.free(req_id)

@@ -1,0 +1,246 @@
+"""The kernels of the product path, as methods that take torch tensors.
+
+`CudaKernels` launches the hand-written sm_100a kernels of csrc/ on torch's current stream
+through their exported C launchers.  Matrix products of bfloat16 activations with at least
+`SKINNY_MAX_ROWS` rows go to the library GEMM behind `torch` (the reference calls cuBLASLt for
+its linear layers, v3/crates/rvllm-cutlass/src/cublaslt.rs); everything else is this
+project's own code.  There is no CPU implementation: without a CUDA device, or when a kernel
+library cannot be built, construction raises `KernelError`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_void_p, c_int, c_float
+from typing import Optional
+
+import torch
+
+from ..errors import KernelError
+from . import build
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+_STATUS = {-1: "a size is out of range", -2: "unsupported dtype", -3: "misaligned pointer or stride",
+           -4: "size not supported by this kernel"}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _check(name: str, status: int):
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{name}: refused, {_STATUS.get(status, 'code %d' % status)}")
+    raise KernelError(f"{name}: CUDA launch failed with error {status}")
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, dims=None):
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous, got strides {t.stride()} for shape {tuple(t.shape)}")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name} must have {dims} dimensions, got shape {tuple(t.shape)}")
+
+
+class AttentionMeta:
+    """Per-step, per-cache-group arguments of the attention kernels (device int32 tensors) and
+    the few host-side numbers that size their launches."""
+    __slots__ = ("block_tables", "cu_seqlens", "ctx_lens", "token_seq", "slot_mapping", "num_seqs",
+                 "max_q_len", "max_ctx_len", "max_blocks", "page_size")
+
+    def __init__(self, block_tables, cu_seqlens, ctx_lens, token_seq, slot_mapping, num_seqs,
+                 max_q_len, max_ctx_len, page_size):
+        self.block_tables, self.cu_seqlens, self.ctx_lens = block_tables, cu_seqlens, ctx_lens
+        self.token_seq, self.slot_mapping = token_seq, slot_mapping
+        self.num_seqs, self.max_q_len, self.max_ctx_len = num_seqs, max_q_len, max_ctx_len
+        self.max_blocks = block_tables.shape[1]
+        self.page_size = page_size
+
+
+class CudaKernels:
+    SKINNY_MAX_ROWS = 0     # rows up to which the weight-streaming GEMM is used (0: not yet)
+
+    def __init__(self, device="cuda:0"):
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: this engine has no CPU path")
+        self.device = torch.device(device)
+        major, minor = torch.cuda.get_device_capability(self.device)
+        if major != 10:
+            raise KernelError(f"the kernels are built for sm_100a; device {device} has compute capability {major}.{minor}")
+        # the float32 path must never round operands to TF32 inside a library product
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.backends.cudnn.allow_tf32 = False
+        self._libs = {}
+
+    # ------------------------------------------------------------------ plumbing
+    def _lib(self, source: str, defines=()):
+        key = (source, tuple(defines))
+        lib = self._libs.get(key)
+        if lib is None:
+            lib = build.load_library(source, defines)
+            self._libs[key] = lib
+        return lib
+
+    @staticmethod
+    def _stream():
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    @staticmethod
+    def _dt(t: torch.Tensor, name: str) -> int:
+        try:
+            return _DT[t.dtype]
+        except KeyError:
+            raise KernelError(f"{name}: dtype {t.dtype} is not supported (float32, bfloat16)") from None
+
+    # ------------------------------------------------------------------ row kernels
+    def gather_rows(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """out[t] = table[ids[t]]; ids int32.  Used for the embedding and for picking logit rows."""
+        _need(table, "table", dims=2); _need(ids, "ids", torch.int32, 1)
+        out = torch.empty((ids.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
+        st = self._lib("elementwise.cu").rv_gather_rows(
+            _ptr(table), _ptr(ids), _ptr(out), c_int(ids.shape[0]), c_int(table.shape[1]),
+            c_int(table.shape[0]), c_int(self._dt(table, "table")), self._stream())
+        _check("gather_rows", st)
+        return out
+
+    def rmsnorm(self, x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
+        _need(x, "x", dims=2); _need(gamma, "gamma", dims=1)
+        if gamma.shape[0] != x.shape[1]:
+            raise KernelError(f"rmsnorm: gamma has {gamma.shape[0]} entries for rows of {x.shape[1]}")
+        out = torch.empty_like(x)
+        st = self._lib("elementwise.cu").rv_rmsnorm(
+            _ptr(x), _ptr(gamma), c_int(self._dt(gamma, "gamma")), _ptr(out), c_int(x.shape[0]),
+            c_int(x.shape[1]), c_float(eps), c_int(self._dt(x, "x")), self._stream())
+        _check("rmsnorm", st)
+        return out
+
+    def silu_mul(self, gate_up: torch.Tensor) -> torch.Tensor:
+        """rows [gate | up] -> silu(gate) * up."""
+        _need(gate_up, "gate_up", dims=2)
+        inter = gate_up.shape[1] // 2
+        if inter * 2 != gate_up.shape[1]:
+            raise KernelError(f"silu_mul: row width {gate_up.shape[1]} is odd")
+        out = torch.empty((gate_up.shape[0], inter), dtype=gate_up.dtype, device=gate_up.device)
+        st = self._lib("elementwise.cu").rv_silu_mul(_ptr(gate_up), _ptr(out), c_int(gate_up.shape[0]),
+                                                    c_int(inter), c_int(self._dt(gate_up, "gate_up")), self._stream())
+        _check("silu_mul", st)
+        return out
+
+    def rope_cache_write(self, qkv, bias, positions, cos, sin, slot_mapping, cache_layer,
+                         num_heads, num_kv_heads, head_dim, write_kv=True) -> torch.Tensor:
+        """Add the q/k/v bias, rotate q and k, write k and v into their cache pages, return q
+        [T, num_heads * head_dim].  qkv rows are [q | k | v], or q alone when `write_kv` is False.
+        cache_layer: [num_pages, 2, num_kv_heads, page_size, head_dim]."""
+        _need(qkv, "qkv", dims=2); _need(positions, "positions", torch.int32, 1)
+        T = qkv.shape[0]
+        width = (num_heads + (2 * num_kv_heads if write_kv else 0)) * head_dim
+        if qkv.shape[1] != width:
+            raise KernelError(f"rope_cache_write: qkv rows have {qkv.shape[1]} columns, expected {width}")
+        if write_kv:
+            _need(cache_layer, "cache_layer", qkv.dtype, 5); _need(slot_mapping, "slot_mapping", torch.int32, 1)
+            if tuple(cache_layer.shape[1:3]) != (2, num_kv_heads) or cache_layer.shape[4] != head_dim:
+                raise KernelError(f"rope_cache_write: cache layer of shape {tuple(cache_layer.shape)} does not "
+                                  f"fit {num_kv_heads} kv heads of {head_dim}")
+        if cos is not None:
+            _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+            if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+                raise KernelError("rope_cache_write: cos/sin tables must be [rows, head_dim/2]")
+        if bias is not None:
+            _need(bias, "bias", dims=1)
+        q = torch.empty((T, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        page = cache_layer.shape[3] if write_kv else 1
+        st = self._lib("elementwise.cu").rv_rope_cache_write(
+            _ptr(qkv), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0), _ptr(positions),
+            _ptr(cos), _ptr(sin), _ptr(slot_mapping if write_kv else None), _ptr(cache_layer if write_kv else None),
+            _ptr(q), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page),
+            c_int(1 if write_kv else 0), c_int(cos.shape[0] if cos is not None else 1), c_int(qkv.shape[1]),
+            c_int(self._dt(qkv, "qkv")), self._stream())
+        _check("rope_cache_write", st)
+        return q
+
+    # ------------------------------------------------------------------ attention
+    def paged_attention(self, q, cache_layer, meta: AttentionMeta, num_heads, num_kv_heads, head_dim,
+                        scale: float, window: Optional[int]) -> torch.Tensor:
+        """Attention of the step's tokens over the paged cache (keys of this step included)."""
+        return self.paged_attention_plain(q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window)
+
+    def paged_attention_plain(self, q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window):
+        _need(q, "q", dims=2); _need(cache_layer, "cache_layer", q.dtype, 5)
+        out = torch.empty_like(q)
+        st = self._lib("attention_ref.cu").rv_paged_attention_ref(
+            _ptr(q), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens),
+            _ptr(meta.token_seq), _ptr(out), c_int(q.shape[0]), c_int(num_heads), c_int(num_kv_heads),
+            c_int(head_dim), c_int(cache_layer.shape[3]), c_int(meta.max_blocks), c_float(scale),
+            c_int(window or 0), c_int(self._dt(q, "q")), self._stream())
+        _check("paged_attention_plain", st)
+        return out
+
+    # ------------------------------------------------------------------ linear layers
+    def linear(self, x, weight, bias=None, residual=None, out_dtype=None) -> torch.Tensor:
+        """x [M, K] . weight [N, K]^T (+ bias) (+ residual), accumulated in float.
+
+        float32 operands: this project's FFMA kernel (no TF32 anywhere).  bfloat16 operands: the
+        library GEMM; the residual is added in its float epilogue (beta = 1).  A weight kept in
+        32 bits under a bfloat16 engine is multiplied in float32."""
+        _need(x, "x", dims=2); _need(weight, "weight", dims=2)
+        M, K = x.shape
+        N = weight.shape[0]
+        if weight.shape[1] != K:
+            raise KernelError(f"linear: x has {K} columns, weight has {weight.shape[1]}")
+        out_dtype = out_dtype or x.dtype
+        if weight.dtype == torch.float32:
+            xf = x if x.dtype == torch.float32 else x.float()
+            rf = None
+            if residual is not None:
+                rf = residual if residual.dtype == torch.float32 else residual.float()
+                _need(rf, "residual", dims=2)
+            if bias is not None:
+                _need(bias, "bias", dims=1)
+            out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+            st = self._lib("gemm_f32.cu").rv_gemm_f32(
+                _ptr(xf), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0),
+                _ptr(rf), _ptr(out), c_int(M), c_int(N), c_int(K), self._stream())
+            _check("gemm_f32", st)
+            return out if out_dtype == torch.float32 else out.to(out_dtype)
+        if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+            raise KernelError(f"linear: unsupported operand types {x.dtype} x {weight.dtype}")
+        return self._linear_bf16(x, weight, bias, residual, out_dtype)
+
+    def _linear_bf16(self, x, weight, bias, residual, out_dtype):
+        if out_dtype == torch.float32:
+            out = torch.mm(x, weight.t(), out_dtype=torch.float32)
+            if bias is not None:
+                out += bias.float()
+            if residual is not None:
+                out += residual.float()
+            return out
+        if residual is not None and bias is None:
+            return torch.addmm(residual, x, weight.t())
+        out = torch.nn.functional.linear(x, weight, bias.to(x.dtype) if bias is not None else None)
+        if residual is not None:
+            out += residual
+        return out
+
+    # ------------------------------------------------------------------ sampling
+    def sample(self, logits, temperature=None, top_k=None, top_p=None, seeds=None, draw_index=None) -> torch.Tensor:
+        """One token id per row of float logits.  All parameter tensors are per row; rows with
+        temperature 0 (or `temperature` None) are greedy."""
+        _need(logits, "logits", torch.float32, 2)
+        R, V = logits.shape
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        if temperature is not None:
+            _need(temperature, "temperature", torch.float32, 1)
+            _need(seeds, "seeds", torch.int64, 1); _need(draw_index, "draw_index", torch.int64, 1)
+        if top_k is not None:
+            _need(top_k, "top_k", torch.int32, 1)
+        if top_p is not None:
+            _need(top_p, "top_p", torch.float32, 1)
+        st = self._lib("sampling.cu").rv_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                                                _ptr(seeds), _ptr(draw_index), _ptr(out), c_int(R), c_int(V),
+                                                self._stream())
+        _check("sample", st)
+        return out

@@ -1,0 +1,126 @@
+"""The generic decoder: an embedding, a run order over layers built from registered parts, a
+final norm and an LM head.  It is built from a `ModelSpec` alone and does not know which
+architecture the spec came from.
+
+Skeleton as the reference's whole-model loop (v3/crates/rvllm-runtime/src/bring_up.rs:535-669
+and rvllm-bench/src/bin/rvllm_eval.rs:430-546): gather, layers, then for the wanted rows only
+final norm and LM head; the LM head is the embedding matrix when the spec names none
+(tie, rvllm-loader/src/load.rs:310-311).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config.spec import LayerSpec, ModelSpec, PartSpec
+from ..errors import ConfigError
+from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, KvCacheNeed, StateNeed,
+                          TensorSpec)
+from ..parts.linear import Linear
+
+
+class _Layer:
+    def __init__(self, spec: LayerSpec, position_encodings: Dict[str, object]):
+        mp = dict(spec.mixer.params)
+        if "position" in mp:
+            key = mp["position"]
+            if key is not None and key not in position_encodings:
+                raise ConfigError(f"layer {spec.prefix!r} names position encoding {key!r}, which the model does not define")
+            mp["position"] = position_encodings.get(key) if key is not None else None
+        self.spec = spec
+        self.mixer = MIXERS.build(spec.mixer.kind, **mp)
+        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward.kind, **spec.feed_forward.params)
+        self.mixer_norm = NORMS.build(spec.mixer_norm.kind, **spec.mixer_norm.params)
+        self.feed_forward_norm = NORMS.build(spec.feed_forward_norm.kind, **spec.feed_forward_norm.params)
+        self.block = BLOCKS.build(spec.block.kind, mixer=self.mixer, feed_forward=self.feed_forward,
+                                  mixer_norm=self.mixer_norm, feed_forward_norm=self.feed_forward_norm,
+                                  **spec.block.params)
+
+    def named_parts(self):
+        n = self.spec.names
+        return [(self.spec.prefix + n.get("mixer", "mixer."), self.mixer),
+                (self.spec.prefix + n.get("feed_forward", "feed_forward."), self.feed_forward),
+                (self.spec.prefix + n.get("mixer_norm", "mixer_norm."), self.mixer_norm),
+                (self.spec.prefix + n.get("feed_forward_norm", "feed_forward_norm."), self.feed_forward_norm)]
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec):
+        problems = spec.validate()
+        if problems:
+            raise ConfigError(problems, "model spec")
+        self.spec = spec
+        self.position_encodings = {k: POSITION_ENCODINGS.build(p.kind, **p.params)
+                                   for k, p in spec.position_encodings.items()}
+        self.layers: List[_Layer] = [_Layer(ls, self.position_encodings) for ls in spec.layers]
+        self.final_norm = NORMS.build(spec.final_norm.kind, **spec.final_norm.params)
+        self.embedding: Optional[torch.Tensor] = None
+        self.lm_head: Optional[torch.Tensor] = None
+        self.dtype = None
+        self.device = None
+
+    # ---- tensors ---------------------------------------------------------------------------
+    def named_parts(self):
+        out = []
+        for layer in self.layers:
+            out.extend(layer.named_parts())
+        out.append((self.spec.final_norm_prefix, self.final_norm))
+        for key, pe in self.position_encodings.items():
+            out.append((f"position.{key}.", pe))
+        return out
+
+    def expected_tensors(self) -> Dict[str, TensorSpec]:
+        s = self.spec
+        specs = {s.embedding_name: TensorSpec((s.vocab_size, s.hidden_size), "matrix")}
+        if s.lm_head_name is not None:
+            specs[s.lm_head_name] = TensorSpec((s.vocab_size, s.hidden_size), "matrix")
+        for prefix, part in self.named_parts():
+            for name, ts in part.tensor_specs().items():
+                specs[prefix + name] = ts
+        return specs
+
+    def load(self, get, dtype: torch.dtype, device, max_len: int) -> None:
+        """`get(full tensor name)` -> tensor on `device` in its engine dtype."""
+        self.dtype, self.device = dtype, torch.device(device)
+        self.embedding = get(self.spec.embedding_name)
+        self.lm_head = get(self.spec.lm_head_name) if self.spec.lm_head_name is not None else self.embedding
+        for prefix, part in self.named_parts():
+            part.bind(lambda name, _p=prefix: get(_p + name))
+        for pe in self.position_encodings.values():
+            pe.prepare(max_len, device)
+
+    # ---- what the cache manager has to provide ---------------------------------------------------
+    def cache_needs(self) -> Dict[int, object]:
+        """cache slot -> KvCacheNeed | StateNeed | None, taken from the entry that writes it."""
+        needs = {}
+        for e in self.spec.run_order:
+            need = self.layers[e.layer].mixer.cache_need()
+            if e.writes_cache:
+                needs[e.cache] = need
+        for e in self.spec.run_order:
+            if not e.writes_cache:
+                need = self.layers[e.layer].mixer.cache_need()
+                if need != needs.get(e.cache):
+                    raise ConfigError(f"layer {e.layer} reads cache slot {e.cache} but needs {need}, "
+                                      f"while its writer provides {needs.get(e.cache)}")
+        return needs
+
+    # ---- the forward pass of one step ----------------------------------------------------------
+    def forward(self, ctx, caches) -> torch.Tensor:
+        x = ctx.kernels.gather_rows(self.embedding, ctx.token_ids)
+        for pe in self.position_encodings.values():
+            x = pe.on_embeddings(x, ctx)
+        for e in self.spec.run_order:
+            x = self.layers[e.layer].block(x, ctx, caches.view(e.cache), e.writes_cache)
+        return x
+
+    def compute_logits(self, hidden: torch.Tensor, ctx) -> torch.Tensor:
+        """float32 logits [R, vocab] at the rows `ctx.logit_rows` of the step."""
+        rows = ctx.kernels.gather_rows(hidden, ctx.logit_rows)
+        y = self.final_norm(rows, ctx)
+        return ctx.kernels.linear(y, self.lm_head, None, None, torch.float32)
+
+
+def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
+    return DecoderModel(spec).expected_tensors()
