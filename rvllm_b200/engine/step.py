@@ -57,6 +57,7 @@ class ModelRunner:
         self._ring_next = 0
         self._dev: Optional[torch.Tensor] = None
         self.steps_run = 0
+        self.last_h2d_bytes = 0
 
     # ---- metadata buffers --------------------------------------------------------------------
     def _buffers(self, n_ints: int):
@@ -164,6 +165,7 @@ class ModelRunner:
                 cu += q_lens[i]
             group_offsets.append((o_slot, o_bt))
         dev[:off].copy_(host[:off], non_blocking=True)
+        self.last_h2d_bytes = off * 4
         if self.device.type == "cuda":
             ev = self._ring_events[ring_i] or torch.cuda.Event()
             ev.record()

@@ -47,9 +47,8 @@ def build_dir() -> str:
     for d in candidates:
         try:
             os.makedirs(d, exist_ok=True)
-            probe = os.path.join(d, f".w{os.getpid()}")
-            with open(probe, "w"):
-                pass
+            fd, probe = tempfile.mkstemp(prefix=".w", dir=d)
+            os.close(fd)
             os.unlink(probe)
             return d
         except OSError:

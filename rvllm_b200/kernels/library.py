@@ -19,6 +19,7 @@ from ..errors import KernelError
 from . import build
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
+COUNTERS = {'launches': 0}   # kernels of this project launched so far (library GEMMs are not counted)
 _STATUS = {-1: "a size is out of range", -2: "unsupported dtype", -3: "misaligned pointer or stride",
            -4: "size not supported by this kernel"}
 
@@ -29,6 +30,7 @@ def _ptr(t: Optional[torch.Tensor]):
 
 def _check(name: str, status: int):
     if status == 0:
+        COUNTERS['launches'] += 1
         return
     if status < 0:
         raise KernelError(f"{name}: refused, {_STATUS.get(status, 'code %d' % status)}")
