@@ -1,0 +1,415 @@
+// Paged flash attention for bfloat16, prefill and decode from one template.
+//
+// The rows of a tile are (token, query head) pairs of ONE key/value head: the G = nh / nkv
+// query heads that share a key/value head are packed into the row dimension, so every key and
+// value is fetched once per group.  A CTA owns a tile of 16 * WARPS_M rows of one sequence and
+// one kv head, and walks the keys in tiles of 64 through the sequence's block table:
+//   prefill / mixed steps: WARPS_M = 4, WARPS_N = 1 - the four warps own 16 rows each;
+//   decode (one token per sequence): WARPS_M = 1, WARPS_N = 4 - the warps share 16 rows and own
+//     16 of the tile's 64 keys each; their partial results are merged through shared memory.
+// The keys of a sequence can also be split over `num_splits` CTAs; each writes a partial
+// (unnormalised sum, running maximum, denominator) to scratch memory and a second kernel merges
+// them with the same algebra.  Scores, softmax and the weighted sum are in float; the two
+// products run on the tensor cores (mma.sync m16n8k16, bf16 in, float accumulate).
+//
+// Rule (v3/kernels/paged_attention_sm89.cu:277-308 of the reference): a sequence's q_len tokens
+// of this step are the tail of its ctx_len cached tokens; token i sits at position
+// p = ctx_len - q_len + i and sees keys (p - window, p] (all of [0, p] without a window).
+// Cache layer layout: [num_pages, 2 (k, v), nkv, page_size, HEAD_DIM], page_size a power of two.
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 128
+#endif
+static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head_dim must be a multiple of 16 up to 256");
+
+#define KV_TILE 64
+// a row of the shared-memory tiles is padded by 16 bytes: the stride is an odd multiple of
+// 16 bytes, so the 8 rows an ldmatrix reads fall into different banks
+#define ROW_BYTES (HEAD_DIM * 2 + 16)
+#define TILE_BYTES (KV_TILE * ROW_BYTES)
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    const int n = valid ? 16 : 0;     // src-size 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct FlashParams {
+    const __nv_bfloat16* q;        // [n_tokens, nh, HEAD_DIM]
+    const __nv_bfloat16* cache;    // one layer
+    const int* block_tables;       // [num_seqs, max_blocks]
+    const int* cu_seqlens;         // [num_seqs + 1]
+    const int* ctx_lens;           // [num_seqs]
+    __nv_bfloat16* out;            // [n_tokens, nh, HEAD_DIM]
+    float* part_o;                 // [num_splits, n_tokens, nh, HEAD_DIM]   (num_splits > 1)
+    float* part_ml;                // [num_splits, n_tokens, nh, 2]
+    int n_tokens, nh, nkv, page_shift, page_size, max_blocks;
+    float scale_log2e;
+    int window;
+    int num_splits;
+    int row_tiles;                 // row tiles per sequence the grid provides
+    int q_filter;                  // 0: every sequence, 1: only q_len == 1, 2: only q_len > 1
+};
+
+template <int WARPS_M, int WARPS_N>
+__global__ void __launch_bounds__(WARPS_M * WARPS_N * 32)
+flash_paged_kernel(const FlashParams p) {
+    constexpr int HD = HEAD_DIM;
+    constexpr int M_TILE = 16 * WARPS_M;
+    constexpr int KW = KV_TILE / WARPS_N;          // keys of a tile that one warp owns
+    constexpr int NTHREADS = WARPS_M * WARPS_N * 32;
+    constexpr int CHUNKS = HD / 8;                 // 16-byte chunks per row
+    extern __shared__ __align__(16) unsigned char smem[];
+
+    const int seq = blockIdx.z, kvh = blockIdx.y;
+    const int tile_m = blockIdx.x / p.num_splits, split = blockIdx.x - tile_m * p.num_splits;
+    const int G = p.nh / p.nkv;
+    const int ctx = p.ctx_lens[seq];
+    const int q_start = p.cu_seqlens[seq];
+    const int q_len = p.cu_seqlens[seq + 1] - q_start;
+    if (q_len <= 0) return;
+    if ((p.q_filter == 1 && q_len != 1) || (p.q_filter == 2 && q_len == 1)) return;
+    const int rows_total = q_len * G;
+    const int row0 = tile_m * M_TILE;
+    if (row0 >= rows_total) return;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_m = warp / WARPS_N, warp_n = warp - warp_m * WARPS_N;
+    const int quad = lane >> 2, tq = lane & 3;
+
+    // the two rows this thread holds of its warp's 16
+    int r[2], pos[2], lo[2], head[2], tok[2];
+    bool valid[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        r[i] = row0 + warp_m * 16 + quad + 8 * i;
+        const bool in_range = r[i] < rows_total;
+        const int t = in_range ? r[i] / G : 0;
+        tok[i] = q_start + t;
+        head[i] = kvh * G + (in_range ? r[i] - t * G : 0);
+        valid[i] = in_range && ctx > 0;
+        pos[i] = valid[i] ? ctx - q_len + t : -1;
+        lo[i] = (p.window > 0 && pos[i] - p.window + 1 > 0) ? pos[i] - p.window + 1 : 0;
+    }
+
+    // key range of the whole row tile, and this split's share of its key tiles
+    const int last_row = min(rows_total, row0 + M_TILE) - 1;
+    const int pos_first = ctx - q_len + row0 / G, pos_last = ctx - q_len + last_row / G;
+    const int key_lo = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
+    const int key_hi = ctx > 0 ? pos_last + 1 : 0;
+    const int tile_lo = key_lo / KV_TILE, tile_hi = (key_hi + KV_TILE - 1) / KV_TILE;
+    const int per_split = (tile_hi - tile_lo + p.num_splits - 1) / p.num_splits;
+    const int t_begin = tile_lo + split * per_split;
+    const int t_end = min(tile_hi, t_begin + per_split);
+
+    // Q fragments (A operand, 16 rows x HD), straight from global memory
+    uint32_t qa[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const __nv_bfloat16* qp = p.q + ((size_t)tok[i] * p.nh + head[i]) * HD + ks * 16 + tq * 2;
+            qa[ks][i] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp) : 0u;
+            qa[ks][i + 2] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp + 8) : 0u;
+        }
+    }
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    const int* table = p.block_tables + (size_t)seq * p.max_blocks;
+    const size_t page_stride = (size_t)2 * p.nkv * p.page_size * HD;
+    const size_t v_off = (size_t)p.nkv * p.page_size * HD;
+    const __nv_bfloat16* kv_base = p.cache + (size_t)kvh * p.page_size * HD;
+
+    auto load_tile = [&](int t, int stage) {
+        unsigned char* ks = smem + (size_t)stage * 2 * TILE_BYTES;
+        unsigned char* vs = ks + TILE_BYTES;
+        for (int idx = tid; idx < KV_TILE * CHUNKS; idx += NTHREADS) {
+            const int row = idx / CHUNKS, c = idx - row * CHUNKS;
+            const int key = t * KV_TILE + row;
+            const bool ok = key >= key_lo && key < key_hi;
+            const __nv_bfloat16* src = p.cache;
+            if (ok) {
+                const int page = table[key >> p.page_shift];
+                src = kv_base + (size_t)page * page_stride + (size_t)(key & (p.page_size - 1)) * HD + c * 8;
+            }
+            cp_async_16(ks + row * ROW_BYTES + c * 16, src, ok);
+            cp_async_16(vs + row * ROW_BYTES + c * 16, ok ? src + v_off : src, ok);
+        }
+    };
+
+    if (t_begin < t_end) load_tile(t_begin, 0);
+    cp_async_commit();
+    int stage = 0;
+    for (int t = t_begin; t < t_end; ++t) {
+        if (t + 1 < t_end) load_tile(t + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const unsigned char* ks = smem + (size_t)stage * 2 * TILE_BYTES;
+        const unsigned char* vs = ks + TILE_BYTES;
+
+        // S = Q K^T for this warp's rows and its KW keys of the tile
+        float s[KW / 8][4];
+#pragma unroll
+        for (int n = 0; n < KW / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+            for (int n2 = 0; n2 < KW / 16; ++n2) {
+                uint32_t b[4];
+                const int key_row = warp_n * KW + n2 * 16 + (lane >> 4) * 8 + (lane & 7);
+                const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4(b, ks + key_row * ROW_BYTES + col * 2);
+                mma_bf16(s[2 * n2], qa[kk], b[0], b[1]);
+                mma_bf16(s[2 * n2 + 1], qa[kk], b[2], b[3]);
+            }
+        }
+        // scale, mask, running maximum
+        const int key0 = t * KV_TILE + warp_n * KW + tq * 2;
+        float m_tile[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < KW / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = e >> 1;
+                const int key = key0 + n * 8 + (e & 1);
+                const bool see = key <= pos[i] && key >= lo[i];
+                const float v = see ? s[n][e] * p.scale_log2e : -INFINITY;
+                s[n][e] = v;
+                m_tile[i] = fmaxf(m_tile[i], v);
+            }
+        }
+        float alpha[2], m_safe[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            m_tile[i] = fmaxf(m_tile[i], __shfl_xor_sync(0xffffffffu, m_tile[i], 1));
+            m_tile[i] = fmaxf(m_tile[i], __shfl_xor_sync(0xffffffffu, m_tile[i], 2));
+            const float m_new = fmaxf(m_run[i], m_tile[i]);
+            m_safe[i] = m_new == -INFINITY ? 0.f : m_new;
+            alpha[i] = exp2f(m_run[i] - m_safe[i]);
+            m_run[i] = m_new;
+        }
+        float l_tile[2] = {0.f, 0.f};
+#pragma unroll
+        for (int n = 0; n < KW / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = exp2f(s[n][e] - m_safe[e >> 1]);
+                s[n][e] = pv;
+                l_tile[e >> 1] += pv;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * alpha[i] + l_tile[i];
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+            o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < KW / 16; ++kk) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int n2 = 0; n2 < HD / 16; ++n2) {
+                uint32_t b[4];
+                const int key_row = warp_n * KW + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                const int col = n2 * 16 + (lane >> 4) * 8;
+                ldmatrix_x4_trans(b, vs + key_row * ROW_BYTES + col * 2);
+                mma_bf16(o[2 * n2], pa, b[0], b[1]);
+                mma_bf16(o[2 * n2 + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+        stage ^= 1;
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+
+    if (WARPS_N > 1) {
+        // merge the warps that shared the rows: (m, l, O) -> shared memory, warp 0 of each row
+        // block combines.  The key/value buffers are free now.
+        __syncthreads();
+        float* mo = reinterpret_cast<float*>(smem);                 // [WARPS_N][16][HD]
+        float* mml = mo + WARPS_N * 16 * HD;                        // [WARPS_N][16][2]
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int row = quad + 8 * i;
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) {
+                float* dst = mo + ((size_t)warp_n * 16 + row) * HD + n * 8 + tq * 2;
+                dst[0] = o[n][2 * i]; dst[1] = o[n][2 * i + 1];
+            }
+            if (tq == 0) {
+                mml[(warp_n * 16 + row) * 2] = m_run[i];
+                mml[(warp_n * 16 + row) * 2 + 1] = l_run[i];
+            }
+        }
+        __syncthreads();
+        if (warp_n != 0) return;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int row = quad + 8 * i;
+            float m_all = -INFINITY;
+            for (int w = 0; w < WARPS_N; ++w) m_all = fmaxf(m_all, mml[(w * 16 + row) * 2]);
+            const float m_s = m_all == -INFINITY ? 0.f : m_all;
+            float l_all = 0.f;
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) { o[n][2 * i] = 0.f; o[n][2 * i + 1] = 0.f; }
+            for (int w = 0; w < WARPS_N; ++w) {
+                const float f = exp2f(mml[(w * 16 + row) * 2] - m_s);
+                l_all += mml[(w * 16 + row) * 2 + 1] * f;
+                if (f > 0.f) {
+#pragma unroll
+                    for (int n = 0; n < HD / 8; ++n) {
+                        const float* src = mo + ((size_t)w * 16 + row) * HD + n * 8 + tq * 2;
+                        o[n][2 * i] += src[0] * f; o[n][2 * i + 1] += src[1] * f;
+                    }
+                }
+            }
+            m_run[i] = m_all; l_run[i] = l_all;
+        }
+    }
+
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (r[i] >= rows_total) continue;
+        const size_t row_out = (size_t)tok[i] * p.nh + head[i];
+        if (p.num_splits == 1) {
+            const float inv = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
+            __nv_bfloat16* dst = p.out + row_out * HD + tq * 2;
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n)
+                *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+        } else {
+            const size_t prow = (size_t)split * p.n_tokens * p.nh + row_out;
+            float* dst = p.part_o + prow * HD + tq * 2;
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) { dst[n * 8] = o[n][2 * i]; dst[n * 8 + 1] = o[n][2 * i + 1]; }
+            if (tq == 0) { p.part_ml[prow * 2] = m_run[i]; p.part_ml[prow * 2 + 1] = l_run[i]; }
+        }
+    }
+}
+
+// Merge the partial results of the key splits: one block per (token, head).
+__global__ void flash_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                     __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
+    const int row = blockIdx.x;
+    float m_all = -INFINITY;
+    for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, part_ml[((size_t)s * rows + row) * 2]);
+    const float m_s = m_all == -INFINITY ? 0.f : m_all;
+    float l_all = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+        const float* ml = part_ml + ((size_t)s * rows + row) * 2;
+        l_all += ml[1] * exp2f(ml[0] - m_s);
+    }
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    for (int d = threadIdx.x; d < HEAD_DIM; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < num_splits; ++s) {
+            const float f = exp2f(part_ml[((size_t)s * rows + row) * 2] - m_s);
+            if (f > 0.f) acc += part_o[((size_t)s * rows + row) * HEAD_DIM + d] * f;
+        }
+        out[(size_t)row * HEAD_DIM + d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <int WARPS_M, int WARPS_N>
+static int launch_flash(const FlashParams& p, int num_seqs, cudaStream_t stream) {
+    const int merge_bytes = WARPS_N > 1 ? WARPS_N * 16 * (HEAD_DIM + 2) * 4 : 0;
+    const int smem = max(4 * TILE_BYTES, merge_bytes);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(flash_paged_kernel<WARPS_M, WARPS_N>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const dim3 grid(p.row_tiles * p.num_splits, p.nkv, num_seqs);
+    flash_paged_kernel<WARPS_M, WARPS_N><<<grid, WARPS_M * WARPS_N * 32, smem, stream>>>(p);
+    return rv_launch_status();
+}
+
+RV_EXPORT int rv_flash_head_dim() { return HEAD_DIM; }
+
+// How many floats of scratch `rv_flash_attention` needs for `num_splits` > 1.
+RV_EXPORT long long rv_flash_scratch_floats(int n_tokens, int nh, int num_splits) {
+    return num_splits > 1 ? (long long)num_splits * n_tokens * nh * (HEAD_DIM + 2) : 0;
+}
+
+// mode 0: prefill / mixed tiling (64 rows per CTA); mode 1: decode tiling (16 rows, warps split
+// the keys), for steps in which the selected sequences bring one token each.
+// scratch: float buffer of rv_flash_scratch_floats(...) elements when num_splits > 1.
+RV_EXPORT int rv_flash_attention(const void* q, const void* cache, const int* block_tables, const int* cu_seqlens,
+                                 const int* ctx_lens, void* out, float* scratch, int n_tokens, int num_seqs,
+                                 int nh, int nkv, int hd, int page_size, int max_blocks, float scale, int window,
+                                 int mode, int max_q_len, int num_splits, int q_filter, cudaStream_t stream) {
+    if (hd != HEAD_DIM) return RV_ERR_UNSUPPORTED;
+    if (n_tokens < 0 || num_seqs < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_blocks <= 0 ||
+        max_q_len <= 0 || num_splits < 1)
+        return RV_ERR_BAD_SIZE;
+    if (page_size & (page_size - 1)) return RV_ERR_UNSUPPORTED;
+    if (num_seqs > 65535 || nkv > 65535) return RV_ERR_BAD_SIZE;
+    if (n_tokens == 0 || num_seqs == 0) return RV_OK;
+    if (num_splits > 1 && scratch == nullptr) return RV_ERR_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) % 16)
+        return RV_ERR_ALIGNMENT;
+    FlashParams p;
+    p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache;
+    p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.ctx_lens = ctx_lens;
+    p.out = (__nv_bfloat16*)out;
+    p.part_o = scratch;
+    p.part_ml = scratch ? scratch + (size_t)num_splits * n_tokens * nh * HEAD_DIM : nullptr;
+    p.n_tokens = n_tokens; p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.max_blocks = max_blocks;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.scale_log2e = scale * 1.4426950408889634f;
+    p.window = window; p.num_splits = num_splits; p.q_filter = q_filter;
+    const int G = nh / nkv;
+    const int m_tile = mode == 1 ? 16 : 64;
+    p.row_tiles = (max_q_len * G + m_tile - 1) / m_tile;
+    int st = mode == 1 ? launch_flash<1, 4>(p, num_seqs, stream) : launch_flash<4, 1>(p, num_seqs, stream);
+    if (st != RV_OK) return st;
+    if (num_splits > 1) {
+        flash_combine_kernel<<<n_tokens * nh, HEAD_DIM >= 128 ? 128 : 64, 0, stream>>>(p.part_o, p.part_ml, p.out,
+                                                                                    n_tokens * nh, num_splits);
+        return rv_launch_status();
+    }
+    return RV_OK;
+}

@@ -188,7 +188,8 @@ class ModelRunner:
             ctx.attention.append(AttentionMeta(
                 block_tables=dev[o_bt:o_bt + B * MB].view(B, MB), cu_seqlens=ctx.cu_seqlens, ctx_lens=dev_ctx,
                 token_seq=ctx.token_seq, slot_mapping=dev[o_slot:o_slot + T], num_seqs=B,
-                max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), page_size=ps))
+                max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), page_size=ps,
+                num_decode=sum(1 for n in q_lens if n == 1)))
         return ctx
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

@@ -52,10 +52,11 @@ class AttentionMeta:
     """Per-step, per-cache-group arguments of the attention kernels (device int32 tensors) and
     the few host-side numbers that size their launches."""
     __slots__ = ("block_tables", "cu_seqlens", "ctx_lens", "token_seq", "slot_mapping", "num_seqs",
-                 "max_q_len", "max_ctx_len", "max_blocks", "page_size")
+                 "max_q_len", "max_ctx_len", "max_blocks", "page_size", "num_decode")
 
     def __init__(self, block_tables, cu_seqlens, ctx_lens, token_seq, slot_mapping, num_seqs,
-                 max_q_len, max_ctx_len, page_size):
+                 max_q_len, max_ctx_len, page_size, num_decode=0):
+        self.num_decode = num_decode       # sequences that bring exactly one token
         self.block_tables, self.cu_seqlens, self.ctx_lens = block_tables, cu_seqlens, ctx_lens
         self.token_seq, self.slot_mapping = token_seq, slot_mapping
         self.num_seqs, self.max_q_len, self.max_ctx_len = num_seqs, max_q_len, max_ctx_len
@@ -167,8 +168,51 @@ class CudaKernels:
     # ------------------------------------------------------------------ attention
     def paged_attention(self, q, cache_layer, meta: AttentionMeta, num_heads, num_kv_heads, head_dim,
                         scale: float, window: Optional[int]) -> torch.Tensor:
-        """Attention of the step's tokens over the paged cache (keys of this step included)."""
-        return self.paged_attention_plain(q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window)
+        """Attention of the step's tokens over the paged cache (keys of this step included).
+
+        bfloat16 with a head size that is a multiple of 16 and pages of a power of two go to the
+        tensor-core flash kernel (one token per sequence: the decode tiling, keys split over CTAs
+        when the batch alone cannot fill the GPU); everything else goes to the plain kernel."""
+        page = cache_layer.shape[3]
+        if q.dtype != torch.bfloat16 or head_dim % 16 or head_dim > 256 or (page & (page - 1)):
+            return self.paged_attention_plain(q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window)
+        out = torch.empty_like(q)
+        if meta.max_q_len == 1:
+            self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
+                                 mode=1, num_splits=self.decode_splits(meta, num_heads, num_kv_heads))
+        elif meta.num_decode == 0:
+            self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, mode=0)
+        else:
+            self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
+                                 mode=0, q_filter=2)
+            self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
+                                 mode=1, q_filter=1, max_q_len=1)
+        return out
+
+    @staticmethod
+    def decode_splits(meta: AttentionMeta, num_heads: int, num_kv_heads: int) -> int:
+        """Into how many CTAs the keys of a sequence are split in a decode step: enough to put
+        about two CTAs on each of the 148 SMs, never more than there are key tiles."""
+        group = num_heads // num_kv_heads
+        ctas = meta.num_seqs * num_kv_heads * ((group + 15) // 16)
+        tiles = max(1, (meta.max_ctx_len + 63) // 64)
+        return max(1, min((296 + ctas - 1) // ctas, tiles, 64))
+
+    def flash_attention(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
+                        mode=0, num_splits=1, q_filter=0, max_q_len=None):
+        _need(q, "q", torch.bfloat16, 2); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
+        lib = self._lib("attention_flash.cu", (f"-DHEAD_DIM={head_dim}",))
+        T = q.shape[0]
+        scratch = None
+        if num_splits > 1:
+            scratch = torch.empty((num_splits * T * num_heads * (head_dim + 2),), dtype=torch.float32, device=q.device)
+        st = lib.rv_flash_attention(
+            _ptr(q), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens),
+            _ptr(out), _ptr(scratch), c_int(T), c_int(meta.num_seqs), c_int(num_heads), c_int(num_kv_heads),
+            c_int(head_dim), c_int(cache_layer.shape[3]), c_int(meta.max_blocks), c_float(scale), c_int(window or 0),
+            c_int(mode), c_int(max_q_len or meta.max_q_len), c_int(num_splits), c_int(q_filter), self._stream())
+        _check("flash_attention", st)
+        return out
 
     def paged_attention_plain(self, q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window):
         _need(q, "q", dims=2); _need(cache_layer, "cache_layer", q.dtype, 5)

@@ -6,8 +6,16 @@ from typing import List, Sequence, Tuple
 from . import build
 
 
+FLASH_HEAD_DIMS = (16, 32, 64, 128)
+
+
 def all_variants() -> List[Tuple[str, Sequence[str]]]:
     out: List[Tuple[str, Sequence[str]]] = []
     for src in build.all_sources():
-        out.append((src, ()))
+        if src == "attention_flash.cu":
+            # one library per head size; the build check compiles the sizes of the benchmark
+            # and test configurations, others are compiled when a model first needs them
+            out.extend((src, (f"-DHEAD_DIM={hd}",)) for hd in FLASH_HEAD_DIMS)
+        else:
+            out.append((src, ()))
     return out
