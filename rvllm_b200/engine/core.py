@@ -65,7 +65,8 @@ class Engine:
         needs = self.model.cache_needs()
         num_pages = ec.num_blocks if ec.num_blocks is not None else self._pages_from_memory(needs, ec)
         self.cache = CacheManager(needs, num_pages, ec.block_size, ec.max_num_seqs, self.dtype, self.device)
-        self.runner = ModelRunner(self.model, self.cache, self.kernels, ec.max_model_len, self.device)
+        self.runner = ModelRunner(self.model, self.cache, self.kernels, ec.max_model_len, self.device,
+                                  () if ec.enforce_eager else ec.cuda_graph_batch_sizes)
 
     def _pages_from_memory(self, needs: Dict[int, object], ec: EngineConfig) -> int:
         per_page = CacheManager.bytes_per_page(needs, ec.block_size, self.dtype)

@@ -45,8 +45,13 @@ class StepContext:
 
 
 class ModelRunner:
-    def __init__(self, model, cache: CacheManager, kernels, max_model_len: int, device):
+    def __init__(self, model, cache: CacheManager, kernels, max_model_len: int, device,
+                 graph_batch_sizes: Sequence[int] = ()):
         self.model, self.cache, self.kernels = model, cache, kernels
+        self.graph_batch_sizes = tuple(sorted(graph_batch_sizes))
+        self._graphs = {}
+        self._graph_pool = None
+        self._graph_event = None
         self.max_model_len = max_model_len
         self.device = torch.device(device)
         self.max_blocks = cache.blocks_for(max_model_len)
@@ -112,17 +117,32 @@ class ModelRunner:
             starts.append(self.cache.append(e.req_id, len(e.tokens)))
         return starts
 
-    def pack(self, entries: Sequence[StepEntry], starts: List[int]) -> StepContext:
+    def pack(self, entries: Sequence[StepEntry], starts: List[int], pad_to: Optional[int] = None,
+             buffers=None) -> StepContext:
+        """Write the step's metadata into a pinned buffer and send it to the device in one copy.
+
+        With `pad_to` the batch is padded to that many one-token sequences (padding rows: token
+        0, context length 0, slot -1, state slot -1 - they write nothing and attend to nothing;
+        v3/crates/rvllm-metadata/src/pack.rs:35-40,79-86 of the reference pads the same way), block
+        tables get the full width, and the layout depends on `pad_to` alone, so that a captured
+        CUDA graph can be replayed on the buffer."""
         cache = self.cache
-        B = len(entries)
-        q_lens = [len(e.tokens) for e in entries]
+        n_real = len(entries)
+        B = pad_to if pad_to is not None else n_real
+        q_lens = [len(e.tokens) for e in entries] + [1] * (B - n_real)
         T = sum(q_lens)
-        ctx_lens = [s + n for s, n in zip(starts, q_lens)]
-        R = sum(len(e.want) for e in entries)
+        ctx_lens = [s + n for s, n in zip(starts, q_lens)] + [0] * (B - n_real)
+        wants = [list(e.want) for e in entries]
+        if pad_to is not None:
+            wants = [[0]] * B
+        R = sum(len(w) for w in wants)
         G = len(cache.groups)
-        MB = max(1, cache.blocks_for(max(ctx_lens)))
+        MB = self.max_blocks if pad_to is not None else max(1, cache.blocks_for(max(ctx_lens)))
         n_ints = 3 * T + (B + 1) + 2 * B + R + G * (T + B * MB) + 16
-        ring_i, host, dev = self._buffers(n_ints)
+        if buffers is None:
+            ring_i, host, dev = self._buffers(n_ints)
+        else:
+            ring_i, (host, dev) = None, buffers
         h = host.numpy()
         off = 0
 
@@ -137,16 +157,22 @@ class ModelRunner:
         cu = 0
         rows: List[int] = []
         h[o_cu] = 0
-        for i, e in enumerate(entries):
+        for i in range(B):
             n = q_lens[i]
-            h[o_tok + cu:o_tok + cu + n] = np.asarray(e.tokens, dtype=np.int32)
-            h[o_pos + cu:o_pos + cu + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
+            if i < n_real:
+                e = entries[i]
+                h[o_tok + cu:o_tok + cu + n] = np.asarray(e.tokens, dtype=np.int32)
+                h[o_pos + cu:o_pos + cu + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
+                h[o_state + i] = cache.state_slot(e.req_id)
+            else:
+                h[o_tok + cu] = 0
+                h[o_pos + cu] = 0
+                h[o_state + i] = -1
             h[o_seq + cu:o_seq + cu + n] = i
-            rows.extend(cu + w for w in e.want)
+            rows.extend(cu + w for w in wants[i])
             cu += n
             h[o_cu + i + 1] = cu
             h[o_ctx + i] = ctx_lens[i]
-            h[o_state + i] = cache.state_slot(e.req_id)
         if R:
             h[o_rows:o_rows + R] = np.asarray(rows, dtype=np.int32)
         group_offsets = []
@@ -154,6 +180,7 @@ class ModelRunner:
         for gi in range(G):
             o_slot, o_bt = take(T), take(B * MB)
             h[o_bt:o_bt + B * MB] = -1
+            h[o_slot:o_slot + T] = -1
             cu = 0
             for i, e in enumerate(entries):
                 table = cache.block_table(e.req_id, gi)
@@ -166,7 +193,7 @@ class ModelRunner:
             group_offsets.append((o_slot, o_bt))
         dev[:off].copy_(host[:off], non_blocking=True)
         self.last_h2d_bytes = off * 4
-        if self.device.type == "cuda":
+        if self.device.type == "cuda" and ring_i is not None:
             ev = self._ring_events[ring_i] or torch.cuda.Event()
             ev.record()
             self._ring_events[ring_i] = ev
@@ -184,11 +211,12 @@ class ModelRunner:
         ctx.q_lens, ctx.ctx_lens = q_lens, ctx_lens
         ctx.req_ids = [e.req_id for e in entries]
         ctx.attention = []
+        max_ctx = self.max_model_len if pad_to is not None else max(ctx_lens)
         for (o_slot, o_bt) in group_offsets:
             ctx.attention.append(AttentionMeta(
                 block_tables=dev[o_bt:o_bt + B * MB].view(B, MB), cu_seqlens=ctx.cu_seqlens, ctx_lens=dev_ctx,
                 token_seq=ctx.token_seq, slot_mapping=dev[o_slot:o_slot + T], num_seqs=B,
-                max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), page_size=ps,
+                max_q_len=max(q_lens), max_ctx_len=max_ctx, page_size=ps,
                 num_decode=sum(1 for n in q_lens if n == 1)))
         return ctx
 
@@ -199,13 +227,66 @@ class ModelRunner:
             return None
         self.validate(entries)
         starts = self.reserve(entries)
-        ctx = self.pack(entries, starts)
-        hidden = self.model.forward(ctx, self.cache)
-        logits = self.model.compute_logits(hidden, ctx) if ctx.logit_rows.numel() else None
+        bucket = self._graph_bucket(entries)
+        if bucket is not None:
+            logits = self._step_graph(entries, starts, bucket)
+        else:
+            ctx = self.pack(entries, starts)
+            hidden = self.model.forward(ctx, self.cache)
+            logits = self.model.compute_logits(hidden, ctx) if ctx.logit_rows.numel() else None
         for e in entries:
             self.cache.release_passed(e.req_id)
         self.steps_run += 1
         return logits
+
+    # ---- decode steps replayed from CUDA graphs -------------------------------------------------
+    def _graph_bucket(self, entries: Sequence[StepEntry]) -> Optional[int]:
+        """The batch-size bucket whose graph can run this step: every entry brings one token and
+        wants its logits, and a bucket is large enough."""
+        if not self.graph_batch_sizes or self.device.type != "cuda":
+            return None
+        for e in entries:
+            if len(e.tokens) != 1 or len(e.want) != 1:
+                return None
+        for b in self.graph_batch_sizes:
+            if b >= len(entries):
+                return b
+        return None
+
+    def _step_graph(self, entries, starts, bucket: int) -> torch.Tensor:
+        state = self._graphs.get(bucket)
+        if state is None:
+            # the first step of a bucket runs eagerly: it loads every kernel library and lets the
+            # GEMM library set itself up; the graph is captured right after it for later steps
+            ctx = self.pack(entries, starts)
+            hidden = self.model.forward(ctx, self.cache)
+            logits = self.model.compute_logits(hidden, ctx)
+            self._graphs[bucket] = self._capture(bucket)
+            return logits
+        host, dev, graph, out = state
+        self._graph_event.synchronize()
+        self.pack(entries, starts, pad_to=bucket, buffers=(host, dev))
+        self._graph_event.record()
+        graph.replay()
+        return out[:len(entries)]
+
+    def _capture(self, bucket: int):
+        G = len(self.cache.groups)
+        n_ints = 3 * bucket + (bucket + 1) + 2 * bucket + bucket + G * (bucket + bucket * self.max_blocks) + 16
+        host = torch.empty((n_ints,), dtype=torch.int32, pin_memory=True)
+        dev = torch.empty((n_ints,), dtype=torch.int32, device=self.device)
+        ctx = self.pack([], [], pad_to=bucket, buffers=(host, dev))   # all rows padded: writes nothing
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            hidden = self.model.forward(ctx, self.cache)
+            out = self.model.compute_logits(hidden, ctx)
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        if self._graph_event is None:
+            self._graph_event = torch.cuda.Event()
+            self._graph_event.record()
+        return host, dev, graph, out
 
     def finish(self, req_id: Hashable) -> None:
         """Give back everything the request holds."""

@@ -65,7 +65,7 @@ class AttentionMeta:
 
 
 class CudaKernels:
-    SKINNY_MAX_ROWS = 0     # rows up to which the weight-streaming GEMM is used (0: not yet)
+    SKINNY_MAX_ROWS = 0     # rows up to which the weight-streaming GEMM replaces the library GEMM (0: off)
 
     def __init__(self, device="cuda:0"):
         if not torch.cuda.is_available():
@@ -257,6 +257,10 @@ class CudaKernels:
         return self._linear_bf16(x, weight, bias, residual, out_dtype)
 
     def _linear_bf16(self, x, weight, bias, residual, out_dtype):
+        M, K = x.shape
+        if 0 < M <= self.SKINNY_MAX_ROWS and K % 8 == 0 and out_dtype in (torch.bfloat16, torch.float32) \
+                and (residual is None or (residual.dtype == torch.bfloat16 and out_dtype == torch.bfloat16)):
+            return self.linear_skinny(x, weight, bias, residual, out_dtype)
         if out_dtype == torch.float32:
             out = torch.mm(x, weight.t(), out_dtype=torch.float32)
             if bias is not None:
@@ -270,6 +274,34 @@ class CudaKernels:
         if residual is not None:
             out += residual
         return out
+
+    def linear_skinny(self, x, weight, bias=None, residual=None, out_dtype=None, gated=False, tiles_per_cta=0):
+        """The weight-streaming tensor-core GEMM for at most 64 rows of bfloat16 activations.
+        gated: weight rows are [gate | up]; returns silu(x gate^T) * (x up^T)."""
+        _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
+        M, K = x.shape
+        N = weight.shape[0]
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+        if bias is not None:
+            _need(bias, "bias", dims=1)
+        if residual is not None:
+            _need(residual, "residual", torch.bfloat16, 2)
+        st = self._lib("gemm_skinny.cu").rv_gemm_skinny_bf16(
+            _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0),
+            _ptr(residual), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0), c_int(M), c_int(N), c_int(K),
+            c_int(1 if gated else 0), c_int(tiles_per_cta), self._stream())
+        _check("gemm_skinny", st)
+        return out
+
+    def gate_up_silu(self, x, weight) -> torch.Tensor:
+        """silu(x Wg^T) * (x Wu^T) for weight rows [Wg | Wu]: one fused kernel for few bfloat16
+        rows, else the product followed by the SiLU kernel."""
+        M, K = x.shape
+        if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < M <= self.SKINNY_MAX_ROWS \
+                and K % 8 == 0 and weight.shape[0] % 2 == 0:
+            return self.linear_skinny(x, weight, gated=True)
+        return self.silu_mul(self.linear(x, weight))
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature=None, top_k=None, top_p=None, seeds=None, draw_index=None) -> torch.Tensor:

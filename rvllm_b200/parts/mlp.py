@@ -25,8 +25,7 @@ class GatedMLP(Part):
         self.down.bind(get)
 
     def __call__(self, x, ctx, residual=None):
-        gu = self.gate_up(x, ctx)
-        h = ctx.kernels.silu_mul(gu)
+        h = ctx.kernels.gate_up_silu(x, self.gate_up.weight)
         return self.down(h, ctx, residual=residual)
 
 

@@ -93,6 +93,9 @@ class EmulatedKernels:
             y = y + residual.float()
         return y.to(out_dtype or x.dtype)
 
+    def gate_up_silu(self, x, weight):
+        return self.silu_mul(self.linear(x, weight))
+
     def sample(self, logits, temperature=None, top_k=None, top_p=None, seeds=None, draw_index=None):
         from plain_impl import sample as plain_sample
         out = []
