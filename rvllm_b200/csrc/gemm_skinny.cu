@@ -172,9 +172,11 @@ template <int MT, int NT, bool GATED>
 static int launch_skinny(SkinnyParams& p, cudaStream_t stream) {
     // K chunk: as large as fits beside nothing else; shared memory is reused for the reduction
     const int budget = 160 * 1024;
+    // a multiple of 32 * SK_WARPS: warp w then owns the k steps congruent to w whatever the chunk
+    // size is, so the order of summation does not depend on M
     int kc = (budget / (MT * 8 * 2)) - X_PAD;
-    kc &= ~31;
-    const int k32 = (p.K + 31) & ~31;
+    kc &= ~(32 * SK_WARPS - 1);
+    const int k32 = (p.K + 32 * SK_WARPS - 1) & ~(32 * SK_WARPS - 1);
     if (kc > k32) kc = k32;
     p.kc = kc;
     const size_t x_bytes = (size_t)MT * 8 * (kc + X_PAD) * 2;

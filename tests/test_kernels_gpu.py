@@ -1,0 +1,260 @@
+"""Each CUDA kernel alone against its plain reference (tests/plain_impl.py), in float32 and
+bfloat16, at sizes other than the engine's own tests use."""
+import math
+
+import pytest
+import torch
+
+import plain_impl as P
+from gpu_tools import paged_setup, rel_err
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 2e-6
+BF16_TOL = 1e-2      # a bfloat16 result carries half an ulp (2^-9) of its own rounding
+
+
+@pytest.fixture(scope="module")
+def K():
+    from rvllm_b200.kernels import get_library
+    return get_library("cuda:0")
+
+
+def tol(dtype):
+    return F32_TOL if dtype == torch.float32 else BF16_TOL
+
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width", [(7, 100), (300, 4096), (1, 13)])
+def test_gather_rows(K, dtype, rows, width):
+    torch.manual_seed(0)
+    table = torch.randn(rows, width, device="cuda").to(dtype)
+    ids = torch.randint(0, rows, (37,), device="cuda", dtype=torch.int32)
+    out = K.gather_rows(table, ids)
+    assert torch.equal(out.cpu(), P.embedding(ids.tolist(), table.cpu()))
+    ids[3] = rows + 5                                   # the host refuses such ids; the kernel writes zeros
+    assert float(K.gather_rows(table, ids)[3].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width,eps", [(5, 100, 1e-5), (3, 4100, 1e-6), (64, 24, 1e-2)])
+def test_rmsnorm(K, dtype, rows, width, eps):
+    torch.manual_seed(1)
+    x = (torch.randn(rows, width, device="cuda") * 3).to(dtype)
+    gamma = (1 + 0.1 * torch.randn(width, device="cuda")).to(dtype)
+    ref = P.rms_norm(x.double().cpu(), gamma.double().cpu(), eps)
+    assert rel_err(K.rmsnorm(x, gamma, eps), ref) < tol(dtype)
+    g32 = gamma.float()                                 # a weight the checkpoint stores in 32 bits stays so
+    assert rel_err(K.rmsnorm(x, g32, eps), P.rms_norm(x.double().cpu(), g32.double().cpu(), eps)) < tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,inter", [(3, 172), (17, 1000), (1, 7)])
+def test_silu_mul(K, dtype, rows, inter):
+    torch.manual_seed(2)
+    gu = (torch.randn(rows, 2 * inter, device="cuda") * 4).to(dtype)
+    g, u = gu[:, :inter].double().cpu(), gu[:, inter:].double().cpu()
+    assert rel_err(K.silu_mul(gu), g / (1 + torch.exp(-g)) * u) < tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,page,bias", [(5, 1, 48, 4, True), (8, 8, 16, 32, False), (6, 3, 128, 16, True)])
+def test_rope_bias_cache_write(K, dtype, nh, nkv, hd, page, bias):
+    from rvllm_b200.parts import RotaryEncoding
+    torch.manual_seed(3)
+    T, n_pages = 23, 9
+    rope = RotaryEncoding(hd, 50000.0, None)
+    rope.prepare(300, "cuda")
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device="cuda").to(dtype)
+    b = torch.randn((nh + 2 * nkv) * hd, device="cuda").to(dtype) if bias else None
+    positions = torch.randint(0, 300, (T,), dtype=torch.int32)
+    slots = torch.randperm(n_pages * page)[:T].to(torch.int32)
+    slots[5] = -1                                       # a padded row writes nothing
+    cache = torch.zeros(n_pages, 2, nkv, page, hd, device="cuda", dtype=dtype)
+    q = K.rope_cache_write(qkv, b, positions.cuda(), rope.cos, rope.sin, slots.cuda(), cache, nh, nkv, hd)
+    x = qkv.double().cpu() + (b.double().cpu() if bias else 0)
+    inv = P.rope_inv_freq(hd, 50000.0, None)
+    q_ref = P.apply_rope(x[:, :nh * hd].view(T, nh, hd), positions.tolist(), inv)
+    k_ref = P.apply_rope(x[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd), positions.tolist(), inv)
+    v_ref = x[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    assert rel_err(q.view(T, nh, hd), q_ref) < tol(dtype)
+    want = torch.zeros(n_pages, 2, nkv, page, hd, dtype=torch.float64)
+    for t in range(T):
+        s = int(slots[t])
+        if s >= 0:
+            want[s // page, 0, :, s % page] = k_ref[t]
+            want[s // page, 1, :, s % page] = v_ref[t]
+    assert rel_err(cache, want) < tol(dtype)
+    assert float(cache.double().cpu()[want == 0].abs().max()) == 0.0     # nothing else was touched
+    # q alone (a layer that reads another layer's cache)
+    q_only = K.rope_cache_write(qkv[:, :nh * hd].contiguous(), b[:nh * hd] if bias else None, positions.cuda(),
+                                rope.cos, rope.sin, None, None, nh, nkv, hd, write_kv=False)
+    assert torch.equal(q_only, q)
+    # no position encoding: bias only
+    q_plain = K.rope_cache_write(qkv, b, positions.cuda(), None, None, slots.cuda(), cache, nh, nkv, hd)
+    assert rel_err(q_plain.view(T, nh, hd), x[:, :nh * hd].view(T, nh, hd)) < tol(dtype)
+
+
+def _attention_case(nh, nkv, hd, page, q_lens, ctx_lens, window, seed):
+    torch.manual_seed(seed)
+    ks = [torch.randn(c, nkv, hd) for c in ctx_lens]
+    vs = [torch.randn(c, nkv, hd) for c in ctx_lens]
+    qs = [torch.randn(n, nh, hd) for n in q_lens]
+    return ks, vs, qs
+
+
+def _attention_ref(ks, vs, qs, ctx_lens, q_lens, scale, window, dtype):
+    outs = []
+    for k, v, q, c, n in zip(ks, vs, qs, ctx_lens, q_lens):
+        k, v, q = (t.to(dtype).double() for t in (k, v, q))
+        full_q = torch.zeros(c, q.shape[1], q.shape[2], dtype=torch.float64)
+        full_q[c - n:] = q
+        outs.append(P.causal_attention(full_q, k, v, scale, window)[c - n:])
+    return torch.cat(outs)
+
+
+ATT_CASES = [
+    # nh, nkv, hd, page, q_lens, ctx_lens, window
+    (4, 2, 16, 16, [5], [5], None),
+    (6, 2, 32, 8, [70, 1, 1, 2], [70, 9, 129, 64], 40),
+    (7, 7, 48, 4, [33, 1, 7], [33, 40, 100], None),
+    (12, 4, 64, 32, [1, 1, 1], [500, 31, 1], None),
+    (10, 2, 80, 16, [64, 65], [64, 200], 64),
+    (3, 1, 256, 16, [9, 1], [30, 77], None),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ATT_CASES)
+def test_paged_attention_plain_kernel(K, dtype, case):
+    nh, nkv, hd, page, q_lens, ctx_lens, window = case
+    ks, vs, qs = _attention_case(nh, nkv, hd, page, q_lens, ctx_lens, window, 4)
+    cache, meta = paged_setup(ks, vs, q_lens, page, dtype)
+    q = torch.cat(qs).reshape(sum(q_lens), nh * hd).cuda().to(dtype)
+    scale = 1 / math.sqrt(hd)
+    out = K.paged_attention_plain(q, cache, meta, nh, nkv, hd, scale, window)
+    ref = _attention_ref(ks, vs, qs, ctx_lens, q_lens, scale, window, dtype)
+    assert rel_err(out.view(-1, nh, hd), ref) < (1e-5 if dtype == torch.float32 else BF16_TOL)
+
+
+@pytest.mark.parametrize("case", ATT_CASES)
+def test_flash_attention_kernel(K, case):
+    nh, nkv, hd, page, q_lens, ctx_lens, window = case
+    ks, vs, qs = _attention_case(nh, nkv, hd, page, q_lens, ctx_lens, window, 5)
+    cache, meta = paged_setup(ks, vs, q_lens, page, torch.bfloat16)
+    q = torch.cat(qs).reshape(sum(q_lens), nh * hd).cuda().bfloat16()
+    scale = 1 / math.sqrt(hd)
+    ref = _attention_ref(ks, vs, qs, ctx_lens, q_lens, scale, window, torch.bfloat16)
+    out = K.paged_attention(q, cache, meta, nh, nkv, hd, scale, window)        # the product path's dispatch
+    assert rel_err(out.view(-1, nh, hd), ref) < BF16_TOL
+    plain = K.paged_attention_plain(q, cache, meta, nh, nkv, hd, scale, window)
+    assert rel_err(out, plain.double()) < BF16_TOL
+    if max(q_lens) == 1:
+        for splits in (2, 5):                                                   # keys split over CTAs and merged
+            o2 = torch.empty_like(q)
+            K.flash_attention(q, cache, meta, o2, nh, nkv, hd, scale, window, mode=1, num_splits=splits)
+            assert rel_err(o2.view(-1, nh, hd), ref) < BF16_TOL
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_a_far_key_among_hundreds(K, dtype):
+    """One key far back is made to dominate: the output must be its value row.  Random scores
+    would hide a kernel that drops or misplaces a page of keys."""
+    nh, nkv, hd, page = 4, 2, 64, 16
+    ctx = 777
+    for target in (0, 15, 16, 300, 511, 512, 776):         # first key, page edges, tile edges, the last key
+        torch.manual_seed(target)
+        k = torch.randn(ctx, nkv, hd) * 0.1
+        v = torch.randn(ctx, nkv, hd)
+        q = torch.randn(1, nh, hd) * 0.1
+        direction = torch.randn(hd)
+        direction /= direction.norm()
+        k[target] = direction * 12.0
+        q[0] = direction * 12.0                             # score 144 * scale = 18: e^18 against 776 keys near e^0
+        cache, meta = paged_setup([k], [v], [1], page, dtype, seed=target)
+        out = K.paged_attention(q.reshape(1, nh * hd).cuda().to(dtype), cache, meta, nh, nkv, hd, 1 / math.sqrt(hd), None)
+        want = v[target][[0, 0, 1, 1]].to(dtype).double()
+        got = out.view(nh, hd).double().cpu()
+        assert float((got - want).abs().max()) < 0.1, f"key {target} was not found"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_window_edge(K, dtype):
+    """The key just inside the window dominates when it may be seen; the key just outside never does."""
+    nh, nkv, hd, page, window = 2, 1, 32, 8, 24
+    ctx, q_len = 100, 10
+    torch.manual_seed(0)
+    direction = torch.randn(hd)
+    direction /= direction.norm()
+    for which in ("inside", "outside"):
+        k = torch.randn(ctx, nkv, hd) * 0.1
+        v = torch.randn(ctx, nkv, hd)
+        q = direction.repeat(q_len, nh, 1) * 12.0
+        p_last = ctx - 1
+        marked = p_last - window + 1 if which == "inside" else p_last - window      # edge of the LAST query's window
+        k[marked] = direction * 12.0
+        cache, meta = paged_setup([k], [v], [q_len], page, dtype)
+        out = K.paged_attention(q.reshape(q_len, nh * hd).cuda().to(dtype), cache, meta, nh, nkv, hd,
+                                1 / math.sqrt(hd), window).view(q_len, nh, hd).double().cpu()
+        hit = float((out[-1, 0] - v[marked, 0].to(dtype).double()).abs().max()) < 0.1
+        assert hit == (which == "inside")
+        # the earlier queries of the portion have their own windows: the marked key is inside them all
+        assert float((out[0, 0] - v[marked, 0].to(dtype).double()).abs().max()) < 0.1
+
+
+@pytest.mark.parametrize("M,N,Kd,bias,res", [(1, 7, 5, False, False), (33, 261, 172, True, True),
+                                             (130, 64, 300, False, True), (5, 1000, 2048, True, False)])
+def test_gemm_f32_is_true_32_bit(K, M, N, Kd, bias, res):
+    torch.manual_seed(6)
+    x = torch.randn(M, Kd, device="cuda")
+    w = torch.randn(N, Kd, device="cuda")
+    # operands with more mantissa bits than TF32 keeps: a reduced-precision product would be off by 1e-3
+    b = torch.randn(N, device="cuda") if bias else None
+    r = torch.randn(M, N, device="cuda") if res else None
+    ref = x.double().cpu() @ w.double().cpu().t()
+    if bias:
+        ref += b.double().cpu()
+    if res:
+        ref += r.double().cpu()
+    out = K.linear(x, w, b, r)
+    assert out.dtype == torch.float32 and rel_err(out, ref) < 3e-6
+    again = K.linear(x[:1].contiguous(), w, b, r[:1].contiguous() if res else None)
+    assert torch.equal(again, out[:1])                      # a row does not depend on the rest of the batch
+
+
+@pytest.mark.parametrize("M,N,Kd", [(1, 64, 64), (3, 100, 200), (17, 520, 4096), (40, 96, 1024), (64, 1000, 328)])
+def test_gemm_skinny_bf16(K, M, N, Kd):
+    torch.manual_seed(7)
+    x = torch.randn(M, Kd, device="cuda").bfloat16()
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(N, device="cuda").bfloat16()
+    r = torch.randn(M, N, device="cuda").bfloat16()
+    ref = x.double().cpu() @ w.double().cpu().t()
+    for tiles in (0, 1, 2, 4):
+        assert rel_err(K.linear_skinny(x, w, tiles_per_cta=tiles), ref) < BF16_TOL
+    full = ref + b.double().cpu() + r.double().cpu()
+    assert rel_err(K.linear_skinny(x, w, b, r), full) < BF16_TOL
+    assert rel_err(K.linear_skinny(x, w, b.float(), None, torch.float32), ref + b.double().cpu()) < 1e-5
+    if N % 2 == 0:
+        g, u = ref[:, :N // 2], ref[:, N // 2:]
+        assert rel_err(K.linear_skinny(x, w, gated=True), g / (1 + torch.exp(-g)) * u) < BF16_TOL
+    one = K.linear_skinny(x[:1].contiguous(), w, out_dtype=torch.float32)
+    assert torch.equal(one, K.linear_skinny(x, w, out_dtype=torch.float32)[:1])
+
+
+@pytest.mark.parametrize("M,N,Kd,res,f32out", [(200, 300, 172, True, False), (64, 261, 80, False, True),
+                                               (2048, 512, 256, True, False)])
+def test_linear_bf16_library_path(K, M, N, Kd, res, f32out):
+    torch.manual_seed(8)
+    x = torch.randn(M, Kd, device="cuda").bfloat16()
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    r = torch.randn(M, N, device="cuda").bfloat16() if res else None
+    ref = x.double().cpu() @ w.double().cpu().t() + (r.double().cpu() if res else 0)
+    out = K.linear(x, w, None, r, torch.float32 if f32out else None)
+    assert out.dtype == (torch.float32 if f32out else torch.bfloat16)
+    assert rel_err(out, ref) < (1e-5 if f32out else BF16_TOL)
+    # a matrix the checkpoint keeps in 32 bits is multiplied in float32
+    assert rel_err(K.linear(x, w.float(), None, r), ref) < BF16_TOL
