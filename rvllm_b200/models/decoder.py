@@ -109,6 +109,8 @@ class DecoderModel:
     # ---- the forward pass of one step ----------------------------------------------------------
     def forward(self, ctx, caches) -> torch.Tensor:
         x = ctx.kernels.gather_rows(self.embedding, ctx.token_ids)
+        if x.dtype != self.dtype:
+            x = x.to(self.dtype)       # a table the checkpoint keeps in 32 bits; activations have the engine's type
         for pe in self.position_encodings.values():
             x = pe.on_embeddings(x, ctx)
         for e in self.spec.run_order:

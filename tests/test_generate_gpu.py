@@ -1,0 +1,108 @@
+"""Generation through the Python entry point on the GPU."""
+import pytest
+import torch
+
+import plain_impl
+from model_tools import model_folder, random_requests
+
+pytestmark = pytest.mark.gpu
+
+
+def make_llm(name, dtype, **kw):
+    from rvllm_b200 import LLM
+    args = dict(dtype=dtype, block_size=8, num_blocks=96, max_model_len=256, max_num_seqs=4, max_num_batched_tokens=48)
+    args.update(kw)
+    return LLM(model_folder(name), **args)
+
+
+@pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen2"])
+def test_greedy_float32_equals_plain(name):
+    from rvllm_b200 import SamplingParams
+    cfg, w = plain_impl.read_model_folder(model_folder(name))
+    prompts = list(random_requests(cfg["vocab_size"], (5, 17, 33, 60, 2), seed=2).values())
+    llm = make_llm(name, "float32", max_prefill_chunk=16)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.outputs[0].token_ids == plain_impl.greedy_generate(cfg, w, p, 10)
+    llm.engine.cache.check()
+    assert not llm.engine.cache.requests
+
+
+@pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen2"])
+def test_greedy_bfloat16_follows_plain_where_the_margin_allows(name):
+    """bfloat16 may flip a token only where the plain logits' two best are closer than its error."""
+    from rvllm_b200 import SamplingParams
+    cfg, w = plain_impl.read_model_folder(model_folder(name))
+    prompts = list(random_requests(cfg["vocab_size"], (9, 40, 70), seed=5).values())
+    llm = make_llm(name, "bfloat16")
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        ids = list(p)
+        for tok in o.outputs[0].token_ids:
+            logits = plain_impl.forward(cfg, w, ids)[-1]
+            top = torch.topk(logits, 2).values
+            margin = float(top[0] - top[1]) / float(logits.abs().max())
+            if margin > 4e-2:
+                assert tok == int(logits.argmax()), f"flipped at a margin of {margin:.3f}"
+            ids.append(tok)                                  # follow the engine's own continuation
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuda_graph_decode_equals_eager_and_batching_does_not_change_samples(dtype):
+    from rvllm_b200 import SamplingParams
+    cfg, _ = plain_impl.read_model_folder(model_folder("tiny_qwen2"))
+    prompts = list(random_requests(cfg["vocab_size"], (5, 23, 70, 9, 41), seed=8).values())
+    sp = SamplingParams(temperature=0.8, top_k=40, seed=3, max_tokens=24, ignore_eos=True)
+    eager = make_llm("tiny_qwen2", dtype, enforce_eager=True, max_num_seqs=8)
+    a = [o.outputs[0].token_ids for o in eager.generate(prompts, sp)]
+    graphs = make_llm("tiny_qwen2", dtype, enforce_eager=False, max_num_seqs=8)
+    b = [o.outputs[0].token_ids for o in graphs.generate(prompts, sp)]
+    assert graphs.engine.runner._graphs, "no decode step was replayed from a graph"
+    assert a == b
+    if dtype == "float32":
+        # other portions, other batches: one request at a time, tiny token budget
+        alone = make_llm("tiny_qwen2", dtype, max_num_seqs=1, max_num_batched_tokens=7)
+        c = [o.outputs[0].token_ids for o in alone.generate(prompts, sp)]
+        assert a == c
+
+
+def test_finish_reasons_and_stop_tokens():
+    from rvllm_b200 import SamplingParams
+    cfg, w = plain_impl.read_model_folder(model_folder("tiny_llama"))
+    prompt = random_requests(cfg["vocab_size"], (12,), seed=6)["r0"]
+    free_run = plain_impl.greedy_generate(cfg, w, prompt, 8)
+    llm = make_llm("tiny_llama", "float32")
+    out = llm.generate([prompt], SamplingParams(max_tokens=8, stop_token_ids=(free_run[3],), ignore_eos=True))[0]
+    first = free_run.index(free_run[3])
+    assert out.outputs[0].token_ids == free_run[:first + 1] and out.outputs[0].finish_reason == "stop"
+    out = llm.generate([prompt], SamplingParams(max_tokens=5, ignore_eos=True))[0]
+    assert out.outputs[0].finish_reason == "length" and len(out.outputs[0].token_ids) == 5
+
+
+def test_preemption_on_the_gpu_keeps_outputs():
+    from rvllm_b200 import SamplingParams
+    cfg, _ = plain_impl.read_model_folder(model_folder("tiny_qwen2"))
+    prompts = list(random_requests(cfg["vocab_size"], (30, 28, 26, 20), seed=4).values())
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    roomy = make_llm("tiny_qwen2", "float32", num_blocks=64, max_num_batched_tokens=32)
+    want = [o.outputs[0].token_ids for o in roomy.generate(prompts, sp)]
+    tight = make_llm("tiny_qwen2", "float32", num_blocks=14, max_num_batched_tokens=32)
+    outs = tight.generate(prompts, sp)
+    assert sum(o.num_preemptions for o in outs) > 0
+    assert [o.outputs[0].token_ids for o in outs] == want
+    tight.engine.cache.check()
+
+
+def test_random_weights_without_a_folder_and_loud_errors():
+    import tiny_configs
+    from rvllm_b200 import ConfigError, KvExhausted, LLM, SamplingParams, config_from_dict
+    cfg = config_from_dict(tiny_configs.get("baseline1"))
+    llm = LLM(config=cfg, random_weights=True, seed=4, dtype="bfloat16", num_blocks=4, max_model_len=128, max_num_seqs=2)
+    out = llm.generate([[1, 2, 3]], SamplingParams(max_tokens=4, ignore_eos=True))[0]
+    assert len(out.outputs[0].token_ids) == 4
+    with pytest.raises(KvExhausted):
+        llm.generate([[1] * 100], SamplingParams(max_tokens=400))       # 128 tokens would need 8 pages; there are 4
+    with pytest.raises(ConfigError):
+        LLM(config=cfg)                                                  # no folder and no random weights
+    with pytest.raises(ConfigError, match="tokenizer"):
+        llm.generate(["text needs a tokenizer"], SamplingParams())

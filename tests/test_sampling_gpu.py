@@ -1,0 +1,91 @@
+"""The sampling kernel against the plain sampler."""
+import pytest
+import torch
+
+import plain_impl as P
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from rvllm_b200.kernels import get_library
+    return get_library("cuda:0")
+
+
+def test_greedy_ties_and_nan(K):
+    logits = torch.randn(6, 1000)
+    logits[0, 17] = logits[0, 900] = 9.0                 # a tie: the lowest index wins
+    logits[1, 0] = 50.0
+    logits[2, 999] = 50.0
+    logits[3, 5] = float("nan")                           # NaN never wins
+    logits[3, 6] = 40.0
+    logits[4] = -3.0                                      # all equal: index 0
+    out = K.sample(logits.cuda()).tolist()
+    assert out[:5] == [17, 0, 999, 6, 0]
+    assert out[5] == P.argmax_lowest(logits[5])
+    big = torch.randn(3, 128256)
+    assert K.sample(big.cuda()).tolist() == [P.argmax_lowest(r) for r in big]
+
+
+@pytest.mark.parametrize("vocab", [383, 5000, 128256])
+@pytest.mark.parametrize("top_k,top_p", [(0, 1.0), (20, 1.0), (0, 0.8), (50, 0.9)])
+def test_draws_match_the_plain_sampler(K, vocab, top_k, top_p):
+    torch.manual_seed(vocab + top_k)
+    R = 24
+    logits = torch.randn(R, vocab) * (2.5 if vocab < 10000 else 8.0)    # peaked, so that steps of the CDF are wide
+    temps = torch.tensor([0.7 + 0.05 * (i % 5) for i in range(R)])
+    temps[3] = 0.0                                        # a greedy row among sampled ones
+    seeds = torch.arange(100, 100 + R, dtype=torch.int64)
+    draws = torch.arange(R, dtype=torch.int64) * 7
+    out = K.sample(logits.cuda(), temps.cuda(), torch.full((R,), top_k, dtype=torch.int32).cuda() if top_k else None,
+                   torch.full((R,), top_p).cuda() if top_p < 1 else None, seeds.cuda(), draws.cuda()).tolist()
+    checked = 0
+    for r in range(R):
+        tok, margin = P.sample(logits[r], float(temps[r]), int(seeds[r]), int(draws[r]), top_k, top_p)
+        if margin < 1e-4:
+            continue          # u sits on a step of the CDF: float rounding may pick the neighbour
+        if top_p < 1.0:
+            p = torch.softmax(logits[r].double() / float(temps[r]), 0) if temps[r] > 0 else None
+            if p is not None:
+                sp = torch.sort(p, descending=True).values
+                cs = torch.cumsum(sp, 0)
+                n = int((cs < top_p).sum()) + 1
+                if abs(float(cs[n - 1]) - top_p) < 3e-6 or (n > 1 and abs(float(cs[n - 2]) - top_p) < 3e-6):
+                    continue  # the top-p cut itself sits on a rounding edge
+        assert out[r] == tok, f"row {r}: kernel {out[r]}, plain {tok} (margin {margin:.2e})"
+        checked += 1
+    assert checked >= R // 2
+
+
+def test_distribution_and_batch_independence(K):
+    z = torch.tensor([0.5, 1.5, 0.0, 1.0, -1.0, 2.0])
+    n = 6000
+    logits = z.repeat(n, 1).cuda()
+    temps = torch.full((n,), 0.8).cuda()
+    seeds = torch.full((n,), 77, dtype=torch.int64).cuda()
+    draws = torch.arange(n, dtype=torch.int64).cuda()
+    out = K.sample(logits, temps, None, None, seeds, draws)
+    counts = torch.bincount(out.long().cpu(), minlength=6).double()
+    want = torch.softmax(z.double() / 0.8, 0) * n
+    assert float(((counts - want) ** 2 / want).sum()) < 20.5          # 5 degrees of freedom, p = 0.001
+    # the same (seed, output index) gives the same token whatever else is in the batch
+    sub = K.sample(logits[100:103].contiguous(), temps[:3].contiguous(), None, None, seeds[:3].contiguous(),
+                   draws[100:103].contiguous())
+    assert sub.tolist() == out[100:103].tolist()
+
+
+def test_sampler_object_and_parameter_checks(K):
+    from rvllm_b200 import Sampler, SamplingError, SamplingParams
+    s = Sampler(K)
+    logits = torch.randn(3, 500).cuda()
+    greedy = s.sample(logits, [SamplingParams()] * 3, [0, 0, 0], [0, 0, 0])
+    assert greedy.tolist() == [P.argmax_lowest(r) for r in logits.cpu()]
+    mixed = s.sample(logits, [SamplingParams(), SamplingParams(temperature=1.0, top_k=1), SamplingParams(temperature=0.5, top_p=0.01)],
+                     [1, 2, 3], [0, 0, 0])
+    assert mixed.tolist() == greedy.tolist()                          # top_k = 1 and a tiny top_p are greedy too
+    for bad in (dict(temperature=-1.0), dict(top_p=0.0), dict(top_p=1.5), dict(top_k=-2), dict(max_tokens=0)):
+        with pytest.raises(SamplingError):
+            SamplingParams(**bad)
+    with pytest.raises(SamplingError):
+        s.sample(logits, [SamplingParams()], [0], [0])
