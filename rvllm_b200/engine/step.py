@@ -23,7 +23,7 @@ import torch
 
 from ..cache import CacheManager
 from ..errors import KvExhausted, SchedulerError
-from ..kernels.library import AttentionMeta
+from ..kernels.library import COUNTERS, AttentionMeta
 
 
 @dataclass
@@ -263,11 +263,12 @@ class ModelRunner:
             logits = self.model.compute_logits(hidden, ctx)
             self._graphs[bucket] = self._capture(bucket)
             return logits
-        host, dev, graph, out = state
+        host, dev, graph, out, launches = state
         self._graph_event.synchronize()
         self.pack(entries, starts, pad_to=bucket, buffers=(host, dev))
         self._graph_event.record()
         graph.replay()
+        COUNTERS["launches"] += launches       # the kernels of this project inside the replayed graph
         return out[:len(entries)]
 
     def _capture(self, bucket: int):
@@ -278,15 +279,18 @@ class ModelRunner:
         ctx = self.pack([], [], pad_to=bucket, buffers=(host, dev))   # all rows padded: writes nothing
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
+        before = COUNTERS["launches"]
         with torch.cuda.graph(graph, pool=self._graph_pool):
             hidden = self.model.forward(ctx, self.cache)
             out = self.model.compute_logits(hidden, ctx)
+        launches = COUNTERS["launches"] - before
+        COUNTERS["launches"] = before          # captured, not run
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
         if self._graph_event is None:
             self._graph_event = torch.cuda.Event()
             self._graph_event.record()
-        return host, dev, graph, out
+        return host, dev, graph, out, launches
 
     def finish(self, req_id: Hashable) -> None:
         """Give back everything the request holds."""
