@@ -413,3 +413,73 @@ RV_EXPORT int rv_flash_attention(const void* q, const void* cache, const int* bl
     }
     return RV_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// rv_flash_attention_static: the same attention, for callers that may not allocate.
+// Declared and documented in attention_flash_static.h.  It has no counterpart in the reference.
+//
+// The split-key partials live in a file-scope device array instead of a caller's buffer.  In host
+// code the array's name is only a stand-in for the symbol, not an address a kernel can use, so
+// its device address is fetched once per device with cudaGetSymbolAddress (with that device
+// current) and kept; kernels get that address.
+#include "attention_flash_static.h"
+#include <stdarg.h>
+#include <stdio.h>
+
+static __device__ __align__(256) float g_static_scratch[RV_FLASH_STATIC_SCRATCH_FLOATS];
+
+#define RV_STATIC_MAX_DEVICES 64
+static float* g_static_scratch_addr[RV_STATIC_MAX_DEVICES];   // zero-initialised: not set up yet
+
+static void static_fail(char* err, int err_len, const char* fmt, ...) {
+    if (!err || err_len <= 0) return;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(err, (size_t)err_len, fmt, ap);
+    va_end(ap);
+}
+
+RV_EXPORT int rv_flash_attention_static(const void* q, const void* cache, const int* block_tables,
+                                        const int* cu_seqlens, const int* ctx_lens, void* out, int n_tokens,
+                                        int num_seqs, int nh, int nkv, int hd, int page_size, int max_blocks,
+                                        float scale, int window, int mode, int max_q_len, int num_splits,
+                                        cudaStream_t stream, char* err, int err_len) {
+    if (err && err_len > 0) err[0] = 0;
+    if (num_splits < 1 || n_tokens < 0 || nh <= 0) {
+        static_fail(err, err_len, "rv_flash_attention_static: bad sizes (num_splits %d, n_tokens %d, num_heads %d)", num_splits, n_tokens, nh);
+        return RV_ERR_BAD_SIZE;
+    }
+    const long long need = rv_flash_scratch_floats(n_tokens, nh, num_splits);
+    if (need > (long long)RV_FLASH_STATIC_SCRATCH_FLOATS) {
+        static_fail(err, err_len, "rv_flash_attention_static: this call needs %lld floats of scratch, the built-in "
+                    "array holds %lld; use fewer key splits or rv_flash_attention with a buffer of your own",
+                    need, (long long)RV_FLASH_STATIC_SCRATCH_FLOATS);
+        return RV_ERR_SCRATCH_TOO_LARGE;
+    }
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess || device < 0 || device >= RV_STATIC_MAX_DEVICES) {
+        static_fail(err, err_len, "rv_flash_attention_static: cannot use device %d (CUDA error %d)", device, (int)e);
+        return e != cudaSuccess ? (int)e : RV_ERR_UNSUPPORTED;
+    }
+    if (g_static_scratch_addr[device] == nullptr) {
+        // first call on this device: look the array's device address up (this may load the
+        // module, which is why the first call belongs before any stream capture)
+        float* addr = nullptr;
+        e = cudaGetSymbolAddress((void**)&addr, g_static_scratch);
+        if (e != cudaSuccess || addr == nullptr) {
+            static_fail(err, err_len, "rv_flash_attention_static: cudaGetSymbolAddress failed on device %d (CUDA error %d)",
+                        device, (int)e);
+            return e != cudaSuccess ? (int)e : RV_ERR_UNSUPPORTED;
+        }
+        g_static_scratch_addr[device] = addr;
+    }
+    // Nothing in the scratch has to be zero at entry: every element the merge kernel reads was
+    // written by the attention kernel of the same call (empty key ranges write m = -inf, l = 0).
+    const int st = rv_flash_attention(q, cache, block_tables, cu_seqlens, ctx_lens, out,
+                                      num_splits > 1 ? g_static_scratch_addr[device] : nullptr, n_tokens, num_seqs,
+                                      nh, nkv, hd, page_size, max_blocks, scale, window, mode, max_q_len, num_splits,
+                                      /*q_filter=*/0, stream);
+    if (st != RV_OK) static_fail(err, err_len, "rv_flash_attention_static: the attention launch was refused or failed (code %d)", st);
+    return st;
+}
