@@ -67,10 +67,67 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const void* __restrict__
     }
 }
 
+// bfloat16 rows whose width is a multiple of 8: every thread keeps its 16-byte pieces of the row
+// in registers, so the row is read from memory once.
+template <int VPT>
+__global__ void rmsnorm_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ gamma,
+                                        int gamma_dtype, __nv_bfloat16* __restrict__ out, int width, float eps) {
+    __shared__ float scratch[33];
+    const int nvec = width >> 3;
+    const uint4* row = reinterpret_cast<const uint4*>(x + (size_t)blockIdx.x * width);
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * width);
+    uint4 v[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        v[i] = c < nvec ? row[c] : make_uint4(0, 0, 0, 0);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            ss = fmaf(f.x, f.x, ss);
+            ss = fmaf(f.y, f.y, ss);
+        }
+    }
+    ss = rv_block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)width + eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c >= nvec) continue;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            const float g0 = rv_load_param(gamma, gamma_dtype, c * 8 + 2 * j);
+            const float g1 = rv_load_param(gamma, gamma_dtype, c * 8 + 2 * j + 1);
+            oh[j] = __floats2bfloat162_rn(f.x * r * g0, f.y * r * g1);
+        }
+        dst[c] = o;
+    }
+}
+
 RV_EXPORT int rv_rmsnorm(const void* x, const void* gamma, int gamma_dtype, void* out, int n_rows,
                          int width, float eps, int dtype, cudaStream_t stream) {
     if (n_rows < 0 || width <= 0) return RV_ERR_BAD_SIZE;
     if (n_rows == 0) return RV_OK;
+    if (dtype == RV_DTYPE_BF16 && width % 8 == 0 && width <= 8 * 4 * 1024 &&
+        (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
+        const int nvec = width / 8;
+        int threads = 32;
+        while (threads < 256 && threads < nvec) threads <<= 1;
+        while (threads < 1024 && threads * 4 < nvec) threads <<= 1;
+        const int vpt = (nvec + threads - 1) / threads;
+        const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
+        __nv_bfloat16* op = (__nv_bfloat16*)out;
+        if (vpt <= 1) rmsnorm_bf16_vec_kernel<1><<<n_rows, threads, 0, stream>>>(xp, gamma, gamma_dtype, op, width, eps);
+        else if (vpt <= 2) rmsnorm_bf16_vec_kernel<2><<<n_rows, threads, 0, stream>>>(xp, gamma, gamma_dtype, op, width, eps);
+        else rmsnorm_bf16_vec_kernel<4><<<n_rows, threads, 0, stream>>>(xp, gamma, gamma_dtype, op, width, eps);
+        return rv_launch_status();
+    }
     int threads = 32;
     while (threads < 1024 && threads * 4 < width) threads <<= 1;
     if (dtype == RV_DTYPE_F32)
@@ -141,6 +198,77 @@ __global__ void rope_cache_write_kernel(const T* __restrict__ qkv, const void* _
     }
 }
 
+// bfloat16 with head_dim a multiple of 16: one block per token walks all heads of the row with
+// 16-byte loads (8 rotation pairs at a time: 8 elements of the first half, 8 of the second).
+__global__ void rope_cache_write_bf16_vec_kernel(const __nv_bfloat16* __restrict__ qkv, const void* __restrict__ bias,
+                                                 int bias_dtype, const int* __restrict__ positions,
+                                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                 const int* __restrict__ slot_mapping, __nv_bfloat16* __restrict__ cache,
+                                                 __nv_bfloat16* __restrict__ q_out, int nh, int nkv, int hd, int page_size,
+                                                 int write_kv, int table_rows, int row_stride) {
+    const int t = blockIdx.x;
+    const int half = hd >> 1;
+    const int vec_half = half >> 3;                 // 16-byte pieces per half head
+    int pos = positions[t];
+    if (pos < 0) pos = 0;
+    if (pos >= table_rows) pos = table_rows - 1;
+    const int slot = write_kv ? slot_mapping[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot - page * page_size : 0;
+    const int n_rot_heads = write_kv ? nh + nkv : nh;
+    const __nv_bfloat16* row = qkv + (size_t)t * row_stride;
+    // rotated heads (q, then k)
+    for (int item = threadIdx.x; item < n_rot_heads * vec_half; item += blockDim.x) {
+        const int head = item / vec_half, c = item - head * vec_half;
+        __nv_bfloat16* dst;
+        if (head < nh) {
+            dst = q_out + (size_t)t * nh * hd + (size_t)head * hd;
+        } else {
+            if (slot < 0) continue;
+            dst = cache + ((((size_t)page * 2) * nkv + (head - nh)) * page_size + off) * hd;
+        }
+        const __nv_bfloat16* src = row + (size_t)head * hd;
+        const uint4 av = *reinterpret_cast<const uint4*>(src + c * 8);
+        const uint4 bv = *reinterpret_cast<const uint4*>(src + half + c * 8);
+        const __nv_bfloat16* ae = reinterpret_cast<const __nv_bfloat16*>(&av);
+        const __nv_bfloat16* be = reinterpret_cast<const __nv_bfloat16*>(&bv);
+        uint4 oa, ob;
+        __nv_bfloat16* oae = reinterpret_cast<__nv_bfloat16*>(&oa);
+        __nv_bfloat16* obe = reinterpret_cast<__nv_bfloat16*>(&ob);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = c * 8 + j;
+            float a = __bfloat162float(ae[j]), b = __bfloat162float(be[j]);
+            if (bias) {
+                a += rv_load_param(bias, bias_dtype, head * hd + i);
+                b += rv_load_param(bias, bias_dtype, head * hd + i + half);
+            }
+            float cs = 1.f, sn = 0.f;
+            if (cos_t) { cs = cos_t[(size_t)pos * half + i]; sn = sin_t[(size_t)pos * half + i]; }
+            oae[j] = __float2bfloat16_rn(a * cs - b * sn);
+            obe[j] = __float2bfloat16_rn(a * sn + b * cs);
+        }
+        *reinterpret_cast<uint4*>(dst + c * 8) = oa;
+        *reinterpret_cast<uint4*>(dst + half + c * 8) = ob;
+    }
+    // value heads: bias only
+    if (write_kv && slot >= 0) {
+        const int vec_head = hd >> 3;
+        for (int item = threadIdx.x; item < nkv * vec_head; item += blockDim.x) {
+            const int head = item / vec_head, c = item - head * vec_head;
+            const int col0 = (nh + nkv + head) * hd;
+            uint4 v = *reinterpret_cast<const uint4*>(row + col0 + c * 8);
+            if (bias) {
+                __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    e[j] = __float2bfloat16_rn(__bfloat162float(e[j]) + rv_load_param(bias, bias_dtype, col0 + c * 8 + j));
+            }
+            __nv_bfloat16* dst = cache + ((((size_t)page * 2 + 1) * nkv + head) * page_size + off) * hd;
+            *reinterpret_cast<uint4*>(dst + c * 8) = v;
+        }
+    }
+}
+
 RV_EXPORT int rv_rope_cache_write(const void* qkv, const void* bias, int bias_dtype, const int* positions,
                                   const float* cos_t, const float* sin_t, const int* slot_mapping,
                                   void* cache, void* q_out, int n_tokens, int nh, int nkv, int hd,
@@ -151,6 +279,16 @@ RV_EXPORT int rv_rope_cache_write(const void* qkv, const void* bias, int bias_dt
     if ((cos_t == nullptr) != (sin_t == nullptr)) return RV_ERR_BAD_SIZE;
     if (row_stride < (write_kv ? nh + 2 * nkv : nh) * hd) return RV_ERR_BAD_SIZE;
     if (n_tokens == 0) return RV_OK;
+    if (dtype == RV_DTYPE_BF16 && hd % 16 == 0 && row_stride % 8 == 0 &&
+        (reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(cache)) % 16 == 0) {
+        const int items = (write_kv ? nh + nkv : nh) * (hd / 16);
+        int threads = 32;
+        while (threads < 256 && threads < items) threads <<= 1;
+        rope_cache_write_bf16_vec_kernel<<<n_tokens, threads, 0, stream>>>(
+            (const __nv_bfloat16*)qkv, bias, bias_dtype, positions, cos_t, sin_t, slot_mapping, (__nv_bfloat16*)cache,
+            (__nv_bfloat16*)q_out, nh, nkv, hd, page_size, write_kv, table_rows, row_stride);
+        return rv_launch_status();
+    }
     const dim3 grid(n_tokens, write_kv ? nh + 2 * nkv : nh);
     const int threads = hd / 2 >= 128 ? 128 : (hd / 2 >= 64 ? 64 : 32);
     if (dtype == RV_DTYPE_F32)
@@ -179,11 +317,44 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     }
 }
 
+// bfloat16 with inter a multiple of 8: 16-byte loads of gate and up, one 16-byte store.
+__global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
+                                         int inter, size_t total_vec) {
+    const int vec_per_row = inter >> 3;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_vec; idx += stride) {
+        const size_t row = idx / vec_per_row;
+        const int c = (int)(idx - row * vec_per_row);
+        const uint4 g = *reinterpret_cast<const uint4*>(gate_up + row * 2 * inter + c * 8);
+        const uint4 u = *reinterpret_cast<const uint4*>(gate_up + row * 2 * inter + inter + c * 8);
+        const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
+        const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&u);
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 gf = __bfloat1622float2(gh[j]);
+            const float2 uf = __bfloat1622float2(uh[j]);
+            oh[j] = __floats2bfloat162_rn(gf.x / (1.0f + expf(-gf.x)) * uf.x, gf.y / (1.0f + expf(-gf.y)) * uf.y);
+        }
+        *reinterpret_cast<uint4*>(out + row * inter + c * 8) = o;
+    }
+}
+
 RV_EXPORT int rv_silu_mul(const void* gate_up, void* out, int n_rows, int inter, int dtype, cudaStream_t stream) {
     if (n_rows < 0 || inter <= 0) return RV_ERR_BAD_SIZE;
     if (n_rows == 0) return RV_OK;
     const size_t total = (size_t)n_rows * inter;
     const int threads = 256;
+    if (dtype == RV_DTYPE_BF16 && inter % 8 == 0 &&
+        (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
+        const size_t total_vec = total / 8;
+        size_t vb = (total_vec + threads - 1) / threads;
+        if (vb > 148 * 32) vb = 148 * 32;
+        silu_mul_bf16_vec_kernel<<<(int)vb, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
+                                                                 inter, total_vec);
+        return rv_launch_status();
+    }
     size_t blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == RV_DTYPE_F32)

@@ -40,9 +40,40 @@ __device__ __forceinline__ void argmax_combine(float& v, int& i, float ov, int o
 __device__ int block_argmax(const float* row, int V, float* s_val, int* s_idx) {
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best || (v == best && i < idx)) { best = v; idx = i; }   // NaN compares false
+    if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        // 16-byte loads, two independent chains; indices rise within a chain, so a strict
+        // comparison keeps the lowest index of equal values
+        float b1 = -INFINITY;
+        int i1 = 0x7fffffff;
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        const int n4 = V >> 2;
+        int i = threadIdx.x;
+        for (; i + (int)blockDim.x < n4; i += 2 * blockDim.x) {
+            const float4 a = r4[i], b = r4[i + blockDim.x];
+            const int ia = i * 4, ib = (i + blockDim.x) * 4;
+            if (a.x > best) { best = a.x; idx = ia; }
+            if (a.y > best) { best = a.y; idx = ia + 1; }
+            if (a.z > best) { best = a.z; idx = ia + 2; }
+            if (a.w > best) { best = a.w; idx = ia + 3; }
+            if (b.x > b1) { b1 = b.x; i1 = ib; }
+            if (b.y > b1) { b1 = b.y; i1 = ib + 1; }
+            if (b.z > b1) { b1 = b.z; i1 = ib + 2; }
+            if (b.w > b1) { b1 = b.w; i1 = ib + 3; }
+        }
+        if (i < n4) {
+            const float4 a = r4[i];
+            const int ia = i * 4;
+            if (a.x > best || (a.x == best && ia < idx)) { best = a.x; idx = ia; }
+            if (a.y > best || (a.y == best && ia + 1 < idx)) { best = a.y; idx = ia + 1; }
+            if (a.z > best || (a.z == best && ia + 2 < idx)) { best = a.z; idx = ia + 2; }
+            if (a.w > best || (a.w == best && ia + 3 < idx)) { best = a.w; idx = ia + 3; }
+        }
+        argmax_combine(best, idx, b1, i1);
+    } else {
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float v = row[i];
+            if (v > best || (v == best && i < idx)) { best = v; idx = i; }   // NaN compares false
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -94,7 +125,18 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 
     // mass of everything
     float part = 0.f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) part += expf((row[i] - m) * inv_t);
+    if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        float p1 = 0.f;
+        for (int i = threadIdx.x; i < (V >> 2); i += blockDim.x) {
+            const float4 a = r4[i];
+            part += expf((a.x - m) * inv_t) + expf((a.y - m) * inv_t);
+            p1 += expf((a.z - m) * inv_t) + expf((a.w - m) * inv_t);
+        }
+        part += p1;
+    } else {
+        for (int i = threadIdx.x; i < V; i += blockDim.x) part += expf((row[i] - m) * inv_t);
+    }
     const float total = rv_block_sum(part, s_val);
 
     // threshold key: keep tokens whose order key is >= tau

@@ -104,6 +104,15 @@ def compile_library(source: str, defines: Sequence[str] = (), verbose: bool = Tr
             pass
         raise KernelError(f"nvcc failed for {source} (exit {proc.returncode}):\n{' '.join(cmd)}\n{log}")
     os.replace(tmp, out)
+    # older builds of the same source and defines are of no use any more
+    stem = os.path.basename(out).rsplit("_", 1)[0] + "_"
+    for name in os.listdir(os.path.dirname(out)):
+        if name.startswith(stem) and name.endswith(".so") and len(name) == len(os.path.basename(out)) \
+                and name != os.path.basename(out):
+            try:
+                os.unlink(os.path.join(os.path.dirname(out), name))
+            except OSError:
+                pass
     if verbose:
         print(f"[rvllm_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return out
