@@ -1,0 +1,406 @@
+// bfloat16 linear layer on the fifth-generation tensor cores of sm_100a:
+//     out[M, N] = x[M, K] . W[N, K]^T  (+ residual[M, N]),  float accumulate, bf16 or float out,
+// or, GATED, with W rows [gate (N/2) | up (N/2)]:  out[M, N/2] = silu(x Wg^T) * (x Wu^T).
+//
+// Structure (one CTA per SM, persistent over output tiles of 128 x 256):
+//   warp 0   TMA producer: cp.async.bulk.tensor loads of a 128 x 64 tile of x and a 256 x 64 tile
+//            of W per stage (128-byte swizzle), 4 stages, completion on mbarriers;
+//   warp 1   MMA issuer: one elected thread issues tcgen05.mma (M = 128, N = 256, K = 16, both
+//            operands K-major from shared memory, accumulator in tensor memory); tcgen05.commit
+//            frees a stage for the producer and, after the last k block, hands the accumulator to
+//            the epilogue.  Two accumulators (2 x 256 TMEM columns) let tile i+1 start while
+//            tile i is written out;
+//   warps 2-5  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, add the residual / apply
+//            SiLU-gate in float, round once, store.
+// No cluster, no multicast.  Every wait on an mbarrier is bounded: when a wait gives up, the CTA
+// sets an abort flag, every role leaves its loop, the producer waits (bounded) for its loads in
+// flight, tensor memory is freed, the kernel writes a status word and returns.
+//
+// Shapes: the five products of a layer at prefill time
+// (v3/crates/rvllm-runtime/src/layer_exec.rs:240-266,433-444,478-488,511-522 of the reference,
+// which calls cuBLASLt; its residual epilogue beta = 1 is cublaslt.rs:335-368, and its fused
+// gate-up-SiLU idea is kernels/cutlass_gateup_silu.cu).
+#include "common.cuh"
+#include <cuda.h>
+
+#define BM 128
+#define BN 256
+#define BK 64
+#define STAGES 4
+#define UMMA_K 16
+#define A_TILE_BYTES (BM * BK * 2)
+#define B_TILE_BYTES (BN * BK * 2)
+#define STAGE_BYTES (A_TILE_BYTES + B_TILE_BYTES)
+#define NUM_THREADS 192
+#define TMEM_COLS 512
+#define SPIN_LIMIT (1u << 24)
+
+#define EPI_PLAIN 0
+#define EPI_RESIDUAL 1
+#define EPI_GATED 2
+
+struct GemmParams {
+    void* out;
+    const __nv_bfloat16* residual;
+    int* status;            // device word: 0 ok, else the code of the wait that gave up
+    int M, N, K;
+    int out_f32;
+    int epilogue;
+    int m_tiles, n_tiles;
+};
+
+// ---------------------------------------------------------------- small PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up or another role already did.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = code;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (stride offset), leading offset unused (1), version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address, bits [0, 14)
+    d |= (uint64_t)1 << 16;                               // leading byte offset (16-byte units), bits [16, 30)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset, bits [32, 46)
+    d |= (uint64_t)1 << 46;                               // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                               // layout type: 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor: float accumulator, bf16 x bf16, both K-major, N = 256, M = 128.
+__device__ __forceinline__ uint32_t umma_idesc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // the tiles need 1024-byte alignment for the 128-byte swizzle
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int num_tiles = p.m_tiles * p.n_tiles;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const bool gated = p.epilogue == EPI_GATED;
+    const int half_n = p.N >> 1;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int issued = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % p.m_tiles) * BM;
+                const int nt = tile / p.m_tiles;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, &abort_flag, 1)) { ok = false; break; }
+                    const uint32_t a_dst = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
+                    const uint32_t b_dst = a_dst + A_TILE_BYTES;
+                    const uint32_t bar = full0 + 8 * stage;
+                    mbar_expect_tx(bar, STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, kb * BK, m0, bar);
+                    if (gated) {       // 128 gate rows, then the 128 up rows of the same columns
+                        tma_load_2d(b_dst, &map_b, kb * BK, nt * (BN / 2), bar);
+                        tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, kb * BK, half_n + nt * (BN / 2), bar);
+                    } else {
+                        tma_load_2d(b_dst, &map_b, kb * BK, nt * BN, bar);
+                        tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, kb * BK, nt * BN + BN / 2, bar);
+                    }
+                    ++issued;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // gave up: let the loads in flight land before the CTA's shared memory goes away
+                const int pending = issued < STAGES ? issued : STAGES;
+                for (int i = 0; i < pending; ++i) {
+                    int s = stage - 1 - i;
+                    uint32_t ph = phase;
+                    while (s < 0) { s += STAGES; ph ^= 1; }
+                    for (uint32_t it = 0; it < (1u << 20); ++it)
+                        if (mbar_try(full0 + 8 * s, ph)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc();
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                const uint32_t use = (uint32_t)(local >> 1);
+                if (!mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, &abort_flag, 2)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t tmem_c = tmem_base + (uint32_t)buf * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full0 + 8 * stage, phase, &abort_flag, 3)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
+                    const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_TILE_BYTES);
+#pragma unroll
+                    for (int j = 0; j < BK / UMMA_K; ++j) {
+                        // 16 k = 32 bytes further along the 128-byte row: +2 in 16-byte units
+                        tcgen05_mma_bf16(tmem_c, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (kb | j) != 0);
+                    }
+                    tcgen05_commit(empty0 + 8 * stage);     // the stage is free once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tcgen05_commit(tfull0 + 8 * buf);   // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;                       // the TMEM lanes this warp may read
+        int local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const uint32_t use = (uint32_t)(local >> 1);
+            if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_flag, 4)) { ok = false; break; }
+            tcgen05_fence_after();
+            const int m = (tile % p.m_tiles) * BM + quarter * 32 + lane;
+            const int nt = tile / p.m_tiles;
+            const uint32_t taddr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(quarter * 32) << 16);
+            if (gated) {
+                const int n_out0 = nt * (BN / 2);
+                for (int c = 0; c < BN / 2; c += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_ld_32x32(taddr + c, g);
+                    tmem_ld_32x32(taddr + BN / 2 + c, u);
+                    tmem_ld_wait();
+                    if (m < p.M) {
+                        const int n = n_out0 + c;
+                        if (!p.out_f32 && n + 32 <= half_n && (half_n & 7) == 0) {
+                            __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * half_n + n;
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                uint4 o;
+                                __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const int e = v * 8 + 2 * j;
+                                    oh[j] = __floats2bfloat162_rn(silu_f(__uint_as_float(g[e])) * __uint_as_float(u[e]),
+                                                                  silu_f(__uint_as_float(g[e + 1])) * __uint_as_float(u[e + 1]));
+                                }
+                                *reinterpret_cast<uint4*>(dst + v * 8) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                if (n + e >= half_n) continue;
+                                const float val = silu_f(__uint_as_float(g[e])) * __uint_as_float(u[e]);
+                                if (p.out_f32) ((float*)p.out)[(size_t)m * half_n + n + e] = val;
+                                else ((__nv_bfloat16*)p.out)[(size_t)m * half_n + n + e] = __float2bfloat16_rn(val);
+                            }
+                        }
+                    }
+                }
+            } else {
+                const int n0 = nt * BN;
+                for (int c = 0; c < BN; c += 32) {
+                    if (n0 + c >= p.N) break;              // uniform over the warp
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + c, r);
+                    tmem_ld_wait();
+                    if (m < p.M) {
+                        const int n = n0 + c;
+                        const bool vec = n + 32 <= p.N && (p.N & 7) == 0;
+                        if (vec && !p.out_f32) {
+                            __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * p.N + n;
+                            const __nv_bfloat16* res = p.residual ? p.residual + (size_t)m * p.N + n : nullptr;
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                uint4 rv = make_uint4(0, 0, 0, 0);
+                                if (res) rv = *reinterpret_cast<const uint4*>(res + v * 8);
+                                const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv);
+                                uint4 o;
+                                __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const int e = v * 8 + 2 * j;
+                                    const float2 rf = __bfloat1622float2(rh[j]);
+                                    oh[j] = __floats2bfloat162_rn(__uint_as_float(r[e]) + rf.x, __uint_as_float(r[e + 1]) + rf.y);
+                                }
+                                *reinterpret_cast<uint4*>(dst + v * 8) = o;
+                            }
+                        } else if (vec && p.out_f32 && !p.residual && (p.N & 3) == 0) {
+                            float4* dst = reinterpret_cast<float4*>((float*)p.out + (size_t)m * p.N + n);
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                dst[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                     __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                if (n + e >= p.N) continue;
+                                float val = __uint_as_float(r[e]);
+                                if (p.residual) val += __bfloat162float(p.residual[(size_t)m * p.N + n + e]);
+                                if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n + e] = val;
+                                else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n + e] = __float2bfloat16_rn(val);
+                            }
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+    }
+    if (threadIdx.x == 0 && abort_flag != 0 && p.status) atomicCAS(p.status, 0, abort_flag);
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+// A [rows, cols] row-major bf16 matrix, loaded in boxes of box_rows x 64 columns with 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return RV_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? RV_OK : RV_ERR_BAD_SIZE;
+}
+
+// epilogue: 0 plain, 1 + residual (bf16 [M, N]), 2 gated (W rows [gate | up], out has N/2 columns).
+// status: optional device int that receives a non-zero code if a wait inside the kernel gave up.
+RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* residual, void* out, int out_f32,
+                                   int M, int N, int K, int epilogue, int* status, int max_ctas,
+                                   cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0) return RV_ERR_BAD_SIZE;
+    if (K % 8) return RV_ERR_UNSUPPORTED;                          // rows must start on 16-byte boundaries
+    if (epilogue == EPI_GATED && (N & 1)) return RV_ERR_BAD_SIZE;
+    if (epilogue == EPI_RESIDUAL && (!residual || out_f32)) return RV_ERR_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out) |
+         reinterpret_cast<uintptr_t>(residual)) % 16)
+        return RV_ERR_ALIGNMENT;
+    if (M == 0) return RV_OK;
+    alignas(64) CUtensorMap map_a, map_b;
+    int st = make_map(&map_a, x, M, K, BM);
+    if (st != RV_OK) return st;
+    st = make_map(&map_b, w, N, K, BN / 2);
+    if (st != RV_OK) return st;
+    GemmParams p;
+    p.out = out; p.residual = epilogue == EPI_RESIDUAL ? (const __nv_bfloat16*)residual : nullptr;
+    p.status = status; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.epilogue = epilogue;
+    p.m_tiles = (M + BM - 1) / BM;
+    // gated: a tile is 128 gate rows and the 128 up rows of the same output columns; gate rows past
+    // N/2 read up rows, whose products the epilogue never stores
+    p.n_tiles = epilogue == EPI_GATED ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
+    const int smem = STAGES * STAGE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    int ctas = p.m_tiles * p.n_tiles;
+    const int limit = max_ctas > 0 ? max_ctas : 148;
+    if (ctas > limit) ctas = limit;
+    gemm_tcgen05_kernel<<<ctas, NUM_THREADS, smem, stream>>>(map_a, map_b, p);
+    return rv_launch_status();
+}

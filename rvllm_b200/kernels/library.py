@@ -1,10 +1,10 @@
 """The kernels of the product path, as methods that take torch tensors.
 
 `CudaKernels` launches the hand-written sm_100a kernels of csrc/ on torch's current stream
-through their exported C launchers.  Matrix products of bfloat16 activations with at least
-`SKINNY_MAX_ROWS` rows go to the library GEMM behind `torch` (the reference calls cuBLASLt for
-its linear layers, v3/crates/rvllm-cutlass/src/cublaslt.rs); everything else is this
-project's own code.  There is no CPU implementation: without a CUDA device, or when a kernel
+through their exported C launchers.  bfloat16 matrix products with at least `TCGEN05_MIN_ROWS` rows
+run on this project's tcgen05 / TMEM / TMA kernel; with fewer rows (decode) they go to the library
+GEMM behind `torch` (the reference calls cuBLASLt for its linear layers,
+v3/crates/rvllm-cutlass/src/cublaslt.rs); everything else is this project's own code.  There is no CPU implementation: without a CUDA device, or when a kernel
 library cannot be built, construction raises `KernelError`.
 """
 from __future__ import annotations
@@ -66,6 +66,7 @@ class AttentionMeta:
 
 class CudaKernels:
     SKINNY_MAX_ROWS = 0     # rows up to which the weight-streaming GEMM replaces the library GEMM (0: off)
+    TCGEN05_MIN_ROWS = 128  # rows from which the tcgen05 GEMM of this project is used for bfloat16
 
     def __init__(self, device="cuda:0"):
         if not torch.cuda.is_available():
@@ -261,6 +262,9 @@ class CudaKernels:
         if 0 < M <= self.SKINNY_MAX_ROWS and K % 8 == 0 and out_dtype in (torch.bfloat16, torch.float32) \
                 and (residual is None or (residual.dtype == torch.bfloat16 and out_dtype == torch.bfloat16)):
             return self.linear_skinny(x, weight, bias, residual, out_dtype)
+        if M >= self.TCGEN05_MIN_ROWS and K % 8 == 0 and bias is None and out_dtype in (torch.bfloat16, torch.float32) \
+                and (residual is None or (residual.dtype == torch.bfloat16 and out_dtype == torch.bfloat16)):
+            return self.linear_tcgen05(x, weight, residual, out_dtype)
         if out_dtype == torch.float32:
             out = torch.mm(x, weight.t(), out_dtype=torch.float32)
             if bias is not None:
@@ -294,6 +298,24 @@ class CudaKernels:
         _check("gemm_skinny", st)
         return out
 
+    def linear_tcgen05(self, x, weight, residual=None, out_dtype=None, gated=False, status=None, max_ctas=0):
+        """The tcgen05 / TMEM / TMA GEMM for bfloat16 (any M; K a multiple of 8).  gated: weight rows
+        are [gate | up] and the result is silu(x gate^T) * (x up^T).  `status`: optional int32 device
+        tensor that receives a non-zero code if a bounded wait inside the kernel gave up."""
+        _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
+        M, K = x.shape
+        N = weight.shape[0]
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+        if residual is not None:
+            _need(residual, "residual", torch.bfloat16, 2)
+        epilogue = 2 if gated else (1 if residual is not None else 0)
+        st = self._lib("gemm_tcgen05.cu").rv_gemm_tcgen05_bf16(
+            _ptr(x), _ptr(weight), _ptr(residual), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0),
+            c_int(M), c_int(N), c_int(K), c_int(epilogue), _ptr(status), c_int(max_ctas), self._stream())
+        _check("gemm_tcgen05", st)
+        return out
+
     def gate_up_silu(self, x, weight) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) for weight rows [Wg | Wu]: one fused kernel for few bfloat16
         rows, else the product followed by the SiLU kernel."""
@@ -301,6 +323,9 @@ class CudaKernels:
         if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < M <= self.SKINNY_MAX_ROWS \
                 and K % 8 == 0 and weight.shape[0] % 2 == 0:
             return self.linear_skinny(x, weight, gated=True)
+        if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and M >= self.TCGEN05_MIN_ROWS \
+                and K % 8 == 0 and weight.shape[0] % 2 == 0:
+            return self.linear_tcgen05(x, weight, gated=True)
         return self.silu_mul(self.linear(x, weight))
 
     # ------------------------------------------------------------------ sampling

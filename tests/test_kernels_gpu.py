@@ -258,3 +258,27 @@ def test_linear_bf16_library_path(K, M, N, Kd, res, f32out):
     assert rel_err(out, ref) < (1e-5 if f32out else BF16_TOL)
     # a matrix the checkpoint keeps in 32 bits is multiplied in float32
     assert rel_err(K.linear(x, w.float(), None, r), ref) < BF16_TOL
+
+
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (100, 200, 72), (257, 520, 4096), (640, 96, 1032), (2048, 1000, 328)])
+def test_gemm_tcgen05_bf16(K, M, N, Kd):
+    """The tcgen05 kernel: tails in M, N and K, several tiles per CTA, every epilogue."""
+    torch.manual_seed(9)
+    x = torch.randn(M, Kd, device="cuda").bfloat16()
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    r = torch.randn(M, N, device="cuda").bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ref = x.double().cpu() @ w.double().cpu().t()
+    for ctas in (0, 1, 3):                                   # 1 and 3: a CTA walks many tiles, both accumulators
+        assert rel_err(K.linear_tcgen05(x, w, status=status, max_ctas=ctas), ref) < BF16_TOL
+    assert rel_err(K.linear_tcgen05(x, w, r, status=status), ref + r.double().cpu()) < BF16_TOL
+    assert rel_err(K.linear_tcgen05(x, w, None, torch.float32, status=status), ref) < 1e-5
+    if N % 2 == 0:
+        g, u = ref[:, :N // 2], ref[:, N // 2:]
+        want = g / (1 + torch.exp(-g)) * u
+        assert rel_err(K.linear_tcgen05(x, w, gated=True, status=status), want) < BF16_TOL
+        assert rel_err(K.linear_tcgen05(x, w, None, torch.float32, gated=True, status=status, max_ctas=2), want) < 1e-5
+    assert int(status.item()) == 0, "a bounded wait inside the kernel gave up"
+    # the product path picks it from TCGEN05_MIN_ROWS rows on
+    if M >= K.TCGEN05_MIN_ROWS:
+        assert torch.equal(K.linear(x, w, None, r), K.linear_tcgen05(x, w, r))
