@@ -77,6 +77,8 @@ struct FlashParams {
 template <int WARPS_M, int WARPS_N>
 __global__ void __launch_bounds__(WARPS_M * WARPS_N * 32)
 flash_paged_kernel(const FlashParams p) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     constexpr int HD = HEAD_DIM;
     constexpr int M_TILE = 16 * WARPS_M;
     constexpr int KW = KV_TILE / WARPS_N;          // keys of a tile that one warp owns
@@ -330,6 +332,8 @@ flash_paged_kernel(const FlashParams p) {
 // Merge the partial results of the key splits: one block per (token, head).
 __global__ void flash_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                      __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     const int row = blockIdx.x;
     float m_all = -INFINITY;
     for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, part_ml[((size_t)s * rows + row) * 2]);
@@ -362,7 +366,7 @@ static int launch_flash(const FlashParams& p, int num_seqs, cudaStream_t stream)
         configured = true;
     }
     const dim3 grid(p.row_tiles * p.num_splits, p.nkv, num_seqs);
-    flash_paged_kernel<WARPS_M, WARPS_N><<<grid, WARPS_M * WARPS_N * 32, smem, stream>>>(p);
+    RV_LAUNCH_ST = rv_launch(flash_paged_kernel<WARPS_M, WARPS_N>, dim3(grid), dim3(WARPS_M * WARPS_N * 32), smem, stream, p);
     return rv_launch_status();
 }
 
@@ -407,8 +411,8 @@ RV_EXPORT int rv_flash_attention(const void* q, const void* cache, const int* bl
     int st = mode == 1 ? launch_flash<1, 4>(p, num_seqs, stream) : launch_flash<4, 1>(p, num_seqs, stream);
     if (st != RV_OK) return st;
     if (num_splits > 1) {
-        flash_combine_kernel<<<n_tokens * nh, HEAD_DIM >= 128 ? 128 : 64, 0, stream>>>(p.part_o, p.part_ml, p.out,
-                                                                                    n_tokens * nh, num_splits);
+        RV_LAUNCH_ST = rv_launch(flash_combine_kernel, dim3(n_tokens * nh), dim3(HEAD_DIM >= 128 ? 128 : 64), 0, stream,
+                                 p.part_o, p.part_ml, p.out, n_tokens * nh, num_splits);
         return rv_launch_status();
     }
     return RV_OK;

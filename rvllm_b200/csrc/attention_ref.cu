@@ -19,6 +19,8 @@ __global__ void paged_attention_ref_kernel(const T* __restrict__ q, const T* __r
                                            const int* __restrict__ ctx_lens, const int* __restrict__ token_seq,
                                            T* __restrict__ out, int n_tokens, int nh, int nkv, int hd,
                                            int page_size, int max_blocks, float scale, int window) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int t = blockIdx.x;
@@ -89,11 +91,11 @@ RV_EXPORT int rv_paged_attention_ref(const void* q, const void* cache, const int
     const int warps = 4;
     const dim3 grid(n_tokens, (nh + warps - 1) / warps);
     if (dtype == RV_DTYPE_F32)
-        paged_attention_ref_kernel<float><<<grid, warps * 32, 0, stream>>>(
+        RV_LAUNCH_ST = rv_launch(paged_attention_ref_kernel<float>, dim3(grid), dim3(warps * 32), 0, stream, 
             (const float*)q, (const float*)cache, block_tables, cu_seqlens, ctx_lens, token_seq, (float*)out,
             n_tokens, nh, nkv, hd, page_size, max_blocks, scale, window);
     else if (dtype == RV_DTYPE_BF16)
-        paged_attention_ref_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
+        RV_LAUNCH_ST = rv_launch(paged_attention_ref_kernel<__nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_tables, cu_seqlens, ctx_lens, token_seq,
             (__nv_bfloat16*)out, n_tokens, nh, nkv, hd, page_size, max_blocks, scale, window);
     else

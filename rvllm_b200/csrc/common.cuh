@@ -19,7 +19,41 @@
 
 #define RV_EXPORT extern "C" __attribute__((visibility("default")))
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// Kernels of a step run back to back on one stream.  Launched with the programmatic-serialization
+// attribute, a kernel may be scheduled while its predecessor is still running: what it does before
+// rv_pdl_wait() (set-up, fetching weights, which no kernel of the step writes) overlaps the
+// predecessor's tail; everything after rv_pdl_wait() sees the predecessor complete.  Without the
+// attribute both calls do nothing.  The switch is per library (rv_set_pdl).
+static int g_rv_pdl = 0;
+RV_EXPORT void rv_set_pdl(int on) { g_rv_pdl = on; }
+
+__device__ __forceinline__ void rv_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void rv_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline int rv_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_rv_pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+    return RV_OK;
+}
+
+// the status of the most recent rv_launch of this thread (launchers write RV_LAUNCH_ST = rv_launch(...))
+static thread_local int rv_launch_st = 0;
+#define RV_LAUNCH_ST rv_launch_st
+
 static inline int rv_launch_status() {
+    const int s = rv_launch_st;
+    rv_launch_st = 0;
+    if (s != RV_OK) return s;
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? RV_OK : (int)e;
 }

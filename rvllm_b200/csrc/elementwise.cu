@@ -14,6 +14,8 @@
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                    T* __restrict__ out, int width, int rows_in_table) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < rows_in_table;
@@ -37,9 +39,9 @@ RV_EXPORT int rv_gather_rows(const void* table, const int* ids, void* out, int n
     if (n_rows == 0) return RV_OK;
     const int threads = width >= 2048 ? 256 : 128;
     if (dtype == RV_DTYPE_F32)
-        gather_rows_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)table, ids, (float*)out, width, rows_in_table);
+        RV_LAUNCH_ST = rv_launch(gather_rows_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (const float*)table, ids, (float*)out, width, rows_in_table);
     else if (dtype == RV_DTYPE_BF16)
-        gather_rows_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out, width, rows_in_table);
+        RV_LAUNCH_ST = rv_launch(gather_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out, width, rows_in_table);
     else
         return RV_ERR_BAD_DTYPE;
     return rv_launch_status();
@@ -51,6 +53,8 @@ RV_EXPORT int rv_gather_rows(const void* table, const int* ids, void* out, int n
 template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const void* __restrict__ gamma, int gamma_dtype,
                                T* __restrict__ out, int width, float eps) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     __shared__ float scratch[33];
     const T* row = x + (size_t)blockIdx.x * width;
     T* dst = out + (size_t)blockIdx.x * width;
@@ -72,6 +76,8 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const void* __restrict__
 template <int VPT>
 __global__ void rmsnorm_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ gamma,
                                         int gamma_dtype, __nv_bfloat16* __restrict__ out, int width, float eps) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     __shared__ float scratch[33];
     const int nvec = width >> 3;
     const uint4* row = reinterpret_cast<const uint4*>(x + (size_t)blockIdx.x * width);
@@ -123,17 +129,17 @@ RV_EXPORT int rv_rmsnorm(const void* x, const void* gamma, int gamma_dtype, void
         const int vpt = (nvec + threads - 1) / threads;
         const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
         __nv_bfloat16* op = (__nv_bfloat16*)out;
-        if (vpt <= 1) rmsnorm_bf16_vec_kernel<1><<<n_rows, threads, 0, stream>>>(xp, gamma, gamma_dtype, op, width, eps);
-        else if (vpt <= 2) rmsnorm_bf16_vec_kernel<2><<<n_rows, threads, 0, stream>>>(xp, gamma, gamma_dtype, op, width, eps);
-        else rmsnorm_bf16_vec_kernel<4><<<n_rows, threads, 0, stream>>>(xp, gamma, gamma_dtype, op, width, eps);
+        if (vpt <= 1) RV_LAUNCH_ST = rv_launch(rmsnorm_bf16_vec_kernel<1>, dim3(n_rows), dim3(threads), 0, stream, xp, gamma, gamma_dtype, op, width, eps);
+        else if (vpt <= 2) RV_LAUNCH_ST = rv_launch(rmsnorm_bf16_vec_kernel<2>, dim3(n_rows), dim3(threads), 0, stream, xp, gamma, gamma_dtype, op, width, eps);
+        else RV_LAUNCH_ST = rv_launch(rmsnorm_bf16_vec_kernel<4>, dim3(n_rows), dim3(threads), 0, stream, xp, gamma, gamma_dtype, op, width, eps);
         return rv_launch_status();
     }
     int threads = 32;
     while (threads < 1024 && threads * 4 < width) threads <<= 1;
     if (dtype == RV_DTYPE_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)x, gamma, gamma_dtype, (float*)out, width, eps);
+        RV_LAUNCH_ST = rv_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (const float*)x, gamma, gamma_dtype, (float*)out, width, eps);
     else if (dtype == RV_DTYPE_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>((const __nv_bfloat16*)x, gamma, gamma_dtype, (__nv_bfloat16*)out, width, eps);
+        RV_LAUNCH_ST = rv_launch(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, (const __nv_bfloat16*)x, gamma, gamma_dtype, (__nv_bfloat16*)out, width, eps);
     else
         return RV_ERR_BAD_DTYPE;
     return rv_launch_status();
@@ -152,6 +158,8 @@ __global__ void rope_cache_write_kernel(const T* __restrict__ qkv, const void* _
                                         const float* __restrict__ sin_t, const int* __restrict__ slot_mapping,
                                         T* __restrict__ cache, T* __restrict__ q_out, int nh, int nkv, int hd,
                                         int page_size, int write_kv, int table_rows, int row_stride) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     const int t = blockIdx.x;
     const int head = blockIdx.y;
     const int half = hd >> 1;
@@ -206,6 +214,8 @@ __global__ void rope_cache_write_bf16_vec_kernel(const __nv_bfloat16* __restrict
                                                  const int* __restrict__ slot_mapping, __nv_bfloat16* __restrict__ cache,
                                                  __nv_bfloat16* __restrict__ q_out, int nh, int nkv, int hd, int page_size,
                                                  int write_kv, int table_rows, int row_stride) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     const int t = blockIdx.x;
     const int half = hd >> 1;
     const int vec_half = half >> 3;                 // 16-byte pieces per half head
@@ -284,7 +294,7 @@ RV_EXPORT int rv_rope_cache_write(const void* qkv, const void* bias, int bias_dt
         const int items = (write_kv ? nh + nkv : nh) * (hd / 16);
         int threads = 32;
         while (threads < 256 && threads < items) threads <<= 1;
-        rope_cache_write_bf16_vec_kernel<<<n_tokens, threads, 0, stream>>>(
+        RV_LAUNCH_ST = rv_launch(rope_cache_write_bf16_vec_kernel, dim3(n_tokens), dim3(threads), 0, stream, 
             (const __nv_bfloat16*)qkv, bias, bias_dtype, positions, cos_t, sin_t, slot_mapping, (__nv_bfloat16*)cache,
             (__nv_bfloat16*)q_out, nh, nkv, hd, page_size, write_kv, table_rows, row_stride);
         return rv_launch_status();
@@ -292,11 +302,11 @@ RV_EXPORT int rv_rope_cache_write(const void* qkv, const void* bias, int bias_dt
     const dim3 grid(n_tokens, write_kv ? nh + 2 * nkv : nh);
     const int threads = hd / 2 >= 128 ? 128 : (hd / 2 >= 64 ? 64 : 32);
     if (dtype == RV_DTYPE_F32)
-        rope_cache_write_kernel<float><<<grid, threads, 0, stream>>>(
+        RV_LAUNCH_ST = rv_launch(rope_cache_write_kernel<float>, dim3(grid), dim3(threads), 0, stream, 
             (const float*)qkv, bias, bias_dtype, positions, cos_t, sin_t, slot_mapping, (float*)cache,
             (float*)q_out, nh, nkv, hd, page_size, write_kv, table_rows, row_stride);
     else if (dtype == RV_DTYPE_BF16)
-        rope_cache_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+        RV_LAUNCH_ST = rv_launch(rope_cache_write_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, 
             (const __nv_bfloat16*)qkv, bias, bias_dtype, positions, cos_t, sin_t, slot_mapping,
             (__nv_bfloat16*)cache, (__nv_bfloat16*)q_out, nh, nkv, hd, page_size, write_kv, table_rows, row_stride);
     else
@@ -307,6 +317,8 @@ RV_EXPORT int rv_rope_cache_write(const void* qkv, const void* bias, int bias_dt
 // ------------------------------------------------------------------ SiLU(gate) * up
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
         const size_t row = idx / inter;
@@ -320,6 +332,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 // bfloat16 with inter a multiple of 8: 16-byte loads of gate and up, one 16-byte store.
 __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
                                          int inter, size_t total_vec) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     const int vec_per_row = inter >> 3;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_vec; idx += stride) {
@@ -351,16 +365,16 @@ RV_EXPORT int rv_silu_mul(const void* gate_up, void* out, int n_rows, int inter,
         const size_t total_vec = total / 8;
         size_t vb = (total_vec + threads - 1) / threads;
         if (vb > 148 * 32) vb = 148 * 32;
-        silu_mul_bf16_vec_kernel<<<(int)vb, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
+        RV_LAUNCH_ST = rv_launch(silu_mul_bf16_vec_kernel, dim3((int)vb), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
                                                                  inter, total_vec);
         return rv_launch_status();
     }
     size_t blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == RV_DTYPE_F32)
-        silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+        RV_LAUNCH_ST = rv_launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, total);
     else if (dtype == RV_DTYPE_BF16)
-        silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+        RV_LAUNCH_ST = rv_launch(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
     else
         return RV_ERR_BAD_DTYPE;
     return rv_launch_status();

@@ -17,6 +17,8 @@ __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, const void* __restrict__ bias,
                 int bias_dtype, const float* __restrict__ residual, float* __restrict__ out,
                 int M, int N, int K) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     __shared__ float xs[TK][TM + 1];
     __shared__ float ws[TK][TN + 1];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -74,6 +76,6 @@ RV_EXPORT int rv_gemm_f32(const float* x, const float* w, const void* bias, int 
     if (M == 0) return RV_OK;
     const dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
     if (grid.y > 65535) return RV_ERR_BAD_SIZE;
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, w, bias, bias_dtype, residual, out, M, N, K);
+    RV_LAUNCH_ST = rv_launch(gemm_f32_kernel, dim3(grid), dim3(256), 0, stream, x, w, bias, bias_dtype, residual, out, M, N, K);
     return rv_launch_status();
 }

@@ -44,6 +44,8 @@ struct SkinnyParams {
 template <int MT, int NT, bool GATED>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const SkinnyParams p) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -192,7 +194,7 @@ static int launch_skinny(SkinnyParams& p, cudaStream_t stream) {
     const int rows_per_cta = GATED ? (NT / 2) * 16 : NT * 16;
     const int n_rows = GATED ? p.N / 2 : p.N;
     const int grid = (n_rows + rows_per_cta - 1) / rows_per_cta;
-    gemm_skinny_kernel<MT, NT, GATED><<<grid, SK_THREADS, smem, stream>>>(p);
+    RV_LAUNCH_ST = rv_launch(gemm_skinny_kernel<MT, NT, GATED>, dim3(grid), dim3(SK_THREADS), smem, stream, p);
     return rv_launch_status();
 }
 

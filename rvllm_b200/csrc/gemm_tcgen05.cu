@@ -21,7 +21,7 @@
 // which calls cuBLASLt; its residual epilogue beta = 1 is cublaslt.rs:335-368, and its fused
 // gate-up-SiLU idea is kernels/cutlass_gateup_silu.cu).
 #include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 #define BM 128
 #define BN 256
@@ -33,7 +33,6 @@
 #define STAGE_BYTES (A_TILE_BYTES + B_TILE_BYTES)
 #define NUM_THREADS 192
 #define TMEM_COLS 512
-#define SPIN_LIMIT (1u << 24)
 
 #define EPI_PLAIN 0
 #define EPI_RESIDUAL 1
@@ -49,76 +48,6 @@ struct GemmParams {
     int m_tiles, n_tiles;
 };
 
-// ---------------------------------------------------------------- small PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false when it gave up or another role already did.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
-        if (mbar_try(bar, parity)) return true;
-        if ((it & 255u) == 255u && *abort_flag) return false;
-    }
-    *abort_flag = code;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                                 uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
-// groups of 8 rows 1024 bytes apart (stride offset), leading offset unused (1), version 1.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address, bits [0, 14)
-    d |= (uint64_t)1 << 16;                               // leading byte offset (16-byte units), bits [16, 30)
-    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset, bits [32, 46)
-    d |= (uint64_t)1 << 46;                               // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                               // layout type: 128-byte swizzle
-    return d;
-}
-
-// Instruction descriptor: float accumulator, bf16 x bf16, both K-major, N = 256, M = 128.
-__device__ __forceinline__ uint32_t umma_idesc() {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
 
@@ -132,6 +61,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
 
+    rv_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
     const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
@@ -150,6 +80,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    rv_pdl_wait();          // the set-up above overlapped the previous kernel; its results are needed from here
 
     const int num_tiles = p.m_tiles * p.n_tiles;
     const int num_kb = (p.K + BK - 1) / BK;
@@ -199,7 +130,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc();
+            const uint32_t idesc = umma_idesc_bf16(BM, BN);
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
@@ -336,36 +267,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)ptr;
-    }
-    return fn;
-}
-
-// A [rows, cols] row-major bf16 matrix, loaded in boxes of box_rows x 64 columns with 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return RV_ERR_UNSUPPORTED;
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? RV_OK : RV_ERR_BAD_SIZE;
-}
-
 // epilogue: 0 plain, 1 + residual (bf16 [M, N]), 2 gated (W rows [gate | up], out has N/2 columns).
 // status: optional device int that receives a non-zero code if a wait inside the kernel gave up.
 RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* residual, void* out, int out_f32,
@@ -380,9 +281,9 @@ RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* res
         return RV_ERR_ALIGNMENT;
     if (M == 0) return RV_OK;
     alignas(64) CUtensorMap map_a, map_b;
-    int st = make_map(&map_a, x, M, K, BM);
+    int st = rv_make_bf16_map(&map_a, x, M, K, BM);
     if (st != RV_OK) return st;
-    st = make_map(&map_b, w, N, K, BN / 2);
+    st = rv_make_bf16_map(&map_b, w, N, K, BN / 2);
     if (st != RV_OK) return st;
     GemmParams p;
     p.out = out; p.residual = epilogue == EPI_RESIDUAL ? (const __nv_bfloat16*)residual : nullptr;
@@ -401,6 +302,6 @@ RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* res
     int ctas = p.m_tiles * p.n_tiles;
     const int limit = max_ctas > 0 ? max_ctas : 148;
     if (ctas > limit) ctas = limit;
-    gemm_tcgen05_kernel<<<ctas, NUM_THREADS, smem, stream>>>(map_a, map_b, p);
+    RV_LAUNCH_ST = rv_launch(gemm_tcgen05_kernel, dim3(ctas), dim3(NUM_THREADS), smem, stream, map_a, map_b, p);
     return rv_launch_status();
 }

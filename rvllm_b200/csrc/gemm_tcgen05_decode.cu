@@ -1,0 +1,322 @@
+// bfloat16 linear layer for few rows (decode) on the fifth-generation tensor cores:
+//     out[M, N] = x[M, K] . W[N, K]^T (+ bias[N]) (+ residual[M, N]),       M <= 128,
+// or GATED with W rows [gate (N/2) | up (N/2)]:  out[M, N/2] = silu(x Wg^T) * (x Wu^T).
+//
+// The product is computed transposed: the WEIGHTS are the 128-row A operand of tcgen05.mma and
+// the batch is its N dimension (16 to 128 columns of tensor memory), so a CTA streams a tile of
+// 128 output features through a TMA pipeline and every weight byte is read from HBM exactly once
+// whatever the batch size.  Small N would leave most SMs idle, so K is also split over CTAs;
+// the CTAs of a tile write float partials to scratch memory, and the CTA that arrives last (an
+// atomic counter per tile, no spinning) adds them in split order and runs the epilogue.  The sum
+// of a row therefore does not depend on which CTA came last, nor on the other rows of the batch.
+//
+//   warp 0   TMA producer (one thread): weight tile 128 x 64 and activation tile MB x 64 per
+//            stage, 128-byte swizzle, 4 stages;
+//   warp 1   MMA issuer (one thread): tcgen05.mma M = 128, N = MB, K = 16; tcgen05.commit frees
+//            stages and finally publishes the accumulator;
+//   warps 2-5  epilogue: tcgen05.ld of each thread's feature row, split reduction, bias,
+//            residual, SiLU-gate, rounding, coalesced stores.
+// Every mbarrier wait is bounded (see gemm_tcgen05.cu); no cluster, no multicast.
+//
+// Shapes: the five products of a layer and the LM head at decode time
+// (v3/crates/rvllm-runtime/src/layer_exec.rs:240-266,433-444,478-488,511-522 and
+// bring_up.rs:648-658 of the reference, which calls cuBLASLt there).
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+#define TILE_F 128           // output features per tile (UMMA M)
+#define BK 64
+#define STAGES 4
+#define UMMA_K 16
+#define A_BYTES (TILE_F * BK * 2)
+#define NUM_THREADS 192
+
+struct DecodeGemmParams {
+    void* out;
+    const __nv_bfloat16* residual;
+    const void* bias;
+    int bias_dtype;
+    float* scratch;          // [tiles, splits, MB, 128] float partials (splits > 1)
+    int* counters;           // [tiles], zero between launches
+    int* status;
+    int M, N, K;
+    int out_f32, gated;
+    int splits, n_tiles;
+};
+
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int MB>
+__global__ void __launch_bounds__(NUM_THREADS)
+gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                   const DecodeGemmParams p) {
+    constexpr int B_BYTES = MB * BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int TMEM_COLS = MB < 32 ? 32 : MB;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+    __shared__ int is_last;
+
+    rv_pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), tfull = smem_u32(&bars[2 * STAGES]);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        is_last = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(tfull, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int tile = blockIdx.x / p.splits, split = blockIdx.x - tile * p.splits;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const int per = (num_kb + p.splits - 1) / p.splits;
+    const int kb0 = split * per, kb1 = min(num_kb, kb0 + per);
+    const int half_n = p.N >> 1;
+    // first weight row of the tile's (two) halves
+    const int row_a = p.gated ? tile * (TILE_F / 2) : tile * TILE_F;
+    const int row_b = p.gated ? half_n + tile * (TILE_F / 2) : tile * TILE_F + TILE_F / 2;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0, issued = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            // The weights are written by no kernel of a step: the first stages' weight tiles are
+            // requested before waiting for the previous kernel, whose tail this overlaps.  The
+            // activations follow after the wait; a stage's barrier completes when both have landed.
+            const int early = min(STAGES, kb1 - kb0);
+            for (int i = 0; i < early; ++i) {
+                const uint32_t a_dst = smem_u32(tiles + (size_t)i * STAGE_BYTES);
+                const uint32_t bar = full0 + 8 * i;
+                mbar_expect_tx(bar, STAGE_BYTES);
+                tma_load_2d(a_dst, &map_w, (kb0 + i) * BK, row_a, bar);
+                tma_load_2d(a_dst + A_BYTES / 2, &map_w, (kb0 + i) * BK, row_b, bar);
+            }
+            rv_pdl_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(smem_u32(tiles + (size_t)i * STAGE_BYTES) + A_BYTES, &map_x, (kb0 + i) * BK, 0, full0 + 8 * i);
+            issued = early;
+            stage = early % STAGES;
+            phase = early == STAGES ? 1 : 0;
+            for (int kb = kb0 + early; kb < kb1; ++kb) {
+                if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, &abort_flag, 1)) { ok = false; break; }
+                const uint32_t a_dst = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
+                const uint32_t bar = full0 + 8 * stage;
+                mbar_expect_tx(bar, STAGE_BYTES);
+                tma_load_2d(a_dst, &map_w, kb * BK, row_a, bar);
+                tma_load_2d(a_dst + A_BYTES / 2, &map_w, kb * BK, row_b, bar);
+                tma_load_2d(a_dst + A_BYTES, &map_x, kb * BK, 0, bar);
+                ++issued;
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) {
+                const int pending = issued < STAGES ? issued : STAGES;
+                for (int i = 0; i < pending; ++i) {
+                    int s = stage - 1 - i;
+                    uint32_t ph = phase;
+                    while (s < 0) { s += STAGES; ph ^= 1; }
+                    for (uint32_t it = 0; it < (1u << 20); ++it)
+                        if (mbar_try(full0 + 8 * s, ph)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(TILE_F, MB);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!mbar_wait(full0 + 8 * stage, phase, &abort_flag, 3)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t a_addr = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
+                const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+                for (int j = 0; j < BK / UMMA_K; ++j)
+                    tcgen05_mma_bf16(tmem_base, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (kb > kb0) || j != 0);
+                tcgen05_commit(empty0 + 8 * stage);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (ok) tcgen05_commit(tfull);
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const int quarter = warp & 3;
+        const int f = quarter * 32 + lane;                  // feature row of this thread within the tile
+        const int et = (warp - 2) * 32 + lane;              // 0..127 among the epilogue threads
+        const bool have = kb1 > kb0;
+        rv_pdl_wait();
+        if (have) mbar_wait(tfull, 0, &abort_flag, 4);
+        // every epilogue thread comes here in bounded time; after the barrier they all see the same
+        // abort flag, so the named barriers below are never reached by only some of them
+        epi_sync();
+        const bool ok = abort_flag == 0;
+        tcgen05_fence_after();
+        float* fin = reinterpret_cast<float*>(tiles);       // [128][MB + 1], the stages are free now
+        if (ok) {
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            float* part = p.splits > 1 ? p.scratch + ((size_t)(tile * p.splits + split) * MB) * TILE_F : nullptr;
+#pragma unroll
+            for (int c = 0; c < MB; c += 16) {
+                uint32_t r[16];
+                if (have) {
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                                 : "r"(taddr + c));
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) r[e] = 0u;    // this split got no k block: it adds zeros
+                }
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    if (part) {
+                        if (c + e < p.M) part[(size_t)(c + e) * TILE_F + f] = __uint_as_float(r[e]);   // real rows only
+                    } else {
+                        fin[f * (MB + 1) + c + e] = __uint_as_float(r[e]);
+                    }
+                }
+            }
+            bool finish = true;
+            if (p.splits > 1) {
+                __threadfence();
+                epi_sync();
+                if (et == 0) is_last = atomicAdd(&p.counters[tile], 1) == p.splits - 1;
+                epi_sync();
+                finish = is_last != 0;
+                if (finish) {
+                    __threadfence();
+                    const float* base = p.scratch + ((size_t)tile * p.splits * MB) * TILE_F;
+                    // the loads of four rows (up to 8 splits each) are in flight together; every row
+                    // is summed in split order
+                    for (int m0 = 0; m0 < p.M; m0 += 4) {
+                        float v[4] = {0.f, 0.f, 0.f, 0.f};
+                        for (int s0 = 0; s0 < p.splits; s0 += 8) {
+                            float t[4][8];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    t[j][i] = (m0 + j < p.M && s0 + i < p.splits)
+                                                  ? __ldcg(base + ((size_t)(s0 + i) * MB + m0 + j) * TILE_F + f) : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) v[j] += t[j][i];
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (m0 + j < p.M) fin[f * (MB + 1) + m0 + j] = v[j];
+                    }
+                    if (et == 0) p.counters[tile] = 0;     // ready for the next launch
+                }
+            }
+            if (finish) {
+                epi_sync();
+                if (p.gated) {
+                    // features 0..63 are gate rows, 64..127 the up rows of the same output columns
+                    const int fo = et & 63;
+                    const int n = tile * (TILE_F / 2) + fo;
+                    for (int m = et >> 6; m < p.M; m += 2) {
+                        if (n >= half_n) break;
+                        const float g = fin[fo * (MB + 1) + m], u = fin[(fo + 64) * (MB + 1) + m];
+                        const float v = g / (1.0f + expf(-g)) * u;
+                        if (p.out_f32) ((float*)p.out)[(size_t)m * half_n + n] = v;
+                        else ((__nv_bfloat16*)p.out)[(size_t)m * half_n + n] = __float2bfloat16_rn(v);
+                    }
+                } else {
+                    const int n = tile * TILE_F + et;
+                    if (n < p.N) {
+                        const float b = p.bias ? rv_load_param(p.bias, p.bias_dtype, n) : 0.f;
+                        for (int m = 0; m < p.M; ++m) {
+                            float v = fin[et * (MB + 1) + m] + b;
+                            if (p.residual) v += __bfloat162float(p.residual[(size_t)m * p.N + n]);
+                            if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n] = v;
+                            else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+    }
+    if (threadIdx.x == 0 && abort_flag != 0 && p.status) atomicCAS(p.status, 0, abort_flag);
+}
+
+template <int MB>
+static int launch_decode(const CUtensorMap& mw, const CUtensorMap& mx, const DecodeGemmParams& p, cudaStream_t stream) {
+    const int stage = A_BYTES + MB * BK * 2;
+    const int fin = TILE_F * (MB + 1) * 4;
+    const int smem = (STAGES * stage > fin ? STAGES * stage : fin) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    RV_LAUNCH_ST = rv_launch(gemm_decode_kernel<MB>, dim3(p.n_tiles * p.splits), dim3(NUM_THREADS), smem, stream, mw, mx, p);
+    return rv_launch_status();
+}
+
+// Rows of batch padding this kernel would use for M rows (16, 32, 64 or 128).
+RV_EXPORT int rv_gemm_decode_padded_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
+
+// Number of 128-feature tiles, so that the caller can size `scratch` (tiles * splits * padded rows
+// * 128 floats when splits > 1) and `counters` (tiles ints, zero before the first launch; the
+// kernel leaves them zero).
+RV_EXPORT int rv_gemm_decode_tiles(int N, int gated) {
+    return gated ? (N / 2 + TILE_F / 2 - 1) / (TILE_F / 2) : (N + TILE_F - 1) / TILE_F;
+}
+
+RV_EXPORT int rv_gemm_tcgen05_decode_bf16(const void* x, const void* w, const void* bias, int bias_dtype,
+                                          const void* residual, void* out, int out_f32, int M, int N, int K,
+                                          int gated, int splits, float* scratch, int* counters, int* status,
+                                          cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || splits < 1) return RV_ERR_BAD_SIZE;
+    if (M > 128) return RV_ERR_UNSUPPORTED;
+    if (K % 8) return RV_ERR_UNSUPPORTED;
+    if (gated && ((N & 1) || bias || residual)) return RV_ERR_BAD_SIZE;
+    if (residual && out_f32) return RV_ERR_BAD_SIZE;
+    if (splits > 1 && (!scratch || !counters)) return RV_ERR_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return RV_ERR_ALIGNMENT;
+    if (M == 0) return RV_OK;
+    const int num_kb = (K + BK - 1) / BK;
+    if (splits > num_kb) splits = num_kb;
+    const int mb = rv_gemm_decode_padded_rows(M);
+    alignas(64) CUtensorMap mw, mx;
+    int st = rv_make_bf16_map(&mw, w, N, K, TILE_F / 2);
+    if (st != RV_OK) return st;
+    st = rv_make_bf16_map(&mx, x, M, K, mb);
+    if (st != RV_OK) return st;
+    DecodeGemmParams p;
+    p.out = out; p.residual = (const __nv_bfloat16*)residual; p.bias = bias; p.bias_dtype = bias_dtype;
+    p.scratch = scratch; p.counters = counters; p.status = status;
+    p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.gated = gated; p.splits = splits;
+    p.n_tiles = rv_gemm_decode_tiles(N, gated);
+    switch (mb) {
+        case 16: return launch_decode<16>(mw, mx, p, stream);
+        case 32: return launch_decode<32>(mw, mx, p, stream);
+        case 64: return launch_decode<64>(mw, mx, p, stream);
+        default: return launch_decode<128>(mw, mx, p, stream);
+    }
+}

@@ -106,6 +106,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const unsigned long long* __restrict__ seeds, const long long* __restrict__ draw_index,
               int* __restrict__ out, int V) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
     __shared__ float s_val[33];
     __shared__ int s_idx[33];
     __shared__ float s_scan[SAMPLE_THREADS / 32 + 1];
@@ -238,6 +240,6 @@ RV_EXPORT int rv_sample(const float* logits, const float* temperature, const int
     if (n_rows < 0 || vocab <= 0) return RV_ERR_BAD_SIZE;
     if (n_rows == 0) return RV_OK;
     if (temperature && (!seeds || !draw_index)) return RV_ERR_BAD_SIZE;
-    sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, temperature, top_k, top_p, seeds, draw_index, out, vocab);
+    RV_LAUNCH_ST = rv_launch(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, temperature, top_k, top_p, seeds, draw_index, out, vocab);
     return rv_launch_status();
 }

@@ -10,6 +10,7 @@ library cannot be built, construction raises `KernelError`.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_void_p, c_int, c_float
 from typing import Optional
 
@@ -67,6 +68,9 @@ class AttentionMeta:
 class CudaKernels:
     SKINNY_MAX_ROWS = 0     # rows up to which the weight-streaming GEMM replaces the library GEMM (0: off)
     TCGEN05_MIN_ROWS = 128  # rows from which the tcgen05 GEMM of this project is used for bfloat16
+    DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
+    DECODE_SPLIT_ROWS = 4   # ... when K has to be split over CTAs, only up to this many rows
+    pdl = os.environ.get("RVLLM_NO_PDL") != "1"   # programmatic dependent launch between kernels
 
     def __init__(self, device="cuda:0"):
         if not torch.cuda.is_available():
@@ -79,6 +83,7 @@ class CudaKernels:
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
         self._libs = {}
+        self._decode_counters = None
 
     # ------------------------------------------------------------------ plumbing
     def _lib(self, source: str, defines=()):
@@ -86,6 +91,7 @@ class CudaKernels:
         lib = self._libs.get(key)
         if lib is None:
             lib = build.load_library(source, defines)
+            lib.rv_set_pdl(c_int(1 if self.pdl else 0))
             self._libs[key] = lib
         return lib
 
@@ -259,6 +265,9 @@ class CudaKernels:
 
     def _linear_bf16(self, x, weight, bias, residual, out_dtype):
         M, K = x.shape
+        if self._use_decode_gemm(M, weight.shape[0], K, False) and out_dtype in (torch.bfloat16, torch.float32) \
+                and (residual is None or (residual.dtype == torch.bfloat16 and out_dtype == torch.bfloat16)):
+            return self.linear_decode(x, weight, bias, residual, out_dtype)
         if 0 < M <= self.SKINNY_MAX_ROWS and K % 8 == 0 and out_dtype in (torch.bfloat16, torch.float32) \
                 and (residual is None or (residual.dtype == torch.bfloat16 and out_dtype == torch.bfloat16)):
             return self.linear_skinny(x, weight, bias, residual, out_dtype)
@@ -316,10 +325,58 @@ class CudaKernels:
         _check("gemm_tcgen05", st)
         return out
 
+    def _use_decode_gemm(self, M: int, N: int, K: int, gated: bool) -> bool:
+        """Whether the weight-streaming tcgen05 GEMM serves this product: few rows, and either
+        enough 128-feature tiles to fill the GPU without splitting K, or so few rows that the
+        split reduction is cheap."""
+        if not (0 < M <= self.DECODE_MAX_ROWS) or K % 8:
+            return False
+        tiles = ((N // 2 + 63) // 64) if gated else (N + 127) // 128
+        return M <= self.DECODE_SPLIT_ROWS or self.gemm_splits(tiles, K) == 1
+
+    def gemm_splits(self, n_tiles: int, K: int) -> int:
+        """Into how many CTAs the K dimension of a decode GEMM is cut: about two CTAs per SM, at
+        least four 64-wide k blocks each."""
+        num_kb = (K + 63) // 64
+        return max(1, min(296 // max(n_tiles, 1), num_kb // 4, 32))
+
+    def linear_decode(self, x, weight, bias=None, residual=None, out_dtype=None, gated=False, splits=None, status=None):
+        """The weight-streaming tcgen05 GEMM for at most 128 rows of bfloat16 activations."""
+        _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
+        M, K = x.shape
+        N = weight.shape[0]
+        lib = self._lib("gemm_tcgen05_decode.cu")
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+        tiles = lib.rv_gemm_decode_tiles(c_int(N), c_int(1 if gated else 0))
+        if splits is None:
+            splits = self.gemm_splits(tiles, K)
+        splits = max(1, min(splits, (K + 63) // 64))
+        scratch = None
+        if splits > 1:
+            if self._decode_counters is None or self._decode_counters.numel() < tiles:
+                self._decode_counters = torch.zeros((max(tiles, 4096),), dtype=torch.int32, device=x.device)
+            mb = lib.rv_gemm_decode_padded_rows(c_int(M))
+            scratch = torch.empty((tiles * splits * mb * 128,), dtype=torch.float32, device=x.device)
+        if bias is not None:
+            _need(bias, "bias", dims=1)
+        if residual is not None:
+            _need(residual, "residual", torch.bfloat16, 2)
+        st = lib.rv_gemm_tcgen05_decode_bf16(
+            _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0), _ptr(residual),
+            _ptr(out), c_int(1 if out_dtype == torch.float32 else 0), c_int(M), c_int(N), c_int(K),
+            c_int(1 if gated else 0), c_int(splits), _ptr(scratch), _ptr(self._decode_counters if splits > 1 else None),
+            _ptr(status), self._stream())
+        _check("gemm_tcgen05_decode", st)
+        return out
+
     def gate_up_silu(self, x, weight) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) for weight rows [Wg | Wu]: one fused kernel for few bfloat16
         rows, else the product followed by the SiLU kernel."""
         M, K = x.shape
+        if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[0] % 2 == 0 \
+                and self._use_decode_gemm(M, weight.shape[0], K, True):
+            return self.linear_decode(x, weight, gated=True)
         if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < M <= self.SKINNY_MAX_ROWS \
                 and K % 8 == 0 and weight.shape[0] % 2 == 0:
             return self.linear_skinny(x, weight, gated=True)

@@ -282,3 +282,32 @@ def test_gemm_tcgen05_bf16(K, M, N, Kd):
     # the product path picks it from TCGEN05_MIN_ROWS rows on
     if M >= K.TCGEN05_MIN_ROWS:
         assert torch.equal(K.linear(x, w, None, r), K.linear_tcgen05(x, w, r))
+
+
+@pytest.mark.parametrize("M,N,Kd", [(1, 128, 64), (3, 100, 200), (8, 520, 4096), (17, 261, 1032), (64, 1000, 328), (128, 384, 2048)])
+def test_gemm_tcgen05_decode_bf16(K, M, N, Kd):
+    """The weight-streaming tcgen05 kernel: every padded batch width, K split over CTAs and merged
+    by the last arrival, every epilogue; counters are left ready for the next launch."""
+    torch.manual_seed(10)
+    x = torch.randn(M, Kd, device="cuda").bfloat16()
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(N, device="cuda").bfloat16()
+    r = torch.randn(M, N, device="cuda").bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ref = x.double().cpu() @ w.double().cpu().t()
+    for splits in (1, 2, 5, None):
+        assert rel_err(K.linear_decode(x, w, splits=splits, status=status), ref) < BF16_TOL
+    full = ref + b.double().cpu() + r.double().cpu()
+    for _ in range(2):                                       # twice: the tile counters were reset
+        assert rel_err(K.linear_decode(x, w, b, r, splits=3, status=status), full) < BF16_TOL
+    assert rel_err(K.linear_decode(x, w, b.float(), None, torch.float32, splits=4, status=status), ref + b.double().cpu()) < 1e-5
+    if N % 2 == 0:
+        g, u = ref[:, :N // 2], ref[:, N // 2:]
+        want = g / (1 + torch.exp(-g)) * u
+        for splits in (1, 3):
+            assert rel_err(K.linear_decode(x, w, gated=True, splits=splits, status=status), want) < BF16_TOL
+    assert int(status.item()) == 0, "a bounded wait inside the kernel gave up"
+    one = K.linear_decode(x[:1].contiguous(), w, out_dtype=torch.float32, splits=4)
+    assert torch.equal(one, K.linear_decode(x, w, out_dtype=torch.float32, splits=4)[:1])     # batch-invariant
+    if K._decode_counters is not None:
+        assert int(K._decode_counters.abs().sum().item()) == 0
