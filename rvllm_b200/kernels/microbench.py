@@ -1,0 +1,92 @@
+"""Run one kernel of the engine alone on a given shape and print its time and throughput.
+
+    python -m rvllm_b200.kernels.microbench decode_gemm  --m 8 --n 28672 --k 4096 [--gated]
+    python -m rvllm_b200.kernels.microbench prefill_gemm --m 2048 --n 6144 --k 4096 [--gated]
+    python -m rvllm_b200.kernels.microbench decode_attention  --batch 32 --ctx 2048
+    python -m rvllm_b200.kernels.microbench prefill_attention --tokens 2048
+
+Used for timing a kernel in isolation (CUDA events, warm-up, inputs rotated so that L2 does not
+help) and as the small, self-ending workload of a profiler capture.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def timed(fns, iters: int, warmup: int = 3):
+    for i in range(warmup):
+        fns[i % len(fns)]()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(iters):
+        fns[i % len(fns)]()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def main(argv=None) -> int:
+    from . import AttentionMeta, get_library
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["decode_gemm", "prefill_gemm", "decode_attention", "prefill_attention"])
+    ap.add_argument("--m", type=int, default=8)
+    ap.add_argument("--n", type=int, default=28672)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--gated", action="store_true")
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--iters", type=int, default=5)
+    args = ap.parse_args(argv)
+    K = get_library("cuda:0")
+    torch.manual_seed(0)
+    dev = "cuda"
+    out = {"kernel": args.kernel}
+    if args.kernel in ("decode_gemm", "prefill_gemm"):
+        copies = max(2, int(300e6 // (args.n * args.k * 2)) + 1)
+        ws = [(torch.randn(args.n, args.k, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+        x = torch.randn(args.m, args.k, device=dev).bfloat16()
+        if args.kernel == "decode_gemm":
+            fns = [(lambda w=w: K.linear_decode(x, w, gated=args.gated)) for w in ws]
+        else:
+            fns = [(lambda w=w: K.linear_tcgen05(x, w, gated=args.gated)) for w in ws]
+        ms = timed(fns, args.iters)
+        out.update(m=args.m, n=args.n, k=args.k, gated=args.gated, us=round(ms * 1e3, 2),
+                   weight_gb_s=round(args.n * args.k * 2 / ms / 1e6, 1),
+                   tflops=round(2 * args.m * args.n * args.k / ms / 1e9, 1))
+    else:
+        nh, nkv, hd, ps = args.heads, args.kv_heads, args.head_dim, args.page
+        if args.kernel == "decode_attention":
+            B, q_lens, ctx = args.batch, [1] * args.batch, args.ctx
+        else:
+            B, q_lens, ctx = 1, [args.tokens], args.tokens
+        MB = (ctx + ps - 1) // ps
+        cache = torch.randn(B * MB, 2, nkv, ps, hd, device=dev).bfloat16()
+        bt = torch.arange(B * MB, dtype=torch.int32, device=dev).view(B, MB)
+        T = sum(q_lens)
+        q = torch.randn(T, nh * hd, device=dev).bfloat16()
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev)
+        ctxs = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+        seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(q_lens)]).to(dev)
+        meta = AttentionMeta(bt, cu, ctxs, seq, None, B, max(q_lens), ctx, ps, sum(1 for n in q_lens if n == 1))
+        ms = timed([lambda: K.paged_attention(q, cache, meta, nh, nkv, hd, hd ** -0.5, None)], args.iters)
+        kv_bytes = B * ctx * 2 * nkv * hd * 2
+        out.update(batch=B, ctx=ctx, heads=nh, kv_heads=nkv, head_dim=hd, us=round(ms * 1e3, 2))
+        if args.kernel == "decode_attention":
+            out.update(kv_gb_s=round(kv_bytes / ms / 1e6, 1), splits=K.decode_splits(meta, nh, nkv))
+        else:
+            out.update(tflops=round(4 * nh * hd * ctx * ctx / 2 / ms / 1e9, 1))
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
