@@ -24,6 +24,7 @@
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head_dim must be a multiple of 16 up to 256");
 
 #define KV_TILE 64
+#define TABLE_CACHE 1024   // block-table entries of a CTA's key range kept in shared memory
 // a row of the shared-memory tiles is padded by 16 bytes: the stride is an odd multiple of
 // 16 bytes, so the 8 rows an ldmatrix reads fall into different banks
 #define ROW_BYTES (HEAD_DIM * 2 + 16)
@@ -145,6 +146,16 @@ flash_paged_kernel(const FlashParams p) {
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     const int* table = p.block_tables + (size_t)seq * p.max_blocks;
+    // The page numbers of this CTA's key range are copied to shared memory once: a tile's loads
+    // then start without first waiting for a read of the block table in global memory.
+    __shared__ int s_table[TABLE_CACHE];
+    const int blk_lo = (t_begin * KV_TILE) >> p.page_shift;
+    const int blk_hi = t_begin < t_end ? ((min(t_end * KV_TILE, key_hi) - 1) >> p.page_shift) + 1 : blk_lo;
+    const bool table_cached = blk_hi - blk_lo <= TABLE_CACHE;
+    if (table_cached) {
+        for (int i = tid; i < blk_hi - blk_lo; i += NTHREADS) s_table[i] = table[blk_lo + i];
+        __syncthreads();
+    }
     const size_t page_stride = (size_t)2 * p.nkv * p.page_size * HD;
     const size_t v_off = (size_t)p.nkv * p.page_size * HD;
     const __nv_bfloat16* kv_base = p.cache + (size_t)kvh * p.page_size * HD;
@@ -158,7 +169,8 @@ flash_paged_kernel(const FlashParams p) {
             const bool ok = key >= key_lo && key < key_hi;
             const __nv_bfloat16* src = p.cache;
             if (ok) {
-                const int page = table[key >> p.page_shift];
+                const int blk = key >> p.page_shift;
+                const int page = table_cached ? s_table[blk - blk_lo] : table[blk];
                 src = kv_base + (size_t)page * page_stride + (size_t)(key & (p.page_size - 1)) * HD + c * 8;
             }
             cp_async_16(ks + row * ROW_BYTES + c * 16, src, ok);

@@ -86,7 +86,7 @@ class LLM:
         batch = self.scheduler.schedule()
         entries = []
         for e in batch.entries:
-            toks = e.request.all_tokens[e.start:e.start + e.num_tokens]
+            toks = e.request.tokens(e.start, e.num_tokens)
             entries.append(StepEntry(e.request.req_id, toks, (e.num_tokens - 1,) if e.samples else ()))
         logits = self.engine.runner.step(entries)
         sampled: Dict[Hashable, int] = {}

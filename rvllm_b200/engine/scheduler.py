@@ -56,6 +56,15 @@ class Request:
     def remaining(self) -> int:
         return len(self.prompt) + len(self.output) - self.num_computed
 
+    def tokens(self, start: int, n: int) -> List[int]:
+        """Tokens [start, start + n) of prompt + output, without joining the two lists."""
+        p = len(self.prompt)
+        if start >= p:
+            return self.output[start - p:start - p + n]
+        if start + n <= p:
+            return self.prompt[start:start + n]
+        return self.prompt[start:] + self.output[:start + n - p]
+
 
 @dataclass
 class ScheduledEntry:

@@ -154,6 +154,9 @@ class ModelRunner:
 
         o_tok, o_pos, o_seq = take(T), take(T), take(T)
         o_cu, o_ctx, o_state, o_rows = take(B + 1), take(B), take(B), take(R)
+        if pad_to is not None:
+            return self._pack_decode(entries, starts, B, MB, h, host, dev,
+                                     (o_tok, o_pos, o_seq, o_cu, o_ctx, o_state, o_rows), take)
         cu = 0
         rows: List[int] = []
         h[o_cu] = 0
@@ -218,6 +221,59 @@ class ModelRunner:
                 token_seq=ctx.token_seq, slot_mapping=dev[o_slot:o_slot + T], num_seqs=B,
                 max_q_len=max(q_lens), max_ctx_len=max_ctx, page_size=ps,
                 num_decode=sum(1 for n in q_lens if n == 1)))
+        return ctx
+
+    def _pack_decode(self, entries, starts, B, MB, h, host, dev, offs, take) -> StepContext:
+        """`pack` for a padded batch of one-token sequences (T = R = B): whole-array writes."""
+        cache = self.cache
+        o_tok, o_pos, o_seq, o_cu, o_ctx, o_state, o_rows = offs
+        n = len(entries)
+        ar = np.arange(B + 1, dtype=np.int32)
+        h[o_tok:o_tok + B] = 0
+        h[o_pos:o_pos + B] = 0
+        h[o_ctx:o_ctx + B] = 0
+        h[o_state:o_state + B] = -1
+        if n:
+            h[o_tok:o_tok + n] = [e.tokens[0] for e in entries]
+            h[o_pos:o_pos + n] = starts
+            h[o_ctx:o_ctx + n] = np.asarray(starts, dtype=np.int32) + 1
+            h[o_state:o_state + n] = [cache.state_slot(e.req_id) for e in entries]
+        h[o_seq:o_seq + B] = ar[:B]
+        h[o_cu:o_cu + B + 1] = ar
+        h[o_rows:o_rows + B] = ar[:B]
+        ps = cache.page_size
+        group_offsets = []
+        for gi in range(len(cache.groups)):
+            o_slot, o_bt = take(B), take(B * MB)
+            bt = h[o_bt:o_bt + B * MB].reshape(B, MB)
+            bt[:] = -1
+            h[o_slot:o_slot + B] = -1
+            for i, e in enumerate(entries):
+                table = cache.block_table(e.req_id, gi)
+                bt[i, :len(table)] = table
+                pos = starts[i]
+                h[o_slot + i] = table[pos // ps] * ps + pos % ps
+            group_offsets.append((o_slot, o_bt))
+        off = group_offsets[-1][1] + B * MB if group_offsets else o_rows + B
+        dev[:off].copy_(host[:off], non_blocking=True)
+        self.last_h2d_bytes = off * 4
+        ctx = StepContext()
+        ctx.kernels = self.kernels
+        ctx.num_tokens, ctx.num_seqs = B, B
+        ctx.token_ids = dev[o_tok:o_tok + B]
+        ctx.positions = dev[o_pos:o_pos + B]
+        ctx.token_seq = dev[o_seq:o_seq + B]
+        ctx.cu_seqlens = dev[o_cu:o_cu + B + 1]
+        dev_ctx = dev[o_ctx:o_ctx + B]
+        ctx.state_slots = dev[o_state:o_state + B]
+        ctx.logit_rows = dev[o_rows:o_rows + B]
+        ctx.q_lens = [1] * B
+        ctx.ctx_lens = [s + 1 for s in starts] + [0] * (B - n)
+        ctx.req_ids = [e.req_id for e in entries]
+        ctx.attention = [AttentionMeta(
+            block_tables=dev[o_bt:o_bt + B * MB].view(B, MB), cu_seqlens=ctx.cu_seqlens, ctx_lens=dev_ctx,
+            token_seq=ctx.token_seq, slot_mapping=dev[o_slot:o_slot + B], num_seqs=B, max_q_len=1,
+            max_ctx_len=self.max_model_len, page_size=ps, num_decode=B) for (o_slot, o_bt) in group_offsets]
         return ctx
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

@@ -198,12 +198,25 @@ class CudaKernels:
 
     @staticmethod
     def decode_splits(meta: AttentionMeta, num_heads: int, num_kv_heads: int) -> int:
-        """Into how many CTAs the keys of a sequence are split in a decode step: enough to put
-        about two CTAs on each of the 148 SMs, never more than there are key tiles."""
+        """Into how many CTAs the keys of a sequence are split in a decode step.  Three CTAs of
+        this kernel fit an SM (444 on the GPU).  A batch that cannot fill them is split until it
+        does (never below two 64-key tiles per split, never more than 16 splits: the merge grows
+        with them); a batch that overfills them a little is split so that the last wave is full."""
         group = num_heads // num_kv_heads
         ctas = meta.num_seqs * num_kv_heads * ((group + 15) // 16)
         tiles = max(1, (meta.max_ctx_len + 63) // 64)
-        return max(1, min((296 + ctas - 1) // ctas, tiles, 64))
+        slots = 444
+        if ctas >= slots:
+            best, best_eff = 1, 0.0
+            for s in (1, 2, 3, 4):
+                if s > 1 and tiles // s < 4:
+                    break
+                waves = ctas * s / slots
+                eff = waves / -(-ctas * s // slots)
+                if eff > best_eff + 0.02:
+                    best, best_eff = s, eff
+            return best
+        return max(1, min(-(-slots // ctas), max(1, tiles // 2), 16))
 
     def flash_attention(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
                         mode=0, num_splits=1, q_filter=0, max_q_len=None):

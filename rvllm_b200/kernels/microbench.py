@@ -45,6 +45,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--splits", type=int, default=0, help="key splits of the decode attention (0: the library's choice)")
     args = ap.parse_args(argv)
     K = get_library("cuda:0")
     torch.manual_seed(0)
@@ -77,11 +78,24 @@ def main(argv=None) -> int:
         ctxs = torch.full((B,), ctx, dtype=torch.int32, device=dev)
         seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(q_lens)]).to(dev)
         meta = AttentionMeta(bt, cu, ctxs, seq, None, B, max(q_lens), ctx, ps, sum(1 for n in q_lens if n == 1))
-        ms = timed([lambda: K.paged_attention(q, cache, meta, nh, nkv, hd, hd ** -0.5, None)], args.iters)
+        if args.kernel == "decode_attention" and args.splits > 0:
+            o = torch.empty_like(q)
+            fn = lambda: K.flash_attention(q, cache, meta, o, nh, nkv, hd, hd ** -0.5, None, mode=1, num_splits=args.splits)
+        else:
+            fn = lambda: K.paged_attention(q, cache, meta, nh, nkv, hd, hd ** -0.5, None)
+        # one CUDA graph of several launches: device time without the host's launch cost
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(4):
+                fn()
+        ms = timed([graph.replay], args.iters) / 4
         kv_bytes = B * ctx * 2 * nkv * hd * 2
         out.update(batch=B, ctx=ctx, heads=nh, kv_heads=nkv, head_dim=hd, us=round(ms * 1e3, 2))
         if args.kernel == "decode_attention":
-            out.update(kv_gb_s=round(kv_bytes / ms / 1e6, 1), splits=K.decode_splits(meta, nh, nkv))
+            out.update(kv_gb_s=round(kv_bytes / ms / 1e6, 1), splits=args.splits or K.decode_splits(meta, nh, nkv))
         else:
             out.update(tflops=round(4 * nh * hd * ctx * ctx / 2 / ms / 1e9, 1))
     print(json.dumps(out))
