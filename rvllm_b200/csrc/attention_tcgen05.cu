@@ -1,0 +1,407 @@
+// Paged flash attention for prompt portions on the fifth-generation tensor cores (bfloat16).
+//
+// A CTA owns 128 rows - (token, query head) pairs of ONE key/value head, the G = nh / nkv heads of
+// a group packed side by side (128 / G tokens) - and walks the sequence's keys in tiles of 64:
+//   S = Q K^T        tcgen05.mma, Q [128 x hd] and K [64 x hd] K-major in shared memory (TMA,
+//                    128-byte swizzle), S [128 x 64] float in tensor memory;
+//   softmax          four warps, one thread per row: tcgen05.ld of the row, scale, causal / window
+//                    mask, running maximum and sum in float, P = exp2(s - m) written as bfloat16
+//                    into shared memory in the swizzled K-major layout;
+//   O += P V         tcgen05.mma, V [64 keys x hd] as the MN-major B operand straight from the
+//                    cache's [key][hd] pages, O [128 x hd] float accumulated in tensor memory.
+// The reference maximum of a row is only raised when the true maximum has grown by more than 2^8
+// (then O is rescaled in tensor memory), so most tiles need no pass over O; the final division
+// by the row sum uses the same reference.  One thread issues all TMA loads and MMAs; pages are
+// fetched one TMA box per (page, half of hd) through the block table.  Two CTAs fit an SM, so
+// the softmax of one overlaps the MMAs of the other.  Every mbarrier wait is bounded.
+//
+// Rule as in attention_flash.cu (v3/kernels/paged_attention_sm89.cu:277-308 of the reference):
+// token i of the step's q_len tokens sits at p = ctx_len - q_len + i and sees keys (p - window, p].
+// Cache layer layout: [num_pages, 2 (k, v), nkv, page_size, HEAD_DIM].
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 128
+#endif
+static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "this kernel is built for head sizes 64 and 128");
+
+#define ROWS 128
+#define KV_TILE 64
+#define HALVES (HEAD_DIM / 64)                 // 64-element (128-byte) slabs of the head dimension
+#define Q_BYTES (ROWS * HEAD_DIM * 2)
+#define KV_BYTES (KV_TILE * HEAD_DIM * 2)      // one of K or V for a tile
+#define P_BYTES (ROWS * KV_TILE * 2)
+#define NUM_THREADS 160
+#define TMEM_COLS 256
+#define S_COL 0
+#define O_COL 64
+#define TABLE_CACHE 512
+#define RESCALE_LOG2 8.0f
+
+struct AttnParams {
+    const int* block_tables;
+    const int* cu_seqlens;
+    const int* ctx_lens;
+    __nv_bfloat16* out;
+    int* status;
+    int nh, nkv, page_shift, page_size, max_blocks;
+    float scale_log2e;
+    int window;
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// MN-major operand with 128-byte swizzle (V as [key][hd]): 64 consecutive hd elements are one
+// 128-byte row; groups of 8 keys are 1024 bytes apart (stride offset); the next 64 hd elements
+// start `lbo_bytes` further (leading offset).
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                         const AttnParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = base;                               // [HALVES][128 rows x 128 B]
+    unsigned char* k_s = q_s + Q_BYTES;                      // [HALVES][64 keys x 128 B], one stage
+    unsigned char* v_s = k_s + KV_BYTES;                     // [2 stages][HALVES][64 keys x 128 B]
+    unsigned char* p_s = v_s + 2 * KV_BYTES;                 // [128 rows x 128 B]
+    __shared__ __align__(8) uint64_t bars[10];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+    __shared__ int s_table[TABLE_CACHE];
+
+    rv_pdl_launch_dependents();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t bar_q = smem_u32(&bars[0]), bar_k = smem_u32(&bars[1]);
+    const uint32_t bar_v0 = smem_u32(&bars[2]);                                      // v full [2]
+    const uint32_t bar_vfree0 = smem_u32(&bars[4]);                                  // v free [2]
+    const uint32_t bar_s_full = smem_u32(&bars[6]), bar_s_free = smem_u32(&bars[7]);
+    const uint32_t bar_p_full = smem_u32(&bars[8]), bar_o_full = smem_u32(&bars[9]);
+
+    const int seq = blockIdx.z, kvh = blockIdx.y, tile_m = blockIdx.x;
+    const int G = p.nh / p.nkv;
+    rv_pdl_wait();
+    const int ctx = p.ctx_lens[seq];
+    const int q_start = p.cu_seqlens[seq];
+    const int q_len = p.cu_seqlens[seq + 1] - q_start;
+    const int rows_total = q_len * G;
+    const int row0 = tile_m * ROWS;
+    if (q_len <= 1 || ctx <= 0 || row0 >= rows_total) return;          // one-token sequences go to the decode kernel
+
+    const int last_row = min(rows_total, row0 + ROWS) - 1;
+    const int pos_first = ctx - q_len + row0 / G, pos_last = ctx - q_len + last_row / G;
+    const int key_lo = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
+    const int key_hi = pos_last + 1;
+    const int t_begin = key_lo / KV_TILE, t_end = (key_hi + KV_TILE - 1) / KV_TILE;
+    const int blk_lo = (t_begin * KV_TILE) >> p.page_shift;
+    const int blk_hi = ((key_hi - 1) >> p.page_shift) + 1;
+    const bool table_cached = blk_hi - blk_lo <= TABLE_CACHE;
+    const int* table = p.block_tables + (size_t)seq * p.max_blocks;
+
+    if (tid == 0) {
+        abort_flag = 0;
+        mbar_init(bar_q, 1);
+        mbar_init(bar_k, 1);
+        mbar_init(bar_v0, 1); mbar_init(bar_v0 + 8, 1);
+        mbar_init(bar_vfree0, 1); mbar_init(bar_vfree0 + 8, 1);
+        mbar_init(bar_s_full, 1); mbar_init(bar_s_free, 128);
+        mbar_init(bar_p_full, 128); mbar_init(bar_o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    if (table_cached)
+        for (int i = tid; i < blk_hi - blk_lo; i += NUM_THREADS) s_table[i] = table[blk_lo + i];
+    // value tiles start as zeros: a page that is not loaded (beyond the context, or given back by
+    // a window) must not meet a probability of zero with a NaN
+    for (int i = tid; i < 2 * KV_BYTES / 16; i += NUM_THREADS) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+    fence_async_smem();
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int box_keys = p.page_size < KV_TILE ? p.page_size : KV_TILE;     // keys one TMA box brings
+    const int boxes = KV_TILE / box_keys;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ control thread: TMA + MMA
+        if (lane == 0) {
+            auto page_of = [&](int key) { const int b = key >> p.page_shift; return table_cached ? s_table[b - blk_lo] : table[b]; };
+            // one TMA box per (page, half of hd); which = 0 loads keys into the single key buffer,
+            // which = 1 loads values into value stage `stage`
+            auto load_tile = [&](int t, int which, int stage) {
+                const uint32_t bar = which == 0 ? bar_k : bar_v0 + 8 * stage;
+                const uint32_t dst0 = which == 0 ? smem_u32(k_s) : smem_u32(v_s) + (uint32_t)stage * KV_BYTES;
+                int n_boxes = 0;
+                for (int i = 0; i < boxes; ++i) {
+                    const int key = t * KV_TILE + i * box_keys;
+                    if (key >= key_hi) break;
+                    if (key + box_keys <= key_lo) continue;
+                    if (page_of(key) >= 0) ++n_boxes;
+                }
+                mbar_expect_tx(bar, (uint32_t)n_boxes * HALVES * (uint32_t)box_keys * 128u);
+                for (int i = 0; i < boxes; ++i) {
+                    const int key = t * KV_TILE + i * box_keys;
+                    if (key >= key_hi) break;
+                    if (key + box_keys <= key_lo) continue;
+                    const int page = page_of(key);
+                    if (page < 0) continue;
+                    const int row = ((page * 2 + which) * p.nkv + kvh) * p.page_size + (key & (p.page_size - 1));
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h)
+                        tma_load_2d(dst0 + (uint32_t)h * (KV_TILE * 128) + (uint32_t)i * box_keys * 128, &map_kv, h * 64, row, bar);
+                }
+            };
+            // Q: one box of [64 hd, G heads, 128 / G tokens] per half of the head dimension
+            mbar_expect_tx(bar_q, Q_BYTES);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)
+                tma_load_3d(smem_u32(q_s) + h * (ROWS * 128), &map_q, h * 64, kvh * G, q_start + row0 / G, bar_q);
+            load_tile(t_begin, 0, 0);
+            load_tile(t_begin, 1, 0);
+
+            const uint32_t idesc_s = umma_idesc_bf16(ROWS, KV_TILE);
+            const uint32_t idesc_o = umma_idesc_bf16(ROWS, HEAD_DIM) | (1u << 16);       // B is MN-major
+            bool ok = mbar_wait(bar_q, 0, &abort_flag, 1);
+            for (int t = t_begin; t < t_end && ok; ++t) {
+                const int it = t - t_begin, stage = it & 1;
+                if (!mbar_wait(bar_k, it & 1, &abort_flag, 2)) { ok = false; break; }
+                if (it >= 1 && !mbar_wait(bar_s_free, (it - 1) & 1, &abort_flag, 3)) { ok = false; break; }
+                tcgen05_fence_after();
+                // S = Q K^T over the head dimension
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) {
+                    const uint64_t dq = umma_desc(smem_u32(q_s) + h * (ROWS * 128));
+                    const uint64_t dk = umma_desc(smem_u32(k_s) + h * (KV_TILE * 128));
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        tcgen05_mma_bf16(tmem_base + S_COL, dq + (uint64_t)(2 * j), dk + (uint64_t)(2 * j), idesc_s, (h | j) != 0);
+                }
+                tcgen05_commit(bar_s_full);
+                if (t + 1 < t_end) {
+                    // the key buffer is free once this product has read it; the other value stage once
+                    // the P V product of the tile before has read it
+                    if (!mbar_wait(bar_s_full, it & 1, &abort_flag, 4)) { ok = false; break; }
+                    load_tile(t + 1, 0, 0);
+                    if (it >= 1 && !mbar_wait(bar_vfree0 + 8 * (stage ^ 1), ((it - 1) >> 1) & 1, &abort_flag, 5)) { ok = false; break; }
+                    load_tile(t + 1, 1, stage ^ 1);
+                }
+                if (!mbar_wait(bar_v0 + 8 * stage, (it >> 1) & 1, &abort_flag, 6)) { ok = false; break; }
+                // O += P V once the softmax warps have written P (and rescaled O if they had to)
+                if (!mbar_wait(bar_p_full, it & 1, &abort_flag, 7)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint64_t dp = umma_desc(smem_u32(p_s));
+                const uint64_t dv = umma_desc_mn(smem_u32(v_s) + stage * KV_BYTES, KV_TILE * 128);
+#pragma unroll
+                for (int j = 0; j < KV_TILE / 16; ++j)       // 16 keys per MMA: 32 bytes along P's rows, 2048 bytes down V
+                    tcgen05_mma_bf16(tmem_base + O_COL, dp + (uint64_t)(2 * j), dv + (uint64_t)(128 * j), idesc_o, (it | j) != 0);
+                tcgen05_commit(bar_vfree0 + 8 * stage);
+                tcgen05_commit(bar_o_full);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax warps: one thread per row
+        const int r = row0 + warp * 32 + lane;               // packed row; TMEM lane = warp * 32 + lane
+        const bool in_range = r < rows_total;
+        const int tok_i = in_range ? r / G : 0;
+        const int head = kvh * G + (in_range ? r - tok_i * G : 0);
+        const int pos = in_range ? ctx - q_len + tok_i : -1;
+        const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+        const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
+        float m_ref = -INFINITY, l_run = 0.f;
+        const int row_local = warp * 32 + lane;
+        unsigned char* p_row0 = p_s + (row_local >> 3) * 1024 + (row_local & 7) * 128;
+        bool ok = true;
+        for (int t = t_begin; t < t_end; ++t) {
+            const int it = t - t_begin;
+            if (!mbar_wait(bar_s_full, it & 1, &abort_flag, 9)) { ok = false; break; }
+            tcgen05_fence_after();
+            uint32_t s0[32], s1[32];
+            tmem_ld_32x32(t_lane + S_COL, s0);
+            tmem_ld_32x32(t_lane + S_COL + 32, s1);
+            tmem_ld_wait();
+            tcgen05_fence_before();
+            mbar_arrive(bar_s_free);                          // S may be overwritten by the next tile's product
+            const int key0 = t * KV_TILE;
+            float m_tile = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                const int ka = key0 + e, kb = key0 + 32 + e;
+                const float a = (ka <= pos && ka >= lo) ? __uint_as_float(s0[e]) * p.scale_log2e : -INFINITY;
+                const float b = (kb <= pos && kb >= lo) ? __uint_as_float(s1[e]) * p.scale_log2e : -INFINITY;
+                s0[e] = __float_as_uint(a); s1[e] = __float_as_uint(b);
+                m_tile = fmaxf(m_tile, fmaxf(a, b));
+            }
+            // raise the reference maximum only when it is far behind: O then needs a pass
+            const bool first_data = m_ref == -INFINITY && m_tile > -INFINITY;
+            const bool raise = first_data || m_tile > m_ref + RESCALE_LOG2;
+            float factor = 1.f;
+            if (raise) {
+                factor = m_ref == -INFINITY ? 0.f : exp2f(m_ref - m_tile);
+                m_ref = m_tile;
+                l_run *= factor;
+            }
+            const bool any_raise = __any_sync(0xffffffffu, raise && it > 0);
+            if (any_raise) {
+                // O was last written by the P V product of the tile before: wait for it, then scale
+                if (!mbar_wait(bar_o_full, (it - 1) & 1, &abort_flag, 7)) { ok = false; break; }
+                tcgen05_fence_after();
+#pragma unroll
+                for (int c = 0; c < HEAD_DIM; c += 32) {
+                    uint32_t o[32];
+                    tmem_ld_32x32(t_lane + O_COL + c, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
+                    tmem_st_32x32(t_lane + O_COL + c, o);
+                }
+                tmem_st_wait();
+                tcgen05_fence_before();
+            }
+            const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
+            // P has one buffer: the product that read it for the tile before is complete, because this
+            // tile's S (observed above) was committed after it by the same issuing thread
+            unsigned char* p_row = p_row0;
+            float l_tile = 0.f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {                    // 8 chunks of 8 keys = 16 bytes
+                uint4 v;
+                uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int e = c * 8 + 2 * j;
+                    const float x0 = exp2f(__uint_as_float(e < 32 ? s0[e] : s1[e - 32]) - m_safe);
+                    const float x1 = exp2f(__uint_as_float(e + 1 < 32 ? s0[e + 1] : s1[e + 1 - 32]) - m_safe);
+                    l_tile += x0 + x1;
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(x0, x1);
+                    w[j] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (row_local & 7)) << 4)) = v;
+            }
+            l_run += l_tile;
+            fence_async_smem();
+            tcgen05_fence_before();
+            mbar_arrive(bar_p_full);
+        }
+        if (ok) {
+            const int n_it = t_end - t_begin;
+            ok = mbar_wait(bar_o_full, (n_it - 1) & 1, &abort_flag, 10);
+            tcgen05_fence_after();
+            if (ok) {
+                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+                __nv_bfloat16* dst = p.out + ((size_t)(q_start + tok_i) * p.nh + head) * HEAD_DIM;
+#pragma unroll
+                for (int c = 0; c < HEAD_DIM; c += 32) {
+                    uint32_t o[32];
+                    tmem_ld_32x32(t_lane + O_COL + c, o);
+                    tmem_ld_wait();
+                    if (in_range) {
+#pragma unroll
+                        for (int v4 = 0; v4 < 4; ++v4) {
+                            uint4 v;
+                            uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[v4 * 8 + 2 * j]) * inv,
+                                                                          __uint_as_float(o[v4 * 8 + 2 * j + 1]) * inv);
+                                w[j] = *reinterpret_cast<uint32_t*>(&h2);
+                            }
+                            *reinterpret_cast<uint4*>(dst + c + v4 * 8) = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+    }
+    if (tid == 0 && abort_flag != 0 && p.status) atomicCAS(p.status, 0, abort_flag);
+}
+
+// ---------------------------------------------------------------- host side
+static int make_q_map(CUtensorMap* map, const void* q, int n_tokens, int nh, int G) {
+    RvEncodeTiledFn fn = rv_encode_fn();
+    if (!fn) return RV_ERR_UNSUPPORTED;
+    const cuuint64_t dims[3] = {HEAD_DIM, (cuuint64_t)nh, (cuuint64_t)n_tokens};
+    const cuuint64_t strides[2] = {HEAD_DIM * 2, (cuuint64_t)nh * HEAD_DIM * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(ROWS / G)};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? RV_OK : RV_ERR_BAD_SIZE;
+}
+
+RV_EXPORT int rv_attention_tcgen05_head_dim() { return HEAD_DIM; }
+
+// Attention of the sequences that bring more than one token to the step (the others are left to
+// the decode kernel).  Refuses (RV_ERR_UNSUPPORTED) what it is not built for: a head size other
+// than HEAD_DIM, a group size that does not divide 128, pages of fewer than 8 keys.
+RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long num_pages, const int* block_tables,
+                                   const int* cu_seqlens, const int* ctx_lens, void* out, int n_tokens, int num_seqs,
+                                   int nh, int nkv, int hd, int page_size, int max_blocks, float scale, int window,
+                                   int max_q_len, int* status, cudaStream_t stream) {
+    if (hd != HEAD_DIM) return RV_ERR_UNSUPPORTED;
+    if (n_tokens < 0 || num_seqs < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_blocks <= 0 || max_q_len <= 0)
+        return RV_ERR_BAD_SIZE;
+    const int G = nh / nkv;
+    if (G > ROWS || ROWS % G) return RV_ERR_UNSUPPORTED;
+    if ((page_size & (page_size - 1)) || page_size < 8) return RV_ERR_UNSUPPORTED;
+    if (num_seqs > 65535 || nkv > 65535) return RV_ERR_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) % 16)
+        return RV_ERR_ALIGNMENT;
+    if (n_tokens == 0 || num_seqs == 0) return RV_OK;
+    alignas(64) CUtensorMap map_q, map_kv;
+    int st = make_q_map(&map_q, q, n_tokens, nh, G);
+    if (st != RV_OK) return st;
+    st = rv_make_bf16_map(&map_kv, cache, num_pages * 2 * nkv * page_size, HEAD_DIM, page_size < KV_TILE ? page_size : KV_TILE);
+    if (st != RV_OK) return st;
+    AttnParams p;
+    p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.ctx_lens = ctx_lens; p.out = (__nv_bfloat16*)out;
+    p.status = status; p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.max_blocks = max_blocks;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.scale_log2e = scale * 1.4426950408889634f;
+    p.window = window;
+    const int smem = Q_BYTES + 3 * KV_BYTES + P_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const dim3 grid((max_q_len * G + ROWS - 1) / ROWS, nkv, num_seqs);
+    RV_LAUNCH_ST = rv_launch(attention_tcgen05_kernel, grid, dim3(NUM_THREADS), smem, stream, map_q, map_kv, p);
+    return rv_launch_status();
+}

@@ -68,6 +68,8 @@ class AttentionMeta:
 class CudaKernels:
     SKINNY_MAX_ROWS = 0     # rows up to which the weight-streaming GEMM replaces the library GEMM (0: off)
     TCGEN05_MIN_ROWS = 128  # rows from which the tcgen05 GEMM of this project is used for bfloat16
+    TCGEN05_ATTENTION = True           # prompt portions go to the tcgen05 attention kernel when it fits
+    TCGEN05_ATTENTION_MIN_TOKENS = 16  # ... from this many tokens in the longest portion of the step
     DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
     DECODE_SPLIT_ROWS = 4   # ... when K has to be split over CTAs, only up to this many rows
     pdl = os.environ.get("RVLLM_NO_PDL") != "1"   # programmatic dependent launch between kernels
@@ -184,6 +186,14 @@ class CudaKernels:
         if q.dtype != torch.bfloat16 or head_dim % 16 or head_dim > 256 or (page & (page - 1)):
             return self.paged_attention_plain(q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window)
         out = torch.empty_like(q)
+        group = num_heads // num_kv_heads
+        if self.TCGEN05_ATTENTION and meta.max_q_len >= self.TCGEN05_ATTENTION_MIN_TOKENS and head_dim in (64, 128) \
+                and 128 % group == 0 and page >= 8:
+            self.attention_tcgen05(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window)
+            if meta.num_decode:
+                self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
+                                     mode=1, q_filter=1, max_q_len=1)
+            return out
         if meta.max_q_len == 1:
             self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
                                  mode=1, num_splits=self.decode_splits(meta, num_heads, num_kv_heads))
@@ -232,6 +242,19 @@ class CudaKernels:
             c_int(head_dim), c_int(cache_layer.shape[3]), c_int(meta.max_blocks), c_float(scale), c_int(window or 0),
             c_int(mode), c_int(max_q_len or meta.max_q_len), c_int(num_splits), c_int(q_filter), self._stream())
         _check("flash_attention", st)
+        return out
+
+    def attention_tcgen05(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, status=None):
+        """The tcgen05 flash-attention kernel for the sequences of a step that bring more than one
+        token (bfloat16, head size 64 or 128, group size dividing 128, pages of at least 8 keys)."""
+        _need(q, "q", torch.bfloat16, 2); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
+        lib = self._lib("attention_tcgen05.cu", (f"-DHEAD_DIM={head_dim}",))
+        st = lib.rv_attention_tcgen05(
+            _ptr(q), _ptr(cache_layer), ctypes.c_longlong(cache_layer.shape[0]), _ptr(meta.block_tables),
+            _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens), _ptr(out), c_int(q.shape[0]), c_int(meta.num_seqs),
+            c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]), c_int(meta.max_blocks),
+            c_float(scale), c_int(window or 0), c_int(meta.max_q_len), _ptr(status), self._stream())
+        _check("attention_tcgen05", st)
         return out
 
     def paged_attention_plain(self, q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window):

@@ -16,6 +16,8 @@ def all_variants() -> List[Tuple[str, Sequence[str]]]:
             # one library per head size; the build check compiles the sizes of the benchmark
             # and test configurations, others are compiled when a model first needs them
             out.extend((src, (f"-DHEAD_DIM={hd}",)) for hd in FLASH_HEAD_DIMS)
+        elif src == "attention_tcgen05.cu":
+            out.extend((src, (f"-DHEAD_DIM={hd}",)) for hd in (64, 128))
         else:
             out.append((src, ()))
     return out
