@@ -32,11 +32,10 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "this kernel is built for head 
 #define Q_BYTES (ROWS * HEAD_DIM * 2)
 #define KV_BYTES (KV_TILE * HEAD_DIM * 2)      // one of K or V for a tile
 #define P_BYTES (ROWS * KV_TILE * 2)
-#define NUM_THREADS 160
+#define NUM_THREADS 192               // 4 softmax warps, 1 loader warp, 1 MMA warp
 #define TMEM_COLS 256
-#define S_COL 0
-#define O_COL 64
-#define TABLE_CACHE 512
+#define S_COL 0                   // two S buffers: columns 0-63 and 64-127
+#define O_COL 128
 #define RESCALE_LOG2 8.0f
 
 struct AttnParams {
@@ -64,6 +63,12 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
                    "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
                  : "memory");
 }
+// 2^x by the special-function unit; -inf gives 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -83,26 +88,27 @@ __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t lb
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                          const AttnParams p) {
+    // All shared memory is dynamic (no static arrays), so that the tiles start on the 1024-byte
+    // boundary the 128-byte swizzle needs without a pad, and two CTAs fit an SM.
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_s = base;                               // [HALVES][128 rows x 128 B]
-    unsigned char* k_s = q_s + Q_BYTES;                      // [HALVES][64 keys x 128 B], one stage
-    unsigned char* v_s = k_s + KV_BYTES;                     // [2 stages][HALVES][64 keys x 128 B]
+    unsigned char* q_s = smem_raw;                           // [HALVES][128 rows x 128 B]
+    unsigned char* k_s = q_s + Q_BYTES;                      // [2 stages][HALVES][64 keys x 128 B]
+    unsigned char* v_s = k_s + 2 * KV_BYTES;                 // [2 stages][HALVES][64 keys x 128 B]
     unsigned char* p_s = v_s + 2 * KV_BYTES;                 // [128 rows x 128 B]
-    __shared__ __align__(8) uint64_t bars[10];
-    __shared__ uint32_t tmem_base_slot;
-    __shared__ volatile int abort_flag;
-    __shared__ int s_table[TABLE_CACHE];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + P_BYTES);       // 13 barriers
+    uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 13);
+    volatile int& abort_flag = *reinterpret_cast<volatile int*>(bars + 14);
 
     rv_pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t bar_q = smem_u32(&bars[0]), bar_k = smem_u32(&bars[1]);
-    const uint32_t bar_v0 = smem_u32(&bars[2]);                                      // v full [2]
-    const uint32_t bar_vfree0 = smem_u32(&bars[4]);                                  // v free [2]
-    const uint32_t bar_s_full = smem_u32(&bars[6]), bar_s_free = smem_u32(&bars[7]);
-    const uint32_t bar_p_full = smem_u32(&bars[8]), bar_o_full = smem_u32(&bars[9]);
+    const uint32_t bar_q = smem_u32(&bars[0]), bar_k0 = smem_u32(&bars[1]);          // k full [2]
+    const uint32_t bar_v0 = smem_u32(&bars[3]);                                      // v full [2]
+    const uint32_t bar_vfree0 = smem_u32(&bars[5]);                                  // v free [2]
+    const uint32_t bar_s_full0 = smem_u32(&bars[7]), bar_s_free0 = smem_u32(&bars[9]);   // [2] each
+    const uint32_t bar_p_full = smem_u32(&bars[11]), bar_o_full = smem_u32(&bars[12]);
 
-    const int seq = blockIdx.z, kvh = blockIdx.y, tile_m = blockIdx.x;
+    // row tiles late in the prompt see the most keys: they are started first
+    const int seq = blockIdx.z, kvh = blockIdx.y, tile_m = gridDim.x - 1 - blockIdx.x;
     const int G = p.nh / p.nkv;
     rv_pdl_wait();
     const int ctx = p.ctx_lens[seq];
@@ -117,27 +123,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int key_lo = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
     const int key_hi = pos_last + 1;
     const int t_begin = key_lo / KV_TILE, t_end = (key_hi + KV_TILE - 1) / KV_TILE;
-    const int blk_lo = (t_begin * KV_TILE) >> p.page_shift;
-    const int blk_hi = ((key_hi - 1) >> p.page_shift) + 1;
-    const bool table_cached = blk_hi - blk_lo <= TABLE_CACHE;
     const int* table = p.block_tables + (size_t)seq * p.max_blocks;
 
     if (tid == 0) {
         abort_flag = 0;
         mbar_init(bar_q, 1);
-        mbar_init(bar_k, 1);
+        mbar_init(bar_k0, 1); mbar_init(bar_k0 + 8, 1);
         mbar_init(bar_v0, 1); mbar_init(bar_v0 + 8, 1);
         mbar_init(bar_vfree0, 1); mbar_init(bar_vfree0 + 8, 1);
-        mbar_init(bar_s_full, 1); mbar_init(bar_s_free, 128);
-        mbar_init(bar_p_full, 128); mbar_init(bar_o_full, 1);
+        mbar_init(bar_s_full0, 1); mbar_init(bar_s_full0 + 8, 1);
+        // the softmax warps arrive once per warp (after a warp barrier), not once per thread
+        mbar_init(bar_s_free0, 4); mbar_init(bar_s_free0 + 8, 4);
+        mbar_init(bar_p_full, 4); mbar_init(bar_o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
-    if (table_cached)
-        for (int i = tid; i < blk_hi - blk_lo; i += NUM_THREADS) s_table[i] = table[blk_lo + i];
     // value tiles start as zeros: a page that is not loaded (beyond the context, or given back by
     // a window) must not meet a probability of zero with a NaN
     for (int i = tid; i < 2 * KV_BYTES / 16; i += NUM_THREADS) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
@@ -150,79 +153,94 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int box_keys = p.page_size < KV_TILE ? p.page_size : KV_TILE;     // keys one TMA box brings
     const int boxes = KV_TILE / box_keys;
 
+    const int n_it = t_end - t_begin;
     if (warp == 4) {
-        // ------------------------------------------------------------ control thread: TMA + MMA
-        if (lane == 0) {
-            auto page_of = [&](int key) { const int b = key >> p.page_shift; return table_cached ? s_table[b - blk_lo] : table[b]; };
-            // one TMA box per (page, half of hd); which = 0 loads keys into the single key buffer,
-            // which = 1 loads values into value stage `stage`
-            auto load_tile = [&](int t, int which, int stage) {
-                const uint32_t bar = which == 0 ? bar_k : bar_v0 + 8 * stage;
-                const uint32_t dst0 = which == 0 ? smem_u32(k_s) : smem_u32(v_s) + (uint32_t)stage * KV_BYTES;
-                int n_boxes = 0;
-                for (int i = 0; i < boxes; ++i) {
-                    const int key = t * KV_TILE + i * box_keys;
-                    if (key >= key_hi) break;
-                    if (key + box_keys <= key_lo) continue;
-                    if (page_of(key) >= 0) ++n_boxes;
-                }
-                mbar_expect_tx(bar, (uint32_t)n_boxes * HALVES * (uint32_t)box_keys * 128u);
-                for (int i = 0; i < boxes; ++i) {
-                    const int key = t * KV_TILE + i * box_keys;
-                    if (key >= key_hi) break;
-                    if (key + box_keys <= key_lo) continue;
-                    const int page = page_of(key);
-                    if (page < 0) continue;
-                    const int row = ((page * 2 + which) * p.nkv + kvh) * p.page_size + (key & (p.page_size - 1));
+        // ------------------------------------------------------------ loader warp: TMA
+        // Lane 0 waits on barriers (the result is broadcast); the lanes share the TMA boxes of a tile,
+        // one (page, both halves of hd) each.  Keys of tile it + 2 follow the product that read the
+        // buffer (tile it); values of tile it + 1 follow the P V product of tile it - 1.
+        auto wait_all = [&](uint32_t bar, uint32_t parity, int code) -> bool {
+            int ok_l = 1;
+            if (lane == 0) ok_l = mbar_wait(bar, parity, &abort_flag, code) ? 1 : 0;
+            return __shfl_sync(0xffffffffu, ok_l, 0) != 0;
+        };
+        auto load_tile = [&](int t, int which, int stage) {
+            const uint32_t bar = (which == 0 ? bar_k0 : bar_v0) + 8 * stage;
+            const uint32_t dst0 = smem_u32(which == 0 ? k_s : v_s) + (uint32_t)stage * KV_BYTES;
+            const int key = t * KV_TILE + lane * box_keys;
+            int page = -1;
+            if (lane < boxes && key < key_hi && key + box_keys > key_lo) page = __ldg(table + (key >> p.page_shift));
+            const unsigned mask = __ballot_sync(0xffffffffu, page >= 0);
+            if (lane == 0) mbar_expect_tx(bar, (uint32_t)__popc(mask) * HALVES * (uint32_t)box_keys * 128u);
+            __syncwarp();
+            if (page >= 0) {
+                const int row = ((page * 2 + which) * p.nkv + kvh) * p.page_size + (key & (p.page_size - 1));
 #pragma unroll
-                    for (int h = 0; h < HALVES; ++h)
-                        tma_load_2d(dst0 + (uint32_t)h * (KV_TILE * 128) + (uint32_t)i * box_keys * 128, &map_kv, h * 64, row, bar);
-                }
-            };
-            // Q: one box of [64 hd, G heads, 128 / G tokens] per half of the head dimension
+                for (int h = 0; h < HALVES; ++h)
+                    tma_load_2d(dst0 + (uint32_t)h * (KV_TILE * 128) + (uint32_t)lane * box_keys * 128, &map_kv, h * 64, row, bar);
+            }
+            __syncwarp();
+        };
+        // Q: one box of [64 hd, G heads, 128 / G tokens] per half of the head dimension
+        if (lane == 0) {
             mbar_expect_tx(bar_q, Q_BYTES);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
                 tma_load_3d(smem_u32(q_s) + h * (ROWS * 128), &map_q, h * 64, kvh * G, q_start + row0 / G, bar_q);
-            load_tile(t_begin, 0, 0);
-            load_tile(t_begin, 1, 0);
-
+        }
+        load_tile(t_begin, 0, 0);
+        load_tile(t_begin, 1, 0);
+        if (n_it > 1) load_tile(t_begin + 1, 0, 1);
+        for (int it = 0; it < n_it; ++it) {
+            const int t = t_begin + it;
+            if (it + 2 < n_it) {
+                if (!wait_all(bar_s_full0 + 8 * (it & 1), (it >> 1) & 1, 3)) break;
+                load_tile(t + 2, 0, it & 1);
+            }
+            if (it + 1 < n_it) {
+                if (it >= 1 && !wait_all(bar_vfree0 + 8 * ((it + 1) & 1), ((it - 1) >> 1) & 1, 4)) break;
+                load_tile(t + 1, 1, (it + 1) & 1);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA warp: one thread issues
+        if (lane == 0) {
             const uint32_t idesc_s = umma_idesc_bf16(ROWS, KV_TILE);
             const uint32_t idesc_o = umma_idesc_bf16(ROWS, HEAD_DIM) | (1u << 16);       // B is MN-major
-            bool ok = mbar_wait(bar_q, 0, &abort_flag, 1);
-            for (int t = t_begin; t < t_end && ok; ++t) {
-                const int it = t - t_begin, stage = it & 1;
-                if (!mbar_wait(bar_k, it & 1, &abort_flag, 2)) { ok = false; break; }
-                if (it >= 1 && !mbar_wait(bar_s_free, (it - 1) & 1, &abort_flag, 3)) { ok = false; break; }
+            auto mma_s = [&](int buf) {          // S[buf] = Q K[buf]^T over the head dimension
                 tcgen05_fence_after();
-                // S = Q K^T over the head dimension
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) {
                     const uint64_t dq = umma_desc(smem_u32(q_s) + h * (ROWS * 128));
-                    const uint64_t dk = umma_desc(smem_u32(k_s) + h * (KV_TILE * 128));
+                    const uint64_t dk = umma_desc(smem_u32(k_s) + buf * KV_BYTES + h * (KV_TILE * 128));
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        tcgen05_mma_bf16(tmem_base + S_COL, dq + (uint64_t)(2 * j), dk + (uint64_t)(2 * j), idesc_s, (h | j) != 0);
+                        tcgen05_mma_bf16(tmem_base + S_COL + buf * KV_TILE, dq + (uint64_t)(2 * j), dk + (uint64_t)(2 * j),
+                                         idesc_s, (h | j) != 0);
                 }
-                tcgen05_commit(bar_s_full);
-                if (t + 1 < t_end) {
-                    // the key buffer is free once this product has read it; the other value stage once
-                    // the P V product of the tile before has read it
-                    if (!mbar_wait(bar_s_full, it & 1, &abort_flag, 4)) { ok = false; break; }
-                    load_tile(t + 1, 0, 0);
-                    if (it >= 1 && !mbar_wait(bar_vfree0 + 8 * (stage ^ 1), ((it - 1) >> 1) & 1, &abort_flag, 5)) { ok = false; break; }
-                    load_tile(t + 1, 1, stage ^ 1);
+                tcgen05_commit(bar_s_full0 + 8 * buf);
+            };
+            bool ok = mbar_wait(bar_q, 0, &abort_flag, 1) && mbar_wait(bar_k0, 0, &abort_flag, 2);
+            if (ok) mma_s(0);
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int b = it & 1;
+                if (it + 1 < n_it) {
+                    // S(it + 1) is produced while the softmax warps work on S(it); its buffer was read by
+                    // the softmax of tile it - 1
+                    if (!(ok = mbar_wait(bar_k0 + 8 * (b ^ 1), ((it + 1) >> 1) & 1, &abort_flag, 5))) break;
+                    if (it >= 1 && !(ok = mbar_wait(bar_s_free0 + 8 * (b ^ 1), (((it + 1) >> 1) - 1) & 1, &abort_flag, 6))) break;
+                    mma_s(b ^ 1);
                 }
-                if (!mbar_wait(bar_v0 + 8 * stage, (it >> 1) & 1, &abort_flag, 6)) { ok = false; break; }
+                if (!(ok = mbar_wait(bar_v0 + 8 * b, (it >> 1) & 1, &abort_flag, 7))) break;
                 // O += P V once the softmax warps have written P (and rescaled O if they had to)
-                if (!mbar_wait(bar_p_full, it & 1, &abort_flag, 7)) { ok = false; break; }
+                if (!(ok = mbar_wait(bar_p_full, it & 1, &abort_flag, 8))) break;
                 tcgen05_fence_after();
                 const uint64_t dp = umma_desc(smem_u32(p_s));
-                const uint64_t dv = umma_desc_mn(smem_u32(v_s) + stage * KV_BYTES, KV_TILE * 128);
+                const uint64_t dv = umma_desc_mn(smem_u32(v_s) + b * KV_BYTES, KV_TILE * 128);
 #pragma unroll
-                for (int j = 0; j < KV_TILE / 16; ++j)       // 16 keys per MMA: 32 bytes along P's rows, 2048 bytes down V
+                for (int j = 0; j < KV_TILE / 16; ++j)   // 16 keys per MMA: 32 bytes along P's rows, 2048 bytes down V
                     tcgen05_mma_bf16(tmem_base + O_COL, dp + (uint64_t)(2 * j), dv + (uint64_t)(128 * j), idesc_o, (it | j) != 0);
-                tcgen05_commit(bar_vfree0 + 8 * stage);
+                tcgen05_commit(bar_vfree0 + 8 * b);
                 tcgen05_commit(bar_o_full);
             }
         }
@@ -241,37 +259,61 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         bool ok = true;
         for (int t = t_begin; t < t_end; ++t) {
             const int it = t - t_begin;
-            if (!mbar_wait(bar_s_full, it & 1, &abort_flag, 9)) { ok = false; break; }
+            const int sb = it & 1;
+#ifdef ATTN_TRACE
+            const bool tr = p.status && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0 && it < 24;
+            if (tr) p.status[8 + it * 5 + 0] = (int)clock64();
+#endif
+            if (!mbar_wait(bar_s_full0 + 8 * sb, (it >> 1) & 1, &abort_flag, 9)) { ok = false; break; }
+#ifdef ATTN_TRACE
+            if (tr) p.status[8 + it * 5 + 1] = (int)clock64();
+#endif
             tcgen05_fence_after();
             uint32_t s0[32], s1[32];
-            tmem_ld_32x32(t_lane + S_COL, s0);
-            tmem_ld_32x32(t_lane + S_COL + 32, s1);
+            tmem_ld_32x32(t_lane + S_COL + sb * KV_TILE, s0);
+            tmem_ld_32x32(t_lane + S_COL + sb * KV_TILE + 32, s1);
             tmem_ld_wait();
             tcgen05_fence_before();
-            mbar_arrive(bar_s_free);                          // S may be overwritten by the next tile's product
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_s_free0 + 8 * sb);   // this S buffer may be overwritten two tiles on
             const int key0 = t * KV_TILE;
-            float m_tile = -INFINITY;
+            // Scores stay raw in the registers; scale and reference maximum are applied in one FMA
+            // before the exponential.  Only tiles that cross the row's visible range need masks.
+            float m_raw = -INFINITY;
+            if (key0 + KV_TILE - 1 <= pos && key0 >= lo) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-                const int ka = key0 + e, kb = key0 + 32 + e;
-                const float a = (ka <= pos && ka >= lo) ? __uint_as_float(s0[e]) * p.scale_log2e : -INFINITY;
-                const float b = (kb <= pos && kb >= lo) ? __uint_as_float(s1[e]) * p.scale_log2e : -INFINITY;
-                s0[e] = __float_as_uint(a); s1[e] = __float_as_uint(b);
-                m_tile = fmaxf(m_tile, fmaxf(a, b));
+                for (int e = 0; e < 32; ++e)
+                    m_raw = fmaxf(m_raw, fmaxf(__uint_as_float(s0[e]), __uint_as_float(s1[e])));
+            } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const int ka = key0 + e, kb = key0 + 32 + e;
+                    if (!(ka <= pos && ka >= lo)) s0[e] = 0xff800000u;        // -inf
+                    if (!(kb <= pos && kb >= lo)) s1[e] = 0xff800000u;
+                    m_raw = fmaxf(m_raw, fmaxf(__uint_as_float(s0[e]), __uint_as_float(s1[e])));
+                }
             }
+            const float m_tile = m_raw * p.scale_log2e;       // the scale is positive: the maximum commutes
             // raise the reference maximum only when it is far behind: O then needs a pass
             const bool first_data = m_ref == -INFINITY && m_tile > -INFINITY;
             const bool raise = first_data || m_tile > m_ref + RESCALE_LOG2;
             float factor = 1.f;
             if (raise) {
-                factor = m_ref == -INFINITY ? 0.f : exp2f(m_ref - m_tile);
+                factor = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - m_tile);
                 m_ref = m_tile;
                 l_run *= factor;
             }
+            // The P V product of the tile before must be complete before P is overwritten (S of this
+            // tile was produced ahead of it) and before O is rescaled.
+#ifdef ATTN_TRACE
+            if (tr) p.status[8 + it * 5 + 2] = (int)clock64();
+#endif
+            if (it > 0 && !mbar_wait(bar_o_full, (it - 1) & 1, &abort_flag, 11)) { ok = false; break; }
+#ifdef ATTN_TRACE
+            if (tr) p.status[8 + it * 5 + 3] = (int)clock64();
+#endif
             const bool any_raise = __any_sync(0xffffffffu, raise && it > 0);
             if (any_raise) {
-                // O was last written by the P V product of the tile before: wait for it, then scale
-                if (!mbar_wait(bar_o_full, (it - 1) & 1, &abort_flag, 7)) { ok = false; break; }
                 tcgen05_fence_after();
 #pragma unroll
                 for (int c = 0; c < HEAD_DIM; c += 32) {
@@ -285,11 +327,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tmem_st_wait();
                 tcgen05_fence_before();
             }
-            const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
-            // P has one buffer: the product that read it for the tile before is complete, because this
-            // tile's S (observed above) was committed after it by the same issuing thread
+            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
             unsigned char* p_row = p_row0;
-            float l_tile = 0.f;
+            float l_tile = 0.f, l_tile2 = 0.f;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {                    // 8 chunks of 8 keys = 16 bytes
                 uint4 v;
@@ -297,21 +337,26 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int e = c * 8 + 2 * j;
-                    const float x0 = exp2f(__uint_as_float(e < 32 ? s0[e] : s1[e - 32]) - m_safe);
-                    const float x1 = exp2f(__uint_as_float(e + 1 < 32 ? s0[e + 1] : s1[e + 1 - 32]) - m_safe);
-                    l_tile += x0 + x1;
+                    const float x0 = fast_exp2(fmaf(__uint_as_float(e < 32 ? s0[e] : s1[e - 32]), p.scale_log2e, neg_m));
+                    const float x1 = fast_exp2(fmaf(__uint_as_float(e + 1 < 32 ? s0[e + 1] : s1[e + 1 - 32]), p.scale_log2e, neg_m));
+                    l_tile += x0;
+                    l_tile2 += x1;
                     __nv_bfloat162 h2 = __floats2bfloat162_rn(x0, x1);
                     w[j] = *reinterpret_cast<uint32_t*>(&h2);
                 }
                 *reinterpret_cast<uint4*>(p_row + ((c ^ (row_local & 7)) << 4)) = v;
             }
+            l_tile += l_tile2;
             l_run += l_tile;
             fence_async_smem();
             tcgen05_fence_before();
-            mbar_arrive(bar_p_full);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_p_full);
+#ifdef ATTN_TRACE
+            if (tr) p.status[8 + it * 5 + 4] = (int)clock64();
+#endif
         }
         if (ok) {
-            const int n_it = t_end - t_begin;
             ok = mbar_wait(bar_o_full, (n_it - 1) & 1, &abort_flag, 10);
             tcgen05_fence_after();
             if (ok) {
@@ -394,7 +439,7 @@ RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long n
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.window = window;
-    const int smem = Q_BYTES + 3 * KV_BYTES + P_BYTES + 1024;
+    const int smem = Q_BYTES + 4 * KV_BYTES + P_BYTES + 256;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

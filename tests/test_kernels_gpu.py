@@ -311,3 +311,36 @@ def test_gemm_tcgen05_decode_bf16(K, M, N, Kd):
     assert torch.equal(one, K.linear_decode(x, w, out_dtype=torch.float32, splits=4)[:1])     # batch-invariant
     if K._decode_counters is not None:
         assert int(K._decode_counters.abs().sum().item()) == 0
+
+
+TC_ATT_CASES = [
+    # nh, nkv, hd, page, q_lens, ctx_lens, window
+    (4, 1, 128, 16, [32], [32], None),
+    (8, 2, 128, 16, [200], [500], None),
+    (8, 2, 64, 8, [70, 1, 33], [70, 9, 129], 40),
+    (2, 2, 64, 32, [300], [300], None),
+    (16, 1, 128, 64, [40, 50], [300, 50], 100),
+    (32, 8, 128, 16, [333, 1, 64], [777, 100, 64], None),
+    (8, 8, 128, 128, [17], [400], 256),
+]
+
+
+@pytest.mark.parametrize("case", TC_ATT_CASES)
+def test_attention_tcgen05_kernel(K, case):
+    """The tcgen05 attention kernel for prompt portions (sequences of one token are left alone),
+    through the product path's dispatch and directly, with its status word."""
+    nh, nkv, hd, page, q_lens, ctx_lens, window = case
+    ks, vs, qs = _attention_case(nh, nkv, hd, page, q_lens, ctx_lens, window, 11)
+    cache, meta = paged_setup(ks, vs, q_lens, page, torch.bfloat16)
+    q = torch.cat(qs).reshape(sum(q_lens), nh * hd).cuda().bfloat16()
+    scale = 1 / math.sqrt(hd)
+    ref = _attention_ref(ks, vs, qs, ctx_lens, q_lens, scale, window, torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.zeros_like(q)
+    K.attention_tcgen05(q, cache, meta, out, nh, nkv, hd, scale, window, status=status)
+    rows = torch.cat([torch.full((n,), n > 1) for n in q_lens])
+    assert rel_err(out.view(-1, nh, hd)[rows.cuda()], ref[rows]) < BF16_TOL
+    assert float(out.view(-1, nh, hd)[(~rows).cuda()].abs().sum()) == 0.0        # one-token sequences untouched
+    assert int(status.item()) == 0, "a bounded wait inside the kernel gave up"
+    full = K.paged_attention(q, cache, meta, nh, nkv, hd, scale, window)          # with the decode kernel for the rest
+    assert rel_err(full.view(-1, nh, hd), ref) < BF16_TOL
