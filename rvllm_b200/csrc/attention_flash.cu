@@ -24,6 +24,9 @@
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head_dim must be a multiple of 16 up to 256");
 
 #define KV_TILE 64
+#ifndef DECODE_STAGES
+#define DECODE_STAGES 2     // cp.async stages of the decode tiling (more stages measured slower: fewer CTAs fit an SM)
+#endif
 #define TABLE_CACHE 1024   // block-table entries of a CTA's key range kept in shared memory
 // a row of the shared-memory tiles is padded by 16 bytes: the stride is an odd multiple of
 // 16 bytes, so the 8 rows an ldmatrix reads fall into different banks
@@ -75,7 +78,7 @@ struct FlashParams {
     int q_filter;                  // 0: every sequence, 1: only q_len == 1, 2: only q_len > 1
 };
 
-template <int WARPS_M, int WARPS_N>
+template <int WARPS_M, int WARPS_N, int NSTAGES>
 __global__ void __launch_bounds__(WARPS_M * WARPS_N * 32)
 flash_paged_kernel(const FlashParams p) {
     rv_pdl_launch_dependents();
@@ -178,13 +181,17 @@ flash_paged_kernel(const FlashParams p) {
         }
     };
 
-    if (t_begin < t_end) load_tile(t_begin, 0);
-    cp_async_commit();
+    // NSTAGES - 1 tiles are requested ahead of the one being used
+#pragma unroll
+    for (int i = 0; i < NSTAGES - 1; ++i) {
+        if (t_begin + i < t_end) load_tile(t_begin + i, i);
+        cp_async_commit();
+    }
     int stage = 0;
     for (int t = t_begin; t < t_end; ++t) {
-        if (t + 1 < t_end) load_tile(t + 1, stage ^ 1);
+        if (t + NSTAGES - 1 < t_end) load_tile(t + NSTAGES - 1, (stage + NSTAGES - 1) % NSTAGES);
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<NSTAGES - 1>();
         __syncthreads();
         const unsigned char* ks = smem + (size_t)stage * 2 * TILE_BYTES;
         const unsigned char* vs = ks + TILE_BYTES;
@@ -266,7 +273,7 @@ flash_paged_kernel(const FlashParams p) {
             }
         }
         __syncthreads();
-        stage ^= 1;
+        stage = (stage + 1) % NSTAGES;
     }
     cp_async_wait<0>();
 
@@ -366,19 +373,19 @@ __global__ void flash_combine_kernel(const float* __restrict__ part_o, const flo
     }
 }
 
-template <int WARPS_M, int WARPS_N>
+template <int WARPS_M, int WARPS_N, int NSTAGES>
 static int launch_flash(const FlashParams& p, int num_seqs, cudaStream_t stream) {
     const int merge_bytes = WARPS_N > 1 ? WARPS_N * 16 * (HEAD_DIM + 2) * 4 : 0;
-    const int smem = max(4 * TILE_BYTES, merge_bytes);
+    const int smem = max(NSTAGES * 2 * TILE_BYTES, merge_bytes);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(flash_paged_kernel<WARPS_M, WARPS_N>,
+        cudaError_t e = cudaFuncSetAttribute(flash_paged_kernel<WARPS_M, WARPS_N, NSTAGES>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const dim3 grid(p.row_tiles * p.num_splits, p.nkv, num_seqs);
-    RV_LAUNCH_ST = rv_launch(flash_paged_kernel<WARPS_M, WARPS_N>, dim3(grid), dim3(WARPS_M * WARPS_N * 32), smem, stream, p);
+    RV_LAUNCH_ST = rv_launch(flash_paged_kernel<WARPS_M, WARPS_N, NSTAGES>, dim3(grid), dim3(WARPS_M * WARPS_N * 32), smem, stream, p);
     return rv_launch_status();
 }
 
@@ -420,7 +427,7 @@ RV_EXPORT int rv_flash_attention(const void* q, const void* cache, const int* bl
     const int G = nh / nkv;
     const int m_tile = mode == 1 ? 16 : 64;
     p.row_tiles = (max_q_len * G + m_tile - 1) / m_tile;
-    int st = mode == 1 ? launch_flash<1, 4>(p, num_seqs, stream) : launch_flash<4, 1>(p, num_seqs, stream);
+    int st = mode == 1 ? launch_flash<1, 4, DECODE_STAGES>(p, num_seqs, stream) : launch_flash<4, 1, 2>(p, num_seqs, stream);
     if (st != RV_OK) return st;
     if (num_splits > 1) {
         RV_LAUNCH_ST = rv_launch(flash_combine_kernel, dim3(n_tokens * nh), dim3(HEAD_DIM >= 128 ? 128 : 64), 0, stream,
