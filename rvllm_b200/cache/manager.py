@@ -73,6 +73,7 @@ class CacheManager:
             elif need is not None:
                 raise SchedulerError(f"cache slot {slot}: unknown kind of need {need!r}")
         self.slots = SlotPool(max_seqs)
+        self._has_window = any(g.need.window is not None for g in self.groups)
         self.requests: Dict[Hashable, _Request] = {}
         if allocate:
             for g in self.groups:
@@ -134,12 +135,15 @@ class CacheManager:
         """Reserve room for `n_new` more tokens; returns the position of the first.  Takes every
         page it needs or none (`KvExhausted`)."""
         r = self.requests[req]
-        need = self.pages_needed(req, n_new)
-        for n, g in zip(need, self.groups):
-            if n > g.pool.num_free:
-                raise KvExhausted(n, g.pool.num_free, f"request {req!r}")
-        for n, g, table in zip(need, self.groups, r.tables):
-            table.extend(g.pool.allocate(n, req))
+        blocks = (r.num_tokens + n_new + self.page_size - 1) // self.page_size
+        need = [blocks - len(t) for t in r.tables]
+        if any(need):
+            for n, g in zip(need, self.groups):
+                if n > g.pool.num_free:
+                    raise KvExhausted(n, g.pool.num_free, f"request {req!r}")
+            for n, g, table in zip(need, self.groups, r.tables):
+                if n > 0:
+                    table.extend(g.pool.allocate(n, req))
         start = r.num_tokens
         r.num_tokens += n_new
         return start
@@ -163,6 +167,8 @@ class CacheManager:
         sits at position >= num_tokens and sees keys > position - window."""
         r = self.requests[req]
         freed = 0
+        if not self._has_window:
+            return 0
         for gi, g in enumerate(self.groups):
             w = g.need.window
             if w is None:

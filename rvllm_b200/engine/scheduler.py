@@ -35,7 +35,7 @@ from ..sampling.params import SamplingParams
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 
 
-@dataclass
+@dataclass(eq=False)        # requests are compared by identity (field-wise equality would walk the token lists)
 class Request:
     req_id: Hashable
     prompt: List[int]

@@ -85,9 +85,14 @@ class ModelRunner:
             if e.req_id in seen:
                 raise SchedulerError(f"request {e.req_id!r} appears twice in one step")
             seen.add(e.req_id)
-            if len(e.tokens) == 0:
+            n_tok = len(e.tokens)
+            if n_tok == 0:
                 raise SchedulerError(f"request {e.req_id!r} brings no tokens to the step")
-            bad = [t for t in e.tokens if not 0 <= int(t) < vocab]
+            if n_tok == 1:
+                bad = [] if 0 <= e.tokens[0] < vocab else [e.tokens[0]]
+            else:
+                lo, hi = min(e.tokens), max(e.tokens)
+                bad = [] if (0 <= lo and hi < vocab) else [t for t in e.tokens if not 0 <= int(t) < vocab]
             if bad:
                 raise SchedulerError(f"request {e.req_id!r}: token id {bad[0]} is outside the vocabulary of {vocab}")
             have = self.cache.num_tokens(e.req_id) if self.cache.has(e.req_id) else 0
@@ -99,22 +104,27 @@ class ModelRunner:
 
     def reserve(self, entries: Sequence[StepEntry]) -> List[int]:
         """Admit unknown requests and take the pages of the whole batch, or nothing."""
-        total = [0] * len(self.cache.groups)
+        cache = self.cache
+        n_groups = len(cache.groups)
+        total = [0] * n_groups
+        new = 0
         for e in entries:
-            need = self.cache.pages_needed(e.req_id if self.cache.has(e.req_id) else None, len(e.tokens))
-            total = [a + b for a, b in zip(total, need)]
-        free = self.cache.num_free_pages()
-        for need, have in zip(total, free):
-            if need > have:
-                raise KvExhausted(need, have, "the step's tokens do not fit the free pages")
-        new = sum(1 for e in entries if not self.cache.has(e.req_id))
-        if new > self.cache.slots.num_free:
-            raise SchedulerError(f"{new} new requests but only {self.cache.slots.num_free} request slots are free")
+            known = cache.has(e.req_id)
+            new += 0 if known else 1
+            need = cache.pages_needed(e.req_id if known else None, len(e.tokens))
+            for g in range(n_groups):
+                total[g] += need[g]
+        if any(total):
+            for need, have in zip(total, cache.num_free_pages()):
+                if need > have:
+                    raise KvExhausted(need, have, "the step's tokens do not fit the free pages")
+        if new > cache.slots.num_free:
+            raise SchedulerError(f"{new} new requests but only {cache.slots.num_free} request slots are free")
         starts = []
         for e in entries:
-            if not self.cache.has(e.req_id):
-                self.cache.admit(e.req_id)
-            starts.append(self.cache.append(e.req_id, len(e.tokens)))
+            if not cache.has(e.req_id):
+                cache.admit(e.req_id)
+            starts.append(cache.append(e.req_id, len(e.tokens)))
         return starts
 
     def pack(self, entries: Sequence[StepEntry], starts: List[int], pad_to: Optional[int] = None,
