@@ -1,7 +1,8 @@
 #!/usr/bin/env python3
 """Benchmark of the engine on one B200: decode tokens per second, prefill, roofline.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--shape NAME]
+                    [--workload decode|serve] [--impl ours|reference]
 
 The default run has the layer sizes of Llama-3.1-8B (32 layers, hidden 4096, 32 query heads,
 8 key/value heads of 128, MLP 14336, vocabulary 128256, llama3 rotary scaling) with random
@@ -41,9 +42,22 @@ LLAMA31_8B = {
                      "original_max_position_embeddings": 8192},
     "attention_bias": False, "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "bfloat16",
 }
-FULL_LAYERS = 32
-PROMPT_LEN = 2048
-CONTEXT_LEN = 4096
+QWEN25_7B = {
+    "architectures": ["Qwen2ForCausalLM"], "hidden_size": 3584, "num_hidden_layers": 28,
+    "num_attention_heads": 28, "num_key_value_heads": 4, "head_dim": 128, "intermediate_size": 18944,
+    "vocab_size": 152064, "max_position_embeddings": 32768, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "bfloat16", "use_sliding_window": False,
+}
+QWEN25_32B = {
+    "architectures": ["Qwen2ForCausalLM"], "hidden_size": 5120, "num_hidden_layers": 64,
+    "num_attention_heads": 40, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 27648,
+    "vocab_size": 152064, "max_position_embeddings": 32768, "rms_norm_eps": 1e-5, "rope_theta": 1000000.0,
+    "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "bfloat16", "use_sliding_window": False,
+}
+# name -> (config.json keys, prompt length, context length) of the benchmark configurations
+SHAPES = {"llama-3.1-8b": (LLAMA31_8B, 2048, 4096), "qwen2.5-7b": (QWEN25_7B, 2048, 8192),
+          "qwen2.5-32b": (QWEN25_32B, 1024, 4096)}
+PREFILL_TOKENS = 2048
 PUBLISHED_BASELINE = None     # the reference published nothing for this model, precision or hardware
 
 
@@ -134,7 +148,11 @@ def run_ours(args):
     from rvllm_b200.kernels.library import COUNTERS
 
     peaks = measured_peaks()
-    cfg_dict = dict(LLAMA31_8B)
+    shape, PROMPT_LEN, CONTEXT_LEN = SHAPES[args.shape]
+    cfg_dict = dict(shape)
+    full_layers = cfg_dict["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = full_layers
     cfg_dict["num_hidden_layers"] = args.layers
     config = config_from_dict(cfg_dict)
     batches = sorted({1, args.batch, 64}) if not args.no_points else [args.batch]
@@ -155,23 +173,23 @@ def run_ours(args):
         return torch.cuda.Event(enable_timing=True)
 
     # ---- prefill of one 2,048-token prompt --------------------------------------------------------
-    p = prompts_for(1)[0]
+    p = torch.randint(0, V, (PREFILL_TOKENS,), generator=gen).tolist()
     for _ in range(max(1, min(args.warmup, 3))):
-        runner.step([StepEntry("warm", p, [PROMPT_LEN - 1])])
+        runner.step([StepEntry("warm", p, [PREFILL_TOKENS - 1])])
         runner.finish("warm")
     torch.cuda.synchronize()
     times = []
     for _ in range(3):
         a, b = ev(), ev()
         a.record()
-        runner.step([StepEntry("pf", p, [PROMPT_LEN - 1])])
+        runner.step([StepEntry("pf", p, [PREFILL_TOKENS - 1])])
         b.record()
         torch.cuda.synchronize()
         runner.finish("pf")
         times.append(a.elapsed_time(b))
     pf_ms = min(times)
-    pf_flops = prefill_flops(cfg_dict, args.layers, PROMPT_LEN)
-    prefill = {"value": round(PROMPT_LEN / (pf_ms / 1e3), 1), "tokens": PROMPT_LEN, "ms": round(pf_ms, 3),
+    pf_flops = prefill_flops(cfg_dict, args.layers, PREFILL_TOKENS)
+    prefill = {"value": round(PREFILL_TOKENS / (pf_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
                "frac": round(pf_flops / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
 
     # ---- decode: device-timed steps through the step function ----------------------------------------
@@ -205,7 +223,7 @@ def run_ours(args):
 
     # ---- decode end to end through the entry point ------------------------------------------------
     def decode_e2e(b, steps, warmup):
-        sp = SamplingParams(temperature=0.0, max_tokens=warmup + steps + 8, ignore_eos=True)
+        sp = SamplingParams(temperature=0.0, max_tokens=warmup + steps + b + 16, ignore_eos=True)   # prompts enter one per step
         for pr in prompts_for(b):
             llm.add_request(pr, sp)
         while llm.scheduler.waiting or any(r.remaining > 1 for r in llm.scheduler.running):
@@ -236,15 +254,16 @@ def run_ours(args):
     step_bytes = weight_bytes_per_step(cfg_dict, args.layers) + args.batch * ctx * kv_bytes_per_token(cfg_dict, args.layers)
     achieved = step_bytes / (ms / 1e3) / 1e9
     line = {
-        "metric": "decode tokens/s (Llama-3.1-8B layer sizes, bf16, random weights, 2048-token prompts)",
+        "metric": f"decode tokens/s ({args.shape} layer sizes, bf16, random weights, {PROMPT_LEN}-token prompts)",
         "value": round(tps, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None if PUBLISHED_BASELINE is None else round(tps / PUBLISHED_BASELINE, 3),
         "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids",
         "impl": "ours",
-        "config": {"model": "llama-3.1-8b-shape", "layers": args.layers, "layers_full": FULL_LAYERS,
-                   "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 14336,
-                   "vocab": 128256, "global_batch": args.batch, "prompt_len": PROMPT_LEN, "seq_len": CONTEXT_LEN,
+        "config": {"model": f"{args.shape}-shape", "layers": args.layers, "layers_full": full_layers,
+                   "hidden": cfg_dict["hidden_size"], "heads": cfg_dict["num_attention_heads"],
+                   "kv_heads": cfg_dict["num_key_value_heads"], "head_dim": cfg_dict["head_dim"],
+                   "intermediate": cfg_dict["intermediate_size"], "vocab": cfg_dict["vocab_size"], "global_batch": args.batch, "prompt_len": PROMPT_LEN, "seq_len": CONTEXT_LEN,
                    "decode_context": ctx, "block_size": 16, "parallelism": "single-gpu",
                    "l2": "inputs larger than L2: a step streams all weights", "cuda_graph": not args.eager},
         "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -258,13 +277,64 @@ def run_ours(args):
     print(json.dumps(line))
 
 
+def run_serve(args):
+    """Continuous batching through the entry point: --requests prompts of uneven length arrive at once,
+    prompts are cut into portions under a token budget and run beside the decoding requests."""
+    import torch
+
+    from rvllm_b200 import LLM, SamplingParams, config_from_dict
+    from rvllm_b200.kernels.library import COUNTERS
+
+    shape, _, context = SHAPES[args.shape]
+    cfg_dict = dict(shape)
+    full_layers = cfg_dict["num_hidden_layers"]
+    cfg_dict["num_hidden_layers"] = args.layers or full_layers
+    gen = torch.Generator().manual_seed(0)
+    lo, hi = 128, min(4096, context - args.output_len)
+    lengths = torch.randint(lo, hi + 1, (args.requests,), generator=gen).tolist()
+    prompts = [torch.randint(0, cfg_dict["vocab_size"], (n,), generator=gen).tolist() for n in lengths]
+    pages = sum((n + args.output_len + 15) // 16 + 1 for n in lengths)
+    llm = LLM(config=config_from_dict(cfg_dict), random_weights=True, seed=0, dtype="bfloat16", block_size=16,
+              num_blocks=pages + 8, max_model_len=context, max_num_seqs=args.requests,
+              max_num_batched_tokens=args.budget, enforce_eager=args.eager)
+    sp = SamplingParams(temperature=0.0, max_tokens=args.output_len, ignore_eos=True)
+    llm.generate(prompts[:2], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))     # warm-up
+    clocks = ClockSampler()
+    clocks.start()
+    COUNTERS["launches"] = 0
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = llm.generate(prompts, sp)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    ck = clocks.stop()
+    n_out = sum(len(o.outputs[0].token_ids) for o in outs)
+    print(json.dumps({
+        "metric": f"continuous batching, output tokens/s ({args.shape} layer sizes, bf16, random weights)",
+        "value": round(n_out / dt, 1), "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+        "impl": "ours", "data": "synthetic: random weights, uniform random token ids, all requests arrive at once",
+        "seconds": round(dt, 3), "prompt_tokens": sum(lengths), "output_tokens": n_out,
+        "total_tokens_per_s": round((sum(lengths) + n_out) / dt, 1),
+        "preemptions": sum(o.num_preemptions for o in outs), "gpu_launches": COUNTERS["launches"],
+        "config": {"model": f"{args.shape}-shape", "layers": cfg_dict["num_hidden_layers"], "layers_full": full_layers,
+                   "requests": args.requests, "prompt_len": f"uniform {lo}..{hi}", "output_len": args.output_len,
+                   "token_budget": args.budget, "seq_len": context, "block_size": 16, "cuda_graph": not args.eager},
+        "clocks": ck}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both numbers are reported)")
+    ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES), help="layer sizes of the model")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve"],
+                    help="decode: the contract's line; serve: continuous batching of uneven prompts")
+    ap.add_argument("--requests", type=int, default=64, help="serve: number of requests")
+    ap.add_argument("--output-len", type=int, default=256, help="serve: tokens generated per request")
+    ap.add_argument("--budget", type=int, default=2048, help="serve: tokens per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
@@ -278,7 +348,10 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    run_ours(args)
+    if args.workload == "serve":
+        run_serve(args)
+    else:
+        run_ours(args)
     return 0
 
 

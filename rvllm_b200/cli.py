@@ -41,6 +41,8 @@ def _engine_options(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--num-blocks", type=int, default=int(os.environ["RVLLM_NUM_BLOCKS"]) if "RVLLM_NUM_BLOCKS" in os.environ else None)
     ap.add_argument("--enforce-eager", action="store_true", default=os.environ.get("RVLLM_NO_GRAPH") == "1",
                     help="no CUDA graphs for decode steps (also RVLLM_NO_GRAPH=1)")
+    ap.add_argument("--no-async-scheduling", action="store_true", default=os.environ.get("RVLLM_NO_ASYNC") == "1",
+                    help="wait for every step's tokens before the next step is launched (also RVLLM_NO_ASYNC=1)")
     ap.add_argument("--seed", type=int, default=0)
 
 
@@ -51,7 +53,8 @@ def _llm(args, **over):
     kw = dict(dtype=args.dtype, block_size=args.block_size, num_blocks=args.num_blocks,
               gpu_memory_utilization=args.gpu_memory_utilization, max_model_len=args.max_model_len,
               max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
-              max_prefill_chunk=args.max_prefill_chunk, enforce_eager=args.enforce_eager, seed=args.seed)
+              max_prefill_chunk=args.max_prefill_chunk, enforce_eager=args.enforce_eager, seed=args.seed,
+              async_scheduling=not args.no_async_scheduling)
     kw.update(over)
     return LLM(args.model, **kw)
 

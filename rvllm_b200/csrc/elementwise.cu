@@ -47,6 +47,27 @@ RV_EXPORT int rv_gather_rows(const void* table, const int* ids, void* out, int n
     return rv_launch_status();
 }
 
+// ------------------------------------------------------------------ tokens that arrive late
+// A decode step can be launched before the host has read the ids that the previous step sampled:
+// its one-token sequences then take their token from the previous step's output on the device.
+// Sequence i with source[i] >= 0 gets token_ids[cu_seqlens[i]] = sampled[source[i]].
+__global__ void late_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ cu_seqlens,
+                                   const int* __restrict__ source, const int* __restrict__ sampled,
+                                   int n_seqs, int n_sampled) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_seqs) return;
+    const int j = source[i];
+    if (j >= 0 && j < n_sampled) token_ids[cu_seqlens[i]] = sampled[j];
+}
+
+RV_EXPORT int rv_late_tokens(int* token_ids, const int* cu_seqlens, const int* source, const int* sampled,
+                             int n_seqs, int n_sampled, cudaStream_t stream) {
+    if (n_seqs < 0 || n_sampled < 0) return RV_ERR_BAD_SIZE;
+    if (n_seqs == 0) return RV_OK;
+    late_tokens_kernel<<<(n_seqs + 127) / 128, 128, 0, stream>>>(token_ids, cu_seqlens, source, sampled, n_seqs, n_sampled);
+    return rv_launch_status();
+}
+
 // ------------------------------------------------------------------ RMSNorm
 // One block per row.  The row is read twice (the second read hits L1/L2); the sum of squares,
 // the reciprocal root and the product with gamma are formed in float and rounded once.

@@ -18,8 +18,19 @@ from ..config import EngineConfig
 from ..errors import ConfigError
 from ..sampling import Sampler, SamplingParams, request_seed
 from .core import Engine
-from .scheduler import Request, ScheduledBatch, Scheduler
+from .scheduler import PENDING, Request, ScheduledBatch, Scheduler
 from .step import StepEntry
+
+
+@dataclass
+class _Flight:
+    """A step that has been launched: its batch, the row of each sampling request among the sampled
+    ids, the ids on the device, their pinned copy on the host and the event that says it is there."""
+    batch: ScheduledBatch
+    row_of: Dict[Hashable, int]
+    ids: Optional[torch.Tensor] = None
+    host_ids: Optional[torch.Tensor] = None
+    ready: Optional[object] = None
 
 
 @dataclass
@@ -49,7 +60,7 @@ class LLM:
                  num_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.9,
                  max_model_len: Optional[int] = None, max_num_seqs: int = 64, max_num_batched_tokens: int = 2048,
                  max_prefill_chunk: Optional[int] = None, enable_chunked_prefill: bool = True,
-                 enforce_eager: bool = False):
+                 enforce_eager: bool = False, async_scheduling: bool = True):
         ec = EngineConfig(dtype=dtype, block_size=block_size, num_blocks=num_blocks,
                           gpu_memory_utilization=gpu_memory_utilization, max_model_len=max_model_len,
                           max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
@@ -61,6 +72,10 @@ class LLM:
         self.scheduler = self._new_scheduler()
         self.tokenizer = None
         self._next_id = 0
+        self.async_scheduling = async_scheduling
+        self._in_flight: Optional[_Flight] = None
+        self._id_buffers: List[Optional[torch.Tensor]] = [None, None]
+        self._id_next = 0
         if model is not None:
             from ..tokenizer import Tokenizer
             self.tokenizer = Tokenizer.from_model_dir(model, required=False)
@@ -82,21 +97,67 @@ class LLM:
         return req
 
     def step(self) -> List[Request]:
-        """One scheduling decision and one model step; returns the requests that finished."""
+        """One scheduling decision and one model step; returns the requests that finished.
+
+        With `async_scheduling` a pure decode step is followed at once by the launch of the next
+        one, whose tokens are taken from this step's sampled ids on the device; only then does the
+        host wait for these ids.  So the device does not idle while the host schedules and packs.
+        The tokens produced are the same either way; a request that stops on a token while a step
+        ahead of it is running has that step's row ignored."""
+        flight = self._in_flight or self._launch(None)
+        self._in_flight = None
+        if self.async_scheduling and flight.batch.is_decode_only and self.scheduler.can_run_ahead():
+            self._in_flight = self._launch(flight)
+        finished = self._collect(flight)
+        if self._in_flight is not None and all(e.request.state == "finished" for e in self._in_flight.batch.entries):
+            self._in_flight = None            # every request of the step ahead stopped: nothing to read from it
+        return finished
+
+    def _launch(self, previous: Optional["_Flight"]) -> "_Flight":
+        """Schedule, run and sample one step without waiting for the device."""
         batch = self.scheduler.schedule()
-        entries = []
+        entries, late = [], []
+        source = previous.row_of if previous is not None else {}
         for e in batch.entries:
-            toks = e.request.tokens(e.start, e.num_tokens)
-            entries.append(StepEntry(e.request.req_id, toks, (e.num_tokens - 1,) if e.samples else ()))
-        logits = self.engine.runner.step(entries)
-        sampled: Dict[Hashable, int] = {}
+            req = e.request
+            toks = req.tokens(e.start, e.num_tokens)
+            if toks[-1] == PENDING:           # sampled by the previous step, not read yet
+                late.append(source[req.req_id])
+                toks = [0]
+            else:
+                late.append(-1)
+            entries.append(StepEntry(req.req_id, toks, (e.num_tokens - 1,) if e.samples else ()))
+        late_tokens = (previous.ids, late) if previous is not None and previous.ids is not None else None
+        logits = self.engine.runner.step(entries, late_tokens=late_tokens)
         rows = [e.request for e in batch.entries if e.samples]
+        flight = _Flight(batch, {r.req_id: i for i, r in enumerate(rows)})
         if rows:
-            ids = self.sampler.sample(logits, [r.params for r in rows], [r.seed for r in rows],
-                                      [len(r.output) for r in rows])
-            for r, t in zip(rows, ids.tolist()):
-                sampled[r.req_id] = t
-        return self.scheduler.update(batch, sampled)
+            flight.ids = self.sampler.sample(logits, [r.params for r in rows], [r.seed for r in rows],
+                                             [len(r.output) for r in rows])
+            if flight.ids.is_cuda:
+                host = self._id_buffers[self._id_next]
+                self._id_next ^= 1
+                if host is None or host.numel() < len(rows):
+                    host = torch.empty((max(len(rows), self.config.max_num_seqs),), dtype=torch.int32, pin_memory=True)
+                    self._id_buffers[self._id_next ^ 1] = host
+                flight.host_ids = host[:len(rows)]
+                flight.host_ids.copy_(flight.ids, non_blocking=True)
+                flight.ready = torch.cuda.Event()
+                flight.ready.record()
+            else:
+                flight.host_ids = flight.ids
+        self.scheduler.advance(batch)
+        return flight
+
+    def _collect(self, flight: "_Flight") -> List[Request]:
+        """Wait for the step's sampled ids and account them."""
+        sampled: Dict[Hashable, int] = {}
+        if flight.host_ids is not None:
+            if flight.ready is not None:
+                flight.ready.synchronize()
+            ids = flight.host_ids.tolist()
+            sampled = {rid: ids[i] for rid, i in flight.row_of.items()}
+        return self.scheduler.resolve(flight.batch, sampled)
 
     def generate(self, prompts: Union[Sequence[Sequence[int]], Sequence[str]],
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[RequestOutput]:

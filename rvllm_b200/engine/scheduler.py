@@ -21,6 +21,15 @@ This scheduler does what the spec sketches:
   ("stop"), or has reached `max_model_len` ("length"); its pages and slot are freed at once.
 
 Same arrivals and seeds give the same sequence of batches.
+
+Accounting a step has two halves, so that the next step can be decided while the device still
+computes: `advance` counts the step's tokens and appends a stand-in (`PENDING`) for each token
+that is being sampled, `resolve` puts the sampled ids in their places and finishes requests.
+Between the two, `schedule` treats a stand-in as a token like any other (the step function takes
+its value from the device); a request whose pending token is certainly its last is left out.
+A request that stops on a token while a later step already runs for it is finished at that
+token: the later step's row is ignored and the pages go back at once, which is safe because the
+device runs steps in order.  `update` is the two halves together.
 """
 from __future__ import annotations
 
@@ -33,6 +42,7 @@ from ..errors import KvExhausted, SchedulerError
 from ..sampling.params import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+PENDING = -1        # stands in `Request.output` for a token that is being sampled
 
 
 @dataclass(eq=False)        # requests are compared by identity (field-wise equality would walk the token lists)
@@ -47,6 +57,7 @@ class Request:
     finish_reason: Optional[str] = None
     arrival: int = 0
     num_preemptions: int = 0
+    unresolved: int = 0            # stand-ins at the end of `output`
 
     @property
     def all_tokens(self) -> List[int]:
@@ -72,6 +83,7 @@ class ScheduledEntry:
     start: int                     # index of the first token of the portion in prompt + output
     num_tokens: int
     samples: bool                  # True when the portion ends the known tokens: its last row is sampled
+    out_index: int = -1            # where in the request's output the sampled token goes (set by advance)
 
 
 @dataclass
@@ -154,6 +166,8 @@ class Scheduler:
         for req in order:
             if req not in self.running or budget <= 0:
                 continue
+            if req.unresolved and self._ends_by_length(req):
+                continue                    # its pending token is its last
             n = self._portion(req, budget)
             while not self.cache.can_append(req.req_id, n, reserved):
                 victim = max((r for r in self.running if r.req_id not in scheduled_ids),
@@ -200,33 +214,80 @@ class Scheduler:
         return ScheduledBatch(entries, preempted)
 
     # ---- after the step ------------------------------------------------------------------------
-    def update(self, batch: ScheduledBatch, sampled: Dict[Hashable, int]) -> List[Request]:
-        """Account the step's tokens and the tokens sampled at the ends of portions; returns the
-        requests that finished."""
-        finished = []
+    def _ends_by_length(self, req: Request) -> bool:
+        return (len(req.output) >= req.params.max_tokens
+                or len(req.prompt) + len(req.output) >= self.max_model_len)
+
+    def advance(self, batch: ScheduledBatch) -> None:
+        """First half of the accounting, right after the step is launched: its tokens count as
+        computed and every token being sampled gets a stand-in in its request's output."""
         for e in batch.entries:
             req = e.request
             req.num_computed += e.num_tokens
-            if not e.samples:
+            if e.samples:
+                e.out_index = len(req.output)
+                req.output.append(PENDING)
+                req.unresolved += 1
+
+    def resolve(self, batch: ScheduledBatch, sampled: Dict[Hashable, int]) -> List[Request]:
+        """Second half: the sampled ids replace their stand-ins; returns the requests that finished.
+        Rows of requests that finished at an earlier token are ignored."""
+        finished = []
+        for e in batch.entries:
+            req = e.request
+            if not e.samples or req.state == FINISHED:
                 continue
             tok = int(sampled[req.req_id])
-            req.output.append(tok)
+            req.output[e.out_index] = tok
+            req.unresolved -= 1
             reason = None
             stops = set(req.params.stop_token_ids)
             if not req.params.ignore_eos:
                 stops.update(self.eos_token_ids)
             if tok in stops:
                 reason = "stop"
-            elif len(req.output) >= req.params.max_tokens:
+            elif e.out_index + 1 >= req.params.max_tokens:
                 reason = "length"
-            elif len(req.prompt) + len(req.output) >= self.max_model_len:
+            elif len(req.prompt) + e.out_index + 1 >= self.max_model_len:
                 reason = "length"
             if reason is not None:
+                del req.output[e.out_index + 1:]       # stand-ins of steps launched ahead
+                req.unresolved = 0
                 req.state, req.finish_reason = FINISHED, reason
-                self.running.remove(req)
-                self.cache.free(req.req_id)
+                if req in self.running:
+                    self.running.remove(req)
+                else:
+                    self.waiting.remove(req)           # pre-empted while its token was pending
+                if self.cache.has(req.req_id):
+                    self.cache.free(req.req_id)
                 finished.append(req)
         return finished
+
+    def can_run_ahead(self) -> bool:
+        """True when the next decision is certain before the pending tokens are known: every
+        running request decodes, none can be admitted, at least one goes on after its pending
+        token, and every one that goes on finds room for one more token."""
+        if not self.running or (self.waiting and len(self.running) < self.max_num_seqs):
+            return False
+        reserved = [0] * len(self.cache.groups)
+        goes_on = 0
+        for req in self.running:
+            if req.remaining != 1:
+                return False
+            if req.unresolved and self._ends_by_length(req):
+                continue
+            if not self.cache.can_append(req.req_id, 1, reserved):
+                return False
+            need = self.cache.pages_needed(req.req_id, 1)
+            reserved = [a + b for a, b in zip(reserved, need)]
+            goes_on += 1
+        return goes_on > 0
+
+    def update(self, batch: ScheduledBatch, sampled: Dict[Hashable, int]) -> List[Request]:
+        """Account the step's tokens and the tokens sampled at the ends of portions; returns the
+        requests that finished."""
+        self.advance(batch)
+        return self.resolve(batch, sampled)
 
     def abort(self, req_id: Hashable) -> None:
         for req in list(self.running):

@@ -128,14 +128,18 @@ class ModelRunner:
         return starts
 
     def pack(self, entries: Sequence[StepEntry], starts: List[int], pad_to: Optional[int] = None,
-             buffers=None) -> StepContext:
+             buffers=None, late=None) -> StepContext:
         """Write the step's metadata into a pinned buffer and send it to the device in one copy.
 
         With `pad_to` the batch is padded to that many one-token sequences (padding rows: token
         0, context length 0, slot -1, state slot -1 - they write nothing and attend to nothing;
         v3/crates/rvllm-metadata/src/pack.rs:35-40,79-86 of the reference pads the same way), block
         tables get the full width, and the layout depends on `pad_to` alone, so that a captured
-        CUDA graph can be replayed on the buffer."""
+        CUDA graph can be replayed on the buffer.
+
+        `late` = (sampled ids on the device, one index per entry): an entry with index j >= 0 is a
+        one-token sequence whose token is sampled[j], which the host has not read; its token is
+        put in place on the device after the copy."""
         cache = self.cache
         n_real = len(entries)
         B = pad_to if pad_to is not None else n_real
@@ -148,7 +152,7 @@ class ModelRunner:
         R = sum(len(w) for w in wants)
         G = len(cache.groups)
         MB = self.max_blocks if pad_to is not None else max(1, cache.blocks_for(max(ctx_lens)))
-        n_ints = 3 * T + (B + 1) + 2 * B + R + G * (T + B * MB) + 16
+        n_ints = 3 * T + (B + 1) + 2 * B + R + G * (T + B * MB) + B + 16
         if buffers is None:
             ring_i, host, dev = self._buffers(n_ints)
         else:
@@ -166,7 +170,7 @@ class ModelRunner:
         o_cu, o_ctx, o_state, o_rows = take(B + 1), take(B), take(B), take(R)
         if pad_to is not None:
             return self._pack_decode(entries, starts, B, MB, h, host, dev,
-                                     (o_tok, o_pos, o_seq, o_cu, o_ctx, o_state, o_rows), take)
+                                     (o_tok, o_pos, o_seq, o_cu, o_ctx, o_state, o_rows), take, late)
         cu = 0
         rows: List[int] = []
         h[o_cu] = 0
@@ -204,6 +208,10 @@ class ModelRunner:
                 h[o_slot + cu:o_slot + cu + q_lens[i]] = tb[pos // ps] * ps + pos % ps
                 cu += q_lens[i]
             group_offsets.append((o_slot, o_bt))
+        o_late = take(B)
+        if late is not None:
+            h[o_late:o_late + n_real] = late[1]
+            h[o_late + n_real:o_late + B] = -1
         dev[:off].copy_(host[:off], non_blocking=True)
         self.last_h2d_bytes = off * 4
         if self.device.type == "cuda" and ring_i is not None:
@@ -218,6 +226,8 @@ class ModelRunner:
         ctx.positions = dev[o_pos:o_pos + T]
         ctx.token_seq = dev[o_seq:o_seq + T]
         ctx.cu_seqlens = dev[o_cu:o_cu + B + 1]
+        if late is not None:
+            self.kernels.late_tokens(ctx.token_ids, ctx.cu_seqlens, dev[o_late:o_late + B], late[0])
         dev_ctx = dev[o_ctx:o_ctx + B]
         ctx.state_slots = dev[o_state:o_state + B]
         ctx.logit_rows = dev[o_rows:o_rows + R]
@@ -233,7 +243,7 @@ class ModelRunner:
                 num_decode=sum(1 for n in q_lens if n == 1)))
         return ctx
 
-    def _pack_decode(self, entries, starts, B, MB, h, host, dev, offs, take) -> StepContext:
+    def _pack_decode(self, entries, starts, B, MB, h, host, dev, offs, take, late=None) -> StepContext:
         """`pack` for a padded batch of one-token sequences (T = R = B): whole-array writes."""
         cache = self.cache
         o_tok, o_pos, o_seq, o_cu, o_ctx, o_state, o_rows = offs
@@ -264,7 +274,12 @@ class ModelRunner:
                 pos = starts[i]
                 h[o_slot + i] = table[pos // ps] * ps + pos % ps
             group_offsets.append((o_slot, o_bt))
-        off = group_offsets[-1][1] + B * MB if group_offsets else o_rows + B
+        o_late = take(B)
+        off = o_late
+        if late is not None:
+            h[o_late:o_late + n] = late[1]
+            h[o_late + n:o_late + B] = -1
+            off = o_late + B
         dev[:off].copy_(host[:off], non_blocking=True)
         self.last_h2d_bytes = off * 4
         ctx = StepContext()
@@ -274,6 +289,8 @@ class ModelRunner:
         ctx.positions = dev[o_pos:o_pos + B]
         ctx.token_seq = dev[o_seq:o_seq + B]
         ctx.cu_seqlens = dev[o_cu:o_cu + B + 1]
+        if late is not None:
+            self.kernels.late_tokens(ctx.token_ids, ctx.cu_seqlens, dev[o_late:o_late + B], late[0])
         dev_ctx = dev[o_ctx:o_ctx + B]
         ctx.state_slots = dev[o_state:o_state + B]
         ctx.logit_rows = dev[o_rows:o_rows + B]
@@ -286,18 +303,30 @@ class ModelRunner:
             max_ctx_len=self.max_model_len, page_size=ps, num_decode=B) for (o_slot, o_bt) in group_offsets]
         return ctx
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], late_tokens=None) -> Optional[torch.Tensor]:
         """Run the batch.  Returns float32 logits [wanted places, vocab] in the order of the
-        entries and of each entry's `want` (None if nothing is wanted)."""
+        entries and of each entry's `want` (None if nothing is wanted).
+
+        `late_tokens` = (ids, index): ids is an int32 tensor on the device (what the previous step
+        sampled), index has one number per entry; an entry with index j >= 0 brings one token whose
+        value is ids[j] and is not known on the host yet (its `tokens` holds a stand-in)."""
         if not entries:
             return None
         self.validate(entries)
+        if late_tokens is not None:
+            if len(late_tokens[1]) != len(entries):
+                raise SchedulerError(f"{len(entries)} entries but {len(late_tokens[1])} late-token indices")
+            for e, j in zip(entries, late_tokens[1]):
+                if j >= 0 and len(e.tokens) != 1:
+                    raise SchedulerError(f"request {e.req_id!r}: a late token stands for exactly one token")
+            if all(j < 0 for j in late_tokens[1]):
+                late_tokens = None
         starts = self.reserve(entries)
         bucket = self._graph_bucket(entries)
         if bucket is not None:
-            logits = self._step_graph(entries, starts, bucket)
+            logits = self._step_graph(entries, starts, bucket, late_tokens)
         else:
-            ctx = self.pack(entries, starts)
+            ctx = self.pack(entries, starts, late=late_tokens)
             hidden = self.model.forward(ctx, self.cache)
             logits = self.model.compute_logits(hidden, ctx) if ctx.logit_rows.numel() else None
         for e in entries:
@@ -319,19 +348,19 @@ class ModelRunner:
                 return b
         return None
 
-    def _step_graph(self, entries, starts, bucket: int) -> torch.Tensor:
+    def _step_graph(self, entries, starts, bucket: int, late=None) -> torch.Tensor:
         state = self._graphs.get(bucket)
         if state is None:
             # the first step of a bucket runs eagerly: it loads every kernel library and lets the
             # GEMM library set itself up; the graph is captured right after it for later steps
-            ctx = self.pack(entries, starts)
+            ctx = self.pack(entries, starts, late=late)
             hidden = self.model.forward(ctx, self.cache)
             logits = self.model.compute_logits(hidden, ctx)
             self._graphs[bucket] = self._capture(bucket)
             return logits
         host, dev, graph, out, launches = state
         self._graph_event.synchronize()
-        self.pack(entries, starts, pad_to=bucket, buffers=(host, dev))
+        self.pack(entries, starts, pad_to=bucket, buffers=(host, dev), late=late)
         self._graph_event.record()
         graph.replay()
         COUNTERS["launches"] += launches       # the kernels of this project inside the replayed graph
@@ -339,7 +368,7 @@ class ModelRunner:
 
     def _capture(self, bucket: int):
         G = len(self.cache.groups)
-        n_ints = 3 * bucket + (bucket + 1) + 2 * bucket + bucket + G * (bucket + bucket * self.max_blocks) + 16
+        n_ints = 3 * bucket + (bucket + 1) + 2 * bucket + bucket + G * (bucket + bucket * self.max_blocks) + bucket + 16
         host = torch.empty((n_ints,), dtype=torch.int32, pin_memory=True)
         dev = torch.empty((n_ints,), dtype=torch.int32, device=self.device)
         ctx = self.pack([], [], pad_to=bucket, buffers=(host, dev))   # all rows padded: writes nothing

@@ -119,6 +119,18 @@ class CudaKernels:
         _check("gather_rows", st)
         return out
 
+    def late_tokens(self, token_ids: torch.Tensor, cu_seqlens: torch.Tensor, source: torch.Tensor,
+                    sampled: torch.Tensor) -> None:
+        """token_ids[cu_seqlens[i]] = sampled[source[i]] for every sequence i with source[i] >= 0:
+        tokens that the previous step sampled and the host has not read yet."""
+        _need(token_ids, "token_ids", torch.int32, 1); _need(cu_seqlens, "cu_seqlens", torch.int32, 1)
+        _need(source, "source", torch.int32, 1); _need(sampled, "sampled", torch.int32, 1)
+        if cu_seqlens.shape[0] < source.shape[0]:
+            raise KernelError(f"late_tokens: {source.shape[0]} sequences but {cu_seqlens.shape[0]} sequence starts")
+        st = self._lib("elementwise.cu").rv_late_tokens(_ptr(token_ids), _ptr(cu_seqlens), _ptr(source), _ptr(sampled),
+                                                        c_int(source.shape[0]), c_int(sampled.shape[0]), self._stream())
+        _check("late_tokens", st)
+
     def rmsnorm(self, x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
         _need(x, "x", dims=2); _need(gamma, "gamma", dims=1)
         if gamma.shape[0] != x.shape[1]:

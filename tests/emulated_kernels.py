@@ -17,6 +17,11 @@ class EmulatedKernels:
     def gather_rows(self, table, ids):
         return table[ids.long()].clone()
 
+    def late_tokens(self, token_ids, cu_seqlens, source, sampled):
+        for i, j in enumerate(source.tolist()):
+            if j >= 0:
+                token_ids[int(cu_seqlens[i])] = sampled[j]
+
     def rmsnorm(self, x, gamma, eps):
         xf = x.float()
         r = 1.0 / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps)

@@ -100,6 +100,42 @@ def test_generate_survives_preemption_with_the_same_tokens(emulated):
     assert tight.engine.cache.num_free_pages() == [14, 14]
 
 
+def test_running_a_step_ahead_gives_the_same_tokens(emulated):
+    """Decode steps launched before the previous step's ids are read (tokens taken on the device)
+    produce what one-step-at-a-time produces, also when requests stop on a token or at different
+    lengths while a step ahead of them is already running."""
+    folder = model_folder("tiny_qwen2")
+    cfg = load_config(folder)
+    prompts = list(random_requests(cfg.vocab_size, (30, 9, 26, 20, 3), seed=6).values())
+
+    def run(ahead, stop, **kw):
+        sps = [SamplingParams(temperature=0.8 if i % 2 else 0.0, seed=50 + i, max_tokens=10 + 3 * i,
+                              stop_token_ids=stop, ignore_eos=True) for i in range(len(prompts))]
+        args = dict(dtype="float32", device="cpu", block_size=8, num_blocks=64, max_model_len=128, max_num_seqs=5,
+                    max_num_batched_tokens=64, async_scheduling=ahead)
+        args.update(kw)
+        llm = LLM(folder, **args)
+        steps_ahead = 0
+        reqs = [llm.add_request(p, sp) for p, sp in zip(prompts, sps)]
+        while llm.scheduler.has_unfinished():
+            llm.step()
+            steps_ahead += llm._in_flight is not None
+        llm.engine.cache.check()
+        assert not llm.engine.cache.requests
+        return [(r.output, r.finish_reason) for r in reqs], steps_ahead
+
+    free, _ = run(False, [])
+    stop = [free[1][0][4], free[3][0][7]]              # tokens that two requests produce midway
+    want, none_ahead = run(False, stop)
+    assert none_ahead == 0 and {"stop", "length"} == {r for _, r in want}
+    got, ahead = run(True, stop)
+    assert ahead > 10, "decode steps were meant to be launched ahead"
+    assert got == want
+    # with fewer request slots than requests, and with so few pages that requests are pre-empted
+    assert run(True, stop, max_num_seqs=2)[0] == want
+    assert run(True, stop, num_blocks=16)[0] == want
+
+
 def test_padding_rows_of_a_graph_bucket_change_nothing(emulated):
     """pack(pad_to=...) is what CUDA-graph decode steps run on: padded rows must not write to the
     cache, read a block table or change the real rows' logits."""

@@ -66,6 +66,40 @@ def test_cuda_graph_decode_equals_eager_and_batching_does_not_change_samples(dty
         assert a == c
 
 
+@pytest.mark.parametrize("eager", [False, True])
+def test_running_a_step_ahead_gives_the_same_tokens(eager):
+    """Decode steps launched before the previous step's ids reach the host take their tokens on the
+    device (late_tokens kernel, then the graph or the eager step): same tokens and finish reasons as
+    one step at a time, with requests that stop on a token or at different lengths meanwhile."""
+    from rvllm_b200 import SamplingParams
+    cfg, _ = plain_impl.read_model_folder(model_folder("tiny_qwen2"))
+    prompts = list(random_requests(cfg["vocab_size"], (30, 9, 26, 20, 3, 50), seed=6).values())
+
+    def run(ahead, stop, dtype="float32", same_length=False, **kw):
+        sps = [SamplingParams(temperature=0.8 if i % 2 else 0.0, seed=50 + i, max_tokens=20 if same_length else 10 + 4 * i,
+                              stop_token_ids=stop, ignore_eos=True) for i in range(len(prompts))]
+        llm = make_llm("tiny_qwen2", dtype, max_num_seqs=8, max_num_batched_tokens=128, async_scheduling=ahead,
+                       enforce_eager=eager, **kw)
+        reqs = [llm.add_request(p, sp) for p, sp in zip(prompts, sps)]
+        ahead_steps = 0
+        while llm.scheduler.has_unfinished():
+            llm.step()
+            ahead_steps += llm._in_flight is not None
+        llm.engine.cache.check()
+        assert not llm.engine.cache.requests
+        return [(r.output, r.finish_reason) for r in reqs], ahead_steps
+
+    free, _ = run(False, ())
+    stop = (free[1][0][4], free[3][0][7])
+    want, n0 = run(False, stop)
+    got, n1 = run(True, stop)
+    assert n0 == 0 and n1 > 10
+    assert got == want and {"stop", "length"} == {r for _, r in want}
+    assert run(True, stop, num_blocks=24)[0] == want          # few pages: pre-emption in between
+    # bfloat16, where the make-up of every batch is the same in both modes
+    assert run(True, (), "bfloat16", True)[0] == run(False, (), "bfloat16", True)[0]
+
+
 def test_finish_reasons_and_stop_tokens():
     from rvllm_b200 import SamplingParams
     cfg, w = plain_impl.read_model_folder(model_folder("tiny_llama"))

@@ -167,3 +167,46 @@ def test_abort_frees():
     s.abort("a")
     s.abort("b")
     assert not s.has_unfinished() and cache.num_free_pages() == [64]
+
+
+def test_two_halves_of_the_accounting_let_a_step_run_ahead():
+    """advance / resolve: the next decode step is decided while tokens are pending; a request whose
+    pending token is its last is left out; one that stops while a step ahead of it runs is finished
+    at the stop token, the row ahead is ignored and its pages go back."""
+    from rvllm_b200.engine.scheduler import PENDING
+    cache, s = make(budget=16, eos=(7,))
+    s.add_request(req("a", 5, max_tokens=3))
+    s.add_request(req("b", 6, max_tokens=8))
+    s.add_request(req("c", 3, max_tokens=8))
+    b0, _ = run_step(cache, s, token_of=lambda r: 50)             # prompts whole, first tokens
+    assert not s.can_run_ahead() or b0.is_decode_only is False
+    b1 = s.schedule()                                             # step 1: all decode
+    for e in b1.entries:
+        cache.append(e.request.req_id, 1)
+    s.advance(b1)
+    a, b, c = (e.request for e in b1.entries)
+    assert a.output == [50, PENDING] and a.unresolved == 1 and a.remaining == 1
+    assert s.can_run_ahead()
+    b2 = s.schedule()                                             # step 2, decided before step 1 is read
+    assert [e.request.req_id for e in b2.entries] == ["a", "b", "c"]
+    assert [e.request.tokens(e.start, 1) for e in b2.entries] == [[PENDING]] * 3
+    for e in b2.entries:
+        cache.append(e.request.req_id, 1)
+    s.advance(b2)
+    assert a.output == [50, PENDING, PENDING]
+    assert s.can_run_ahead()                                      # a ends with its pending token, b and c go on
+    done = s.resolve(b1, {"a": 51, "b": 7, "c": 52})              # b stops on EOS while step 2 runs for it
+    assert [r.req_id for r in done] == ["b"] and b.output == [50, 7] and b.finish_reason == "stop"
+    assert not cache.has("b") and b not in s.running
+    b3 = s.schedule()                                             # a is not scheduled: its third token is its last
+    assert [e.request.req_id for e in b3.entries] == ["c"]
+    cache.append("c", 1)
+    s.advance(b3)
+    done = s.resolve(b2, {"a": 53, "b": 99, "c": 54})             # b's row of the step ahead is ignored
+    assert [r.req_id for r in done] == ["a"] and a.output == [50, 51, 53] and a.finish_reason == "length"
+    assert b.output == [50, 7] and c.output == [50, 52, 54, PENDING]
+    s.resolve(b3, {"c": 7})
+    assert c.output == [50, 52, 54, 7] and c.finish_reason == "stop"
+    assert not s.has_unfinished() and not cache.requests
+    cache.check()
+    assert cache.num_free_pages() == [64]
