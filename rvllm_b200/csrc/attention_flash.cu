@@ -82,7 +82,10 @@ template <int WARPS_M, int WARPS_N, int NSTAGES>
 __global__ void __launch_bounds__(WARPS_M * WARPS_N * 32)
 flash_paged_kernel(const FlashParams p) {
     rv_pdl_launch_dependents();
-    rv_pdl_wait();
+    // The step's metadata (sequence starts, context lengths, block tables) was copied to the device
+    // before the step's first kernel started, so it is read here without waiting for the kernel
+    // that precedes this one in the stream; q and the cache, which that kernel may still be
+    // writing, are touched only after rv_pdl_wait() below.
     constexpr int HD = HEAD_DIM;
     constexpr int M_TILE = 16 * WARPS_M;
     constexpr int KW = KV_TILE / WARPS_N;          // keys of a tile that one warp owns
@@ -96,11 +99,12 @@ flash_paged_kernel(const FlashParams p) {
     const int ctx = p.ctx_lens[seq];
     const int q_start = p.cu_seqlens[seq];
     const int q_len = p.cu_seqlens[seq + 1] - q_start;
-    if (q_len <= 0) return;
-    if ((p.q_filter == 1 && q_len != 1) || (p.q_filter == 2 && q_len == 1)) return;
     const int rows_total = q_len * G;
     const int row0 = tile_m * M_TILE;
-    if (row0 >= rows_total) return;
+    if (q_len <= 0 || row0 >= rows_total || (p.q_filter == 1 && q_len != 1) || (p.q_filter == 2 && q_len == 1)) {
+        rv_pdl_wait();          // a CTA without work still keeps the order of the chain of kernels
+        return;
+    }
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int warp_m = warp / WARPS_N, warp_n = warp - warp_m * WARPS_N;
@@ -131,18 +135,6 @@ flash_paged_kernel(const FlashParams p) {
     const int t_begin = tile_lo + split * per_split;
     const int t_end = min(tile_hi, t_begin + per_split);
 
-    // Q fragments (A operand, 16 rows x HD), straight from global memory
-    uint32_t qa[HD / 16][4];
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const __nv_bfloat16* qp = p.q + ((size_t)tok[i] * p.nh + head[i]) * HD + ks * 16 + tq * 2;
-            qa[ks][i] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp) : 0u;
-            qa[ks][i + 2] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp + 8) : 0u;
-        }
-    }
-
     float o[HD / 8][4];
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
@@ -158,6 +150,19 @@ flash_paged_kernel(const FlashParams p) {
     if (table_cached) {
         for (int i = tid; i < blk_hi - blk_lo; i += NTHREADS) s_table[i] = table[blk_lo + i];
         __syncthreads();
+    }
+    rv_pdl_wait();
+
+    // Q fragments (A operand, 16 rows x HD), straight from global memory
+    uint32_t qa[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const __nv_bfloat16* qp = p.q + ((size_t)tok[i] * p.nh + head[i]) * HD + ks * 16 + tq * 2;
+            qa[ks][i] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp) : 0u;
+            qa[ks][i + 2] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp + 8) : 0u;
+        }
     }
     const size_t page_stride = (size_t)2 * p.nkv * p.page_size * HD;
     const size_t v_off = (size_t)p.nkv * p.page_size * HD;
@@ -284,14 +289,17 @@ flash_paged_kernel(const FlashParams p) {
     }
 
     if (WARPS_N > 1) {
-        // merge the warps that shared the rows: (m, l, O) -> shared memory, warp 0 of each row
-        // block combines.  The key/value buffers are free now.
+        // Merge the warps that shared the rows: (m, l, O) of the real rows go to shared memory (the
+        // key/value buffers are free now), then all threads of the CTA share the work of adding
+        // them up, one output element at a time, and write the result.  WARPS_M is 1 here.
         __syncthreads();
         float* mo = reinterpret_cast<float*>(smem);                 // [WARPS_N][16][HD]
         float* mml = mo + WARPS_N * 16 * HD;                        // [WARPS_N][16][2]
+        const int n_rows = min(16, rows_total - row0);
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int row = quad + 8 * i;
+            if (row >= n_rows) continue;
 #pragma unroll
             for (int n = 0; n < HD / 8; ++n) {
                 float* dst = mo + ((size_t)warp_n * 16 + row) * HD + n * 8 + tq * 2;
@@ -303,29 +311,31 @@ flash_paged_kernel(const FlashParams p) {
             }
         }
         __syncthreads();
-        if (warp_n != 0) return;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int row = quad + 8 * i;
+        for (int idx = tid; idx < n_rows * HD; idx += NTHREADS) {
+            const int row = idx / HD, d = idx - row * HD;
             float m_all = -INFINITY;
+#pragma unroll
             for (int w = 0; w < WARPS_N; ++w) m_all = fmaxf(m_all, mml[(w * 16 + row) * 2]);
             const float m_s = m_all == -INFINITY ? 0.f : m_all;
-            float l_all = 0.f;
+            float l_all = 0.f, acc = 0.f;
 #pragma unroll
-            for (int n = 0; n < HD / 8; ++n) { o[n][2 * i] = 0.f; o[n][2 * i + 1] = 0.f; }
             for (int w = 0; w < WARPS_N; ++w) {
                 const float f = exp2f(mml[(w * 16 + row) * 2] - m_s);
                 l_all += mml[(w * 16 + row) * 2 + 1] * f;
-                if (f > 0.f) {
-#pragma unroll
-                    for (int n = 0; n < HD / 8; ++n) {
-                        const float* src = mo + ((size_t)w * 16 + row) * HD + n * 8 + tq * 2;
-                        o[n][2 * i] += src[0] * f; o[n][2 * i + 1] += src[1] * f;
-                    }
-                }
+                acc += mo[((size_t)w * 16 + row) * HD + d] * f;
             }
-            m_run[i] = m_all; l_run[i] = l_all;
+            const int rr = row0 + row;
+            const int t = rr / G;
+            const size_t row_out = (size_t)(q_start + t) * p.nh + kvh * G + (rr - t * G);
+            if (p.num_splits == 1) {
+                p.out[row_out * HD + d] = __float2bfloat16_rn(acc * (l_all > 0.f ? 1.f / l_all : 0.f));
+            } else {
+                const size_t prow = (size_t)split * p.n_tokens * p.nh + row_out;
+                p.part_o[prow * HD + d] = acc;
+                if (d == 0) { p.part_ml[prow * 2] = m_all; p.part_ml[prow * 2 + 1] = l_all; }
+            }
         }
+        return;
     }
 
 #pragma unroll
@@ -348,29 +358,46 @@ flash_paged_kernel(const FlashParams p) {
     }
 }
 
-// Merge the partial results of the key splits: one block per (token, head).
+// Merge the partial results of the key splits: one block per (token, head), one thread per
+// element of the head.  Eight splits are read at a time, maxima, denominators and sums together,
+// so that the kernel costs one round trip to L2 per eight splits; the running result is rescaled
+// as in the attention kernel itself.
 __global__ void flash_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                      __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
     const int row = blockIdx.x;
-    float m_all = -INFINITY;
-    for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, part_ml[((size_t)s * rows + row) * 2]);
-    const float m_s = m_all == -INFINITY ? 0.f : m_all;
-    float l_all = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-        const float* ml = part_ml + ((size_t)s * rows + row) * 2;
-        l_all += ml[1] * exp2f(ml[0] - m_s);
-    }
-    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-    for (int d = threadIdx.x; d < HEAD_DIM; d += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < num_splits; ++s) {
-            const float f = exp2f(part_ml[((size_t)s * rows + row) * 2] - m_s);
-            if (f > 0.f) acc += part_o[((size_t)s * rows + row) * HEAD_DIM + d] * f;
+    const int d = threadIdx.x;
+    if (d >= HEAD_DIM) return;
+    float m_run = -INFINITY, l_run = 0.f, acc = 0.f;
+    for (int s0 = 0; s0 < num_splits; s0 += 8) {
+        float m[8], l[8], o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const bool have = s0 + i < num_splits;
+            const size_t r = (size_t)(have ? s0 + i : s0) * rows + row;
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + r);
+            m[i] = have ? ml.x : -INFINITY;
+            l[i] = have ? ml.y : 0.f;
+            o[i] = __ldcg(part_o + r * HEAD_DIM + d);
         }
-        out[(size_t)row * HEAD_DIM + d] = __float2bfloat16_rn(acc * inv);
+        float m_new = m_run;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m_new = fmaxf(m_new, m[i]);
+        const float m_s = m_new == -INFINITY ? 0.f : m_new;
+        const float keep = exp2f(m_run - m_s);          // 0 while nothing has been seen
+        l_run *= keep;
+        acc *= keep;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float f = exp2f(m[i] - m_s);           // 0 for an empty or absent split
+            l_run += l[i] * f;
+            if (f > 0.f) acc += o[i] * f;                // an empty split's sum may hold anything
+        }
+        m_run = m_new;
     }
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    out[(size_t)row * HEAD_DIM + d] = __float2bfloat16_rn(acc * inv);
 }
 
 template <int WARPS_M, int WARPS_N, int NSTAGES>
@@ -430,7 +457,7 @@ RV_EXPORT int rv_flash_attention(const void* q, const void* cache, const int* bl
     int st = mode == 1 ? launch_flash<1, 4, DECODE_STAGES>(p, num_seqs, stream) : launch_flash<4, 1, 2>(p, num_seqs, stream);
     if (st != RV_OK) return st;
     if (num_splits > 1) {
-        RV_LAUNCH_ST = rv_launch(flash_combine_kernel, dim3(n_tokens * nh), dim3(HEAD_DIM >= 128 ? 128 : 64), 0, stream,
+        RV_LAUNCH_ST = rv_launch(flash_combine_kernel, dim3(n_tokens * nh), dim3((HEAD_DIM + 31) / 32 * 32), 0, stream,
                                  p.part_o, p.part_ml, p.out, n_tokens * nh, num_splits);
         return rv_launch_status();
     }

@@ -16,6 +16,11 @@
 //            stages and finally publishes the accumulator;
 //   warps 2-5  epilogue: tcgen05.ld of each thread's feature row, split reduction, bias,
 //            residual, SiLU-gate, rounding, coalesced stores.
+// A third epilogue serves the q/k/v product of an attention layer: W rows are [q heads | k heads |
+// v heads]; the tile's sums are rounded to bfloat16 as a separate product would store them, then
+// the bias is added, q and k are rotated by the token's position (pairs i, i + head_dim/2, which
+// lie in one tile because 128 is a multiple of head_dim), q goes to its output and k and v go
+// straight into the token's slot of the paged cache - one kernel and one pass less per layer.
 // Every mbarrier wait is bounded (see gemm_tcgen05.cu); no cluster, no multicast.
 //
 // Shapes: the five products of a layer and the LM head at decode time
@@ -42,6 +47,14 @@ struct DecodeGemmParams {
     int M, N, K;
     int out_f32, gated;
     int splits, n_tiles;
+    // rotary epilogue (q_out != nullptr): N = (nh + 2 nkv) * hd, 128 % hd == 0
+    __nv_bfloat16* q_out;            // [M, nh * hd]
+    __nv_bfloat16* kv_cache;         // [pages, 2, nkv, page_size, hd]
+    const int* positions;            // [M]
+    const int* slot_mapping;         // [M], < 0: the row writes no key or value
+    const float* cos_t;              // [table_rows, hd / 2] or nullptr (no rotation)
+    const float* sin_t;
+    int nh, nkv, hd, page_size, table_rows;
 };
 
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -59,6 +72,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
     __shared__ int is_last;
+    __shared__ int row_pos[128], row_slot[128];
 
     rv_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -239,6 +253,60 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         if (p.out_f32) ((float*)p.out)[(size_t)m * half_n + n] = v;
                         else ((__nv_bfloat16*)p.out)[(size_t)m * half_n + n] = __float2bfloat16_rn(v);
                     }
+                } else if (p.q_out) {
+                    // positions and slots of the rows once per CTA, then four rows at a time so that
+                    // their table reads are in flight together
+                    if (et < p.M) {
+                        const int pos = p.positions[et];
+                        row_pos[et] = pos < 0 ? 0 : (pos >= p.table_rows ? p.table_rows - 1 : pos);
+                        row_slot[et] = p.slot_mapping[et];
+                    }
+                    epi_sync();
+                    const int n = tile * TILE_F + et;
+                    if (n < p.N) {
+                        const int hd = p.hd, half = hd >> 1;
+                        const int head = n / hd, d = n - head * hd;
+                        const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
+                        const bool rotate = (is_q || is_k) && p.cos_t != nullptr;
+                        const bool first = d < half;
+                        const int pe = first ? et + half : et - half;          // the pair's other feature
+                        const int i = first ? d : d - half;
+                        const float b = p.bias ? rv_load_param(p.bias, p.bias_dtype, n) : 0.f;
+                        const float bp = p.bias ? rv_load_param(p.bias, p.bias_dtype, first ? n + half : n - half) : 0.f;
+                        const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
+                        for (int m0 = 0; m0 < p.M; m0 += 4) {
+                            float c[4], sn[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                c[j] = 1.f; sn[j] = 0.f;
+                                if (rotate && m0 + j < p.M) {
+                                    c[j] = __ldg(p.cos_t + (size_t)row_pos[m0 + j] * half + i);
+                                    sn[j] = __ldg(p.sin_t + (size_t)row_pos[m0 + j] * half + i);
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int m = m0 + j;
+                                if (m >= p.M) break;
+                                const float own = __bfloat162float(__float2bfloat16_rn(fin[et * (MB + 1) + m])) + b;
+                                float v = own;
+                                if (is_q || is_k) {
+                                    const float other = __bfloat162float(__float2bfloat16_rn(fin[pe * (MB + 1) + m])) + bp;
+                                    v = first ? own * c[j] - other * sn[j] : other * sn[j] + own * c[j];
+                                }
+                                if (is_q) {
+                                    p.q_out[(size_t)m * p.nh * hd + n] = __float2bfloat16_rn(v);
+                                } else {
+                                    const int slot = row_slot[m];
+                                    if (slot >= 0) {
+                                        const int page = slot / p.page_size, off = slot - page * p.page_size;
+                                        p.kv_cache[((((size_t)page * 2 + (is_k ? 0 : 1)) * p.nkv + kvh) * p.page_size + off) * hd + d] =
+                                            __float2bfloat16_rn(v);
+                                    }
+                                }
+                            }
+                        }
+                    }
                 } else {
                     const int n = tile * TILE_F + et;
                     if (n < p.N) {
@@ -288,35 +356,60 @@ RV_EXPORT int rv_gemm_decode_tiles(int N, int gated) {
     return gated ? (N / 2 + TILE_F / 2 - 1) / (TILE_F / 2) : (N + TILE_F - 1) / TILE_F;
 }
 
-RV_EXPORT int rv_gemm_tcgen05_decode_bf16(const void* x, const void* w, const void* bias, int bias_dtype,
-                                          const void* residual, void* out, int out_f32, int M, int N, int K,
-                                          int gated, int splits, float* scratch, int* counters, int* status,
-                                          cudaStream_t stream) {
-    if (M < 0 || N <= 0 || K <= 0 || splits < 1) return RV_ERR_BAD_SIZE;
-    if (M > 128) return RV_ERR_UNSUPPORTED;
-    if (K % 8) return RV_ERR_UNSUPPORTED;
-    if (gated && ((N & 1) || bias || residual)) return RV_ERR_BAD_SIZE;
-    if (residual && out_f32) return RV_ERR_BAD_SIZE;
-    if (splits > 1 && (!scratch || !counters)) return RV_ERR_BAD_SIZE;
+static int run_decode(const void* x, const void* w, DecodeGemmParams p, cudaStream_t stream) {
+    if (p.M < 0 || p.N <= 0 || p.K <= 0 || p.splits < 1) return RV_ERR_BAD_SIZE;
+    if (p.M > 128) return RV_ERR_UNSUPPORTED;
+    if (p.K % 8) return RV_ERR_UNSUPPORTED;
+    if (p.splits > 1 && (!p.scratch || !p.counters)) return RV_ERR_BAD_SIZE;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return RV_ERR_ALIGNMENT;
-    if (M == 0) return RV_OK;
-    const int num_kb = (K + BK - 1) / BK;
-    if (splits > num_kb) splits = num_kb;
-    const int mb = rv_gemm_decode_padded_rows(M);
+    if (p.M == 0) return RV_OK;
+    const int num_kb = (p.K + BK - 1) / BK;
+    if (p.splits > num_kb) p.splits = num_kb;
+    const int mb = rv_gemm_decode_padded_rows(p.M);
     alignas(64) CUtensorMap mw, mx;
-    int st = rv_make_bf16_map(&mw, w, N, K, TILE_F / 2);
+    int st = rv_make_bf16_map(&mw, w, p.N, p.K, TILE_F / 2);
     if (st != RV_OK) return st;
-    st = rv_make_bf16_map(&mx, x, M, K, mb);
+    st = rv_make_bf16_map(&mx, x, p.M, p.K, mb);
     if (st != RV_OK) return st;
-    DecodeGemmParams p;
-    p.out = out; p.residual = (const __nv_bfloat16*)residual; p.bias = bias; p.bias_dtype = bias_dtype;
-    p.scratch = scratch; p.counters = counters; p.status = status;
-    p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.gated = gated; p.splits = splits;
-    p.n_tiles = rv_gemm_decode_tiles(N, gated);
+    p.n_tiles = rv_gemm_decode_tiles(p.N, p.gated);
     switch (mb) {
         case 16: return launch_decode<16>(mw, mx, p, stream);
         case 32: return launch_decode<32>(mw, mx, p, stream);
         case 64: return launch_decode<64>(mw, mx, p, stream);
         default: return launch_decode<128>(mw, mx, p, stream);
     }
+}
+
+RV_EXPORT int rv_gemm_tcgen05_decode_bf16(const void* x, const void* w, const void* bias, int bias_dtype,
+                                          const void* residual, void* out, int out_f32, int M, int N, int K,
+                                          int gated, int splits, float* scratch, int* counters, int* status,
+                                          cudaStream_t stream) {
+    if (gated && ((N & 1) || bias || residual)) return RV_ERR_BAD_SIZE;
+    if (residual && out_f32) return RV_ERR_BAD_SIZE;
+    DecodeGemmParams p = {};
+    p.out = out; p.residual = (const __nv_bfloat16*)residual; p.bias = bias; p.bias_dtype = bias_dtype;
+    p.scratch = scratch; p.counters = counters; p.status = status;
+    p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.gated = gated; p.splits = splits;
+    return run_decode(x, w, p, stream);
+}
+
+// The q/k/v product of an attention layer with bias, rotation and the cache write in its epilogue.
+// w: [(nh + 2 nkv) * hd, K]; q_out: [M, nh * hd]; kv_cache: [pages, 2, nkv, page_size, hd].
+RV_EXPORT int rv_gemm_decode_qkv_rope(const void* x, const void* w, const void* bias, int bias_dtype,
+                                      const int* positions, const float* cos_t, const float* sin_t,
+                                      const int* slot_mapping, void* kv_cache, void* q_out, int M, int K,
+                                      int nh, int nkv, int hd, int page_size, int table_rows, int splits,
+                                      float* scratch, int* counters, int* status, cudaStream_t stream) {
+    if (nh <= 0 || nkv <= 0 || hd <= 0 || (hd & 1) || page_size <= 0 || table_rows <= 0) return RV_ERR_BAD_SIZE;
+    if (TILE_F % hd) return RV_ERR_UNSUPPORTED;           // a rotation pair must lie in one tile
+    if ((cos_t == nullptr) != (sin_t == nullptr)) return RV_ERR_BAD_SIZE;
+    if (!positions || !slot_mapping || !kv_cache || !q_out) return RV_ERR_BAD_SIZE;
+    DecodeGemmParams p = {};
+    p.bias = bias; p.bias_dtype = bias_dtype;
+    p.scratch = scratch; p.counters = counters; p.status = status;
+    p.M = M; p.N = (nh + 2 * nkv) * hd; p.K = K; p.splits = splits;
+    p.q_out = (__nv_bfloat16*)q_out; p.kv_cache = (__nv_bfloat16*)kv_cache; p.positions = positions;
+    p.slot_mapping = slot_mapping; p.cos_t = cos_t; p.sin_t = sin_t;
+    p.nh = nh; p.nkv = nkv; p.hd = hd; p.page_size = page_size; p.table_rows = table_rows;
+    return run_decode(x, w, p, stream);
 }

@@ -128,14 +128,15 @@ class ModelRunner:
         return starts
 
     def pack(self, entries: Sequence[StepEntry], starts: List[int], pad_to: Optional[int] = None,
-             buffers=None, late=None) -> StepContext:
+             buffers=None, late=None, ctx_limit: Optional[int] = None) -> StepContext:
         """Write the step's metadata into a pinned buffer and send it to the device in one copy.
 
         With `pad_to` the batch is padded to that many one-token sequences (padding rows: token
         0, context length 0, slot -1, state slot -1 - they write nothing and attend to nothing;
         v3/crates/rvllm-metadata/src/pack.rs:35-40,79-86 of the reference pads the same way), block
         tables get the full width, and the layout depends on `pad_to` alone, so that a captured
-        CUDA graph can be replayed on the buffer.
+        CUDA graph can be replayed on the buffer; `ctx_limit` is then the context length that the
+        graph's kernels are laid out for (no sequence of the batch is longer).
 
         `late` = (sampled ids on the device, one index per entry): an entry with index j >= 0 is a
         one-token sequence whose token is sampled[j], which the host has not read; its token is
@@ -170,7 +171,8 @@ class ModelRunner:
         o_cu, o_ctx, o_state, o_rows = take(B + 1), take(B), take(B), take(R)
         if pad_to is not None:
             return self._pack_decode(entries, starts, B, MB, h, host, dev,
-                                     (o_tok, o_pos, o_seq, o_cu, o_ctx, o_state, o_rows), take, late)
+                                     (o_tok, o_pos, o_seq, o_cu, o_ctx, o_state, o_rows), take, late,
+                                     ctx_limit or self.max_model_len)
         cu = 0
         rows: List[int] = []
         h[o_cu] = 0
@@ -243,7 +245,7 @@ class ModelRunner:
                 num_decode=sum(1 for n in q_lens if n == 1)))
         return ctx
 
-    def _pack_decode(self, entries, starts, B, MB, h, host, dev, offs, take, late=None) -> StepContext:
+    def _pack_decode(self, entries, starts, B, MB, h, host, dev, offs, take, late=None, ctx_limit=None) -> StepContext:
         """`pack` for a padded batch of one-token sequences (T = R = B): whole-array writes."""
         cache = self.cache
         o_tok, o_pos, o_seq, o_cu, o_ctx, o_state, o_rows = offs
@@ -300,7 +302,7 @@ class ModelRunner:
         ctx.attention = [AttentionMeta(
             block_tables=dev[o_bt:o_bt + B * MB].view(B, MB), cu_seqlens=ctx.cu_seqlens, ctx_lens=dev_ctx,
             token_seq=ctx.token_seq, slot_mapping=dev[o_slot:o_slot + B], num_seqs=B, max_q_len=1,
-            max_ctx_len=self.max_model_len, page_size=ps, num_decode=B) for (o_slot, o_bt) in group_offsets]
+            max_ctx_len=ctx_limit or self.max_model_len, page_size=ps, num_decode=B) for (o_slot, o_bt) in group_offsets]
         return ctx
 
     def step(self, entries: Sequence[StepEntry], late_tokens=None) -> Optional[torch.Tensor]:
@@ -348,7 +350,17 @@ class ModelRunner:
                 return b
         return None
 
+    def _ctx_bucket(self, longest: int) -> int:
+        """The context length a graph is laid out for: 512, 768, 1024, 1536, 2048, ... (the attention
+        kernel's split of the keys depends on it), at most max_model_len."""
+        b = 512
+        while b < longest:
+            b = b * 3 // 2 if (b & (b - 1)) == 0 else b // 3 * 4
+        return min(b, self.max_model_len)
+
     def _step_graph(self, entries, starts, bucket: int, late=None) -> torch.Tensor:
+        ctx_limit = self._ctx_bucket(max(starts) + 1)
+        bucket = (bucket, ctx_limit)
         state = self._graphs.get(bucket)
         if state is None:
             # the first step of a bucket runs eagerly: it loads every kernel library and lets the
@@ -356,22 +368,22 @@ class ModelRunner:
             ctx = self.pack(entries, starts, late=late)
             hidden = self.model.forward(ctx, self.cache)
             logits = self.model.compute_logits(hidden, ctx)
-            self._graphs[bucket] = self._capture(bucket)
+            self._graphs[bucket] = self._capture(*bucket)
             return logits
         host, dev, graph, out, launches = state
         self._graph_event.synchronize()
-        self.pack(entries, starts, pad_to=bucket, buffers=(host, dev), late=late)
+        self.pack(entries, starts, pad_to=bucket[0], buffers=(host, dev), late=late, ctx_limit=ctx_limit)
         self._graph_event.record()
         graph.replay()
         COUNTERS["launches"] += launches       # the kernels of this project inside the replayed graph
         return out[:len(entries)]
 
-    def _capture(self, bucket: int):
+    def _capture(self, bucket: int, ctx_limit: int):
         G = len(self.cache.groups)
         n_ints = 3 * bucket + (bucket + 1) + 2 * bucket + bucket + G * (bucket + bucket * self.max_blocks) + bucket + 16
         host = torch.empty((n_ints,), dtype=torch.int32, pin_memory=True)
         dev = torch.empty((n_ints,), dtype=torch.int32, device=self.device)
-        ctx = self.pack([], [], pad_to=bucket, buffers=(host, dev))   # all rows padded: writes nothing
+        ctx = self.pack([], [], pad_to=bucket, buffers=(host, dev), ctx_limit=ctx_limit)   # all rows padded: writes nothing
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         before = COUNTERS["launches"]

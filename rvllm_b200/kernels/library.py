@@ -72,6 +72,7 @@ class CudaKernels:
     TCGEN05_ATTENTION_MIN_TOKENS = 16  # ... from this many tokens in the longest portion of the step
     DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
     DECODE_SPLIT_ROWS = 4   # ... when K has to be split over CTAs, only up to this many rows
+    FUSED_QKV_MAX_ROWS = 4  # rows up to which q/k/v product, rotation and cache write are one kernel
     pdl = os.environ.get("RVLLM_NO_PDL") != "1"   # programmatic dependent launch between kernels
 
     def __init__(self, device="cuda:0"):
@@ -221,24 +222,23 @@ class CudaKernels:
     @staticmethod
     def decode_splits(meta: AttentionMeta, num_heads: int, num_kv_heads: int) -> int:
         """Into how many CTAs the keys of a sequence are split in a decode step.  Three CTAs of
-        this kernel fit an SM (444 on the GPU).  A batch that cannot fill them is split until it
-        does (never below two 64-key tiles per split, never more than 16 splits: the merge grows
-        with them); a batch that overfills them a little is split so that the last wave is full."""
+        the kernel fit an SM (444 on the GPU) and run in waves; a CTA costs about 4 us plus 2.25 us
+        per 64-key tile (measured with all slots busy, where the tiles' bytes arrive at the speed
+        of the memory), the merge kernel 2.5 us.  The split count with the least modelled time is
+        taken: it fills one wave when the batch is small and keeps the last wave full when it is
+        large."""
         group = num_heads // num_kv_heads
         ctas = meta.num_seqs * num_kv_heads * ((group + 15) // 16)
         tiles = max(1, (meta.max_ctx_len + 63) // 64)
-        slots = 444
-        if ctas >= slots:
-            best, best_eff = 1, 0.0
-            for s in (1, 2, 3, 4):
-                if s > 1 and tiles // s < 4:
-                    break
-                waves = ctas * s / slots
-                eff = waves / -(-ctas * s // slots)
-                if eff > best_eff + 0.02:
-                    best, best_eff = s, eff
-            return best
-        return max(1, min(-(-slots // ctas), max(1, tiles // 2), 16))
+        best, best_t = 1, float("inf")
+        for s in range(1, min(16, tiles) + 1):
+            per = -(-tiles // s)
+            if s > 1 and per < 2:
+                break
+            t = -(-ctas * s // 444) * (4.0 + 2.25 * per) + (2.5 if s > 1 else 0.0)
+            if t < best_t - 1e-9:
+                best, best_t = s, t
+        return best
 
     def flash_attention(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
                         mode=0, num_splits=1, q_filter=0, max_q_len=None):
@@ -417,6 +417,60 @@ class CudaKernels:
             _ptr(status), self._stream())
         _check("gemm_tcgen05_decode", st)
         return out
+
+    def qkv_rope_cache_write(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
+                             num_heads, num_kv_heads, head_dim) -> torch.Tensor:
+        """The q/k/v product of the step's rows, then bias, rotation of q and k and the write of k
+        and v into the rows' cache slots; returns q [T, num_heads * head_dim].  For few bfloat16
+        rows this is one kernel (the decode GEMM's rotary epilogue); otherwise the product and
+        `rope_cache_write` run one after the other, with the same result."""
+        M, K = x.shape
+        if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < M <= self.FUSED_QKV_MAX_ROWS
+                and 128 % head_dim == 0 and K % 8 == 0 and weight.shape[0] == (num_heads + 2 * num_kv_heads) * head_dim):
+            return self._qkv_rope_fused(x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
+                                        num_heads, num_kv_heads, head_dim)
+        qkv = self.linear(x, weight)
+        return self.rope_cache_write(qkv, bias, positions, cos, sin, slot_mapping, cache_layer,
+                                     num_heads, num_kv_heads, head_dim)
+
+    def _qkv_rope_fused(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
+                        num_heads, num_kv_heads, head_dim, splits=None, status=None):
+        _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
+        _need(positions, "positions", torch.int32, 1); _need(slot_mapping, "slot_mapping", torch.int32, 1)
+        _need(cache_layer, "cache_layer", torch.bfloat16, 5)
+        M, K = x.shape
+        N = weight.shape[0]
+        if weight.shape[1] != K or positions.shape[0] < M or slot_mapping.shape[0] < M:
+            raise KernelError("qkv_rope_cache_write: shapes of x, weight, positions and slot_mapping do not agree")
+        if tuple(cache_layer.shape[1:3]) != (2, num_kv_heads) or cache_layer.shape[4] != head_dim:
+            raise KernelError(f"qkv_rope_cache_write: cache layer of shape {tuple(cache_layer.shape)} does not "
+                              f"fit {num_kv_heads} kv heads of {head_dim}")
+        if cos is not None:
+            _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+            if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+                raise KernelError("qkv_rope_cache_write: cos/sin tables must be [rows, head_dim/2]")
+        if bias is not None:
+            _need(bias, "bias", dims=1)
+        lib = self._lib("gemm_tcgen05_decode.cu")
+        tiles = lib.rv_gemm_decode_tiles(c_int(N), c_int(0))
+        if splits is None:
+            splits = self.gemm_splits(tiles, K)
+        splits = max(1, min(splits, (K + 63) // 64))
+        scratch = None
+        if splits > 1:
+            if self._decode_counters is None or self._decode_counters.numel() < tiles:
+                self._decode_counters = torch.zeros((max(tiles, 4096),), dtype=torch.int32, device=x.device)
+            mb = lib.rv_gemm_decode_padded_rows(c_int(M))
+            scratch = torch.empty((tiles * splits * mb * 128,), dtype=torch.float32, device=x.device)
+        q = torch.empty((M, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
+        st = lib.rv_gemm_decode_qkv_rope(
+            _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0),
+            _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(cache_layer), _ptr(q), c_int(M), c_int(K),
+            c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]),
+            c_int(cos.shape[0] if cos is not None else 1), c_int(splits), _ptr(scratch),
+            _ptr(self._decode_counters if splits > 1 else None), _ptr(status), self._stream())
+        _check("gemm_decode_qkv_rope", st)
+        return q
 
     def gate_up_silu(self, x, weight) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) for weight rows [Wg | Wu]: one fused kernel for few bfloat16

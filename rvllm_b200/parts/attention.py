@@ -47,12 +47,15 @@ class PagedAttention(Part):
         tables = self.position.rotation_tables() if self.position is not None else None
         cos, sin = tables if tables is not None else (None, None)
         # the bias is added inside the rotation kernel, in float, before the rotation
-        qkv = self.qkv(x, ctx, with_bias=False, rows=None if write_cache else self.q_dim)
         bias = self.qkv.bias
-        if bias is not None and not write_cache:
-            bias = bias[:self.q_dim]
-        q = k.rope_cache_write(qkv, bias, ctx.positions, cos, sin, meta.slot_mapping, cache.kv,
-                               self.num_heads, self.num_kv_heads, self.head_dim, write_kv=write_cache)
+        if write_cache:
+            q = k.qkv_rope_cache_write(x, self.qkv.weight, bias, ctx.positions, cos, sin, meta.slot_mapping,
+                                       cache.kv, self.num_heads, self.num_kv_heads, self.head_dim)
+        else:                             # a layer that reads another layer's cache needs its queries only
+            q_rows = self.qkv(x, ctx, with_bias=False, rows=self.q_dim)
+            q = k.rope_cache_write(q_rows, bias[:self.q_dim] if bias is not None else None, ctx.positions, cos, sin,
+                                   meta.slot_mapping, cache.kv, self.num_heads, self.num_kv_heads, self.head_dim,
+                                   write_kv=False)
         o = k.paged_attention(q, cache.kv, meta, self.num_heads, self.num_kv_heads, self.head_dim,
                               self.scale, self.window)
         return self.out(o, ctx, residual=residual)

@@ -62,6 +62,11 @@ class EmulatedKernels:
                 cache_layer[slot // ps, 1, :, slot % ps, :] = v[t]
         return q.reshape(T, q_dim).to(qkv.dtype)
 
+    def qkv_rope_cache_write(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
+                             num_heads, num_kv_heads, head_dim):
+        return self.rope_cache_write(self.linear(x, weight), bias, positions, cos, sin, slot_mapping, cache_layer,
+                                     num_heads, num_kv_heads, head_dim)
+
     def paged_attention(self, q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window):
         T = q.shape[0]
         ps = cache_layer.shape[3]

@@ -10,6 +10,8 @@ from gpu_tools import paged_setup, rel_err
 
 pytestmark = pytest.mark.gpu
 
+from rvllm_b200.kernels.library import COUNTERS
+
 F32_TOL = 2e-6
 BF16_TOL = 1e-2      # a bfloat16 result carries half an ulp (2^-9) of its own rounding
 
@@ -311,6 +313,66 @@ def test_gemm_tcgen05_decode_bf16(K, M, N, Kd):
     assert torch.equal(one, K.linear_decode(x, w, out_dtype=torch.float32, splits=4)[:1])     # batch-invariant
     if K._decode_counters is not None:
         assert int(K._decode_counters.abs().sum().item()) == 0
+
+
+@pytest.mark.parametrize("M,nh,nkv,hd,Kd,page,bias", [(1, 32, 8, 128, 4096, 16, False), (5, 6, 2, 32, 96, 8, True),
+                                                      (16, 5, 5, 16, 80, 16, True), (3, 4, 1, 64, 264, 4, False)])
+def test_qkv_product_with_rotation_and_cache_write_in_one_kernel(K, M, nh, nkv, hd, Kd, page, bias):
+    """The decode GEMM's rotary epilogue against the two-kernel path (same sums, so the same bits) and
+    against plain float64 arithmetic; rows with slot -1 write nothing; other cache slots stay untouched."""
+    torch.manual_seed(12)
+    N = (nh + 2 * nkv) * hd
+    x = torch.randn(M, Kd, device="cuda").bfloat16()
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(N, device="cuda").bfloat16() if bias else None
+    positions = torch.randint(0, 500, (M,), device="cuda", dtype=torch.int32)
+    ang = torch.arange(512, dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))[None]
+    cos, sin = ang.cos().float().cuda(), ang.sin().float().cuda()
+    pages = 2 * M + 3
+    slots = torch.randperm(pages * page)[:M].to(torch.int32).cuda()
+    if M > 2:
+        slots[1] = -1
+    cache_a = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda").bfloat16()
+    cache_b = cache_a.clone()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for splits in (None, 1, 3):
+        cache_a.fill_(7.0)
+        qa = K._qkv_rope_fused(x, w, b, positions, cos, sin, slots, cache_a, nh, nkv, hd, splits=splits, status=status)
+        qkv = K.linear_decode(x, w, splits=splits)
+        cache_b.fill_(7.0)
+        qb = K.rope_cache_write(qkv, b, positions, cos, sin, slots, cache_b, nh, nkv, hd)
+        assert torch.equal(qa, qb) and torch.equal(cache_a, cache_b)
+    assert int(status.item()) == 0
+    # plain arithmetic
+    y = x.double().cpu() @ w.double().cpu().t()
+    if bias:
+        y = y + b.double().cpu()
+    y = y.view(M, nh + 2 * nkv, hd)
+    c, s_ = ang.cos()[positions.cpu().long()][:, None, :], ang.sin()[positions.cpu().long()][:, None, :]
+    rot = lambda t: torch.cat([t[..., :hd // 2] * c - t[..., hd // 2:] * s_, t[..., :hd // 2] * s_ + t[..., hd // 2:] * c], -1)
+    assert rel_err(qa, rot(y[:, :nh]).reshape(M, nh * hd)) < BF16_TOL
+    kref, vref = rot(y[:, nh:nh + nkv]), y[:, nh + nkv:]
+    written = torch.zeros(pages, page, dtype=torch.bool)
+    for m in range(M):
+        sl = int(slots[m])
+        if sl < 0:
+            continue
+        written[sl // page, sl % page] = True
+        assert rel_err(cache_a[sl // page, 0, :, sl % page], kref[m]) < BF16_TOL
+        assert rel_err(cache_a[sl // page, 1, :, sl % page], vref[m]) < BF16_TOL
+    untouched = cache_a.cpu().float().permute(0, 3, 1, 2, 4)[~written]
+    assert bool((untouched == 7.0).all())
+    # the dispatching entry point runs the fused kernel (with its own choice of splits) for few rows
+    cache_a.fill_(7.0)
+    cache_b.fill_(7.0)
+    qa = K._qkv_rope_fused(x, w, b, positions, cos, sin, slots, cache_a, nh, nkv, hd)
+    before = COUNTERS["launches"]
+    qd = K.qkv_rope_cache_write(x, w, b, positions, cos, sin, slots, cache_b, nh, nkv, hd)
+    if M <= K.FUSED_QKV_MAX_ROWS:
+        assert COUNTERS["launches"] == before + 1 and torch.equal(qd, qa) and torch.equal(cache_a, cache_b)
+    else:                                   # more rows: the product and the rotation kernel, one after the other
+        assert COUNTERS["launches"] == before + 2
+        assert rel_err(qd, qa.double().cpu()) < BF16_TOL and rel_err(cache_b, cache_a.double().cpu()) < BF16_TOL
 
 
 TC_ATT_CASES = [
