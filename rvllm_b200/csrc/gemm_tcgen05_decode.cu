@@ -58,6 +58,10 @@ struct DecodeGemmParams {
 };
 
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
 
 template <int MB>
 __global__ void __launch_bounds__(NUM_THREADS)
@@ -213,6 +217,134 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (et == 0) is_last = atomicAdd(&p.counters[tile], 1) == p.splits - 1;
                 epi_sync();
                 finish = is_last != 0;
+                if (finish && !p.gated && (!p.q_out || p.hd >= 8)) {
+                    // Plain and rotary products: the last CTA adds the partials and runs the epilogue in one pass,
+                    // four neighbouring features per thread (16-byte reads of the partials, 8-byte
+                    // reads of the residual, 8- or 16-byte stores), four rows and four splits in
+                    // flight at a time.  A row is summed in split order, whatever the batch holds.
+                    __threadfence();
+                    const int fq = et & 31, rg = et >> 5;
+                    const int n0 = tile * TILE_F + 4 * fq;
+                    const float* base = p.scratch + ((size_t)tile * p.splits * MB) * TILE_F + 4 * fq;
+                    const bool vec = (p.N & 3) == 0 && n0 + 3 < p.N;
+                    if (p.q_out) {
+                        if (et < p.M) {
+                            const int pos = p.positions[et];
+                            row_pos[et] = pos < 0 ? 0 : (pos >= p.table_rows ? p.table_rows - 1 : pos);
+                            row_slot[et] = p.slot_mapping[et];
+                        }
+                        epi_sync();
+                    }
+                    float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (p.bias) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) if (n0 + e < p.N) bias4[e] = rv_load_param(p.bias, p.bias_dtype, n0 + e);
+                    }
+                    for (int m0 = rg; m0 < p.M; m0 += 16) {
+                        float4 acc[4];
+                        uint2 res[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            res[j] = make_uint2(0u, 0u);
+                            const int m = m0 + 4 * j;
+                            if (p.residual && vec && m < p.M)
+                                res[j] = __ldg(reinterpret_cast<const uint2*>(p.residual + (size_t)m * p.N + n0));
+                        }
+                        for (int s0 = 0; s0 < p.splits; s0 += 4) {
+                            float4 t[4][4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    t[j][i] = (m0 + 4 * j < p.M && s0 + i < p.splits)
+                                                  ? __ldcg(reinterpret_cast<const float4*>(base + ((size_t)(s0 + i) * MB + m0 + 4 * j) * TILE_F))
+                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    acc[j].x += t[j][i].x; acc[j].y += t[j][i].y; acc[j].z += t[j][i].z; acc[j].w += t[j][i].w;
+                                }
+                        }
+                        if (p.q_out) {
+                            // rotary epilogue: hd is a power of two >= 8 and N a multiple of it, so the four
+                            // features lie in one half of one head and their partners (hd / 2 further or
+                            // nearer) are held by the lane hd / 8 away; every lane takes part in the exchange
+                            const int hd = p.hd, half = hd >> 1;
+                            const int head = n0 / hd, d = n0 - head * hd;
+                            const bool live = n0 < p.N;
+                            const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
+                            const bool first = d < half;
+                            const int i0 = first ? d : d - half;
+                            const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int m = m0 + 4 * j;
+                                const bool row_ok = m < p.M;                     // uniform in the warp
+                                float own[4] = {acc[j].x, acc[j].y, acc[j].z, acc[j].w}, other[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    own[e] = __bfloat162float(__float2bfloat16_rn(own[e])) + bias4[e];
+                                    other[e] = __shfl_xor_sync(0xffffffffu, own[e], hd >> 3);
+                                }
+                                if (!row_ok || !live) continue;
+                                float v[4] = {own[0], own[1], own[2], own[3]};
+                                if ((is_q || is_k) && p.cos_t) {
+                                    const float4 c = __ldg(reinterpret_cast<const float4*>(p.cos_t + (size_t)row_pos[m] * half + i0));
+                                    const float4 sn = __ldg(reinterpret_cast<const float4*>(p.sin_t + (size_t)row_pos[m] * half + i0));
+                                    const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e)
+                                        v[e] = first ? own[e] * cc[e] - other[e] * ss[e] : other[e] * ss[e] + own[e] * cc[e];
+                                }
+                                uint2 o2;
+                                o2.x = pack_bf16x2(v[0], v[1]);
+                                o2.y = pack_bf16x2(v[2], v[3]);
+                                if (is_q) {
+                                    *reinterpret_cast<uint2*>(p.q_out + (size_t)m * p.nh * hd + n0) = o2;
+                                } else {
+                                    const int slot = row_slot[m];
+                                    if (slot >= 0) {
+                                        const int page = slot / p.page_size, off = slot - page * p.page_size;
+                                        *reinterpret_cast<uint2*>(p.kv_cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * p.nkv + kvh) * p.page_size + off) * hd + d) = o2;
+                                    }
+                                }
+                            }
+                            continue;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int m = m0 + 4 * j;
+                            if (m >= p.M || n0 >= p.N) continue;
+                            float v[4] = {acc[j].x + bias4[0], acc[j].y + bias4[1], acc[j].z + bias4[2], acc[j].w + bias4[3]};
+                            if (vec) {
+                                if (p.residual) {
+                                    const __nv_bfloat16* re = reinterpret_cast<const __nv_bfloat16*>(&res[j]);
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) v[e] += __bfloat162float(re[e]);
+                                }
+                                if (p.out_f32) {
+                                    *reinterpret_cast<float4*>((float*)p.out + (size_t)m * p.N + n0) = make_float4(v[0], v[1], v[2], v[3]);
+                                } else {
+                                    uint2 o2;
+                                    o2.x = pack_bf16x2(v[0], v[1]);
+                                    o2.y = pack_bf16x2(v[2], v[3]);
+                                    *reinterpret_cast<uint2*>((__nv_bfloat16*)p.out + (size_t)m * p.N + n0) = o2;
+                                }
+                            } else {
+                                for (int e = 0; e < 4 && n0 + e < p.N; ++e) {
+                                    float w = v[e];
+                                    if (p.residual) w += __bfloat162float(p.residual[(size_t)m * p.N + n0 + e]);
+                                    if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n0 + e] = w;
+                                    else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n0 + e] = __float2bfloat16_rn(w);
+                                }
+                            }
+                        }
+                    }
+                    if (et == 0) p.counters[tile] = 0;     // ready for the next launch
+                    finish = false;                        // nothing is left for the shared epilogue below
+                }
                 if (finish) {
                     __threadfence();
                     const float* base = p.scratch + ((size_t)tile * p.splits * MB) * TILE_F;
@@ -311,11 +443,19 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     const int n = tile * TILE_F + et;
                     if (n < p.N) {
                         const float b = p.bias ? rv_load_param(p.bias, p.bias_dtype, n) : 0.f;
-                        for (int m = 0; m < p.M; ++m) {
-                            float v = fin[et * (MB + 1) + m] + b;
-                            if (p.residual) v += __bfloat162float(p.residual[(size_t)m * p.N + n]);
-                            if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n] = v;
-                            else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
+                        for (int m0 = 0; m0 < p.M; m0 += 8) {
+                            float r8[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                r8[j] = (p.residual && m0 + j < p.M) ? __bfloat162float(p.residual[(size_t)(m0 + j) * p.N + n]) : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int m = m0 + j;
+                                if (m >= p.M) break;
+                                const float v = fin[et * (MB + 1) + m] + b + r8[j];
+                                if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n] = v;
+                                else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
+                            }
                         }
                     }
                 }

@@ -71,8 +71,8 @@ class CudaKernels:
     TCGEN05_ATTENTION = True           # prompt portions go to the tcgen05 attention kernel when it fits
     TCGEN05_ATTENTION_MIN_TOKENS = 16  # ... from this many tokens in the longest portion of the step
     DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
-    DECODE_SPLIT_ROWS = 4   # ... when K has to be split over CTAs, only up to this many rows
-    FUSED_QKV_MAX_ROWS = 4  # rows up to which q/k/v product, rotation and cache write are one kernel
+    DECODE_SPLIT_ROWS = 8   # ... when K has to be split over CTAs, only up to this many rows
+    FUSED_QKV_MAX_ROWS = 8  # rows up to which q/k/v product, rotation and cache write are one kernel
     pdl = os.environ.get("RVLLM_NO_PDL") != "1"   # programmatic dependent launch between kernels
 
     def __init__(self, device="cuda:0"):
