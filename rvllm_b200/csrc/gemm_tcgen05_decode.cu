@@ -21,6 +21,11 @@
 // the bias is added, q and k are rotated by the token's position (pairs i, i + head_dim/2, which
 // lie in one tile because 128 is a multiple of head_dim), q goes to its output and k and v go
 // straight into the token's slot of the paged cache - one kernel and one pass less per layer.
+// With `norm_gamma` set the activations arrive unnormalised and the kernel applies RMSNorm itself
+// (at most 16 rows): the epilogue warps, idle during the main loop, first form each row's
+// 1 / sqrt(mean(x^2) + eps) from global memory, then scale every activation tile in shared memory
+// by it and by gamma as soon as its TMA load has landed, and hand the tile to the MMA warp through a
+// second barrier per stage.  The norm kernel and its place in the chain of launches are saved.
 // Every mbarrier wait is bounded (see gemm_tcgen05.cu); no cluster, no multicast.
 //
 // Shapes: the five products of a layer and the LM head at decode time
@@ -35,6 +40,7 @@
 #define UMMA_K 16
 #define A_BYTES (TILE_F * BK * 2)
 #define NUM_THREADS 192
+#define MAX_NORM_K 8192      // longest K range of one CTA for which the fused norm keeps gamma in shared memory
 
 struct DecodeGemmParams {
     void* out;
@@ -55,6 +61,11 @@ struct DecodeGemmParams {
     const float* cos_t;              // [table_rows, hd / 2] or nullptr (no rotation)
     const float* sin_t;
     int nh, nkv, hd, page_size, table_rows;
+    // fused RMSNorm of the activations (norm_gamma != nullptr): x_raw are the rows the map_x loads
+    const void* norm_gamma;          // [K]
+    const __nv_bfloat16* x_raw;      // [M, K]
+    int norm_gamma_dtype;
+    float norm_eps;
 };
 
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -72,20 +83,23 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     constexpr int TMEM_COLS = MB < 32 ? 32 : MB;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    __shared__ __align__(8) uint64_t bars[3 * STAGES + 1];     // full, empty, accumulator ready, normalised
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
     __shared__ int is_last;
     __shared__ int row_pos[128], row_slot[128];
+    __shared__ float norm_red[4][16], norm_rstd[16];
 
     rv_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), tfull = smem_u32(&bars[2 * STAGES]);
+    const uint32_t normed0 = smem_u32(&bars[2 * STAGES + 1]);
+    const bool fused_norm = p.norm_gamma != nullptr;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
         is_last = 0;
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); mbar_init(normed0 + 8 * s, 4); }
         mbar_init(tfull, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -158,7 +172,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             uint32_t phase = 0;
             bool ok = true;
             for (int kb = kb0; kb < kb1; ++kb) {
-                if (!mbar_wait(full0 + 8 * stage, phase, &abort_flag, 3)) { ok = false; break; }
+                if (!mbar_wait((fused_norm ? normed0 : full0) + 8 * stage, phase, &abort_flag, 3)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t a_addr = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
                 const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
@@ -176,7 +190,81 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int f = quarter * 32 + lane;                  // feature row of this thread within the tile
         const int et = (warp - 2) * 32 + lane;              // 0..127 among the epilogue threads
         const bool have = kb1 > kb0;
+        float* gam = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES);   // gamma of this CTA's K range
+        if (fused_norm) {
+            // gamma is a weight: it is fetched before the wait for the previous kernel
+            const int nk = (kb1 - kb0) * BK;
+            for (int i = et; i < nk; i += 128) {
+                const int k = kb0 * BK + i;
+                gam[i] = k < p.K ? rv_load_param(p.norm_gamma, p.norm_gamma_dtype, k) : 0.f;
+            }
+        }
         rv_pdl_wait();
+        if (fused_norm) {
+            // ---- each row's 1 / sqrt(mean(x^2) + eps), four rows' loads in flight together
+            const int cpr = p.K >> 3;                       // 16-byte pieces per row
+            for (int m0 = 0; m0 < p.M; m0 += 4) {
+                float ss[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int c = et; c < cpr; c += 128) {
+                    uint4 v[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        v[j] = m0 + j < p.M ? __ldg(reinterpret_cast<const uint4*>(p.x_raw + (size_t)(m0 + j) * p.K) + c)
+                                            : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j]);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __bfloat1622float2(h[e]);
+                            ss[j] = fmaf(f.x, f.x, ss[j]);
+                            ss[j] = fmaf(f.y, f.y, ss[j]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    ss[j] = rv_warp_sum(ss[j]);
+                    if (lane == 0 && m0 + j < p.M) norm_red[warp - 2][m0 + j] = ss[j];
+                }
+            }
+            epi_sync();
+            if (et < p.M)
+                norm_rstd[et] = 1.0f / sqrtf((norm_red[0][et] + norm_red[1][et] + norm_red[2][et] + norm_red[3][et]) / (float)p.K + p.norm_eps);
+            epi_sync();
+            // ---- scale the activation tiles: thread = one 16-byte piece (row et / 8, piece et % 8 as
+            // stored; the 128-byte swizzle put logical piece c at position c ^ (row % 8))
+            const int row = et >> 3, pc = et & 7;
+            const int lc = pc ^ (row & 7);
+            const float r = row < p.M ? norm_rstd[row] : 0.f;
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                float g[8];
+                {
+                    const float4 g0 = *reinterpret_cast<const float4*>(gam + (kb - kb0) * BK + lc * 8);
+                    const float4 g1 = *reinterpret_cast<const float4*>(gam + (kb - kb0) * BK + lc * 8 + 4);
+                    g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+                }
+                // the whole warp leaves together, or a lane would wait in __syncwarp for ever
+                if (!__all_sync(0xffffffffu, mbar_wait(full0 + 8 * stage, phase, &abort_flag, 5))) break;
+                if (row < p.M) {
+                    uint4* piece = reinterpret_cast<uint4*>(tiles + (size_t)stage * STAGE_BYTES + A_BYTES + row * 128 + pc * 16);
+                    uint4 v = *piece;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = __bfloat1622float2(h[e]);
+                        h[e] = __floats2bfloat162_rn(f.x * r * g[2 * e], f.y * r * g[2 * e + 1]);
+                    }
+                    *piece = v;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(normed0 + 8 * stage);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
         if (have) mbar_wait(tfull, 0, &abort_flag, 4);
         // every epilogue thread comes here in bounded time; after the barrier they all see the same
         // abort flag, so the named barriers below are never reached by only some of them
@@ -475,12 +563,18 @@ template <int MB>
 static int launch_decode(const CUtensorMap& mw, const CUtensorMap& mx, const DecodeGemmParams& p, cudaStream_t stream) {
     const int stage = A_BYTES + MB * BK * 2;
     const int fin = TILE_F * (MB + 1) * 4;
-    const int smem = (STAGES * stage > fin ? STAGES * stage : fin) + 1024;
+    int smem = (STAGES * stage > fin ? STAGES * stage : fin) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             smem + MAX_NORM_K * 4);
         if (e != cudaSuccess) return (int)e;
         configured = true;
+    }
+    if (p.norm_gamma) {
+        const int num_kb = (p.K + BK - 1) / BK;
+        smem = STAGES * stage + ((num_kb + p.splits - 1) / p.splits) * BK * 4 + 1024;    // gamma of a CTA's K range after the stages
+        if (smem < fin + 1024) smem = fin + 1024;
     }
     RV_LAUNCH_ST = rv_launch(gemm_decode_kernel<MB>, dim3(p.n_tiles * p.splits), dim3(NUM_THREADS), smem, stream, mw, mx, p);
     return rv_launch_status();
@@ -500,6 +594,9 @@ static int run_decode(const void* x, const void* w, DecodeGemmParams p, cudaStre
     if (p.M < 0 || p.N <= 0 || p.K <= 0 || p.splits < 1) return RV_ERR_BAD_SIZE;
     if (p.M > 128) return RV_ERR_UNSUPPORTED;
     if (p.K % 8) return RV_ERR_UNSUPPORTED;
+    if (p.norm_gamma && p.M > 16) return RV_ERR_UNSUPPORTED;       // the fused norm serves one 16-row tile
+    if (p.norm_gamma && (p.K + BK - 1) / BK * BK > MAX_NORM_K) return RV_ERR_UNSUPPORTED;
+    p.x_raw = (const __nv_bfloat16*)x;
     if (p.splits > 1 && (!p.scratch || !p.counters)) return RV_ERR_BAD_SIZE;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return RV_ERR_ALIGNMENT;
     if (p.M == 0) return RV_OK;
@@ -523,6 +620,7 @@ static int run_decode(const void* x, const void* w, DecodeGemmParams p, cudaStre
 RV_EXPORT int rv_gemm_tcgen05_decode_bf16(const void* x, const void* w, const void* bias, int bias_dtype,
                                           const void* residual, void* out, int out_f32, int M, int N, int K,
                                           int gated, int splits, float* scratch, int* counters, int* status,
+                                          const void* norm_gamma, int norm_gamma_dtype, float norm_eps,
                                           cudaStream_t stream) {
     if (gated && ((N & 1) || bias || residual)) return RV_ERR_BAD_SIZE;
     if (residual && out_f32) return RV_ERR_BAD_SIZE;
@@ -530,16 +628,19 @@ RV_EXPORT int rv_gemm_tcgen05_decode_bf16(const void* x, const void* w, const vo
     p.out = out; p.residual = (const __nv_bfloat16*)residual; p.bias = bias; p.bias_dtype = bias_dtype;
     p.scratch = scratch; p.counters = counters; p.status = status;
     p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.gated = gated; p.splits = splits;
+    p.norm_gamma = norm_gamma; p.norm_gamma_dtype = norm_gamma_dtype; p.norm_eps = norm_eps;
     return run_decode(x, w, p, stream);
 }
 
+// norm_gamma (both entry points): RMSNorm weights [K] applied to x inside the kernel (M <= 16), or nullptr.
 // The q/k/v product of an attention layer with bias, rotation and the cache write in its epilogue.
 // w: [(nh + 2 nkv) * hd, K]; q_out: [M, nh * hd]; kv_cache: [pages, 2, nkv, page_size, hd].
 RV_EXPORT int rv_gemm_decode_qkv_rope(const void* x, const void* w, const void* bias, int bias_dtype,
                                       const int* positions, const float* cos_t, const float* sin_t,
                                       const int* slot_mapping, void* kv_cache, void* q_out, int M, int K,
                                       int nh, int nkv, int hd, int page_size, int table_rows, int splits,
-                                      float* scratch, int* counters, int* status, cudaStream_t stream) {
+                                      float* scratch, int* counters, int* status, const void* norm_gamma,
+                                      int norm_gamma_dtype, float norm_eps, cudaStream_t stream) {
     if (nh <= 0 || nkv <= 0 || hd <= 0 || (hd & 1) || page_size <= 0 || table_rows <= 0) return RV_ERR_BAD_SIZE;
     if (TILE_F % hd) return RV_ERR_UNSUPPORTED;           // a rotation pair must lie in one tile
     if ((cos_t == nullptr) != (sin_t == nullptr)) return RV_ERR_BAD_SIZE;
@@ -551,5 +652,6 @@ RV_EXPORT int rv_gemm_decode_qkv_rope(const void* x, const void* w, const void* 
     p.q_out = (__nv_bfloat16*)q_out; p.kv_cache = (__nv_bfloat16*)kv_cache; p.positions = positions;
     p.slot_mapping = slot_mapping; p.cos_t = cos_t; p.sin_t = sin_t;
     p.nh = nh; p.nkv = nkv; p.hd = hd; p.page_size = page_size; p.table_rows = table_rows;
+    p.norm_gamma = norm_gamma; p.norm_gamma_dtype = norm_gamma_dtype; p.norm_eps = norm_eps;
     return run_decode(x, w, p, stream);
 }

@@ -72,6 +72,7 @@ class CudaKernels:
     TCGEN05_ATTENTION_MIN_TOKENS = 16  # ... from this many tokens in the longest portion of the step
     DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
     DECODE_SPLIT_ROWS = 8   # ... when K has to be split over CTAs, only up to this many rows
+    FUSED_NORM_MAX_ROWS = 4 # rows up to which an RMSNorm is applied inside the decode GEMM that consumes it
     FUSED_QKV_MAX_ROWS = 8  # rows up to which q/k/v product, rotation and cache write are one kernel
     pdl = os.environ.get("RVLLM_NO_PDL") != "1"   # programmatic dependent launch between kernels
 
@@ -281,8 +282,9 @@ class CudaKernels:
         return out
 
     # ------------------------------------------------------------------ linear layers
-    def linear(self, x, weight, bias=None, residual=None, out_dtype=None) -> torch.Tensor:
+    def linear(self, x, weight, bias=None, residual=None, out_dtype=None, norm=None) -> torch.Tensor:
         """x [M, K] . weight [N, K]^T (+ bias) (+ residual), accumulated in float.
+        norm = (gamma, eps): x is normalised first (RMSNorm); few bfloat16 rows get it inside the GEMM.
 
         float32 operands: this project's FFMA kernel (no TF32 anywhere).  bfloat16 operands: the
         library GEMM; the residual is added in its float epilogue (beta = 1).  A weight kept in
@@ -293,6 +295,13 @@ class CudaKernels:
         if weight.shape[1] != K:
             raise KernelError(f"linear: x has {K} columns, weight has {weight.shape[1]}")
         out_dtype = out_dtype or x.dtype
+        if norm is not None:
+            fuse = (self._can_fuse_norm(x, norm) and weight.dtype == torch.bfloat16 and self._use_decode_gemm(M, N, K, False)
+                    and out_dtype in (torch.bfloat16, torch.float32)
+                    and (residual is None or (residual.dtype == torch.bfloat16 and out_dtype == torch.bfloat16)))
+            if fuse:
+                return self.linear_decode(x, weight, bias, residual, out_dtype, norm=norm)
+            x = self.rmsnorm(x, *norm)
         if weight.dtype == torch.float32:
             xf = x if x.dtype == torch.float32 else x.float()
             rf = None
@@ -388,8 +397,24 @@ class CudaKernels:
         num_kb = (K + 63) // 64
         return max(1, min(296 // max(n_tiles, 1), num_kb // 4, 32))
 
-    def linear_decode(self, x, weight, bias=None, residual=None, out_dtype=None, gated=False, splits=None, status=None):
-        """The weight-streaming tcgen05 GEMM for at most 128 rows of bfloat16 activations."""
+    def _norm_args(self, norm, K):
+        """ctypes arguments for a fused RMSNorm (gamma [K], eps), or the three nulls."""
+        if norm is None:
+            return c_void_p(0), c_int(0), c_float(0.0)
+        gamma, eps = norm
+        _need(gamma, "norm weight", dims=1)
+        if gamma.shape[0] != K:
+            raise KernelError(f"fused norm: gamma has {gamma.shape[0]} entries for rows of {K}")
+        return _ptr(gamma), c_int(self._dt(gamma, "norm weight")), c_float(eps)
+
+    def _can_fuse_norm(self, x, norm) -> bool:
+        return (norm is not None and x.dtype == torch.bfloat16 and 0 < x.shape[0] <= self.FUSED_NORM_MAX_ROWS
+                and x.shape[1] <= 8128)       # the kernel keeps gamma of its K range in shared memory
+
+    def linear_decode(self, x, weight, bias=None, residual=None, out_dtype=None, gated=False, splits=None, status=None,
+                      norm=None):
+        """The weight-streaming tcgen05 GEMM for at most 128 rows of bfloat16 activations.
+        norm = (gamma, eps): RMSNorm applied to x inside the kernel (at most 16 rows)."""
         _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
         M, K = x.shape
         N = weight.shape[0]
@@ -414,27 +439,32 @@ class CudaKernels:
             _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0), _ptr(residual),
             _ptr(out), c_int(1 if out_dtype == torch.float32 else 0), c_int(M), c_int(N), c_int(K),
             c_int(1 if gated else 0), c_int(splits), _ptr(scratch), _ptr(self._decode_counters if splits > 1 else None),
-            _ptr(status), self._stream())
+            _ptr(status), *self._norm_args(norm, K), self._stream())
         _check("gemm_tcgen05_decode", st)
         return out
 
     def qkv_rope_cache_write(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
-                             num_heads, num_kv_heads, head_dim) -> torch.Tensor:
+                             num_heads, num_kv_heads, head_dim, norm=None) -> torch.Tensor:
         """The q/k/v product of the step's rows, then bias, rotation of q and k and the write of k
         and v into the rows' cache slots; returns q [T, num_heads * head_dim].  For few bfloat16
         rows this is one kernel (the decode GEMM's rotary epilogue); otherwise the product and
-        `rope_cache_write` run one after the other, with the same result."""
+        `rope_cache_write` run one after the other, with the same result.
+        norm = (gamma, eps): x is normalised first (RMSNorm), inside the fused kernel where that runs."""
         M, K = x.shape
         if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < M <= self.FUSED_QKV_MAX_ROWS
                 and 128 % head_dim == 0 and K % 8 == 0 and weight.shape[0] == (num_heads + 2 * num_kv_heads) * head_dim):
+            if norm is not None and not self._can_fuse_norm(x, norm):
+                x, norm = self.rmsnorm(x, *norm), None
             return self._qkv_rope_fused(x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
-                                        num_heads, num_kv_heads, head_dim)
+                                        num_heads, num_kv_heads, head_dim, norm=norm)
+        if norm is not None:
+            x = self.rmsnorm(x, *norm)
         qkv = self.linear(x, weight)
         return self.rope_cache_write(qkv, bias, positions, cos, sin, slot_mapping, cache_layer,
                                      num_heads, num_kv_heads, head_dim)
 
     def _qkv_rope_fused(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
-                        num_heads, num_kv_heads, head_dim, splits=None, status=None):
+                        num_heads, num_kv_heads, head_dim, splits=None, status=None, norm=None):
         _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
         _need(positions, "positions", torch.int32, 1); _need(slot_mapping, "slot_mapping", torch.int32, 1)
         _need(cache_layer, "cache_layer", torch.bfloat16, 5)
@@ -468,17 +498,22 @@ class CudaKernels:
             _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(cache_layer), _ptr(q), c_int(M), c_int(K),
             c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]),
             c_int(cos.shape[0] if cos is not None else 1), c_int(splits), _ptr(scratch),
-            _ptr(self._decode_counters if splits > 1 else None), _ptr(status), self._stream())
+            _ptr(self._decode_counters if splits > 1 else None), _ptr(status), *self._norm_args(norm, K), self._stream())
         _check("gemm_decode_qkv_rope", st)
         return q
 
-    def gate_up_silu(self, x, weight) -> torch.Tensor:
+    def gate_up_silu(self, x, weight, norm=None) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) for weight rows [Wg | Wu]: one fused kernel for few bfloat16
-        rows, else the product followed by the SiLU kernel."""
+        rows, else the product followed by the SiLU kernel.  norm = (gamma, eps): x is normalised
+        first (RMSNorm), inside the kernel for few rows."""
         M, K = x.shape
         if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[0] % 2 == 0 \
                 and self._use_decode_gemm(M, weight.shape[0], K, True):
-            return self.linear_decode(x, weight, gated=True)
+            if norm is not None and not self._can_fuse_norm(x, norm):
+                x, norm = self.rmsnorm(x, *norm), None
+            return self.linear_decode(x, weight, gated=True, norm=norm)
+        if norm is not None:
+            x = self.rmsnorm(x, *norm)
         if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < M <= self.SKINNY_MAX_ROWS \
                 and K % 8 == 0 and weight.shape[0] % 2 == 0:
             return self.linear_skinny(x, weight, gated=True)

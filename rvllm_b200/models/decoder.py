@@ -120,8 +120,9 @@ class DecoderModel:
     def compute_logits(self, hidden: torch.Tensor, ctx) -> torch.Tensor:
         """float32 logits [R, vocab] at the rows `ctx.logit_rows` of the step."""
         rows = ctx.kernels.gather_rows(hidden, ctx.logit_rows)
-        y = self.final_norm(rows, ctx)
-        return ctx.kernels.linear(y, self.lm_head, None, None, torch.float32)
+        if hasattr(self.final_norm, "as_rms"):       # the LM head's product applies the norm itself for few rows
+            return ctx.kernels.linear(rows, self.lm_head, None, None, torch.float32, norm=self.final_norm.as_rms())
+        return ctx.kernels.linear(self.final_norm(rows, ctx), self.lm_head, None, None, torch.float32)
 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:

@@ -15,6 +15,8 @@ from .linear import Linear
 
 
 class PagedAttention(Part):
+    takes_input_norm = True           # the q/k/v product can apply the layer's input RMSNorm itself
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  qkv_bias: bool = False, out_bias: bool = False, window: Optional[int] = None,
                  position=None):
@@ -41,7 +43,7 @@ class PagedAttention(Part):
     def cache_need(self):
         return KvCacheNeed(self.num_kv_heads, self.head_dim, self.window)
 
-    def __call__(self, x, ctx, cache, residual=None, write_cache=True):
+    def __call__(self, x, ctx, cache, residual=None, write_cache=True, input_norm=None):
         k = ctx.kernels
         meta = ctx.attention[cache.group]
         tables = self.position.rotation_tables() if self.position is not None else None
@@ -50,8 +52,10 @@ class PagedAttention(Part):
         bias = self.qkv.bias
         if write_cache:
             q = k.qkv_rope_cache_write(x, self.qkv.weight, bias, ctx.positions, cos, sin, meta.slot_mapping,
-                                       cache.kv, self.num_heads, self.num_kv_heads, self.head_dim)
+                                       cache.kv, self.num_heads, self.num_kv_heads, self.head_dim, norm=input_norm)
         else:                             # a layer that reads another layer's cache needs its queries only
+            if input_norm is not None:
+                x = k.rmsnorm(x, *input_norm)
             q_rows = self.qkv(x, ctx, with_bias=False, rows=self.q_dim)
             q = k.rope_cache_write(q_rows, bias[:self.q_dim] if bias is not None else None, ctx.positions, cos, sin,
                                    meta.slot_mapping, cache.kv, self.num_heads, self.num_kv_heads, self.head_dim,

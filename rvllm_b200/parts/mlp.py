@@ -9,6 +9,8 @@ from .linear import Linear
 
 
 class GatedMLP(Part):
+    takes_input_norm = True           # the gate/up product can apply the layer's RMSNorm itself
+
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
         from ..errors import ConfigError
         if activation != "silu":
@@ -24,8 +26,8 @@ class GatedMLP(Part):
         self.gate_up.bind(get)
         self.down.bind(get)
 
-    def __call__(self, x, ctx, residual=None):
-        h = ctx.kernels.gate_up_silu(x, self.gate_up.weight)
+    def __call__(self, x, ctx, residual=None, input_norm=None):
+        h = ctx.kernels.gate_up_silu(x, self.gate_up.weight, norm=input_norm)
         return self.down(h, ctx, residual=residual)
 
 

@@ -23,5 +23,9 @@ class RMSNorm(Part):
     def __call__(self, x, ctx):
         return ctx.kernels.rmsnorm(x, self.weight, self.eps)
 
+    def as_rms(self):
+        """(gamma, eps) for a part that applies this norm to its own input (see parts/block.py)."""
+        return self.weight, self.eps
+
 
 NORMS.register("rmsnorm", RMSNorm)

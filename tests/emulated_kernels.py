@@ -63,8 +63,8 @@ class EmulatedKernels:
         return q.reshape(T, q_dim).to(qkv.dtype)
 
     def qkv_rope_cache_write(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
-                             num_heads, num_kv_heads, head_dim):
-        return self.rope_cache_write(self.linear(x, weight), bias, positions, cos, sin, slot_mapping, cache_layer,
+                             num_heads, num_kv_heads, head_dim, norm=None):
+        return self.rope_cache_write(self.linear(x, weight, norm=norm), bias, positions, cos, sin, slot_mapping, cache_layer,
                                      num_heads, num_kv_heads, head_dim)
 
     def paged_attention(self, q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window):
@@ -95,7 +95,9 @@ class EmulatedKernels:
                     out[t, h] = (p @ V).to(q.dtype)
         return out.view(T, num_heads * head_dim)
 
-    def linear(self, x, weight, bias=None, residual=None, out_dtype=None):
+    def linear(self, x, weight, bias=None, residual=None, out_dtype=None, norm=None):
+        if norm is not None:
+            x = self.rmsnorm(x, *norm)
         y = x.float() @ weight.float().t()
         if bias is not None:
             y = y + bias.float()
@@ -103,8 +105,8 @@ class EmulatedKernels:
             y = y + residual.float()
         return y.to(out_dtype or x.dtype)
 
-    def gate_up_silu(self, x, weight):
-        return self.silu_mul(self.linear(x, weight))
+    def gate_up_silu(self, x, weight, norm=None):
+        return self.silu_mul(self.linear(x, weight, norm=norm))
 
     def sample(self, logits, temperature=None, top_k=None, top_p=None, seeds=None, draw_index=None):
         from plain_impl import sample as plain_sample

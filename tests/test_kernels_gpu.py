@@ -362,6 +362,14 @@ def test_qkv_product_with_rotation_and_cache_write_in_one_kernel(K, M, nh, nkv, 
         assert rel_err(cache_a[sl // page, 1, :, sl % page], vref[m]) < BF16_TOL
     untouched = cache_a.cpu().float().permute(0, 3, 1, 2, 4)[~written]
     assert bool((untouched == 7.0).all())
+    # with the layer's input norm inside the kernel
+    gamma = (1 + 0.1 * torch.randn(Kd, device="cuda")).bfloat16()
+    cache_a.fill_(7.0)
+    cache_b.fill_(7.0)
+    qn = K._qkv_rope_fused(x, w, b, positions, cos, sin, slots, cache_a, nh, nkv, hd, norm=(gamma, 1e-6), status=status)
+    qm = K._qkv_rope_fused(K.rmsnorm(x, gamma, 1e-6), w, b, positions, cos, sin, slots, cache_b, nh, nkv, hd)
+    assert rel_err(qn, qm.double().cpu()) < 4e-3 and rel_err(cache_a, cache_b.double().cpu()) < 4e-3
+    assert int(status.item()) == 0
     # the dispatching entry point runs the fused kernel (with its own choice of splits) for few rows
     cache_a.fill_(7.0)
     cache_b.fill_(7.0)
@@ -373,6 +381,44 @@ def test_qkv_product_with_rotation_and_cache_write_in_one_kernel(K, M, nh, nkv, 
     else:                                   # more rows: the product and the rotation kernel, one after the other
         assert COUNTERS["launches"] == before + 2
         assert rel_err(qd, qa.double().cpu()) < BF16_TOL and rel_err(cache_b, cache_a.double().cpu()) < BF16_TOL
+
+
+@pytest.mark.parametrize("M,N,Kd,gamma_dtype", [(1, 4096, 4096, torch.bfloat16), (8, 512, 328, torch.float32),
+                                                (5, 200, 1032, torch.bfloat16), (16, 384, 64, torch.bfloat16)])
+def test_rmsnorm_inside_the_decode_gemm(K, M, N, Kd, gamma_dtype):
+    """RMSNorm applied to the activation tiles in shared memory (the consuming GEMM's own warps)
+    against the norm kernel followed by the same GEMM, for the plain, gated and rotary epilogues,
+    with and without a split of K; and against plain float64 arithmetic."""
+    torch.manual_seed(13)
+    x = (torch.randn(M, Kd, device="cuda") * 3).bfloat16()
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    gamma = (1 + 0.1 * torch.randn(Kd, device="cuda")).to(gamma_dtype)
+    eps = 1e-5
+    r = torch.randn(M, N, device="cuda").bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    h = K.rmsnorm(x, gamma, eps)
+    xd = x.double().cpu()
+    hd_ = xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + eps) * gamma.double().cpu()
+    ref = hd_ @ w.double().cpu().t()
+    for splits in (1, 3, None):
+        a = K.linear_decode(x, w, None, r, splits=splits, status=status, norm=(gamma, eps))
+        b = K.linear_decode(h, w, None, r, splits=splits, status=status)
+        assert rel_err(a, b.double().cpu()) < 4e-3            # the two round the normalised row alike up to the last bit of 1/rms
+        assert rel_err(a, ref + r.double().cpu()) < BF16_TOL
+        g = K.linear_decode(x, w, gated=True, splits=splits, status=status, norm=(gamma, eps))
+        assert rel_err(g, K.linear_decode(h, w, gated=True, splits=splits, status=status).double().cpu()) < 4e-3
+    one = K.linear_decode(x[:1].contiguous(), w, out_dtype=torch.float32, splits=2, norm=(gamma, eps))
+    assert torch.equal(one, K.linear_decode(x, w, out_dtype=torch.float32, splits=2, norm=(gamma, eps))[:1])   # batch-invariant
+    assert int(status.item()) == 0
+    # dispatching entry points: fused for few rows, norm kernel first otherwise - same numbers within rounding
+    y = K.linear(x, w, None, r, norm=(gamma, eps))
+    assert rel_err(y, ref + r.double().cpu()) < BF16_TOL
+    many = torch.cat([x] * 5)
+    y5 = K.linear(many, w, None, None, norm=(gamma, eps))
+    assert rel_err(y5[:M], ref) < BF16_TOL
+    gref = ref[:, :N // 2] / (1 + torch.exp(-ref[:, :N // 2])) * ref[:, N // 2:]
+    assert rel_err(K.gate_up_silu(x, w, norm=(gamma, eps)), gref) < 2 * BF16_TOL
+    assert rel_err(K.gate_up_silu(many, w, norm=(gamma, eps))[:M], gref) < 2 * BF16_TOL
 
 
 TC_ATT_CASES = [
