@@ -392,10 +392,14 @@ class CudaKernels:
         return M <= self.DECODE_SPLIT_ROWS or self.gemm_splits(tiles, K) == 1
 
     def gemm_splits(self, n_tiles: int, K: int) -> int:
-        """Into how many CTAs the K dimension of a decode GEMM is cut: about two CTAs per SM, at
-        least four 64-wide k blocks each."""
+        """Into how many CTAs the K dimension of a decode GEMM is cut: about two CTAs per SM with
+        at least four 64-wide k blocks each, three per SM where that still leaves sixteen (measured:
+        cutting finer costs more in the merge than it gains in bandwidth)."""
         num_kb = (K + 63) // 64
-        return max(1, min(296 // max(n_tiles, 1), num_kb // 4, 32))
+        two, three = 296 // max(n_tiles, 1), 444 // max(n_tiles, 1)
+        if three > two and num_kb // three >= 16:
+            return min(three, 32)
+        return max(1, min(two, num_kb // 4, 32))
 
     def _norm_args(self, norm, K):
         """ctypes arguments for a fused RMSNorm (gamma [K], eps), or the three nulls."""
