@@ -1,6 +1,7 @@
-"""A toy mixer with state of its own, defined here, is registered, built into a model through a
-toy architecture, loaded from a random-weights folder and stepped - prompts cut into portions,
-decoding, several live requests, slots used again - without touching the framework's files.
+"""Toy parts defined here - a mixer with state of its own, a feed-forward with a router, a position
+encoding added to the embeddings - are registered, built into a model through a toy architecture,
+loaded from a random-weights folder and stepped - prompts cut into portions, decoding, several
+live requests, slots used again - without touching the framework's files.
 
 The toy mixer keeps a running, decayed sum of projected inputs per request:
     s_t = decay * s_{t-1} + x_t W^T ;  y_t = s_t
@@ -18,7 +19,7 @@ import torch
 
 from rvllm_b200 import config_from_dict, kernels as kernel_pkg, register_architecture, write_random_model
 from rvllm_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry, unregister_architecture
-from rvllm_b200.parts import MIXERS, Part, StateNeed, TensorSpec
+from rvllm_b200.parts import FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, Part, StateNeed, TensorSpec
 
 DECAY = 0.9
 
@@ -59,6 +60,60 @@ class RunningSumMixer(Part):
         return y if residual is None else residual + y
 
 
+class RoutedExperts(Part):
+    """Feed-forward with a router: y = sum_e softmax(x R^T)_e * down_e(relu(up_e x)), the router in
+    float32.  Every expert weighs in (no hard choice that a rounding could flip)."""
+
+    def __init__(self, hidden_size: int, expert_size: int, num_experts: int):
+        self.hidden_size, self.expert_size, self.num_experts = hidden_size, expert_size, num_experts
+        self.router = None
+        self.up, self.down = [], []
+
+    def tensor_specs(self):
+        specs = {"router.weight": TensorSpec((self.num_experts, self.hidden_size), "matrix")}
+        for e in range(self.num_experts):
+            specs[f"experts.{e}.up.weight"] = TensorSpec((self.expert_size, self.hidden_size), "matrix")
+            specs[f"experts.{e}.down.weight"] = TensorSpec((self.hidden_size, self.expert_size), "matrix")
+        return specs
+
+    def bind(self, get):
+        self.router = get("router.weight")
+        self.up = [get(f"experts.{e}.up.weight") for e in range(self.num_experts)]
+        self.down = [get(f"experts.{e}.down.weight") for e in range(self.num_experts)]
+
+    def __call__(self, x, ctx, residual=None):
+        xf = x.float()
+        gate = torch.softmax(xf @ self.router.float().t() * 8.0, dim=-1)           # [T, E]
+        y = torch.zeros_like(xf)
+        for e in range(self.num_experts):
+            y = y + gate[:, e:e + 1] * (torch.relu(xf @ self.up[e].float().t()) @ self.down[e].float().t())
+        y = y.to(x.dtype)
+        return y if residual is None else residual + y
+
+
+class LearnedPositions(Part):
+    """A table of position vectors added to the embeddings; no rotation tables."""
+
+    def __init__(self, hidden_size: int, max_len: int):
+        self.hidden_size, self.max_len = hidden_size, max_len
+        self.weight = None
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((self.max_len, self.hidden_size), "matrix")}
+
+    def bind(self, get):
+        self.weight = get("weight")
+
+    def prepare(self, max_len, device):
+        pass
+
+    def rotation_tables(self):
+        return None
+
+    def on_embeddings(self, x, ctx):
+        return x + self.weight[ctx.positions.long()].to(x.dtype)
+
+
 @dataclass(frozen=True)
 class ToyConfig:
     hidden_size: int
@@ -84,8 +139,11 @@ class ToyConfig:
                                                      "head_dim": 16, "scale": 0.25, "position": "rope"})
             else:
                 mixer = PartSpec("running_sum", {"hidden_size": self.hidden_size, "state_size": self.state_size})
+            # even layers have the routed feed-forward, odd ones the gated MLP
+            ffn = (PartSpec("gated_mlp", {"hidden_size": self.hidden_size, "intermediate_size": 40}) if i % 2 else
+                   PartSpec("routed_experts", {"hidden_size": self.hidden_size, "expert_size": 12, "num_experts": 3}))
             layers.append(LayerSpec(prefix=f"layers.{i}.", block=PartSpec("prenorm_residual"), mixer=mixer,
-                                    feed_forward=PartSpec("gated_mlp", {"hidden_size": self.hidden_size, "intermediate_size": 40}),
+                                    feed_forward=ffn,
                                     mixer_norm=norm, feed_forward_norm=norm,
                                     names={"mixer": "mixer.", "feed_forward": "ffn.", "mixer_norm": "norm1.", "feed_forward_norm": "norm2."}))
         # the run order names layer 0 twice (its second run has a state of its own) and lets the
@@ -94,7 +152,8 @@ class ToyConfig:
         return ModelSpec(architecture="ToyForCausalLM", hidden_size=self.hidden_size, vocab_size=self.vocab_size,
                          max_position_embeddings=256, embedding_name="embed.weight", layers=tuple(layers),
                          run_order=order, final_norm=norm, final_norm_prefix="final_norm.", lm_head_name=None,
-                         position_encodings={"rope": PartSpec("rotary", {"head_dim": 16, "theta": 10000.0})})
+                         position_encodings={"rope": PartSpec("rotary", {"head_dim": 16, "theta": 10000.0}),
+                                             "abs": PartSpec("learned_positions", {"hidden_size": self.hidden_size, "max_len": 256})})
 
 
 TOY = {"architectures": ["ToyForCausalLM"], "hidden_size": 24, "state_size": 10, "vocab_size": 50, "num_layers": 2}
@@ -103,9 +162,13 @@ TOY = {"architectures": ["ToyForCausalLM"], "hidden_size": 24, "state_size": 10,
 @pytest.fixture
 def toy_registered():
     MIXERS.register("running_sum", RunningSumMixer)
+    FEED_FORWARDS.register("routed_experts", RoutedExperts)
+    POSITION_ENCODINGS.register("learned_positions", LearnedPositions)
     register_architecture("ToyForCausalLM", ToyConfig)
     yield
     MIXERS.unregister("running_sum")
+    FEED_FORWARDS.unregister("routed_experts")
+    POSITION_ENCODINGS.unregister("learned_positions")
     unregister_architecture("ToyForCausalLM")
 
 
@@ -115,7 +178,7 @@ def reference_logits(folder, tokens):
     from safetensors.torch import load_file
     w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
     T = len(tokens)
-    x = w["embed.weight"][torch.tensor(tokens)]
+    x = w["embed.weight"][torch.tensor(tokens)] + w["position.abs.weight"][:T]
     inv = P.rope_inv_freq(16, 10000.0, None)
     kv = {}
 
@@ -143,7 +206,12 @@ def reference_logits(folder, tokens):
         h = P.rms_norm(x, w[p + "norm1.weight"], 1e-5)
         x = x + (running_sum(h, p) if layer == 0 else attention(h, p, reuse))
         h = P.rms_norm(x, w[p + "norm2.weight"], 1e-5)
-        x = x + P.gated_mlp(h, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
+        if layer == 0:
+            gate = torch.softmax(h @ w[p + "ffn.router.weight"].t() * 8.0, dim=-1)
+            for e in range(3):
+                x = x + gate[:, e:e + 1] * (torch.relu(h @ w[p + f"ffn.experts.{e}.up.weight"].t()) @ w[p + f"ffn.experts.{e}.down.weight"].t())
+        else:
+            x = x + P.gated_mlp(h, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
     return P.rms_norm(x, w["final_norm.weight"], 1e-5) @ w["embed.weight"].t()
 
 
