@@ -358,17 +358,11 @@ flash_paged_kernel(const FlashParams p) {
     }
 }
 
-// Merge the partial results of the key splits: one block per (token, head), one thread per
-// element of the head.  Eight splits are read at a time, maxima, denominators and sums together,
-// so that the kernel costs one round trip to L2 per eight splits; the running result is rescaled
-// as in the attention kernel itself.
-__global__ void flash_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                     __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
-    rv_pdl_launch_dependents();
-    rv_pdl_wait();
-    const int row = blockIdx.x;
-    const int d = threadIdx.x;
-    if (d >= HEAD_DIM) return;
+// Element d of a row's attention output from the partial results of the key splits.  Eight splits
+// are read at a time, maxima, denominators and sums together, so that the merge costs one round
+// trip to L2 per eight splits; the running result is rescaled as in the attention kernel itself.
+__device__ __forceinline__ float merge_splits(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              size_t row, size_t rows, int num_splits, int d) {
     float m_run = -INFINITY, l_run = 0.f, acc = 0.f;
     for (int s0 = 0; s0 < num_splits; s0 += 8) {
         float m[8], l[8], o[8];
@@ -396,8 +390,392 @@ __global__ void flash_combine_kernel(const float* __restrict__ part_o, const flo
         }
         m_run = m_new;
     }
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    out[(size_t)row * HEAD_DIM + d] = __float2bfloat16_rn(acc * inv);
+    return acc * (l_run > 0.f ? 1.f / l_run : 0.f);
+}
+
+// Merge the partial results of the key splits: one block per (token, head), one thread per
+// element of the head.
+__global__ void flash_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                     __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    const int d = threadIdx.x;
+    if (d >= HEAD_DIM) return;
+    out[(size_t)blockIdx.x * HEAD_DIM + d] = __float2bfloat16_rn(merge_splits(part_o, part_ml, blockIdx.x, rows, num_splits, d));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention with the work cut evenly: one token per sequence, as the decode tiling above,
+// but the grid is a fixed number of CTAs (as many as stay resident: three per SM) and every CTA
+// takes the same number of 64-key tiles.  The tiles of all (sequence, kv head) pairs form one list,
+// sequence-major; CTA c takes the tiles [c W, (c + 1) W), W = ceil(total / CTAs), which is a run of
+// pieces, each a range of tiles of one pair.  So no wave is left half empty and a CTA's fixed cost
+// (about 4 us in the kernel above) is paid once or twice per CTA, not once per split.  Every piece
+// leaves (unnormalised sum, maximum, denominator) in scratch memory at [piece of its pair]; the
+// merge kernel below adds a pair's pieces, whose number the attention kernel writes per pair.
+#define BAL_MAX_SEQS 256      // sequences per step this kernel serves (their tile counts live in shared memory)
+#define BAL_TABLE_CACHE 512   // block-table entries of a piece kept in shared memory
+
+struct BalancedParams {
+    const __nv_bfloat16* q;        // [n_tokens, nh, HEAD_DIM]
+    const __nv_bfloat16* cache;
+    const int* block_tables;       // [num_seqs, max_blocks]
+    const int* cu_seqlens;
+    const int* ctx_lens;
+    __nv_bfloat16* out;
+    float* part_o;                 // [max_pieces, n_tokens * nh, HEAD_DIM]
+    float* part_ml;                // [max_pieces, n_tokens * nh, 2]
+    int* piece_count;              // [num_seqs * nkv]: pieces of each pair, written by the kernel
+    int n_tokens, num_seqs, nh, nkv, page_shift, page_size, max_blocks, max_pieces;
+    float scale_log2e;
+    int window;
+};
+
+template <int NSTAGES>
+__global__ void __launch_bounds__(128)
+flash_decode_balanced_kernel(const BalancedParams p) {
+    rv_pdl_launch_dependents();
+    constexpr int HD = HEAD_DIM;
+    constexpr int WARPS_N = 4, KW = KV_TILE / WARPS_N, NTHREADS = 128, CHUNKS = HD / 8;
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ int s_first[BAL_MAX_SEQS + 1];          // tiles of the sequences before this one
+    __shared__ int s_lo[BAL_MAX_SEQS];                 // first key tile of the sequence (window)
+    __shared__ int s_table[BAL_TABLE_CACHE];
+    const int tid = threadIdx.x, lane = tid & 31, warp_n = tid >> 5;
+    const int quad = lane >> 2, tq = lane & 3;
+    const int G = p.nh / p.nkv;
+
+    // ---- the list of tiles (step metadata: read before the wait for the previous kernel)
+    for (int s = tid; s < p.num_seqs; s += NTHREADS) {
+        const int ctx = p.ctx_lens[s];
+        const int q_len = p.cu_seqlens[s + 1] - p.cu_seqlens[s];
+        int lo = 0, n = 0;
+        if (q_len == 1 && ctx > 0) {
+            const int pos = ctx - 1;
+            const int key_lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+            lo = key_lo / KV_TILE;
+            n = (ctx + KV_TILE - 1) / KV_TILE - lo;
+        }
+        s_lo[s] = lo;
+        s_first[s + 1] = n;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        s_first[0] = 0;
+        for (int s = 0; s < p.num_seqs; ++s) { run += s_first[s + 1]; s_first[s + 1] = run; }
+    }
+    __syncthreads();
+    const int total = s_first[p.num_seqs] * p.nkv;
+    const int ctas = gridDim.x, cta = blockIdx.x;
+    const int W = total > 0 ? (total + ctas - 1) / ctas : 1;
+    // pieces of every pair, for the merge kernel: each CTA writes its share of the pairs
+    for (int pair = cta * NTHREADS + tid; pair < p.num_seqs * p.nkv; pair += ctas * NTHREADS) {
+        const int s = pair / p.nkv, kvh = pair - s * p.nkv;
+        const int n = s_first[s + 1] - s_first[s];
+        int count = 0;
+        if (n > 0) {
+            const int u_pair = s_first[s] * p.nkv + kvh * n;
+            count = (u_pair + n - 1) / W - u_pair / W + 1;
+        }
+        p.piece_count[pair] = count;
+    }
+    int u = cta * W;
+    const int u_end = min(total, u + W);
+    rv_pdl_wait();          // every CTA, with or without work, keeps the order of the chain of kernels
+    if (u >= u_end) return;
+
+    const size_t page_stride = (size_t)2 * p.nkv * p.page_size * HD;
+    const size_t v_off = (size_t)p.nkv * p.page_size * HD;
+    const size_t rows_all = (size_t)p.n_tokens * p.nh;
+
+    // first sequence of the run: the last one whose tiles start at or before u
+    int seq;
+    {
+        int lo = 0, hi = p.num_seqs - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (s_first[mid] * p.nkv <= u) lo = mid; else hi = mid - 1;
+        }
+        seq = lo;
+    }
+    while (u < u_end) {
+        while (s_first[seq + 1] * p.nkv <= u) ++seq;                    // skips sequences without tiles
+        const int n_seq = s_first[seq + 1] - s_first[seq];
+        const int in_seq = u - s_first[seq] * p.nkv;
+        const int kvh = in_seq / n_seq;
+        const int t_rel = in_seq - kvh * n_seq;
+        const int n_here = min(n_seq - t_rel, u_end - u);              // tiles of this piece
+        const int u_pair = u - t_rel;
+        const int piece = u / W - u_pair / W;                           // its place among the pair's pieces
+        const int ctx = p.ctx_lens[seq];
+        const int pos = ctx - 1;
+        const int key_lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+        const int t_begin = s_lo[seq] + t_rel, t_end = t_begin + n_here;
+        const int tok = p.cu_seqlens[seq];
+
+        // rows quad and quad + 8 of the 16-row tile; only rows < G are query heads
+        bool valid[2];
+        int head[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = quad + 8 * i;
+            valid[i] = r < G;
+            head[i] = kvh * G + (r < G ? r : 0);
+        }
+        uint32_t qa[HD / 16][4];
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const __nv_bfloat16* qp = p.q + ((size_t)tok * p.nh + head[i]) * HD + ks * 16 + tq * 2;
+                qa[ks][i] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp) : 0u;
+                qa[ks][i + 2] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp + 8) : 0u;
+            }
+        }
+        float o[HD / 8][4];
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+        const int* table = p.block_tables + (size_t)seq * p.max_blocks;
+        const int blk_lo = (t_begin * KV_TILE) >> p.page_shift;
+        const int blk_hi = ((min(t_end * KV_TILE, ctx) - 1) >> p.page_shift) + 1;
+        const bool table_cached = blk_hi - blk_lo <= BAL_TABLE_CACHE;
+        if (table_cached)
+            for (int i = tid; i < blk_hi - blk_lo; i += NTHREADS) s_table[i] = table[blk_lo + i];
+        __syncthreads();              // also: the merge of the piece before this one has left the buffers
+        const __nv_bfloat16* kv_base = p.cache + (size_t)kvh * p.page_size * HD;
+
+        auto load_tile = [&](int t, int stage) {
+            unsigned char* ks = smem + (size_t)stage * 2 * TILE_BYTES;
+            unsigned char* vs = ks + TILE_BYTES;
+            for (int idx = tid; idx < KV_TILE * CHUNKS; idx += NTHREADS) {
+                const int row = idx / CHUNKS, c = idx - row * CHUNKS;
+                const int key = t * KV_TILE + row;
+                const bool ok = key >= key_lo && key < ctx;
+                const __nv_bfloat16* src = p.cache;
+                if (ok) {
+                    const int blk = key >> p.page_shift;
+                    const int page = table_cached ? s_table[blk - blk_lo] : table[blk];
+                    src = kv_base + (size_t)page * page_stride + (size_t)(key & (p.page_size - 1)) * HD + c * 8;
+                }
+                cp_async_16(ks + row * ROW_BYTES + c * 16, src, ok);
+                cp_async_16(vs + row * ROW_BYTES + c * 16, ok ? src + v_off : src, ok);
+            }
+        };
+#pragma unroll
+        for (int i = 0; i < NSTAGES - 1; ++i) {
+            if (t_begin + i < t_end) load_tile(t_begin + i, i);
+            cp_async_commit();
+        }
+        int stage = 0;
+        for (int t = t_begin; t < t_end; ++t) {
+            if (t + NSTAGES - 1 < t_end) load_tile(t + NSTAGES - 1, (stage + NSTAGES - 1) % NSTAGES);
+            cp_async_commit();
+            cp_async_wait<NSTAGES - 1>();
+            __syncthreads();
+            const unsigned char* ks = smem + (size_t)stage * 2 * TILE_BYTES;
+            const unsigned char* vs = ks + TILE_BYTES;
+            float s[KW / 8][4];
+#pragma unroll
+            for (int n = 0; n < KW / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+                for (int n2 = 0; n2 < KW / 16; ++n2) {
+                    uint32_t b[4];
+                    const int key_row = warp_n * KW + n2 * 16 + (lane >> 4) * 8 + (lane & 7);
+                    const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+                    ldmatrix_x4(b, ks + key_row * ROW_BYTES + col * 2);
+                    mma_bf16(s[2 * n2], qa[kk], b[0], b[1]);
+                    mma_bf16(s[2 * n2 + 1], qa[kk], b[2], b[3]);
+                }
+            }
+            const int key0 = t * KV_TILE + warp_n * KW + tq * 2;
+            float m_tile[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < KW / 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + n * 8 + (e & 1);
+                    const bool see = key <= pos && key >= key_lo;
+                    const float v = see ? s[n][e] * p.scale_log2e : -INFINITY;
+                    s[n][e] = v;
+                    m_tile[e >> 1] = fmaxf(m_tile[e >> 1], v);
+                }
+            }
+            float alpha[2], m_safe[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                m_tile[i] = fmaxf(m_tile[i], __shfl_xor_sync(0xffffffffu, m_tile[i], 1));
+                m_tile[i] = fmaxf(m_tile[i], __shfl_xor_sync(0xffffffffu, m_tile[i], 2));
+                const float m_new = fmaxf(m_run[i], m_tile[i]);
+                m_safe[i] = m_new == -INFINITY ? 0.f : m_new;
+                alpha[i] = exp2f(m_run[i] - m_safe[i]);
+                m_run[i] = m_new;
+            }
+            float l_tile[2] = {0.f, 0.f};
+#pragma unroll
+            for (int n = 0; n < KW / 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float pv = exp2f(s[n][e] - m_safe[e >> 1]);
+                    s[n][e] = pv;
+                    l_tile[e >> 1] += pv;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * alpha[i] + l_tile[i];
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) {
+                o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+                o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+            }
+#pragma unroll
+            for (int kk = 0; kk < KW / 16; ++kk) {
+                uint32_t pa[4];
+                pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int n2 = 0; n2 < HD / 16; ++n2) {
+                    uint32_t b[4];
+                    const int key_row = warp_n * KW + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                    const int col = n2 * 16 + (lane >> 4) * 8;
+                    ldmatrix_x4_trans(b, vs + key_row * ROW_BYTES + col * 2);
+                    mma_bf16(o[2 * n2], pa, b[0], b[1]);
+                    mma_bf16(o[2 * n2 + 1], pa, b[2], b[3]);
+                }
+            }
+            __syncthreads();
+            stage = (stage + 1) % NSTAGES;
+        }
+        cp_async_wait<0>();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+            l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+        }
+        // ---- merge the four warps through shared memory and write the piece's partial result
+        __syncthreads();
+        float* mo = reinterpret_cast<float*>(smem);                 // [WARPS_N][16][HD]
+        float* mml = mo + WARPS_N * 16 * HD;                        // [WARPS_N][16][2]
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int row = quad + 8 * i;
+            if (row >= G) continue;
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) {
+                float* dst = mo + ((size_t)warp_n * 16 + row) * HD + n * 8 + tq * 2;
+                dst[0] = o[n][2 * i]; dst[1] = o[n][2 * i + 1];
+            }
+            if (tq == 0) {
+                mml[(warp_n * 16 + row) * 2] = m_run[i];
+                mml[(warp_n * 16 + row) * 2 + 1] = l_run[i];
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < G * HD; idx += NTHREADS) {
+            const int row = idx / HD, d = idx - row * HD;
+            float m_all = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < WARPS_N; ++w) m_all = fmaxf(m_all, mml[(w * 16 + row) * 2]);
+            const float m_s = m_all == -INFINITY ? 0.f : m_all;
+            float l_all = 0.f, acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS_N; ++w) {
+                const float f = exp2f(mml[(w * 16 + row) * 2] - m_s);
+                l_all += mml[(w * 16 + row) * 2 + 1] * f;
+                acc += mo[((size_t)w * 16 + row) * HD + d] * f;
+            }
+            const size_t prow = (size_t)piece * rows_all + (size_t)tok * p.nh + kvh * G + row;
+            p.part_o[prow * HD + d] = acc;
+            if (d == 0) { p.part_ml[prow * 2] = m_all; p.part_ml[prow * 2 + 1] = l_all; }
+        }
+        u += n_here;
+    }
+}
+
+// Merge of the balanced kernel's pieces: one block per (sequence, query head).
+__global__ void flash_balanced_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              const int* __restrict__ piece_count, const int* __restrict__ cu_seqlens,
+                                              __nv_bfloat16* __restrict__ out, int n_tokens, int nh, int nkv) {
+    rv_pdl_launch_dependents();
+    const int seq = blockIdx.x / nh, head = blockIdx.x - seq * nh;
+    const int d = threadIdx.x;
+    const int tok = cu_seqlens[seq];
+    const bool decode = cu_seqlens[seq + 1] - tok == 1;       // metadata of the step: read before the wait
+    rv_pdl_wait();
+    if (!decode || d >= HEAD_DIM) return;
+    const int pieces = piece_count[seq * nkv + head / (nh / nkv)];
+    const size_t row = (size_t)tok * nh + head;
+    out[row * HEAD_DIM + d] = __float2bfloat16_rn(pieces > 0 ? merge_splits(part_o, part_ml, row, (size_t)n_tokens * nh, pieces, d) : 0.f);
+}
+
+// The most pieces a (sequence, kv head) pair can be cut into by `ctas` CTAs when no sequence has more
+// than max_ctx keys: the caller sizes scratch as this * n_tokens * nh * (HEAD_DIM + 2) floats and
+// piece_count as num_seqs * nkv ints.
+RV_EXPORT int rv_flash_balanced_max_pieces(int max_ctx, int nkv, int ctas) {
+    const int tiles = (max_ctx + KV_TILE - 1) / KV_TILE;
+    const int bound = ctas / (nkv > 0 ? nkv : 1) + 2;       // W >= nkv * tiles of the longest sequence / ctas
+    return tiles < bound ? (tiles < 1 ? 1 : tiles) : bound;
+}
+
+// Decode attention (sequences that bring one token; the others are left alone) with the work cut
+// evenly over `ctas` CTAs (0: three per SM).  scratch, piece_count: see rv_flash_balanced_max_pieces.
+RV_EXPORT int rv_flash_decode_balanced(const void* q, const void* cache, const int* block_tables, const int* cu_seqlens,
+                                       const int* ctx_lens, void* out, float* scratch, int* piece_count, int max_pieces,
+                                       int n_tokens, int num_seqs, int nh, int nkv, int hd, int page_size, int max_blocks,
+                                       float scale, int window, int ctas, cudaStream_t stream) {
+    if (hd != HEAD_DIM) return RV_ERR_UNSUPPORTED;
+    if (n_tokens < 0 || num_seqs < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_blocks <= 0 || max_pieces < 1)
+        return RV_ERR_BAD_SIZE;
+    if (page_size & (page_size - 1)) return RV_ERR_UNSUPPORTED;
+    if (nh / nkv > 16 || num_seqs > BAL_MAX_SEQS) return RV_ERR_UNSUPPORTED;
+    if (n_tokens == 0 || num_seqs == 0) return RV_OK;
+    if (!scratch || !piece_count) return RV_ERR_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) % 16)
+        return RV_ERR_ALIGNMENT;
+    BalancedParams p;
+    p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache;
+    p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.ctx_lens = ctx_lens;
+    p.out = (__nv_bfloat16*)out;
+    p.part_o = scratch;
+    p.part_ml = scratch + (size_t)max_pieces * n_tokens * nh * HEAD_DIM;
+    p.piece_count = piece_count;
+    p.n_tokens = n_tokens; p.num_seqs = num_seqs; p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.max_blocks = max_blocks;
+    p.max_pieces = max_pieces;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.scale_log2e = scale * 1.4426950408889634f;
+    p.window = window;
+    if (ctas <= 0) {
+        static int sms = 0;
+        if (sms == 0) {
+            int dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+                sms = 148;
+        }
+        ctas = 3 * sms;
+    }
+    const int merge_bytes = 4 * 16 * (HEAD_DIM + 2) * 4;
+    const int smem = max(DECODE_STAGES * 2 * TILE_BYTES, merge_bytes);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(flash_decode_balanced_kernel<DECODE_STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    RV_LAUNCH_ST = rv_launch(flash_decode_balanced_kernel<DECODE_STAGES>, dim3(ctas), dim3(128), smem, stream, p);
+    int st = rv_launch_status();
+    if (st != RV_OK) return st;
+    RV_LAUNCH_ST = rv_launch(flash_balanced_combine_kernel, dim3(num_seqs * nh), dim3((HEAD_DIM + 31) / 32 * 32), 0, stream,
+                             (const float*)p.part_o, (const float*)p.part_ml, (const int*)piece_count, cu_seqlens, p.out,
+                             n_tokens, nh, nkv);
+    return rv_launch_status();
 }
 
 template <int WARPS_M, int WARPS_N, int NSTAGES>

@@ -72,6 +72,8 @@ class CudaKernels:
     TCGEN05_ATTENTION_MIN_TOKENS = 16  # ... from this many tokens in the longest portion of the step
     DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
     DECODE_SPLIT_ROWS = 8   # ... when K has to be split over CTAs, only up to this many rows
+    BALANCED_DECODE = True  # decode attention by the kernel that cuts all tiles evenly over resident CTAs ...
+    BALANCED_MIN_PAIRS = 256  # ... from this many (sequence, kv head) pairs on
     FUSED_NORM_MAX_ROWS = 4 # rows up to which an RMSNorm is applied inside the decode GEMM that consumes it
     FUSED_QKV_MAX_ROWS = 8  # rows up to which q/k/v product, rotation and cache write are one kernel
     pdl = os.environ.get("RVLLM_NO_PDL") != "1"   # programmatic dependent launch between kernels
@@ -205,12 +207,18 @@ class CudaKernels:
                 and 128 % group == 0 and page >= 8:
             self.attention_tcgen05(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window)
             if meta.num_decode:
-                self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
-                                     mode=1, q_filter=1, max_q_len=1)
+                if self._balanced_ok(meta, group, num_kv_heads):
+                    self.flash_decode_balanced(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window)
+                else:
+                    self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
+                                         mode=1, q_filter=1, max_q_len=1)
             return out
         if meta.max_q_len == 1:
-            self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
-                                 mode=1, num_splits=self.decode_splits(meta, num_heads, num_kv_heads))
+            if self._balanced_ok(meta, group, num_kv_heads):
+                self.flash_decode_balanced(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window)
+            else:
+                self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
+                                     mode=1, num_splits=self.decode_splits(meta, num_heads, num_kv_heads))
         elif meta.num_decode == 0:
             self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, mode=0)
         else:
@@ -240,6 +248,32 @@ class CudaKernels:
             if t < best_t - 1e-9:
                 best, best_t = s, t
         return best
+
+    def _balanced_ok(self, meta, group: int, num_kv_heads: int) -> bool:
+        """The evenly cut decode kernel serves batches whose (sequence, kv head) pairs alone fill more
+        than half of the resident CTAs: there the split kernel leaves waves half empty, and sequences
+        of unequal length (continuous batching) unbalance it; smaller batches are faster split."""
+        return (self.BALANCED_DECODE and group <= 16 and meta.num_seqs <= 256
+                and meta.num_decode * num_kv_heads >= self.BALANCED_MIN_PAIRS)
+
+    def flash_decode_balanced(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, ctas=0):
+        """Decode attention for the sequences of the step that bring one token, the 64-key tiles of
+        all (sequence, kv head) pairs cut evenly over a fixed number of resident CTAs; sequences
+        with more tokens are left alone."""
+        _need(q, "q", torch.bfloat16, 2); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
+        lib = self._lib("attention_flash.cu", (f"-DHEAD_DIM={head_dim}",))
+        T = q.shape[0]
+        grid = ctas or 444
+        pieces = lib.rv_flash_balanced_max_pieces(c_int(meta.max_ctx_len), c_int(num_kv_heads), c_int(grid))
+        scratch = torch.empty((pieces * T * num_heads * (head_dim + 2),), dtype=torch.float32, device=q.device)
+        counts = torch.empty((meta.num_seqs * num_kv_heads,), dtype=torch.int32, device=q.device)
+        st = lib.rv_flash_decode_balanced(
+            _ptr(q), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens), _ptr(out),
+            _ptr(scratch), _ptr(counts), c_int(pieces), c_int(T), c_int(meta.num_seqs), c_int(num_heads),
+            c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]), c_int(meta.max_blocks), c_float(scale),
+            c_int(window or 0), c_int(grid), self._stream())
+        _check("flash_decode_balanced", st)
+        return out
 
     def flash_attention(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
                         mode=0, num_splits=1, q_filter=0, max_q_len=None):

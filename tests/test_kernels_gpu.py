@@ -154,6 +154,18 @@ def test_flash_attention_kernel(K, case):
     assert rel_err(out.view(-1, nh, hd), ref) < BF16_TOL
     plain = K.paged_attention_plain(q, cache, meta, nh, nkv, hd, scale, window)
     assert rel_err(out, plain.double()) < BF16_TOL
+    if 1 in q_lens:
+        # the kernel that cuts all tiles evenly over a fixed number of CTAs: rows of one-token sequences
+        for ctas in (0, 1, 3, 7, 64):
+            o3 = torch.full_like(q, 9.0)
+            K.flash_decode_balanced(q, cache, meta, o3, nh, nkv, hd, scale, window, ctas=ctas)
+            row = 0
+            for n in q_lens:
+                if n == 1:
+                    assert rel_err(o3.view(-1, nh, hd)[row], ref[row]) < BF16_TOL
+                else:
+                    assert bool((o3[row:row + n] == 9.0).all())                # longer sequences are left alone
+                row += n
     if max(q_lens) == 1:
         for splits in (2, 5):                                                   # keys split over CTAs and merged
             o2 = torch.empty_like(q)
