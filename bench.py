@@ -299,6 +299,7 @@ def run_serve(args):
               max_num_batched_tokens=args.budget, enforce_eager=args.eager)
     sp = SamplingParams(temperature=0.0, max_tokens=args.output_len, ignore_eos=True)
     llm.generate(prompts[:2], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))     # warm-up
+    graphs = llm.capture_graphs(hi + args.output_len)      # as a service does when it starts, not while it serves
     clocks = ClockSampler()
     clocks.start()
     COUNTERS["launches"] = 0
@@ -318,7 +319,8 @@ def run_serve(args):
         "preemptions": sum(o.num_preemptions for o in outs), "gpu_launches": COUNTERS["launches"],
         "config": {"model": f"{args.shape}-shape", "layers": cfg_dict["num_hidden_layers"], "layers_full": full_layers,
                    "requests": args.requests, "prompt_len": f"uniform {lo}..{hi}", "output_len": args.output_len,
-                   "token_budget": args.budget, "seq_len": context, "block_size": 16, "cuda_graph": not args.eager},
+                   "token_budget": args.budget, "seq_len": context, "block_size": 16, "cuda_graph": not args.eager,
+                   "graphs_captured_before": graphs},
         "clocks": ck}))
 
 

@@ -44,6 +44,8 @@ def _engine_options(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--no-async-scheduling", action="store_true", default=os.environ.get("RVLLM_NO_ASYNC") == "1",
                     help="wait for every step's tokens before the next step is launched (also RVLLM_NO_ASYNC=1)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--capture-graphs", action="store_true",
+                    help="capture the decode CUDA graphs of every batch and context bucket before the first request")
 
 
 def _llm(args, **over):
@@ -56,7 +58,10 @@ def _llm(args, **over):
               max_prefill_chunk=args.max_prefill_chunk, enforce_eager=args.enforce_eager, seed=args.seed,
               async_scheduling=not args.no_async_scheduling)
     kw.update(over)
-    return LLM(args.model, **kw)
+    llm = LLM(args.model, **kw)
+    if getattr(args, "capture_graphs", False):
+        llm.capture_graphs()
+    return llm
 
 
 def cmd_generate(args) -> int:

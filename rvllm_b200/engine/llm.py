@@ -80,6 +80,11 @@ class LLM:
             from ..tokenizer import Tokenizer
             self.tokenizer = Tokenizer.from_model_dir(model, required=False)
 
+    def capture_graphs(self, max_context: Optional[int] = None) -> int:
+        """Capture the CUDA graphs of the decode steps now (every batch bucket, contexts up to
+        `max_context`, default max_model_len) instead of at the first step that needs each."""
+        return self.engine.runner.capture_decode_graphs(max_context)
+
     def _new_scheduler(self) -> Scheduler:
         ec = self.config
         return Scheduler(self.engine.cache, ec.max_num_seqs, ec.max_num_batched_tokens, ec.max_model_len,

@@ -399,6 +399,38 @@ class ModelRunner:
             self._graph_event.record()
         return host, dev, graph, out, launches
 
+    def capture_decode_graphs(self, max_context: Optional[int] = None, batch_sizes: Optional[Sequence[int]] = None) -> int:
+        """Capture the decode graphs ahead of time, for every batch bucket (or the given ones) and
+        every context bucket up to `max_context` (default: max_model_len), so that no step of a
+        running service pays for a capture.  A graph is captured on a batch of padding rows, which
+        write nothing, so live requests are not disturbed.  Returns the number of graphs captured."""
+        if not self.graph_batch_sizes or self.device.type != "cuda":
+            return 0
+        limit = min(max_context or self.max_model_len, self.max_model_len)
+        ctx_buckets, b = [], self._ctx_bucket(1)
+        while True:
+            ctx_buckets.append(b)
+            if b >= limit:
+                break
+            b = self._ctx_bucket(b + 1)
+        made = 0
+        for bucket in (batch_sizes or self.graph_batch_sizes):
+            if bucket not in self.graph_batch_sizes:
+                raise SchedulerError(f"{bucket} is not one of the graph batch sizes {self.graph_batch_sizes}")
+            for ctx_limit in ctx_buckets:
+                if (bucket, ctx_limit) not in self._graphs:
+                    # a first, uncaptured run of the padded batch: it loads the kernel libraries
+                    # and lets the GEMM library choose its algorithms outside the capture
+                    G = len(self.cache.groups)
+                    n_ints = 3 * bucket + (bucket + 1) + 2 * bucket + bucket + G * (bucket + bucket * self.max_blocks) + bucket + 16
+                    host = torch.empty((n_ints,), dtype=torch.int32, pin_memory=True)
+                    dev = torch.empty((n_ints,), dtype=torch.int32, device=self.device)
+                    ctx = self.pack([], [], pad_to=bucket, buffers=(host, dev), ctx_limit=ctx_limit)
+                    self.model.compute_logits(self.model.forward(ctx, self.cache), ctx)
+                    self._graphs[(bucket, ctx_limit)] = self._capture(bucket, ctx_limit)
+                    made += 1
+        return made
+
     def finish(self, req_id: Hashable) -> None:
         """Give back everything the request holds."""
         if self.cache.has(req_id):

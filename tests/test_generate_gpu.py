@@ -140,3 +140,21 @@ def test_random_weights_without_a_folder_and_loud_errors():
         LLM(config=cfg)                                                  # no folder and no random weights
     with pytest.raises(ConfigError, match="tokenizer"):
         llm.generate(["text needs a tokenizer"], SamplingParams())
+
+
+def test_graphs_captured_ahead_change_nothing():
+    """Decode graphs captured before any request (all batch buckets, contexts up to a limit) are the
+    ones the steps then replay: same tokens as with graphs captured on the way, no capture later."""
+    from rvllm_b200 import SamplingParams
+    cfg, _ = plain_impl.read_model_folder(model_folder("tiny_qwen2"))
+    prompts = list(random_requests(cfg["vocab_size"], (5, 23, 70, 9), seed=8).values())
+    sp = SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True)
+    lazy = make_llm("tiny_qwen2", "bfloat16", max_num_seqs=8)
+    want = [o.outputs[0].token_ids for o in lazy.generate(prompts, sp)]
+    early = make_llm("tiny_qwen2", "bfloat16", max_num_seqs=8)
+    n = early.capture_graphs()
+    assert n == len(early.engine.runner._graphs) and n >= 4
+    assert early.capture_graphs() == 0                                     # nothing left to capture
+    got = [o.outputs[0].token_ids for o in early.generate(prompts, sp)]
+    assert got == want and len(early.engine.runner._graphs) == n
+    early.engine.cache.check()
