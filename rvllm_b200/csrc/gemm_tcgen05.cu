@@ -11,7 +11,11 @@
 //            the epilogue.  Two accumulators (2 x 256 TMEM columns) let tile i+1 start while
 //            tile i is written out;
 //   warps 2-5  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, add the residual / apply
-//            SiLU-gate in float, round once, store.
+//            SiLU-gate in float, round once, store.  For the q/k/v product of an attention layer
+//            the epilogue rounds the sums as a separate product would store them, adds the bias,
+//            rotates q and k by the row's position (a head's two halves are read from tensor memory
+//            side by side), writes q to its output and k and v straight into the row's slot of the
+//            paged cache: the rotary kernel and the round trip of q/k/v through memory are saved.
 // No cluster, no multicast.  Every wait on an mbarrier is bounded: when a wait gives up, the CTA
 // sets an abort flag, every role leaves its loop, the producer waits (bounded) for its loads in
 // flight, tensor memory is freed, the kernel writes a status word and returns.
@@ -37,6 +41,7 @@
 #define EPI_PLAIN 0
 #define EPI_RESIDUAL 1
 #define EPI_GATED 2
+#define EPI_ROPE 3          // the q/k/v product: bias, rotation of q and k, k and v into the paged cache
 
 struct GemmParams {
     void* out;
@@ -46,10 +51,72 @@ struct GemmParams {
     int out_f32;
     int epilogue;
     int m_tiles, n_tiles;
+    // EPI_ROPE: W rows are [q heads | k heads | v heads] of hd (64, 128 or 256) features
+    const void* bias;                // [N] or nullptr
+    int bias_dtype;
+    __nv_bfloat16* q_out;            // [M, nh * hd]
+    __nv_bfloat16* kv_cache;         // [pages, 2, nkv, page_size, hd]
+    const int* positions;            // [M]
+    const int* slot_mapping;         // [M], < 0: the row writes no key or value
+    const float* cos_t;              // [table_rows, hd / 2] or nullptr (no rotation)
+    const float* sin_t;
+    int nh, nkv, hd, page_size, table_rows;
 };
 
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+
+// EPI_ROPE: columns d .. d + 31 (a) and d + hd/2 .. d + hd/2 + 31 (b) of one head of row m.
+__device__ __forceinline__ void store_rope_pair(const GemmParams& p, int m, int head, int d, const uint32_t (&ra)[32],
+                                                const uint32_t (&rb)[32], int pos, int slot) {
+    const int hd = p.hd, half = hd >> 1;
+    const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
+    const int n_a = head * hd + d, n_b = n_a + half;
+    __nv_bfloat16 *dst_a, *dst_b;
+    if (is_q) {
+        dst_a = p.q_out + (size_t)m * p.nh * hd + n_a;
+    } else {
+        if (slot < 0) return;
+        const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
+        const int page = slot / p.page_size, off = slot - page * p.page_size;
+        dst_a = p.kv_cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * p.nkv + kvh) * p.page_size + off) * hd + d;
+    }
+    dst_b = dst_a + half;
+    const bool rotate = (is_q || is_k) && p.cos_t != nullptr;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        float c[8], sn[8];
+        if (rotate) {
+            const float4* cp = reinterpret_cast<const float4*>(p.cos_t + (size_t)pos * half + d + v * 8);
+            const float4* sp = reinterpret_cast<const float4*>(p.sin_t + (size_t)pos * half + d + v * 8);
+            const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+            c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+            sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+        }
+        uint4 oa, ob;
+        __nv_bfloat16* oae = reinterpret_cast<__nv_bfloat16*>(&oa);
+        __nv_bfloat16* obe = reinterpret_cast<__nv_bfloat16*>(&ob);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int e = v * 8 + j;
+            float a = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ra[e])));
+            float b = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rb[e])));
+            if (p.bias) {
+                a += rv_load_param(p.bias, p.bias_dtype, n_a + e);
+                b += rv_load_param(p.bias, p.bias_dtype, n_b + e);
+            }
+            if (rotate) {
+                oae[j] = __float2bfloat16_rn(a * c[j] - b * sn[j]);
+                obe[j] = __float2bfloat16_rn(a * sn[j] + b * c[j]);
+            } else {
+                oae[j] = __float2bfloat16_rn(a);
+                obe[j] = __float2bfloat16_rn(b);
+            }
+        }
+        *reinterpret_cast<uint4*>(dst_a + v * 8) = oa;
+        *reinterpret_cast<uint4*>(dst_b + v * 8) = ob;
+    }
+}
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -204,6 +271,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     }
                 }
+            } else if (p.epilogue == EPI_ROPE) {
+                const int n0 = nt * BN;
+                const int half = p.hd >> 1;
+                int pos = 0, slot = -1;
+                if (m < p.M) {
+                    pos = p.positions[m];
+                    pos = pos < 0 ? 0 : (pos >= p.table_rows ? p.table_rows - 1 : pos);
+                    slot = p.slot_mapping[m];
+                }
+                for (int hb = 0; hb < BN; hb += p.hd) {            // the heads of this tile
+                    if (n0 + hb >= p.N) break;                      // uniform over the warp
+                    const int head = (n0 + hb) / p.hd;
+                    for (int c = 0; c < half; c += 32) {
+                        uint32_t ra[32], rb[32];
+                        tmem_ld_32x32(taddr + hb + c, ra);
+                        tmem_ld_32x32(taddr + hb + half + c, rb);
+                        tmem_ld_wait();
+                        if (m < p.M) store_rope_pair(p, m, head, c, ra, rb, pos, slot);
+                    }
+                }
             } else {
                 const int n0 = nt * BN;
                 for (int c = 0; c < BN; c += 32) {
@@ -285,7 +372,7 @@ RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* res
     if (st != RV_OK) return st;
     st = rv_make_bf16_map(&map_b, w, N, K, BN / 2);
     if (st != RV_OK) return st;
-    GemmParams p;
+    GemmParams p = {};
     p.out = out; p.residual = epilogue == EPI_RESIDUAL ? (const __nv_bfloat16*)residual : nullptr;
     p.status = status; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.epilogue = epilogue;
     p.m_tiles = (M + BM - 1) / BM;
@@ -299,6 +386,47 @@ RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* res
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
+    int ctas = p.m_tiles * p.n_tiles;
+    const int limit = max_ctas > 0 ? max_ctas : 148;
+    if (ctas > limit) ctas = limit;
+    RV_LAUNCH_ST = rv_launch(gemm_tcgen05_kernel, dim3(ctas), dim3(NUM_THREADS), smem, stream, map_a, map_b, p);
+    return rv_launch_status();
+}
+
+// The q/k/v product of an attention layer for many rows, with bias, rotation and the cache write in
+// its epilogue.  w: [(nh + 2 nkv) * hd, K], hd 64, 128 or 256; q_out: [M, nh * hd]; kv_cache:
+// [pages, 2, nkv, page_size, hd]; cos_t / sin_t: [table_rows, hd / 2] floats or both nullptr.
+RV_EXPORT int rv_gemm_tcgen05_qkv_rope(const void* x, const void* w, const void* bias, int bias_dtype,
+                                       const int* positions, const float* cos_t, const float* sin_t,
+                                       const int* slot_mapping, void* kv_cache, void* q_out, int M, int K,
+                                       int nh, int nkv, int hd, int page_size, int table_rows, int* status,
+                                       int max_ctas, cudaStream_t stream) {
+    if (M < 0 || K <= 0 || nh <= 0 || nkv <= 0 || page_size <= 0 || table_rows <= 0) return RV_ERR_BAD_SIZE;
+    if (hd != 64 && hd != 128 && hd != 256) return RV_ERR_UNSUPPORTED;     // a head's halves are whole 32-column chunks of one tile
+    if (K % 8) return RV_ERR_UNSUPPORTED;
+    if ((cos_t == nullptr) != (sin_t == nullptr)) return RV_ERR_BAD_SIZE;
+    if (!positions || !slot_mapping || !kv_cache || !q_out) return RV_ERR_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(q_out) |
+         reinterpret_cast<uintptr_t>(kv_cache) | reinterpret_cast<uintptr_t>(cos_t) | reinterpret_cast<uintptr_t>(sin_t)) % 16)
+        return RV_ERR_ALIGNMENT;
+    if (M == 0) return RV_OK;
+    const int N = (nh + 2 * nkv) * hd;
+    alignas(64) CUtensorMap map_a, map_b;
+    int st = rv_make_bf16_map(&map_a, x, M, K, BM);
+    if (st != RV_OK) return st;
+    st = rv_make_bf16_map(&map_b, w, N, K, BN / 2);
+    if (st != RV_OK) return st;
+    GemmParams p = {};
+    p.status = status; p.M = M; p.N = N; p.K = K; p.epilogue = EPI_ROPE;
+    p.m_tiles = (M + BM - 1) / BM;
+    p.n_tiles = (N + BN - 1) / BN;
+    p.bias = bias; p.bias_dtype = bias_dtype;
+    p.q_out = (__nv_bfloat16*)q_out; p.kv_cache = (__nv_bfloat16*)kv_cache;
+    p.positions = positions; p.slot_mapping = slot_mapping; p.cos_t = cos_t; p.sin_t = sin_t;
+    p.nh = nh; p.nkv = nkv; p.hd = hd; p.page_size = page_size; p.table_rows = table_rows;
+    const int smem = STAGES * STAGE_BYTES + 1024;
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
     int ctas = p.m_tiles * p.n_tiles;
     const int limit = max_ctas > 0 ? max_ctas : 148;
     if (ctas > limit) ctas = limit;

@@ -74,6 +74,7 @@ class CudaKernels:
     DECODE_SPLIT_ROWS = 8   # ... when K has to be split over CTAs, only up to this many rows
     BALANCED_DECODE = True  # decode attention by the kernel that cuts all tiles evenly over resident CTAs ...
     BALANCED_MIN_PAIRS = 256  # ... from this many (sequence, kv head) pairs on
+    FUSED_QKV_PREFILL = True  # from TCGEN05_MIN_ROWS rows on the prefill GEMM rotates and writes the cache in its epilogue
     FUSED_NORM_MAX_ROWS = 4 # rows up to which an RMSNorm is applied inside the decode GEMM that consumes it
     FUSED_QKV_MAX_ROWS = 8  # rows up to which q/k/v product, rotation and cache write are one kernel
     pdl = os.environ.get("RVLLM_NO_PDL") != "1"   # programmatic dependent launch between kernels
@@ -497,9 +498,41 @@ class CudaKernels:
                                         num_heads, num_kv_heads, head_dim, norm=norm)
         if norm is not None:
             x = self.rmsnorm(x, *norm)
+        if (self.FUSED_QKV_PREFILL and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+                and M >= self.TCGEN05_MIN_ROWS and head_dim in (64, 128, 256) and K % 8 == 0
+                and weight.shape[0] == (num_heads + 2 * num_kv_heads) * head_dim):
+            return self._qkv_rope_tcgen05(x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
+                                          num_heads, num_kv_heads, head_dim)
         qkv = self.linear(x, weight)
         return self.rope_cache_write(qkv, bias, positions, cos, sin, slot_mapping, cache_layer,
                                      num_heads, num_kv_heads, head_dim)
+
+    def _qkv_rope_tcgen05(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
+                          num_heads, num_kv_heads, head_dim, status=None, max_ctas=0):
+        """The prefill tcgen05 GEMM with the rotary epilogue (many rows, head sizes 64 / 128 / 256)."""
+        _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
+        _need(positions, "positions", torch.int32, 1); _need(slot_mapping, "slot_mapping", torch.int32, 1)
+        _need(cache_layer, "cache_layer", torch.bfloat16, 5)
+        M, K = x.shape
+        if weight.shape[1] != K or positions.shape[0] < M or slot_mapping.shape[0] < M:
+            raise KernelError("qkv_rope_cache_write: shapes of x, weight, positions and slot_mapping do not agree")
+        if tuple(cache_layer.shape[1:3]) != (2, num_kv_heads) or cache_layer.shape[4] != head_dim:
+            raise KernelError(f"qkv_rope_cache_write: cache layer of shape {tuple(cache_layer.shape)} does not "
+                              f"fit {num_kv_heads} kv heads of {head_dim}")
+        if cos is not None:
+            _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+            if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+                raise KernelError("qkv_rope_cache_write: cos/sin tables must be [rows, head_dim/2]")
+        if bias is not None:
+            _need(bias, "bias", dims=1)
+        q = torch.empty((M, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
+        st = self._lib("gemm_tcgen05.cu").rv_gemm_tcgen05_qkv_rope(
+            _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0),
+            _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(cache_layer), _ptr(q), c_int(M), c_int(K),
+            c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]),
+            c_int(cos.shape[0] if cos is not None else 1), _ptr(status), c_int(max_ctas), self._stream())
+        _check("gemm_tcgen05_qkv_rope", st)
+        return q
 
     def _qkv_rope_fused(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
                         num_heads, num_kv_heads, head_dim, splits=None, status=None, norm=None):

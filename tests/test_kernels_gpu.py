@@ -433,6 +433,59 @@ def test_rmsnorm_inside_the_decode_gemm(K, M, N, Kd, gamma_dtype):
     assert rel_err(K.gate_up_silu(many, w, norm=(gamma, eps))[:M], gref) < 2 * BF16_TOL
 
 
+@pytest.mark.parametrize("M,nh,nkv,hd,Kd,page,bias", [(2048, 32, 8, 128, 512, 16, False), (300, 6, 2, 64, 264, 8, True),
+                                                      (129, 2, 1, 256, 128, 16, True), (640, 5, 5, 128, 96, 4, False)])
+def test_qkv_product_with_rotation_and_cache_write_for_many_rows(K, M, nh, nkv, hd, Kd, page, bias):
+    """The prefill GEMM's rotary epilogue against the product followed by the rotary kernel (same sums,
+    same formula: equal up to the last bit of a contracted multiply-add) and against float64 arithmetic;
+    rows with slot -1 write nothing; other cache slots stay untouched; several tiles per CTA."""
+    torch.manual_seed(14)
+    N = (nh + 2 * nkv) * hd
+    x = torch.randn(M, Kd, device="cuda").bfloat16()
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(N, device="cuda").bfloat16() if bias else None
+    positions = torch.randint(0, 500, (M,), device="cuda", dtype=torch.int32)
+    ang = torch.arange(512, dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))[None]
+    cos, sin = ang.cos().float().cuda(), ang.sin().float().cuda()
+    pages = (2 * M) // page + 3
+    slots = torch.randperm(pages * page)[:M].to(torch.int32).cuda()
+    slots[1] = -1
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cache_b = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda").bfloat16()
+    qb = K.rope_cache_write(K.linear_tcgen05(x, w), b, positions, cos, sin, slots, cache_b, nh, nkv, hd)
+    for ctas in (0, 2):
+        cache_a = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda").bfloat16()
+        qa = K._qkv_rope_tcgen05(x, w, b, positions, cos, sin, slots, cache_a, nh, nkv, hd, status=status, max_ctas=ctas)
+        assert rel_err(qa, qb.double().cpu()) < 4e-3 and rel_err(cache_a, cache_b.double().cpu()) < 4e-3
+        assert float((qa.float() - qb.float()).abs().gt(0).float().mean()) < 0.02      # nearly every element bit-equal
+    assert int(status.item()) == 0
+    y = x.double().cpu() @ w.double().cpu().t()
+    if bias:
+        y = y + b.double().cpu()
+    y = y.view(M, nh + 2 * nkv, hd)
+    c, s_ = ang.cos()[positions.cpu().long()][:, None, :], ang.sin()[positions.cpu().long()][:, None, :]
+    rot = lambda t: torch.cat([t[..., :hd // 2] * c - t[..., hd // 2:] * s_, t[..., :hd // 2] * s_ + t[..., hd // 2:] * c], -1)
+    assert rel_err(qa, rot(y[:, :nh]).reshape(M, nh * hd)) < BF16_TOL
+    kref, vref = rot(y[:, nh:nh + nkv]), y[:, nh + nkv:]
+    written = torch.zeros(pages, page, dtype=torch.bool)
+    for m in range(0, M, 7):
+        sl = int(slots[m])
+        if sl >= 0:
+            assert rel_err(cache_a[sl // page, 0, :, sl % page], kref[m]) < BF16_TOL
+            assert rel_err(cache_a[sl // page, 1, :, sl % page], vref[m]) < BF16_TOL
+    for m in range(M):
+        sl = int(slots[m])
+        if sl >= 0:
+            written[sl // page, sl % page] = True
+    untouched = cache_a.cpu().float().permute(0, 3, 1, 2, 4)[~written]
+    assert bool((untouched == 7.0).all())
+    # the dispatching entry point takes this kernel from TCGEN05_MIN_ROWS rows on
+    cache_c = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda").bfloat16()
+    before = COUNTERS["launches"]
+    qc = K.qkv_rope_cache_write(x, w, b, positions, cos, sin, slots, cache_c, nh, nkv, hd)
+    assert COUNTERS["launches"] == before + 1 and torch.equal(qc, qa) and torch.equal(cache_c, cache_a)
+
+
 TC_ATT_CASES = [
     # nh, nkv, hd, page, q_lens, ctx_lens, window
     (4, 1, 128, 16, [32], [32], None),
