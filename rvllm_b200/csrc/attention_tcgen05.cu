@@ -107,8 +107,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const uint32_t bar_s_full0 = smem_u32(&bars[7]), bar_s_free0 = smem_u32(&bars[9]);   // [2] each
     const uint32_t bar_p_full = smem_u32(&bars[11]), bar_o_full = smem_u32(&bars[12]);
 
-    // row tiles late in the prompt see the most keys: they are started first
-    const int seq = blockIdx.z, kvh = blockIdx.y, tile_m = gridDim.x - 1 - blockIdx.x;
+    // Row tiles late in the prompt see the most keys.  CTAs are handed out in the order of their
+    // linear index (x fastest), so the row tile is the slowest index, counted down: all heads' and
+    // sequences' heaviest tiles start first and the light ones fill the end (with the row tile
+    // as the fastest index the last heads' heavy tiles started late and set the kernel's length).
+    const int kvh = blockIdx.x, seq = blockIdx.y, tile_m = gridDim.z - 1 - blockIdx.z;
     const int G = p.nh / p.nkv;
     rv_pdl_wait();
     const int ctx = p.ctx_lens[seq];
@@ -446,7 +449,8 @@ RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long n
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const dim3 grid((max_q_len * G + ROWS - 1) / ROWS, nkv, num_seqs);
+    const dim3 grid(nkv, num_seqs, (max_q_len * G + ROWS - 1) / ROWS);
+    if (grid.y > 65535 || grid.z > 65535) return RV_ERR_UNSUPPORTED;
     RV_LAUNCH_ST = rv_launch(attention_tcgen05_kernel, grid, dim3(NUM_THREADS), smem, stream, map_q, map_kv, p);
     return rv_launch_status();
 }
