@@ -46,6 +46,24 @@ static inline int rv_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     return RV_OK;
 }
 
+// The same with the grid's CTAs grouped into clusters of `cluster_x` along x (distributed shared memory).
+template <typename... KArgs, typename... Args>
+static inline int rv_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    unsigned cluster_x, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster_x; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_rv_pdl ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+    return RV_OK;
+}
+
 // the status of the most recent rv_launch of this thread (launchers write RV_LAUNCH_ST = rv_launch(...))
 static thread_local int rv_launch_st = 0;
 #define RV_LAUNCH_ST rv_launch_st

@@ -26,7 +26,11 @@
 // 1 / sqrt(mean(x^2) + eps) from global memory, then scale every activation tile in shared memory
 // by it and by gamma as soon as its TMA load has landed, and hand the tile to the MMA warp through a
 // second barrier per stage.  The norm kernel and its place in the chain of launches are saved.
-// Every mbarrier wait is bounded (see gemm_tcgen05.cu); no cluster, no multicast.
+// For up to 8 rows and up to 8 splits the CTAs of a tile are launched as a thread-block cluster: each
+// writes its partial rows into the first CTA's shared memory (st.shared::cluster), one cluster barrier
+// later that CTA adds them in split order and runs the epilogue - no round trip through L2, no
+// fence, no atomic.  Every thread of every CTA reaches the cluster barrier on every path.
+// Every mbarrier wait is bounded (see gemm_tcgen05.cu); no multicast.
 //
 // Shapes: the five products of a layer and the LM head at decode time
 // (v3/crates/rvllm-runtime/src/layer_exec.rs:240-266,433-444,478-488,511-522 and
@@ -53,6 +57,8 @@ struct DecodeGemmParams {
     int M, N, K;
     int out_f32, gated;
     int splits, n_tiles;
+    int cluster;             // 1: the CTAs of a tile are a thread-block cluster and add their partials in the
+                             // first one's shared memory (M <= 8, 2 <= splits <= 8); scratch and counters unused
     // rotary epilogue (q_out != nullptr): N = (nh + 2 nkv) * hd, 128 % hd == 0
     __nv_bfloat16* q_out;            // [M, nh * hd]
     __nv_bfloat16* kv_cache;         // [pages, 2, nkv, page_size, hd]
@@ -69,13 +75,172 @@ struct DecodeGemmParams {
 };
 
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address, in the cluster's shared window, of `addr` (a shared-memory address of this CTA) in CTA `rank`.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// The partials of a tile added up and the epilogue run in one pass, by the epilogue warps of the CTA
+// that finishes the tile: four neighbouring features per thread (16-byte reads of the partials,
+// 8-byte reads of the residual, 8- or 16-byte stores), four rows and four splits in flight at a
+// time.  A row is summed in split order, whatever the batch holds.  The partial of (split s, row m)
+// starts at parts + (s * part_rows + m) * 128, in scratch memory or in the CTA's shared memory.
+// (volatile asm on purpose: plain loads let the compiler hoist all of a thread's loads and spend 47 more registers)
+template <bool IN_SMEM>
+__device__ __forceinline__ float4 load_part(const float* src) {
+    float4 v;
+    if (IN_SMEM)
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(src)) : "memory");
+    else
+        asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(src) : "memory");
+    return v;
+}
+
+template <int MB, bool IN_SMEM>
+__device__ __forceinline__ void finish_from_parts(const DecodeGemmParams& p, int tile, int et, const float* parts,
+                                                  int part_rows, int* row_pos, int* row_slot) {
+    const int fq = et & 31, rg = et >> 5;
+    const int n0 = tile * TILE_F + 4 * fq;
+    const float* base = parts + 4 * fq;
+    const bool vec = (p.N & 3) == 0 && n0 + 3 < p.N;
+    if (p.q_out) {
+        if (et < p.M) {
+            const int pos = p.positions[et];
+            row_pos[et] = pos < 0 ? 0 : (pos >= p.table_rows ? p.table_rows - 1 : pos);
+            row_slot[et] = p.slot_mapping[et];
+        }
+        epi_sync();
+    }
+    float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (p.bias) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) if (n0 + e < p.N) bias4[e] = rv_load_param(p.bias, p.bias_dtype, n0 + e);
+    }
+    for (int m0 = rg; m0 < p.M; m0 += 16) {
+        float4 acc[4];
+        uint2 res[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            res[j] = make_uint2(0u, 0u);
+            const int m = m0 + 4 * j;
+            if (p.residual && vec && m < p.M)
+                res[j] = __ldg(reinterpret_cast<const uint2*>(p.residual + (size_t)m * p.N + n0));
+        }
+        for (int s0 = 0; s0 < p.splits; s0 += 4) {
+            float4 t[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    t[j][i] = (m0 + 4 * j < p.M && s0 + i < p.splits)
+                                  ? load_part<IN_SMEM>(base + ((size_t)(s0 + i) * part_rows + m0 + 4 * j) * TILE_F)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc[j].x += t[j][i].x; acc[j].y += t[j][i].y; acc[j].z += t[j][i].z; acc[j].w += t[j][i].w;
+                }
+        }
+        if (p.q_out) {
+            // rotary epilogue: hd is a power of two >= 8 and N a multiple of it, so the four
+            // features lie in one half of one head and their partners (hd / 2 further or
+            // nearer) are held by the lane hd / 8 away; every lane takes part in the exchange
+            const int hd = p.hd, half = hd >> 1;
+            const int head = n0 / hd, d = n0 - head * hd;
+            const bool live = n0 < p.N;
+            const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
+            const bool first = d < half;
+            const int i0 = first ? d : d - half;
+            const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int m = m0 + 4 * j;
+                const bool row_ok = m < p.M;                     // uniform in the warp
+                float own[4] = {acc[j].x, acc[j].y, acc[j].z, acc[j].w}, other[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    own[e] = __bfloat162float(__float2bfloat16_rn(own[e])) + bias4[e];
+                    other[e] = __shfl_xor_sync(0xffffffffu, own[e], hd >> 3);
+                }
+                if (!row_ok || !live) continue;
+                float v[4] = {own[0], own[1], own[2], own[3]};
+                if ((is_q || is_k) && p.cos_t) {
+                    const float4 c = __ldg(reinterpret_cast<const float4*>(p.cos_t + (size_t)row_pos[m] * half + i0));
+                    const float4 sn = __ldg(reinterpret_cast<const float4*>(p.sin_t + (size_t)row_pos[m] * half + i0));
+                    const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        v[e] = first ? own[e] * cc[e] - other[e] * ss[e] : other[e] * ss[e] + own[e] * cc[e];
+                }
+                uint2 o2;
+                o2.x = pack_bf16x2(v[0], v[1]);
+                o2.y = pack_bf16x2(v[2], v[3]);
+                if (is_q) {
+                    *reinterpret_cast<uint2*>(p.q_out + (size_t)m * p.nh * hd + n0) = o2;
+                } else {
+                    const int slot = row_slot[m];
+                    if (slot >= 0) {
+                        const int page = slot / p.page_size, off = slot - page * p.page_size;
+                        *reinterpret_cast<uint2*>(p.kv_cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * p.nkv + kvh) * p.page_size + off) * hd + d) = o2;
+                    }
+                }
+            }
+            continue;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + 4 * j;
+            if (m >= p.M || n0 >= p.N) continue;
+            float v[4] = {acc[j].x + bias4[0], acc[j].y + bias4[1], acc[j].z + bias4[2], acc[j].w + bias4[3]};
+            if (vec) {
+                if (p.residual) {
+                    const __nv_bfloat16* re = reinterpret_cast<const __nv_bfloat16*>(&res[j]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[e] += __bfloat162float(re[e]);
+                }
+                if (p.out_f32) {
+                    *reinterpret_cast<float4*>((float*)p.out + (size_t)m * p.N + n0) = make_float4(v[0], v[1], v[2], v[3]);
+                } else {
+                    uint2 o2;
+                    o2.x = pack_bf16x2(v[0], v[1]);
+                    o2.y = pack_bf16x2(v[2], v[3]);
+                    *reinterpret_cast<uint2*>((__nv_bfloat16*)p.out + (size_t)m * p.N + n0) = o2;
+                }
+            } else {
+                for (int e = 0; e < 4 && n0 + e < p.N; ++e) {
+                    float w = v[e];
+                    if (p.residual) w += __bfloat162float(p.residual[(size_t)m * p.N + n0 + e]);
+                    if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n0 + e] = w;
+                    else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n0 + e] = __float2bfloat16_rn(w);
+                }
+            }
+        }
+    }
+}
+
 template <int MB>
-__global__ void __launch_bounds__(NUM_THREADS)
+__global__ void __launch_bounds__(NUM_THREADS, 3)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    const DecodeGemmParams p) {
     constexpr int B_BYTES = MB * BK * 2;
@@ -91,6 +256,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __shared__ float norm_red[4][16], norm_rstd[16];
 
     rv_pdl_launch_dependents();
+    // A CTA's shared memory may be written from another CTA of the cluster only once it runs: every
+    // thread arrives here, and waits before the partials are stored (warps 0 and 1 at the end).
+    if (p.cluster) cluster_arrive();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), tfull = smem_u32(&bars[2 * STAGES]);
     const uint32_t normed0 = smem_u32(&bars[2 * STAGES + 1]);
@@ -117,6 +285,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int per = (num_kb + p.splits - 1) / p.splits;
     const int kb0 = split * per, kb1 = min(num_kb, kb0 + per);
     const int half_n = p.N >> 1;
+    // cluster reduction: [splits][8 rows][128 features] floats behind the stages (and gamma), at the
+    // same offset in every CTA of the cluster
+    float* red = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES + (fused_norm ? (size_t)per * BK * 4 : 0));
     // first weight row of the tile's (two) halves
     const int row_a = p.gated ? tile * (TILE_F / 2) : tile * TILE_F;
     const int row_b = p.gated ? half_n + tile * (TILE_F / 2) : tile * TILE_F + TILE_F / 2;
@@ -265,6 +436,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
+        if (p.cluster) cluster_wait();                      // all CTAs of the cluster have started
         if (have) mbar_wait(tfull, 0, &abort_flag, 4);
         // every epilogue thread comes here in bounded time; after the barrier they all see the same
         // abort flag, so the named barriers below are never reached by only some of them
@@ -274,7 +446,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         float* fin = reinterpret_cast<float*>(tiles);       // [128][MB + 1], the stages are free now
         if (ok) {
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            float* part = p.splits > 1 ? p.scratch + ((size_t)(tile * p.splits + split) * MB) * TILE_F : nullptr;
+            float* part = (p.splits > 1 && !p.cluster) ? p.scratch + ((size_t)(tile * p.splits + split) * MB) * TILE_F : nullptr;
+            // the first CTA of the cluster collects the partial rows: [split][row][feature]
+            const uint32_t red_first = p.cluster ? cluster_map(smem_u32(red), 0) + (uint32_t)((split * 8) * TILE_F + f) * 4u : 0u;
 #pragma unroll
             for (int c = 0; c < MB; c += 16) {
                 uint32_t r[16];
@@ -291,7 +465,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 }
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-                    if (part) {
+                    if (p.cluster) {
+                        if (c + e < p.M) st_cluster_f32(red_first + (uint32_t)((c + e) * TILE_F) * 4u, __uint_as_float(r[e]));
+                    } else if (part) {
                         if (c + e < p.M) part[(size_t)(c + e) * TILE_F + f] = __uint_as_float(r[e]);   // real rows only
                     } else {
                         fin[f * (MB + 1) + c + e] = __uint_as_float(r[e]);
@@ -300,138 +476,37 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
             bool finish = true;
             if (p.splits > 1) {
-                __threadfence();
-                epi_sync();
-                if (et == 0) is_last = atomicAdd(&p.counters[tile], 1) == p.splits - 1;
-                epi_sync();
-                finish = is_last != 0;
-                if (finish && !p.gated && (!p.q_out || p.hd >= 8)) {
-                    // Plain and rotary products: the last CTA adds the partials and runs the epilogue in one pass,
-                    // four neighbouring features per thread (16-byte reads of the partials, 8-byte
-                    // reads of the residual, 8- or 16-byte stores), four rows and four splits in
-                    // flight at a time.  A row is summed in split order, whatever the batch holds.
+                // Plain and rotary products: one CTA adds the partials and runs the epilogue in one
+                // pass (finish_from_parts).  In a cluster that is the first CTA, after the cluster's
+                // barrier; else the CTA that arrives last at the tile's counter.
+                bool from_parts = false;
+                const float* parts = nullptr;
+                if (p.cluster) {
+                    cluster_arrive();                      // releases the stores above
+                    cluster_wait();
+                    from_parts = cluster_ctarank() == 0;
+                    parts = red;
+                    finish = false;
+                } else {
                     __threadfence();
-                    const int fq = et & 31, rg = et >> 5;
-                    const int n0 = tile * TILE_F + 4 * fq;
-                    const float* base = p.scratch + ((size_t)tile * p.splits * MB) * TILE_F + 4 * fq;
-                    const bool vec = (p.N & 3) == 0 && n0 + 3 < p.N;
-                    if (p.q_out) {
-                        if (et < p.M) {
-                            const int pos = p.positions[et];
-                            row_pos[et] = pos < 0 ? 0 : (pos >= p.table_rows ? p.table_rows - 1 : pos);
-                            row_slot[et] = p.slot_mapping[et];
-                        }
-                        epi_sync();
+                    epi_sync();
+                    if (et == 0) is_last = atomicAdd(&p.counters[tile], 1) == p.splits - 1;
+                    epi_sync();
+                    finish = is_last != 0;
+                    if (finish && !p.gated && (!p.q_out || p.hd >= 8)) {
+                        __threadfence();
+                        from_parts = true;
+                        parts = p.scratch + ((size_t)tile * p.splits * MB) * TILE_F;
+                        finish = false;                    // nothing is left for the shared epilogue below
                     }
-                    float bias4[4] = {0.f, 0.f, 0.f, 0.f};
-                    if (p.bias) {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) if (n0 + e < p.N) bias4[e] = rv_load_param(p.bias, p.bias_dtype, n0 + e);
+                }
+                if (from_parts) {
+                    if (p.cluster) {
+                        finish_from_parts<MB, true>(p, tile, et, parts, 8, row_pos, row_slot);
+                    } else {
+                        finish_from_parts<MB, false>(p, tile, et, parts, MB, row_pos, row_slot);
+                        if (et == 0) p.counters[tile] = 0;     // ready for the next launch
                     }
-                    for (int m0 = rg; m0 < p.M; m0 += 16) {
-                        float4 acc[4];
-                        uint2 res[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            res[j] = make_uint2(0u, 0u);
-                            const int m = m0 + 4 * j;
-                            if (p.residual && vec && m < p.M)
-                                res[j] = __ldg(reinterpret_cast<const uint2*>(p.residual + (size_t)m * p.N + n0));
-                        }
-                        for (int s0 = 0; s0 < p.splits; s0 += 4) {
-                            float4 t[4][4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                                for (int i = 0; i < 4; ++i)
-                                    t[j][i] = (m0 + 4 * j < p.M && s0 + i < p.splits)
-                                                  ? __ldcg(reinterpret_cast<const float4*>(base + ((size_t)(s0 + i) * MB + m0 + 4 * j) * TILE_F))
-                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    acc[j].x += t[j][i].x; acc[j].y += t[j][i].y; acc[j].z += t[j][i].z; acc[j].w += t[j][i].w;
-                                }
-                        }
-                        if (p.q_out) {
-                            // rotary epilogue: hd is a power of two >= 8 and N a multiple of it, so the four
-                            // features lie in one half of one head and their partners (hd / 2 further or
-                            // nearer) are held by the lane hd / 8 away; every lane takes part in the exchange
-                            const int hd = p.hd, half = hd >> 1;
-                            const int head = n0 / hd, d = n0 - head * hd;
-                            const bool live = n0 < p.N;
-                            const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
-                            const bool first = d < half;
-                            const int i0 = first ? d : d - half;
-                            const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int m = m0 + 4 * j;
-                                const bool row_ok = m < p.M;                     // uniform in the warp
-                                float own[4] = {acc[j].x, acc[j].y, acc[j].z, acc[j].w}, other[4];
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    own[e] = __bfloat162float(__float2bfloat16_rn(own[e])) + bias4[e];
-                                    other[e] = __shfl_xor_sync(0xffffffffu, own[e], hd >> 3);
-                                }
-                                if (!row_ok || !live) continue;
-                                float v[4] = {own[0], own[1], own[2], own[3]};
-                                if ((is_q || is_k) && p.cos_t) {
-                                    const float4 c = __ldg(reinterpret_cast<const float4*>(p.cos_t + (size_t)row_pos[m] * half + i0));
-                                    const float4 sn = __ldg(reinterpret_cast<const float4*>(p.sin_t + (size_t)row_pos[m] * half + i0));
-                                    const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e)
-                                        v[e] = first ? own[e] * cc[e] - other[e] * ss[e] : other[e] * ss[e] + own[e] * cc[e];
-                                }
-                                uint2 o2;
-                                o2.x = pack_bf16x2(v[0], v[1]);
-                                o2.y = pack_bf16x2(v[2], v[3]);
-                                if (is_q) {
-                                    *reinterpret_cast<uint2*>(p.q_out + (size_t)m * p.nh * hd + n0) = o2;
-                                } else {
-                                    const int slot = row_slot[m];
-                                    if (slot >= 0) {
-                                        const int page = slot / p.page_size, off = slot - page * p.page_size;
-                                        *reinterpret_cast<uint2*>(p.kv_cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * p.nkv + kvh) * p.page_size + off) * hd + d) = o2;
-                                    }
-                                }
-                            }
-                            continue;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int m = m0 + 4 * j;
-                            if (m >= p.M || n0 >= p.N) continue;
-                            float v[4] = {acc[j].x + bias4[0], acc[j].y + bias4[1], acc[j].z + bias4[2], acc[j].w + bias4[3]};
-                            if (vec) {
-                                if (p.residual) {
-                                    const __nv_bfloat16* re = reinterpret_cast<const __nv_bfloat16*>(&res[j]);
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e) v[e] += __bfloat162float(re[e]);
-                                }
-                                if (p.out_f32) {
-                                    *reinterpret_cast<float4*>((float*)p.out + (size_t)m * p.N + n0) = make_float4(v[0], v[1], v[2], v[3]);
-                                } else {
-                                    uint2 o2;
-                                    o2.x = pack_bf16x2(v[0], v[1]);
-                                    o2.y = pack_bf16x2(v[2], v[3]);
-                                    *reinterpret_cast<uint2*>((__nv_bfloat16*)p.out + (size_t)m * p.N + n0) = o2;
-                                }
-                            } else {
-                                for (int e = 0; e < 4 && n0 + e < p.N; ++e) {
-                                    float w = v[e];
-                                    if (p.residual) w += __bfloat162float(p.residual[(size_t)m * p.N + n0 + e]);
-                                    if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n0 + e] = w;
-                                    else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n0 + e] = __float2bfloat16_rn(w);
-                                }
-                            }
-                        }
-                    }
-                    if (et == 0) p.counters[tile] = 0;     // ready for the next launch
-                    finish = false;                        // nothing is left for the shared epilogue below
                 }
                 if (finish) {
                     __threadfence();
@@ -548,15 +623,24 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     }
                 }
             }
+        } else if (p.cluster) {
+            cluster_arrive();                              // gave up: the cluster's hand-over still takes place
+            cluster_wait();
         }
     }
 
+    // The cluster's barrier has two phases, and every thread of the cluster takes part in both: the
+    // start (arrive at the top; wait before the partials are stored) and the hand-over of the
+    // partials (arrive after the stores, then wait).  Warps 0 and 1 store nothing: they arrive for the
+    // hand-over here and wait at the very end.
+    if (p.cluster && warp < 2) { cluster_wait(); cluster_arrive(); }
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
     }
     if (threadIdx.x == 0 && abort_flag != 0 && p.status) atomicCAS(p.status, 0, abort_flag);
+    if (p.cluster && warp < 2) cluster_wait();
 }
 
 template <int MB>
@@ -567,16 +651,22 @@ static int launch_decode(const CUtensorMap& mw, const CUtensorMap& mx, const Dec
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             smem + MAX_NORM_K * 4);
+                                             smem + MAX_NORM_K * 4 + 8 * 8 * TILE_F * 4);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    if (p.norm_gamma) {
+    if (p.norm_gamma || p.cluster) {
         const int num_kb = (p.K + BK - 1) / BK;
-        smem = STAGES * stage + ((num_kb + p.splits - 1) / p.splits) * BK * 4 + 1024;    // gamma of a CTA's K range after the stages
+        smem = STAGES * stage + 1024;
+        if (p.norm_gamma) smem += ((num_kb + p.splits - 1) / p.splits) * BK * 4;     // gamma of a CTA's K range behind the stages
+        if (p.cluster) smem += p.splits * 8 * TILE_F * 4;                           // the cluster's partial rows behind that
         if (smem < fin + 1024) smem = fin + 1024;
     }
-    RV_LAUNCH_ST = rv_launch(gemm_decode_kernel<MB>, dim3(p.n_tiles * p.splits), dim3(NUM_THREADS), smem, stream, mw, mx, p);
+    if (p.cluster)
+        RV_LAUNCH_ST = rv_launch_cluster(gemm_decode_kernel<MB>, dim3(p.n_tiles * p.splits), dim3(NUM_THREADS), smem, stream,
+                                         (unsigned)p.splits, mw, mx, p);
+    else
+        RV_LAUNCH_ST = rv_launch(gemm_decode_kernel<MB>, dim3(p.n_tiles * p.splits), dim3(NUM_THREADS), smem, stream, mw, mx, p);
     return rv_launch_status();
 }
 
@@ -597,11 +687,14 @@ static int run_decode(const void* x, const void* w, DecodeGemmParams p, cudaStre
     if (p.norm_gamma && p.M > 16) return RV_ERR_UNSUPPORTED;       // the fused norm serves one 16-row tile
     if (p.norm_gamma && (p.K + BK - 1) / BK * BK > MAX_NORM_K) return RV_ERR_UNSUPPORTED;
     p.x_raw = (const __nv_bfloat16*)x;
-    if (p.splits > 1 && (!p.scratch || !p.counters)) return RV_ERR_BAD_SIZE;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return RV_ERR_ALIGNMENT;
     if (p.M == 0) return RV_OK;
     const int num_kb = (p.K + BK - 1) / BK;
     if (p.splits > num_kb) p.splits = num_kb;
+    // few rows, few splits, an epilogue that adds partials four features at a time: the CTAs of a tile
+    // form a cluster and add up in shared memory
+    p.cluster = (p.cluster && p.splits >= 2 && p.splits <= 8 && p.M <= 8 && !p.gated && (!p.q_out || p.hd >= 8)) ? 1 : 0;
+    if (p.splits > 1 && !p.cluster && (!p.scratch || !p.counters)) return RV_ERR_BAD_SIZE;
     const int mb = rv_gemm_decode_padded_rows(p.M);
     alignas(64) CUtensorMap mw, mx;
     int st = rv_make_bf16_map(&mw, w, p.N, p.K, TILE_F / 2);
@@ -619,7 +712,7 @@ static int run_decode(const void* x, const void* w, DecodeGemmParams p, cudaStre
 
 RV_EXPORT int rv_gemm_tcgen05_decode_bf16(const void* x, const void* w, const void* bias, int bias_dtype,
                                           const void* residual, void* out, int out_f32, int M, int N, int K,
-                                          int gated, int splits, float* scratch, int* counters, int* status,
+                                          int gated, int splits, int cluster, float* scratch, int* counters, int* status,
                                           const void* norm_gamma, int norm_gamma_dtype, float norm_eps,
                                           cudaStream_t stream) {
     if (gated && ((N & 1) || bias || residual)) return RV_ERR_BAD_SIZE;
@@ -627,18 +720,20 @@ RV_EXPORT int rv_gemm_tcgen05_decode_bf16(const void* x, const void* w, const vo
     DecodeGemmParams p = {};
     p.out = out; p.residual = (const __nv_bfloat16*)residual; p.bias = bias; p.bias_dtype = bias_dtype;
     p.scratch = scratch; p.counters = counters; p.status = status;
-    p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.gated = gated; p.splits = splits;
+    p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.gated = gated; p.splits = splits; p.cluster = cluster;
     p.norm_gamma = norm_gamma; p.norm_gamma_dtype = norm_gamma_dtype; p.norm_eps = norm_eps;
     return run_decode(x, w, p, stream);
 }
 
+// cluster (both entry points): 1 asks for the reduction inside a thread-block cluster where the
+// kernel can do it (2 to 8 splits, up to 8 rows, not gated); scratch and counters are then unused.
 // norm_gamma (both entry points): RMSNorm weights [K] applied to x inside the kernel (M <= 16), or nullptr.
 // The q/k/v product of an attention layer with bias, rotation and the cache write in its epilogue.
 // w: [(nh + 2 nkv) * hd, K]; q_out: [M, nh * hd]; kv_cache: [pages, 2, nkv, page_size, hd].
 RV_EXPORT int rv_gemm_decode_qkv_rope(const void* x, const void* w, const void* bias, int bias_dtype,
                                       const int* positions, const float* cos_t, const float* sin_t,
                                       const int* slot_mapping, void* kv_cache, void* q_out, int M, int K,
-                                      int nh, int nkv, int hd, int page_size, int table_rows, int splits,
+                                      int nh, int nkv, int hd, int page_size, int table_rows, int splits, int cluster,
                                       float* scratch, int* counters, int* status, const void* norm_gamma,
                                       int norm_gamma_dtype, float norm_eps, cudaStream_t stream) {
     if (nh <= 0 || nkv <= 0 || hd <= 0 || (hd & 1) || page_size <= 0 || table_rows <= 0) return RV_ERR_BAD_SIZE;
@@ -648,7 +743,7 @@ RV_EXPORT int rv_gemm_decode_qkv_rope(const void* x, const void* w, const void* 
     DecodeGemmParams p = {};
     p.bias = bias; p.bias_dtype = bias_dtype;
     p.scratch = scratch; p.counters = counters; p.status = status;
-    p.M = M; p.N = (nh + 2 * nkv) * hd; p.K = K; p.splits = splits;
+    p.M = M; p.N = (nh + 2 * nkv) * hd; p.K = K; p.splits = splits; p.cluster = cluster;
     p.q_out = (__nv_bfloat16*)q_out; p.kv_cache = (__nv_bfloat16*)kv_cache; p.positions = positions;
     p.slot_mapping = slot_mapping; p.cos_t = cos_t; p.sin_t = sin_t;
     p.nh = nh; p.nkv = nkv; p.hd = hd; p.page_size = page_size; p.table_rows = table_rows;

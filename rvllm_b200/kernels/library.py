@@ -72,6 +72,9 @@ class CudaKernels:
     TCGEN05_ATTENTION_MIN_TOKENS = 16  # ... from this many tokens in the longest portion of the step
     DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
     DECODE_SPLIT_ROWS = 8   # ... when K has to be split over CTAs, only up to this many rows
+    CLUSTER_REDUCE = True        # split-K partials of few rows are added up inside a thread-block cluster
+    CLUSTER_MAX_ROWS = 8
+    CLUSTER_TARGET_CTAS = 225    # of such a product, tiles x splits (measured best at 8B, 7B and 32B layer sizes)
     BALANCED_DECODE = True  # decode attention by the kernel that cuts all tiles evenly over resident CTAs ...
     BALANCED_MIN_PAIRS = 256  # ... from this many (sequence, kv head) pairs on
     FUSED_QKV_PREFILL = True  # from TCGEN05_MIN_ROWS rows on the prefill GEMM rotates and writes the cache in its epilogue
@@ -450,8 +453,21 @@ class CudaKernels:
         return (norm is not None and x.dtype == torch.bfloat16 and 0 < x.shape[0] <= self.FUSED_NORM_MAX_ROWS
                 and x.shape[1] <= 8128)       # the kernel keeps gamma of its K range in shared memory
 
+    def _cluster_policy(self, M, gated, splits, cluster, tiles, K, chosen):
+        """(splits, cluster) of a decode GEMM.  Up to `CLUSTER_MAX_ROWS` rows of a product that is not
+        gated are cut into at most 8 CTAs per tile, which add their partials up inside a cluster; where
+        the caller left the cut open, about `CLUSTER_TARGET_CTAS` CTAs in all (measured: more CTAs
+        than that delay the next kernel's first loads by more than they gain)."""
+        if cluster is None:
+            cluster = self.CLUSTER_REDUCE and not gated and 0 < M <= self.CLUSTER_MAX_ROWS and splits >= 2
+            if cluster:
+                if not chosen:
+                    splits = max(2, min(self.CLUSTER_TARGET_CTAS // max(tiles, 1), ((K + 63) // 64) // 4))
+                splits = min(splits, 8)
+        return splits, bool(cluster)
+
     def linear_decode(self, x, weight, bias=None, residual=None, out_dtype=None, gated=False, splits=None, status=None,
-                      norm=None):
+                      norm=None, cluster=None):
         """The weight-streaming tcgen05 GEMM for at most 128 rows of bfloat16 activations.
         norm = (gamma, eps): RMSNorm applied to x inside the kernel (at most 16 rows)."""
         _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
@@ -461,9 +477,11 @@ class CudaKernels:
         out_dtype = out_dtype or torch.bfloat16
         out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
         tiles = lib.rv_gemm_decode_tiles(c_int(N), c_int(1 if gated else 0))
+        chosen = splits is not None
         if splits is None:
             splits = self.gemm_splits(tiles, K)
         splits = max(1, min(splits, (K + 63) // 64))
+        splits, cluster = self._cluster_policy(M, gated, splits, cluster, tiles, K, chosen)
         scratch = None
         if splits > 1:
             if self._decode_counters is None or self._decode_counters.numel() < tiles:
@@ -477,7 +495,8 @@ class CudaKernels:
         st = lib.rv_gemm_tcgen05_decode_bf16(
             _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0), _ptr(residual),
             _ptr(out), c_int(1 if out_dtype == torch.float32 else 0), c_int(M), c_int(N), c_int(K),
-            c_int(1 if gated else 0), c_int(splits), _ptr(scratch), _ptr(self._decode_counters if splits > 1 else None),
+            c_int(1 if gated else 0), c_int(splits), c_int(1 if cluster else 0), _ptr(scratch),
+            _ptr(self._decode_counters if splits > 1 else None),
             _ptr(status), *self._norm_args(norm, K), self._stream())
         _check("gemm_tcgen05_decode", st)
         return out
@@ -535,7 +554,7 @@ class CudaKernels:
         return q
 
     def _qkv_rope_fused(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
-                        num_heads, num_kv_heads, head_dim, splits=None, status=None, norm=None):
+                        num_heads, num_kv_heads, head_dim, splits=None, status=None, norm=None, cluster=None):
         _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
         _need(positions, "positions", torch.int32, 1); _need(slot_mapping, "slot_mapping", torch.int32, 1)
         _need(cache_layer, "cache_layer", torch.bfloat16, 5)
@@ -554,9 +573,11 @@ class CudaKernels:
             _need(bias, "bias", dims=1)
         lib = self._lib("gemm_tcgen05_decode.cu")
         tiles = lib.rv_gemm_decode_tiles(c_int(N), c_int(0))
+        chosen = splits is not None
         if splits is None:
             splits = self.gemm_splits(tiles, K)
         splits = max(1, min(splits, (K + 63) // 64))
+        splits, cluster = self._cluster_policy(M, False, splits, cluster, tiles, K, chosen)
         scratch = None
         if splits > 1:
             if self._decode_counters is None or self._decode_counters.numel() < tiles:
@@ -568,7 +589,7 @@ class CudaKernels:
             _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0),
             _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(cache_layer), _ptr(q), c_int(M), c_int(K),
             c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]),
-            c_int(cos.shape[0] if cos is not None else 1), c_int(splits), _ptr(scratch),
+            c_int(cos.shape[0] if cos is not None else 1), c_int(splits), c_int(1 if cluster else 0), _ptr(scratch),
             _ptr(self._decode_counters if splits > 1 else None), _ptr(status), *self._norm_args(norm, K), self._stream())
         _check("gemm_decode_qkv_rope", st)
         return q

@@ -327,6 +327,43 @@ def test_gemm_tcgen05_decode_bf16(K, M, N, Kd):
         assert int(K._decode_counters.abs().sum().item()) == 0
 
 
+@pytest.mark.parametrize("M,N,Kd", [(1, 4096, 4096), (8, 520, 1032), (3, 101, 200), (5, 1024, 14336)])
+def test_split_k_added_up_inside_a_cluster(K, M, N, Kd):
+    """The CTAs of a tile as a thread-block cluster that adds its partials in the first CTA's shared
+    memory: the same bits as the merge through scratch memory (both add in split order), for every
+    cluster size, with bias, residual, float output and the fused norm; launches alternate so that a
+    cluster launch follows a plain one and the other way round."""
+    torch.manual_seed(14)
+    x = torch.randn(M, Kd, device="cuda").bfloat16()
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(N, device="cuda").bfloat16()
+    r = torch.randn(M, N, device="cuda").bfloat16()
+    gamma = (1 + 0.1 * torch.randn(Kd, device="cuda")).bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ref = x.double().cpu() @ w.double().cpu().t() + b.double().cpu() + r.double().cpu()
+    for splits in range(2, 9):
+        if splits > (Kd + 63) // 64:
+            break
+        a = K.linear_decode(x, w, b, r, splits=splits, status=status, cluster=True)
+        c = K.linear_decode(x, w, b, r, splits=splits, status=status, cluster=False)
+        assert torch.equal(a, c) and rel_err(a, ref) < BF16_TOL
+        a = K.linear_decode(x, w, None, None, torch.float32, splits=splits, status=status, cluster=True)
+        c = K.linear_decode(x, w, None, None, torch.float32, splits=splits, status=status, cluster=False)
+        assert torch.equal(a, c)
+        if Kd <= 8128:
+            a = K.linear_decode(x, w, None, r, splits=splits, status=status, norm=(gamma, 1e-5), cluster=True)
+            c = K.linear_decode(x, w, None, r, splits=splits, status=status, norm=(gamma, 1e-5), cluster=False)
+            assert torch.equal(a, c)
+    # what a cluster cannot serve falls back to the merge through scratch memory: many rows, many splits
+    many = torch.cat([x] * 3)
+    assert torch.equal(K.linear_decode(many, w, splits=2, cluster=True)[:M], K.linear_decode(x, w, splits=2, cluster=False))
+    if (Kd + 63) // 64 >= 9:
+        assert rel_err(K.linear_decode(x, w, b, r, splits=9, status=status, cluster=True), ref) < BF16_TOL
+    assert int(status.item()) == 0
+    if K._decode_counters is not None:
+        assert int(K._decode_counters.abs().sum().item()) == 0
+
+
 @pytest.mark.parametrize("M,nh,nkv,hd,Kd,page,bias", [(1, 32, 8, 128, 4096, 16, False), (5, 6, 2, 32, 96, 8, True),
                                                       (16, 5, 5, 16, 80, 16, True), (3, 4, 1, 64, 264, 4, False)])
 def test_qkv_product_with_rotation_and_cache_write_in_one_kernel(K, M, nh, nkv, hd, Kd, page, bias):
@@ -354,6 +391,16 @@ def test_qkv_product_with_rotation_and_cache_write_in_one_kernel(K, M, nh, nkv, 
         cache_b.fill_(7.0)
         qb = K.rope_cache_write(qkv, b, positions, cos, sin, slots, cache_b, nh, nkv, hd)
         assert torch.equal(qa, qb) and torch.equal(cache_a, cache_b)
+    if Kd >= 128:                           # the cluster's merge and the one through scratch memory
+        for cluster in (True, False):
+            cache_b.fill_(7.0)
+            qc = K._qkv_rope_fused(x, w, b, positions, cos, sin, slots, cache_b, nh, nkv, hd, splits=2, status=status, cluster=cluster)
+            qkv = K.linear_decode(x, w, splits=2, cluster=False)
+            cache_a.fill_(7.0)
+            qb = K.rope_cache_write(qkv, b, positions, cos, sin, slots, cache_a, nh, nkv, hd)
+            assert torch.equal(qc, qb) and torch.equal(cache_a, cache_b)
+        cache_a.fill_(7.0)
+        qa = K._qkv_rope_fused(x, w, b, positions, cos, sin, slots, cache_a, nh, nkv, hd, splits=3, status=status)
     assert int(status.item()) == 0
     # plain arithmetic
     y = x.double().cpu() @ w.double().cpu().t()
