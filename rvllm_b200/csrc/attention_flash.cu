@@ -469,6 +469,12 @@ flash_decode_balanced_kernel(const BalancedParams p) {
     const int total = s_first[p.num_seqs] * p.nkv;
     const int ctas = gridDim.x, cta = blockIdx.x;
     const int W = total > 0 ? (total + ctas - 1) / ctas : 1;
+    int u = cta * W;
+    const int u_end = min(total, u + W);
+    // Nothing is written before this wait: the buffers of this launch may be memory that a kernel
+    // still running ahead of it in the stream uses under another name (a stream-ordered allocator
+    // hands freed blocks out again at once).
+    rv_pdl_wait();          // every CTA, with or without work, keeps the order of the chain of kernels
     // pieces of every pair, for the merge kernel: each CTA writes its share of the pairs
     for (int pair = cta * NTHREADS + tid; pair < p.num_seqs * p.nkv; pair += ctas * NTHREADS) {
         const int s = pair / p.nkv, kvh = pair - s * p.nkv;
@@ -480,9 +486,6 @@ flash_decode_balanced_kernel(const BalancedParams p) {
         }
         p.piece_count[pair] = count;
     }
-    int u = cta * W;
-    const int u_end = min(total, u + W);
-    rv_pdl_wait();          // every CTA, with or without work, keeps the order of the chain of kernels
     if (u >= u_end) return;
 
     const size_t page_stride = (size_t)2 * p.nkv * p.page_size * HD;

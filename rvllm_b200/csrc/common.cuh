@@ -25,6 +25,9 @@
 // rv_pdl_wait() (set-up, fetching weights, which no kernel of the step writes) overlaps the
 // predecessor's tail; everything after rv_pdl_wait() sees the predecessor complete.  Without the
 // attribute both calls do nothing.  The switch is per library (rv_set_pdl).
+// Two rules for what runs before rv_pdl_wait(): it reads only what no kernel of the step writes
+// (weights, the step's metadata), and it writes no global memory at all - a buffer handed out by a
+// stream-ordered allocator may still be in use, under another name, by a kernel running ahead.
 static int g_rv_pdl = 0;
 RV_EXPORT void rv_set_pdl(int on) { g_rv_pdl = on; }
 

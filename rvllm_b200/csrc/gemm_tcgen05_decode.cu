@@ -26,10 +26,11 @@
 // 1 / sqrt(mean(x^2) + eps) from global memory, then scale every activation tile in shared memory
 // by it and by gamma as soon as its TMA load has landed, and hand the tile to the MMA warp through a
 // second barrier per stage.  The norm kernel and its place in the chain of launches are saved.
-// For up to 8 rows and up to 8 splits the CTAs of a tile are launched as a thread-block cluster: each
-// writes its partial rows into the first CTA's shared memory (st.shared::cluster), one cluster barrier
-// later that CTA adds them in split order and runs the epilogue - no round trip through L2, no
-// fence, no atomic.  Every thread of every CTA reaches the cluster barrier on every path.
+// For up to 64 rows and up to 8 splits the CTAs of a tile are launched as a thread-block cluster.  The
+// rows are dealt out to the CTAs, ceil(M / splits) each; every CTA writes its partial of a row into
+// the shared memory of the CTA that owns the row (st.shared::cluster), and one cluster barrier later
+// each CTA adds its rows' partials in split order and runs their epilogue - no round trip through L2,
+// no fence, no atomic.  Every thread of every CTA reaches the cluster barrier on every path.
 // Every mbarrier wait is bounded (see gemm_tcgen05.cu); no multicast.
 //
 // Shapes: the five products of a layer and the LM head at decode time
@@ -58,7 +59,8 @@ struct DecodeGemmParams {
     int out_f32, gated;
     int splits, n_tiles;
     int cluster;             // 1: the CTAs of a tile are a thread-block cluster and add their partials in the
-                             // first one's shared memory (M <= 8, 2 <= splits <= 8); scratch and counters unused
+                             // cluster's shared memory (M <= 64, 2 <= splits <= 8); scratch and counters unused
+    int cluster_rows;        // rows that each CTA of the cluster finishes: ceil(M / splits)
     // rotary epilogue (q_out != nullptr): N = (nh + 2 nkv) * hd, 128 % hd == 0
     __nv_bfloat16* q_out;            // [M, nh * hd]
     __nv_bfloat16* kv_cache;         // [pages, 2, nkv, page_size, hd]
@@ -103,7 +105,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // that finishes the tile: four neighbouring features per thread (16-byte reads of the partials,
 // 8-byte reads of the residual, 8- or 16-byte stores), four rows and four splits in flight at a
 // time.  A row is summed in split order, whatever the batch holds.  The partial of (split s, row m)
-// starts at parts + (s * part_rows + m) * 128, in scratch memory or in the CTA's shared memory.
+// starts at parts + (s * part_rows + m - row_begin) * 128, in scratch memory or in the CTA's shared
+// memory; the rows [row_begin, row_end) are finished.
 // (volatile asm on purpose: plain loads let the compiler hoist all of a thread's loads and spend 47 more registers)
 template <bool IN_SMEM>
 __device__ __forceinline__ float4 load_part(const float* src) {
@@ -117,7 +120,7 @@ __device__ __forceinline__ float4 load_part(const float* src) {
 
 template <int MB, bool IN_SMEM>
 __device__ __forceinline__ void finish_from_parts(const DecodeGemmParams& p, int tile, int et, const float* parts,
-                                                  int part_rows, int* row_pos, int* row_slot) {
+                                                  int part_rows, int row_begin, int row_end, int* row_pos, int* row_slot) {
     const int fq = et & 31, rg = et >> 5;
     const int n0 = tile * TILE_F + 4 * fq;
     const float* base = parts + 4 * fq;
@@ -135,7 +138,7 @@ __device__ __forceinline__ void finish_from_parts(const DecodeGemmParams& p, int
 #pragma unroll
         for (int e = 0; e < 4; ++e) if (n0 + e < p.N) bias4[e] = rv_load_param(p.bias, p.bias_dtype, n0 + e);
     }
-    for (int m0 = rg; m0 < p.M; m0 += 16) {
+    for (int m0 = row_begin + rg; m0 < row_end; m0 += 16) {
         float4 acc[4];
         uint2 res[4];
 #pragma unroll
@@ -143,7 +146,7 @@ __device__ __forceinline__ void finish_from_parts(const DecodeGemmParams& p, int
             acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
             res[j] = make_uint2(0u, 0u);
             const int m = m0 + 4 * j;
-            if (p.residual && vec && m < p.M)
+            if (p.residual && vec && m < row_end)
                 res[j] = __ldg(reinterpret_cast<const uint2*>(p.residual + (size_t)m * p.N + n0));
         }
         for (int s0 = 0; s0 < p.splits; s0 += 4) {
@@ -152,8 +155,8 @@ __device__ __forceinline__ void finish_from_parts(const DecodeGemmParams& p, int
             for (int j = 0; j < 4; ++j)
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    t[j][i] = (m0 + 4 * j < p.M && s0 + i < p.splits)
-                                  ? load_part<IN_SMEM>(base + ((size_t)(s0 + i) * part_rows + m0 + 4 * j) * TILE_F)
+                    t[j][i] = (m0 + 4 * j < row_end && s0 + i < p.splits)
+                                  ? load_part<IN_SMEM>(base + ((size_t)(s0 + i) * part_rows + m0 + 4 * j - row_begin) * TILE_F)
                                   : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
@@ -176,7 +179,7 @@ __device__ __forceinline__ void finish_from_parts(const DecodeGemmParams& p, int
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int m = m0 + 4 * j;
-                const bool row_ok = m < p.M;                     // uniform in the warp
+                const bool row_ok = m < row_end;                 // uniform in the warp
                 float own[4] = {acc[j].x, acc[j].y, acc[j].z, acc[j].w}, other[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -211,7 +214,7 @@ __device__ __forceinline__ void finish_from_parts(const DecodeGemmParams& p, int
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int m = m0 + 4 * j;
-            if (m >= p.M || n0 >= p.N) continue;
+            if (m >= row_end || n0 >= p.N) continue;
             float v[4] = {acc[j].x + bias4[0], acc[j].y + bias4[1], acc[j].z + bias4[2], acc[j].w + bias4[3]};
             if (vec) {
                 if (p.residual) {
@@ -240,7 +243,7 @@ __device__ __forceinline__ void finish_from_parts(const DecodeGemmParams& p, int
 }
 
 template <int MB>
-__global__ void __launch_bounds__(NUM_THREADS, 3)
+__global__ void __launch_bounds__(NUM_THREADS, MB <= 16 ? 3 : 2)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    const DecodeGemmParams p) {
     constexpr int B_BYTES = MB * BK * 2;
@@ -285,8 +288,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int per = (num_kb + p.splits - 1) / p.splits;
     const int kb0 = split * per, kb1 = min(num_kb, kb0 + per);
     const int half_n = p.N >> 1;
-    // cluster reduction: [splits][8 rows][128 features] floats behind the stages (and gamma), at the
-    // same offset in every CTA of the cluster
+    // cluster reduction: [splits][cluster_rows][128 features] floats behind the stages (and gamma),
+    // at the same offset in every CTA of the cluster
     float* red = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES + (fused_norm ? (size_t)per * BK * 4 : 0));
     // first weight row of the tile's (two) halves
     const int row_a = p.gated ? tile * (TILE_F / 2) : tile * TILE_F;
@@ -447,8 +450,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (ok) {
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
             float* part = (p.splits > 1 && !p.cluster) ? p.scratch + ((size_t)(tile * p.splits + split) * MB) * TILE_F : nullptr;
-            // the first CTA of the cluster collects the partial rows: [split][row][feature]
-            const uint32_t red_first = p.cluster ? cluster_map(smem_u32(red), 0) + (uint32_t)((split * 8) * TILE_F + f) * 4u : 0u;
+            // row m goes to the CTA m / cluster_rows of the cluster, at [split][m % cluster_rows][feature]
+            const uint32_t red_mine = smem_u32(red) + (uint32_t)((split * p.cluster_rows) * TILE_F + f) * 4u;
 #pragma unroll
             for (int c = 0; c < MB; c += 16) {
                 uint32_t r[16];
@@ -463,10 +466,12 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                     for (int e = 0; e < 16; ++e) r[e] = 0u;    // this split got no k block: it adds zeros
                 }
+                int owner = c / p.cluster_rows, local = c - owner * p.cluster_rows;
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                     if (p.cluster) {
-                        if (c + e < p.M) st_cluster_f32(red_first + (uint32_t)((c + e) * TILE_F) * 4u, __uint_as_float(r[e]));
+                        if (c + e < p.M) st_cluster_f32(cluster_map(red_mine + (uint32_t)(local * TILE_F) * 4u, owner), __uint_as_float(r[e]));
+                        if (++local == p.cluster_rows) { local = 0; ++owner; }
                     } else if (part) {
                         if (c + e < p.M) part[(size_t)(c + e) * TILE_F + f] = __uint_as_float(r[e]);   // real rows only
                     } else {
@@ -476,15 +481,15 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
             bool finish = true;
             if (p.splits > 1) {
-                // Plain and rotary products: one CTA adds the partials and runs the epilogue in one
-                // pass (finish_from_parts).  In a cluster that is the first CTA, after the cluster's
-                // barrier; else the CTA that arrives last at the tile's counter.
+                // Plain and rotary products: the partials are added and the epilogue is run in one
+                // pass (finish_from_parts).  In a cluster every CTA does so for its rows, after the
+                // cluster's barrier; else the CTA that arrives last at the tile's counter, for all rows.
                 bool from_parts = false;
                 const float* parts = nullptr;
                 if (p.cluster) {
                     cluster_arrive();                      // releases the stores above
                     cluster_wait();
-                    from_parts = cluster_ctarank() == 0;
+                    from_parts = split * p.cluster_rows < p.M;      // (the rank in the cluster is the split)
                     parts = red;
                     finish = false;
                 } else {
@@ -502,9 +507,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 }
                 if (from_parts) {
                     if (p.cluster) {
-                        finish_from_parts<MB, true>(p, tile, et, parts, 8, row_pos, row_slot);
+                        finish_from_parts<MB, true>(p, tile, et, parts, p.cluster_rows, split * p.cluster_rows,
+                                                    min(p.M, (split + 1) * p.cluster_rows), row_pos, row_slot);
                     } else {
-                        finish_from_parts<MB, false>(p, tile, et, parts, MB, row_pos, row_slot);
+                        finish_from_parts<MB, false>(p, tile, et, parts, MB, 0, p.M, row_pos, row_slot);
                         if (et == 0) p.counters[tile] = 0;     // ready for the next launch
                     }
                 }
@@ -651,7 +657,7 @@ static int launch_decode(const CUtensorMap& mw, const CUtensorMap& mx, const Dec
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             smem + MAX_NORM_K * 4 + 8 * 8 * TILE_F * 4);
+                                             smem + MAX_NORM_K * 4 + (64 + 8) * TILE_F * 4);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -659,7 +665,7 @@ static int launch_decode(const CUtensorMap& mw, const CUtensorMap& mx, const Dec
         const int num_kb = (p.K + BK - 1) / BK;
         smem = STAGES * stage + 1024;
         if (p.norm_gamma) smem += ((num_kb + p.splits - 1) / p.splits) * BK * 4;     // gamma of a CTA's K range behind the stages
-        if (p.cluster) smem += p.splits * 8 * TILE_F * 4;                           // the cluster's partial rows behind that
+        if (p.cluster) smem += p.splits * p.cluster_rows * TILE_F * 4;              // the partials of this CTA's rows behind that
         if (smem < fin + 1024) smem = fin + 1024;
     }
     if (p.cluster)
@@ -693,7 +699,8 @@ static int run_decode(const void* x, const void* w, DecodeGemmParams p, cudaStre
     if (p.splits > num_kb) p.splits = num_kb;
     // few rows, few splits, an epilogue that adds partials four features at a time: the CTAs of a tile
     // form a cluster and add up in shared memory
-    p.cluster = (p.cluster && p.splits >= 2 && p.splits <= 8 && p.M <= 8 && !p.gated && (!p.q_out || p.hd >= 8)) ? 1 : 0;
+    p.cluster = (p.cluster && p.splits >= 2 && p.splits <= 8 && p.M <= 64 && !p.gated && (!p.q_out || p.hd >= 8)) ? 1 : 0;
+    p.cluster_rows = (p.M + p.splits - 1) / p.splits;
     if (p.splits > 1 && !p.cluster && (!p.scratch || !p.counters)) return RV_ERR_BAD_SIZE;
     const int mb = rv_gemm_decode_padded_rows(p.M);
     alignas(64) CUtensorMap mw, mx;
@@ -726,7 +733,7 @@ RV_EXPORT int rv_gemm_tcgen05_decode_bf16(const void* x, const void* w, const vo
 }
 
 // cluster (both entry points): 1 asks for the reduction inside a thread-block cluster where the
-// kernel can do it (2 to 8 splits, up to 8 rows, not gated); scratch and counters are then unused.
+// kernel can do it (2 to 8 splits, up to 64 rows, not gated); scratch and counters are then unused.
 // norm_gamma (both entry points): RMSNorm weights [K] applied to x inside the kernel (M <= 16), or nullptr.
 // The q/k/v product of an attention layer with bias, rotation and the cache write in its epilogue.
 // w: [(nh + 2 nkv) * hd, K]; q_out: [M, nh * hd]; kv_cache: [pages, 2, nkv, page_size, hd].

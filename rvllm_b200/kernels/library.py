@@ -73,13 +73,13 @@ class CudaKernels:
     DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
     DECODE_SPLIT_ROWS = 8   # ... when K has to be split over CTAs, only up to this many rows
     CLUSTER_REDUCE = True        # split-K partials of few rows are added up inside a thread-block cluster
-    CLUSTER_MAX_ROWS = 8
+    CLUSTER_MAX_ROWS = 32        # (with 64 rows one CTA fits an SM and the library's GEMM is faster)
     CLUSTER_TARGET_CTAS = 225    # of such a product, tiles x splits (measured best at 8B, 7B and 32B layer sizes)
     BALANCED_DECODE = True  # decode attention by the kernel that cuts all tiles evenly over resident CTAs ...
     BALANCED_MIN_PAIRS = 256  # ... from this many (sequence, kv head) pairs on
     FUSED_QKV_PREFILL = True  # from TCGEN05_MIN_ROWS rows on the prefill GEMM rotates and writes the cache in its epilogue
     FUSED_NORM_MAX_ROWS = 0 # rows up to which an RMSNorm is applied inside the decode GEMM that consumes it
-    FUSED_QKV_MAX_ROWS = 8  # rows up to which q/k/v product, rotation and cache write are one kernel
+    FUSED_QKV_MAX_ROWS = 32 # rows up to which q/k/v product, rotation and cache write are one kernel
     pdl = os.environ.get("RVLLM_NO_PDL") != "1"   # programmatic dependent launch between kernels
 
     def __init__(self, device="cuda:0"):
@@ -427,7 +427,8 @@ class CudaKernels:
         if not (0 < M <= self.DECODE_MAX_ROWS) or K % 8:
             return False
         tiles = ((N // 2 + 63) // 64) if gated else (N + 127) // 128
-        return M <= self.DECODE_SPLIT_ROWS or self.gemm_splits(tiles, K) == 1
+        split_rows = self.CLUSTER_MAX_ROWS if (self.CLUSTER_REDUCE and not gated) else self.DECODE_SPLIT_ROWS
+        return M <= max(split_rows, self.DECODE_SPLIT_ROWS) or self.gemm_splits(tiles, K) == 1
 
     def gemm_splits(self, n_tiles: int, K: int) -> int:
         """Into how many CTAs the K dimension of a decode GEMM is cut: about two CTAs per SM with

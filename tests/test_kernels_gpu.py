@@ -327,7 +327,8 @@ def test_gemm_tcgen05_decode_bf16(K, M, N, Kd):
         assert int(K._decode_counters.abs().sum().item()) == 0
 
 
-@pytest.mark.parametrize("M,N,Kd", [(1, 4096, 4096), (8, 520, 1032), (3, 101, 200), (5, 1024, 14336)])
+@pytest.mark.parametrize("M,N,Kd", [(1, 4096, 4096), (8, 520, 1032), (3, 101, 200), (5, 1024, 14336),
+                                    (9, 384, 4096), (17, 520, 1032), (32, 4096, 4096), (33, 256, 2048), (64, 1000, 1032)])
 def test_split_k_added_up_inside_a_cluster(K, M, N, Kd):
     """The CTAs of a tile as a thread-block cluster that adds its partials in the first CTA's shared
     memory: the same bits as the merge through scratch memory (both add in split order), for every
@@ -350,12 +351,12 @@ def test_split_k_added_up_inside_a_cluster(K, M, N, Kd):
         a = K.linear_decode(x, w, None, None, torch.float32, splits=splits, status=status, cluster=True)
         c = K.linear_decode(x, w, None, None, torch.float32, splits=splits, status=status, cluster=False)
         assert torch.equal(a, c)
-        if Kd <= 8128:
+        if Kd <= 8128 and M <= 16:
             a = K.linear_decode(x, w, None, r, splits=splits, status=status, norm=(gamma, 1e-5), cluster=True)
             c = K.linear_decode(x, w, None, r, splits=splits, status=status, norm=(gamma, 1e-5), cluster=False)
             assert torch.equal(a, c)
     # what a cluster cannot serve falls back to the merge through scratch memory: many rows, many splits
-    many = torch.cat([x] * 3)
+    many = torch.cat([x] * (65 // M + 1))
     assert torch.equal(K.linear_decode(many, w, splits=2, cluster=True)[:M], K.linear_decode(x, w, splits=2, cluster=False))
     if (Kd + 63) // 64 >= 9:
         assert rel_err(K.linear_decode(x, w, b, r, splits=9, status=status, cluster=True), ref) < BF16_TOL
