@@ -58,3 +58,31 @@ def test_bfloat16_mixed_batches_run_clean_and_repeat():
     b, _, _ = run("bfloat16", prompts, sp, num_blocks=600, max_num_seqs=16, max_num_batched_tokens=384)
     assert a == b
     assert all(len(t) == 40 for t in a)
+
+
+def test_bfloat16_batch_of_32_in_one_chain_of_dependent_launches():
+    """32 sequences of 8 kv heads decode together: the evenly cut attention kernel and its merge
+    kernel run between this project's own GEMMs (cluster reduce, rotation in the epilogue), every
+    kernel launched while its predecessor still runs.  A kernel that wrote before its wait for the
+    predecessor once corrupted a buffer still in use; so: no error, the same tokens twice, and the
+    same tokens as with eager steps."""
+    from rvllm_b200 import SamplingParams
+    wide = dict(MID, num_attention_heads=16, num_key_value_heads=8, head_dim=32, hidden_size=512)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 1000, (int(n),), generator=g).tolist() for n in torch.randint(100, 400, (32,), generator=g)]
+    sp = SamplingParams(temperature=0.0, max_tokens=48, ignore_eos=True)
+
+    def go(**extra):
+        from rvllm_b200 import LLM, config_from_dict
+        llm = LLM(config=config_from_dict(dict(wide)), random_weights=True, seed=3, dtype="bfloat16", block_size=16,
+                  max_model_len=1024, num_blocks=1600, max_num_seqs=32, max_num_batched_tokens=2048, **extra)
+        outs = llm.generate(prompts, sp)
+        llm.engine.cache.check()
+        return [o.outputs[0].token_ids for o in outs], llm
+
+    a, llm = go()
+    assert any(k[0] == 32 for k in llm.engine.runner._graphs), "the 32-row decode graph should have been used"
+    b, _ = go()
+    assert a == b
+    c, _ = go(enforce_eager=True)
+    assert a == c
