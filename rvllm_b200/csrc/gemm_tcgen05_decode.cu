@@ -61,6 +61,7 @@ struct DecodeGemmParams {
     int cluster;             // 1: the CTAs of a tile are a thread-block cluster and add their partials in the
                              // cluster's shared memory (M <= 64, 2 <= splits <= 8); scratch and counters unused
     int cluster_rows;        // rows that each CTA of the cluster finishes: ceil(M / splits)
+    int l2_ahead;            // k blocks beyond the shared-memory stages whose weights are asked into L2 before the wait
     // rotary epilogue (q_out != nullptr): N = (nh + 2 nkv) * hd, 128 % hd == 0
     __nv_bfloat16* q_out;            // [M, nh * hd]
     __nv_bfloat16* kv_cache;         // [pages, 2, nkv, page_size, hd]
@@ -310,6 +311,12 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 mbar_expect_tx(bar, STAGE_BYTES);
                 tma_load_2d(a_dst, &map_w, (kb0 + i) * BK, row_a, bar);
                 tma_load_2d(a_dst + A_BYTES / 2, &map_w, (kb0 + i) * BK, row_b, bar);
+            }
+            // ... and the weights of the k blocks after them are asked into L2: while this kernel waits
+            // for its predecessor (a norm, the merge of the attention's key splits) the memory is idle
+            for (int kb = kb0 + early; kb < min(kb1, kb0 + early + p.l2_ahead); ++kb) {
+                tma_prefetch_2d(&map_w, kb * BK, row_a);
+                tma_prefetch_2d(&map_w, kb * BK, row_b);
             }
             rv_pdl_wait();
             for (int i = 0; i < early; ++i)
@@ -686,7 +693,13 @@ RV_EXPORT int rv_gemm_decode_tiles(int N, int gated) {
     return gated ? (N / 2 + TILE_F / 2 - 1) / (TILE_F / 2) : (N + TILE_F - 1) / TILE_F;
 }
 
+static int g_l2_ahead = 0;
+// How many k blocks of weights beyond its shared-memory stages a CTA asks into L2 before it waits for
+// the previous kernel (0: none).
+RV_EXPORT void rv_gemm_decode_set_l2_ahead(int k_blocks) { g_l2_ahead = k_blocks < 0 ? 0 : k_blocks; }
+
 static int run_decode(const void* x, const void* w, DecodeGemmParams p, cudaStream_t stream) {
+    p.l2_ahead = g_l2_ahead;
     if (p.M < 0 || p.N <= 0 || p.K <= 0 || p.splits < 1) return RV_ERR_BAD_SIZE;
     if (p.M > 128) return RV_ERR_UNSUPPORTED;
     if (p.K % 8) return RV_ERR_UNSUPPORTED;
