@@ -98,9 +98,37 @@ template <int VPT>
 __global__ void rmsnorm_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ gamma,
                                         int gamma_dtype, __nv_bfloat16* __restrict__ out, int width, float eps) {
     rv_pdl_launch_dependents();
-    rv_pdl_wait();
     __shared__ float scratch[33];
     const int nvec = width >> 3;
+    // gamma is a weight: it is fetched before the wait for the kernel that writes x, 16 or 32 bytes
+    // at a time where its address allows
+    float g[VPT][8];
+    const bool g_vec = (reinterpret_cast<uintptr_t>(gamma) & 15) == 0;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c >= nvec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[i][j] = 0.f;
+        } else if (g_vec && gamma_dtype == RV_DTYPE_BF16) {
+            const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gamma) + c);
+            const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(gh[j]);
+                g[i][2 * j] = f.x; g[i][2 * j + 1] = f.y;
+            }
+        } else if (g_vec && gamma_dtype == RV_DTYPE_F32) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * c);
+            const float4 b = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * c + 1);
+            g[i][0] = a.x; g[i][1] = a.y; g[i][2] = a.z; g[i][3] = a.w;
+            g[i][4] = b.x; g[i][5] = b.y; g[i][6] = b.z; g[i][7] = b.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[i][j] = rv_load_param(gamma, gamma_dtype, c * 8 + j);
+        }
+    }
+    rv_pdl_wait();
     const uint4* row = reinterpret_cast<const uint4*>(x + (size_t)blockIdx.x * width);
     uint4* dst = reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * width);
     uint4 v[VPT];
@@ -129,9 +157,7 @@ __global__ void rmsnorm_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, con
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float2 f = __bfloat1622float2(h[j]);
-            const float g0 = rv_load_param(gamma, gamma_dtype, c * 8 + 2 * j);
-            const float g1 = rv_load_param(gamma, gamma_dtype, c * 8 + 2 * j + 1);
-            oh[j] = __floats2bfloat162_rn(f.x * r * g0, f.y * r * g1);
+            oh[j] = __floats2bfloat162_rn(f.x * r * g[i][2 * j], f.y * r * g[i][2 * j + 1]);
         }
         dst[c] = o;
     }
