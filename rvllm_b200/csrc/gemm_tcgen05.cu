@@ -16,9 +16,22 @@
 //            rotates q and k by the row's position (a head's two halves are read from tensor memory
 //            side by side), writes q to its output and k and v straight into the row's slot of the
 //            paged cache: the rotary kernel and the round trip of q/k/v through memory are saved.
-// No cluster, no multicast.  Every wait on an mbarrier is bounded: when a wait gives up, the CTA
+// No multicast load.  Every wait on an mbarrier is bounded: when a wait gives up, the CTA
 // sets an abort flag, every role leaves its loop, the producer waits (bounded) for its loads in
 // flight, tensor memory is freed, the kernel writes a status word and returns.
+//
+// Compiled with -DRV_PAIR=1 the same source is the kernel on PAIRS of CTAs (tcgen05 cta_group::2).  Two
+// CTAs on neighbouring SMs (a thread-block cluster of 2) own one output tile of 256 x 256.  Each CTA
+// fetches its own 128 rows of x and only HALF of the tile's 256 weight rows (32 KB per stage instead of
+// 48 KB, six stages instead of four); the first CTA of the pair issues tcgen05.mma.cta_group::2, which
+// reads the two halves of the weights from the two CTAs' shared memory and accumulates 128 rows x 256
+// columns in each CTA's tensor memory.  Both CTAs' loads are counted on the first CTA's mbarrier;
+// tcgen05.commit with multicast frees a stage in both CTAs and hands the accumulator to both CTAs'
+// epilogue warps, which arrive on the first CTA's barrier when they have read it out; the pair leaves
+// together through a cluster barrier.  Why it is faster: with one CTA a k block takes (load latency +
+// MMA time) / 4 stages, because four stages of 48 KB are all that fit, and 128 x 256 x 64 MACs per
+// 0.39 us ask for 123 GB/s per SM with about 1.2 us of latency; 32 KB per k block need 98 KB in flight.
+// The epilogues and the sums are the same in both builds (same bits).
 //
 // Shapes: the five products of a layer at prefill time
 // (v3/crates/rvllm-runtime/src/layer_exec.rs:240-266,433-444,478-488,511-522 of the reference,
@@ -27,13 +40,26 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 
+#ifndef RV_PAIR
+#define RV_PAIR 0
+#endif
 #define BM 128
 #define BN 256
 #define BK 64
-#define STAGES 4
 #define UMMA_K 16
 #define A_TILE_BYTES (BM * BK * 2)
+#if RV_PAIR
+#define STAGES 6
+#define TILE_ROWS (2 * BM)                      // rows of an output tile: both CTAs' 128
+#define B_TILE_BYTES (BN / 2 * BK * 2)          // this CTA's half of the tile's weight rows
+#define CTA_GROUP "2"
+#define gemm_tcgen05_kernel gemm_tcgen05_pair_kernel
+#else
+#define STAGES 4
+#define TILE_ROWS BM
 #define B_TILE_BYTES (BN * BK * 2)
+#define CTA_GROUP "1"
+#endif
 #define STAGE_BYTES (A_TILE_BYTES + B_TILE_BYTES)
 #define NUM_THREADS 192
 #define TMEM_COLS 512
@@ -50,7 +76,7 @@ struct GemmParams {
     int M, N, K;
     int out_f32;
     int epilogue;
-    int m_tiles, n_tiles;
+    int m_tiles, n_tiles;   // tiles of TILE_ROWS rows x 256 columns
     // EPI_ROPE: W rows are [q heads | k heads | v heads] of hd (64, 128 or 256) features
     const void* bias;                // [N] or nullptr
     int bias_dtype;
@@ -118,6 +144,50 @@ __device__ __forceinline__ void store_rope_pair(const GemmParams& p, int m, int 
     }
 }
 
+// ---- a pair of CTAs (RV_PAIR): addresses in the other CTA, loads and commits that signal across the pair
+__device__ __forceinline__ uint32_t pair_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t pair_map(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+// TMA tile load into this CTA's shared memory whose bytes are counted on `bar`, a barrier of either CTA
+// of the pair (an address in the cluster's shared window)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                      uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrive on the barrier at this shared-memory offset in BOTH CTAs once the MMAs issued so far are done
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void pair_sync() {
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+// the MMA and the commit of this build
+__device__ __forceinline__ void mma_issue(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    if (RV_PAIR) tcgen05_mma_bf16_pair(tmem_c, da, db, idesc, accumulate);
+    else tcgen05_mma_bf16(tmem_c, da, db, idesc, accumulate);
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    if (RV_PAIR) tcgen05_commit_pair(bar);
+    else tcgen05_commit(bar);
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
@@ -133,23 +203,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
     const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
 
+    // pair: rank 0 issues the MMAs and owns the barriers that count both CTAs (full, tempty)
+    const uint32_t rank = RV_PAIR ? pair_rank() : 0u;
     if (threadIdx.x == 0) {
         abort_flag = 0;
+        // full: one arrival (the producer; in a pair the first CTA's, with the bytes of both CTAs);
+        // empty, tfull: one arrival from the commit; tempty: the four epilogue warps (of both CTAs)
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, RV_PAIR ? 8 : 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+        // (with cta_group::2 one warp of each CTA of the pair executes the allocation; both get the same address)
+        asm volatile("tcgen05.alloc.cta_group::" CTA_GROUP ".sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::" CTA_GROUP ".sync.aligned;" ::);
     }
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    if (RV_PAIR) pair_sync();       // both CTAs' barriers exist before either signals the other's
     rv_pdl_wait();          // the set-up above overlapped the previous kernel; its results are needed from here
 
     const int num_tiles = p.m_tiles * p.n_tiles;
+    // the persistent workers: CTAs, or pairs of CTAs
+    const int worker = RV_PAIR ? blockIdx.x >> 1 : blockIdx.x, num_workers = RV_PAIR ? gridDim.x >> 1 : gridDim.x;
     const int num_kb = (p.K + BK - 1) / BK;
     const bool gated = p.epilogue == EPI_GATED;
     const int half_n = p.N >> 1;
@@ -161,13 +239,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t phase = 0;
             int issued = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % p.m_tiles) * BM;
+            for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
+                const int m0 = (tile % p.m_tiles) * TILE_ROWS + (int)rank * BM;      // this CTA's 128 rows
                 const int nt = tile / p.m_tiles;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, &abort_flag, 1)) { ok = false; break; }
                     const uint32_t a_dst = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
                     const uint32_t b_dst = a_dst + A_TILE_BYTES;
+                    if (RV_PAIR) {
+                        // this CTA's 128 of the tile's 256 weight rows (gated: the first CTA has the gate
+                        // rows, the second the up rows of the same output columns); the first CTA's
+                        // barrier counts both CTAs' bytes
+                        const int w0 = gated ? (rank == 0 ? nt * (BN / 2) : half_n + nt * (BN / 2)) : nt * BN + (int)rank * (BN / 2);
+                        const uint32_t bar = pair_map(full0 + 8 * stage, 0);
+                        if (rank == 0) mbar_expect_tx(full0 + 8 * stage, 2 * STAGE_BYTES);
+                        tma_load_2d_pair(a_dst, &map_a, kb * BK, m0, bar);
+                        tma_load_2d_pair(b_dst, &map_b, kb * BK, w0, bar);
+                        ++issued;
+                        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                        continue;
+                    }
                     const uint32_t bar = full0 + 8 * stage;
                     mbar_expect_tx(bar, STAGE_BYTES);
                     tma_load_2d(a_dst, &map_a, kb * BK, m0, bar);
@@ -196,13 +287,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16(BM, BN);
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = umma_idesc_bf16(TILE_ROWS, BN);
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            for (int tile = worker; tile < num_tiles && ok; tile += num_workers, ++local) {
                 const int buf = local & 1;
                 const uint32_t use = (uint32_t)(local >> 1);
                 if (!mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, &abort_flag, 2)) { ok = false; break; }
@@ -216,12 +307,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < BK / UMMA_K; ++j) {
                         // 16 k = 32 bytes further along the 128-byte row: +2 in 16-byte units
-                        tcgen05_mma_bf16(tmem_c, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (kb | j) != 0);
+                        mma_issue(tmem_c, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (kb | j) != 0);
                     }
-                    tcgen05_commit(empty0 + 8 * stage);     // the stage is free once these MMAs have read it
+                    mma_commit(empty0 + 8 * stage);         // the stage is free (in both CTAs) once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
-                if (ok) tcgen05_commit(tfull0 + 8 * buf);   // accumulator complete
+                if (ok) mma_commit(tfull0 + 8 * buf);       // accumulator complete (in both CTAs)
             }
         }
     } else {
@@ -229,12 +320,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quarter = warp & 3;                       // the TMEM lanes this warp may read
         int local = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        for (int tile = worker; tile < num_tiles && ok; tile += num_workers, ++local) {
             const int buf = local & 1;
             const uint32_t use = (uint32_t)(local >> 1);
             if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_flag, 4)) { ok = false; break; }
             tcgen05_fence_after();
-            const int m = (tile % p.m_tiles) * BM + quarter * 32 + lane;
+            const int m = (tile % p.m_tiles) * TILE_ROWS + (int)rank * BM + quarter * 32 + lane;
             const int nt = tile / p.m_tiles;
             const uint32_t taddr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(quarter * 32) << 16);
             if (gated) {
@@ -340,20 +431,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+            if (lane == 0) {
+                if (RV_PAIR) mbar_arrive_cluster(pair_map(tempty0 + 8 * buf, 0));    // the first CTA's barrier counts both CTAs' warps
+                else mbar_arrive(tempty0 + 8 * buf);
+            }
         }
     }
 
     // ---------------------------------------------------------------- teardown
     tcgen05_fence_before();
     __syncthreads();
+    // a pair leaves together: neither CTA frees tensor memory or exits while the other may still use its shared memory or barriers
+    if (RV_PAIR) pair_sync();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+        asm volatile("tcgen05.dealloc.cta_group::" CTA_GROUP ".sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
     }
     if (threadIdx.x == 0 && abort_flag != 0 && p.status) atomicCAS(p.status, 0, abort_flag);
 }
 
 // ---------------------------------------------------------------- host side
+// One CTA per tile and SM, or (RV_PAIR) one cluster of two CTAs per tile and pair of SMs.
+static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, int max_ctas, cudaStream_t stream) {
+    const int smem = STAGES * STAGE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    int workers = p.m_tiles * p.n_tiles;
+    const int limit = (max_ctas > 0 ? max_ctas : 148) / (RV_PAIR ? 2 : 1);
+    if (workers > limit) workers = limit;
+    if (workers < 1) workers = 1;
+#if RV_PAIR
+    RV_LAUNCH_ST = rv_launch_cluster(gemm_tcgen05_kernel, dim3(2 * workers), dim3(NUM_THREADS), smem, stream, 2u, map_a, map_b, p);
+#else
+    RV_LAUNCH_ST = rv_launch(gemm_tcgen05_kernel, dim3(workers), dim3(NUM_THREADS), smem, stream, map_a, map_b, p);
+#endif
+    return rv_launch_status();
+}
+
+// 1 if this library was built for pairs of CTAs
+RV_EXPORT int rv_gemm_tcgen05_is_pair() { return RV_PAIR; }
+
 // epilogue: 0 plain, 1 + residual (bf16 [M, N]), 2 gated (W rows [gate | up], out has N/2 columns).
 // status: optional device int that receives a non-zero code if a wait inside the kernel gave up.
 RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* residual, void* out, int out_f32,
@@ -375,22 +495,11 @@ RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* res
     GemmParams p = {};
     p.out = out; p.residual = epilogue == EPI_RESIDUAL ? (const __nv_bfloat16*)residual : nullptr;
     p.status = status; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.epilogue = epilogue;
-    p.m_tiles = (M + BM - 1) / BM;
+    p.m_tiles = (M + TILE_ROWS - 1) / TILE_ROWS;
     // gated: a tile is 128 gate rows and the 128 up rows of the same output columns; gate rows past
     // N/2 read up rows, whose products the epilogue never stores
     p.n_tiles = epilogue == EPI_GATED ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
-    const int smem = STAGES * STAGE_BYTES + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    int ctas = p.m_tiles * p.n_tiles;
-    const int limit = max_ctas > 0 ? max_ctas : 148;
-    if (ctas > limit) ctas = limit;
-    RV_LAUNCH_ST = rv_launch(gemm_tcgen05_kernel, dim3(ctas), dim3(NUM_THREADS), smem, stream, map_a, map_b, p);
-    return rv_launch_status();
+    return launch_gemm(map_a, map_b, p, max_ctas, stream);
 }
 
 // The q/k/v product of an attention layer for many rows, with bias, rotation and the cache write in
@@ -418,18 +527,11 @@ RV_EXPORT int rv_gemm_tcgen05_qkv_rope(const void* x, const void* w, const void*
     if (st != RV_OK) return st;
     GemmParams p = {};
     p.status = status; p.M = M; p.N = N; p.K = K; p.epilogue = EPI_ROPE;
-    p.m_tiles = (M + BM - 1) / BM;
+    p.m_tiles = (M + TILE_ROWS - 1) / TILE_ROWS;
     p.n_tiles = (N + BN - 1) / BN;
     p.bias = bias; p.bias_dtype = bias_dtype;
     p.q_out = (__nv_bfloat16*)q_out; p.kv_cache = (__nv_bfloat16*)kv_cache;
     p.positions = positions; p.slot_mapping = slot_mapping; p.cos_t = cos_t; p.sin_t = sin_t;
     p.nh = nh; p.nkv = nkv; p.hd = hd; p.page_size = page_size; p.table_rows = table_rows;
-    const int smem = STAGES * STAGE_BYTES + 1024;
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    int ctas = p.m_tiles * p.n_tiles;
-    const int limit = max_ctas > 0 ? max_ctas : 148;
-    if (ctas > limit) ctas = limit;
-    RV_LAUNCH_ST = rv_launch(gemm_tcgen05_kernel, dim3(ctas), dim3(NUM_THREADS), smem, stream, map_a, map_b, p);
-    return rv_launch_status();
+    return launch_gemm(map_a, map_b, p, max_ctas, stream);
 }

@@ -68,6 +68,7 @@ class AttentionMeta:
 class CudaKernels:
     SKINNY_MAX_ROWS = 0     # rows up to which the weight-streaming GEMM replaces the library GEMM (0: off)
     TCGEN05_MIN_ROWS = 128  # rows from which the tcgen05 GEMM of this project is used for bfloat16
+    PAIR_GEMM = True                   # the tcgen05 GEMM runs on pairs of CTAs (cta_group::2) where the rows fill its 256-row tiles
     TCGEN05_ATTENTION = True           # prompt portions go to the tcgen05 attention kernel when it fits
     TCGEN05_ATTENTION_MIN_TOKENS = 16  # ... from this many tokens in the longest portion of the step
     DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
@@ -405,10 +406,18 @@ class CudaKernels:
         _check("gemm_skinny", st)
         return out
 
-    def linear_tcgen05(self, x, weight, residual=None, out_dtype=None, gated=False, status=None, max_ctas=0):
+    def _prefill_gemm_lib(self, M: int, pair=None):
+        """The tcgen05 GEMM library for M rows: built for pairs of CTAs (tiles of 256 rows) unless the
+        last tile's second half would be empty, or for one CTA per tile (tiles of 128 rows)."""
+        if pair is None:
+            pair = self.PAIR_GEMM and (M % 256 == 0 or M % 256 > 128)
+        return self._lib("gemm_tcgen05.cu", ("-DRV_PAIR=1",) if pair else ())
+
+    def linear_tcgen05(self, x, weight, residual=None, out_dtype=None, gated=False, status=None, max_ctas=0, pair=None):
         """The tcgen05 / TMEM / TMA GEMM for bfloat16 (any M; K a multiple of 8).  gated: weight rows
         are [gate | up] and the result is silu(x gate^T) * (x up^T).  `status`: optional int32 device
-        tensor that receives a non-zero code if a bounded wait inside the kernel gave up."""
+        tensor that receives a non-zero code if a bounded wait inside the kernel gave up.  `pair`:
+        the build on pairs of CTAs (cta_group::2) or on single CTAs; default: by the number of rows."""
         _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
         M, K = x.shape
         N = weight.shape[0]
@@ -417,7 +426,7 @@ class CudaKernels:
         if residual is not None:
             _need(residual, "residual", torch.bfloat16, 2)
         epilogue = 2 if gated else (1 if residual is not None else 0)
-        st = self._lib("gemm_tcgen05.cu").rv_gemm_tcgen05_bf16(
+        st = self._prefill_gemm_lib(M, pair).rv_gemm_tcgen05_bf16(
             _ptr(x), _ptr(weight), _ptr(residual), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0),
             c_int(M), c_int(N), c_int(K), c_int(epilogue), _ptr(status), c_int(max_ctas), self._stream())
         _check("gemm_tcgen05", st)
@@ -531,7 +540,7 @@ class CudaKernels:
                                      num_heads, num_kv_heads, head_dim)
 
     def _qkv_rope_tcgen05(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
-                          num_heads, num_kv_heads, head_dim, status=None, max_ctas=0):
+                          num_heads, num_kv_heads, head_dim, status=None, max_ctas=0, pair=None):
         """The prefill tcgen05 GEMM with the rotary epilogue (many rows, head sizes 64 / 128 / 256)."""
         _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
         _need(positions, "positions", torch.int32, 1); _need(slot_mapping, "slot_mapping", torch.int32, 1)
@@ -549,7 +558,7 @@ class CudaKernels:
         if bias is not None:
             _need(bias, "bias", dims=1)
         q = torch.empty((M, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
-        st = self._lib("gemm_tcgen05.cu").rv_gemm_tcgen05_qkv_rope(
+        st = self._prefill_gemm_lib(M, pair).rv_gemm_tcgen05_qkv_rope(
             _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0),
             _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(cache_layer), _ptr(q), c_int(M), c_int(K),
             c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]),

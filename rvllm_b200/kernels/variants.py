@@ -18,6 +18,8 @@ def all_variants() -> List[Tuple[str, Sequence[str]]]:
             out.extend((src, (f"-DHEAD_DIM={hd}",)) for hd in FLASH_HEAD_DIMS)
         elif src == "attention_tcgen05.cu":
             out.extend((src, (f"-DHEAD_DIM={hd}",)) for hd in (64, 128))
+        elif src == "gemm_tcgen05.cu":
+            out.extend([(src, ()), (src, ("-DRV_PAIR=1",))])         # one CTA per tile, and pairs of CTAs
         else:
             out.append((src, ()))
     return out

@@ -283,15 +283,18 @@ def test_gemm_tcgen05_bf16(K, M, N, Kd):
     r = torch.randn(M, N, device="cuda").bfloat16()
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     ref = x.double().cpu() @ w.double().cpu().t()
-    for ctas in (0, 1, 3):                                   # 1 and 3: a CTA walks many tiles, both accumulators
-        assert rel_err(K.linear_tcgen05(x, w, status=status, max_ctas=ctas), ref) < BF16_TOL
-    assert rel_err(K.linear_tcgen05(x, w, r, status=status), ref + r.double().cpu()) < BF16_TOL
-    assert rel_err(K.linear_tcgen05(x, w, None, torch.float32, status=status), ref) < 1e-5
-    if N % 2 == 0:
-        g, u = ref[:, :N // 2], ref[:, N // 2:]
-        want = g / (1 + torch.exp(-g)) * u
-        assert rel_err(K.linear_tcgen05(x, w, gated=True, status=status), want) < BF16_TOL
-        assert rel_err(K.linear_tcgen05(x, w, None, torch.float32, gated=True, status=status, max_ctas=2), want) < 1e-5
+    # both builds of the kernel: one CTA per tile of 128 rows, and pairs of CTAs (cta_group::2) per tile of 256 rows
+    for pair in (False, True):
+        for ctas in (0, 2, 6):                               # 2 and 6: a CTA (a pair) walks many tiles, both accumulators
+            assert rel_err(K.linear_tcgen05(x, w, status=status, max_ctas=ctas, pair=pair), ref) < BF16_TOL
+        assert rel_err(K.linear_tcgen05(x, w, r, status=status, pair=pair), ref + r.double().cpu()) < BF16_TOL
+        assert rel_err(K.linear_tcgen05(x, w, None, torch.float32, status=status, pair=pair), ref) < 1e-5
+        if N % 2 == 0:
+            g, u = ref[:, :N // 2], ref[:, N // 2:]
+            want = g / (1 + torch.exp(-g)) * u
+            assert rel_err(K.linear_tcgen05(x, w, gated=True, status=status, pair=pair), want) < BF16_TOL
+            assert rel_err(K.linear_tcgen05(x, w, None, torch.float32, gated=True, status=status, max_ctas=2, pair=pair), want) < 1e-5
+    assert torch.equal(K.linear_tcgen05(x, w, r, pair=True), K.linear_tcgen05(x, w, r, pair=False))    # the same sums
     assert int(status.item()) == 0, "a bounded wait inside the kernel gave up"
     # the product path picks it from TCGEN05_MIN_ROWS rows on
     if M >= K.TCGEN05_MIN_ROWS:
@@ -501,9 +504,9 @@ def test_qkv_product_with_rotation_and_cache_write_for_many_rows(K, M, nh, nkv, 
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     cache_b = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda").bfloat16()
     qb = K.rope_cache_write(K.linear_tcgen05(x, w), b, positions, cos, sin, slots, cache_b, nh, nkv, hd)
-    for ctas in (0, 2):
+    for ctas, pair in ((0, False), (2, False), (0, True), (4, True)):
         cache_a = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda").bfloat16()
-        qa = K._qkv_rope_tcgen05(x, w, b, positions, cos, sin, slots, cache_a, nh, nkv, hd, status=status, max_ctas=ctas)
+        qa = K._qkv_rope_tcgen05(x, w, b, positions, cos, sin, slots, cache_a, nh, nkv, hd, status=status, max_ctas=ctas, pair=pair)
         assert rel_err(qa, qb.double().cpu()) < 4e-3 and rel_err(cache_a, cache_b.double().cpu()) < 4e-3
         assert float((qa.float() - qb.float()).abs().gt(0).float().mean()) < 0.02      # nearly every element bit-equal
     assert int(status.item()) == 0
