@@ -1,0 +1,75 @@
+"""The host-side choices of the kernel library (how a product is cut over CTAs, which build of a
+kernel serves a shape): plain arithmetic, checked without a GPU."""
+from types import SimpleNamespace
+
+from rvllm_b200.kernels.library import CudaKernels
+
+
+def _k():
+    return CudaKernels.__new__(CudaKernels)        # the policies read class constants only
+
+
+def test_split_k_of_the_decode_gemm():
+    k = _k()
+    # many tiles: no split; few tiles: about two CTAs per SM with at least four k blocks each
+    assert k.gemm_splits(1002, 4096) == 1 and k.gemm_splits(224, 4096) == 1
+    assert k.gemm_splits(32, 4096) == 9 and k.gemm_splits(48, 4096) == 6
+    assert k.gemm_splits(32, 14336) == 13                    # three per SM where sixteen k blocks are left for each
+    assert k.gemm_splits(4, 64) == 1 and k.gemm_splits(1, 128) == 1
+
+
+def test_cluster_reduce_is_chosen_for_few_rows_and_caps_the_splits():
+    k = _k()
+    # left open: about CLUSTER_TARGET_CTAS CTAs in all, at most 8 per tile, at least four k blocks each
+    assert k._cluster_policy(8, False, 9, None, 32, 4096, False) == (7, True)
+    assert k._cluster_policy(1, False, 6, None, 48, 4096, False) == (4, True)
+    assert k._cluster_policy(32, False, 13, None, 32, 14336, False) == (7, True)
+    assert k._cluster_policy(4, False, 2, None, 8, 512, False) == (2, True)
+    # given by the caller: kept, up to 8
+    assert k._cluster_policy(8, False, 3, None, 32, 4096, True) == (3, True)
+    assert k._cluster_policy(8, False, 12, None, 32, 4096, True) == (8, True)
+    # no cluster: one split, gated products, more rows than CLUSTER_MAX_ROWS, or when asked not to
+    assert k._cluster_policy(8, False, 1, None, 1002, 4096, False) == (1, False)
+    assert k._cluster_policy(8, True, 2, None, 224, 4096, False) == (2, False)
+    assert k._cluster_policy(k.CLUSTER_MAX_ROWS + 1, False, 9, None, 32, 4096, False) == (9, False)
+    assert k._cluster_policy(8, False, 9, False, 32, 4096, False) == (9, False)
+
+
+def test_which_products_take_the_weight_streaming_gemm():
+    k = _k()
+    assert k._use_decode_gemm(8, 4096, 4096, False) and k._use_decode_gemm(32, 4096, 14336, False)
+    assert not k._use_decode_gemm(64, 4096, 4096, False)     # K would have to be split: the library there
+    assert k._use_decode_gemm(64, 28672, 4096, True) and k._use_decode_gemm(64, 128256, 4096, False)
+    assert not k._use_decode_gemm(65, 28672, 4096, True) and not k._use_decode_gemm(8, 4096, 4100, False)
+    assert not k._use_decode_gemm(0, 4096, 4096, False)
+
+
+def test_the_prefill_gemm_and_its_build_are_chosen_by_rows():
+    k = _k()
+    assert not k._tcgen05_fills(127, 4096) and k._tcgen05_fills(128, 4096) and k._tcgen05_fills(2048, 28672, True)
+    # with a threshold on how full the rounds of the persistent workers are
+    k.TCGEN05_MIN_FILL = 0.8
+    try:
+        assert k._tcgen05_fills(2048, 4096) and k._tcgen05_fills(2048, 6144) and k._tcgen05_fills(2048, 28672, True)
+        assert not k._tcgen05_fills(512, 4096) and not k._tcgen05_fills(1536, 4096) and k._tcgen05_fills(1536, 6144)
+    finally:
+        del k.TCGEN05_MIN_FILL
+    # pairs of CTAs where the last 256-row tile has rows in its second half
+    picked = []
+    k._lib = lambda source, defines=(): picked.append((source, tuple(defines)))
+    for rows in (2048, 300, 129, 256, 128, 640):
+        k._prefill_gemm_lib(rows)
+    assert [bool(d) for _, d in picked] == [True, False, True, True, False, False]
+    assert all(src == "gemm_tcgen05.cu" for src, _ in picked)
+
+
+def test_key_splits_of_decode_attention_follow_the_wave_model():
+    meta = lambda seqs, ctx: SimpleNamespace(num_seqs=seqs, max_ctx_len=ctx)
+    assert CudaKernels.decode_splits(meta(8, 2088), 32, 8) == 6           # 384 CTAs: one wave of 444
+    assert CudaKernels.decode_splits(meta(1, 2048), 32, 8) == 16          # two tiles per CTA at least
+    for seqs in (1, 2, 3, 5, 8, 13, 24, 31):                              # never a split of fewer than two tiles, never more than 16
+        for ctx in (1, 64, 65, 300, 1000, 4096, 100000):
+            s = CudaKernels.decode_splits(meta(seqs, ctx), 32, 8)
+            tiles = (ctx + 63) // 64
+            assert 1 <= s <= 16 and (s == 1 or -(-tiles // s) >= 2)
+    assert CudaKernels.decode_splits(meta(4, 64), 32, 8) == 1             # one tile: nothing to split
