@@ -2,10 +2,12 @@
 
 `CudaKernels` launches the hand-written sm_100a kernels of csrc/ on torch's current stream
 through their exported C launchers.  bfloat16 matrix products with at least `TCGEN05_MIN_ROWS` rows
-run on this project's tcgen05 / TMEM / TMA kernel; with fewer rows (decode) they go to the library
-GEMM behind `torch` (the reference calls cuBLASLt for its linear layers,
-v3/crates/rvllm-cutlass/src/cublaslt.rs); everything else is this project's own code.  There is no CPU implementation: without a CUDA device, or when a kernel
-library cannot be built, construction raises `KernelError`.
+run on this project's tcgen05 / TMEM / TMA kernel (on pairs of CTAs where the rows fill its tiles);
+with up to 32 rows, and with up to 64 where K need not be split, on its weight-streaming tcgen05
+kernel; what lies between goes to the library GEMM behind `torch` (the reference calls cuBLASLt for
+all its linear layers, v3/crates/rvllm-cutlass/src/cublaslt.rs).  Everything else is this project's
+own code.  There is no CPU implementation: without a CUDA device, or when a kernel library cannot be
+built, construction raises `KernelError`.
 """
 from __future__ import annotations
 
