@@ -250,15 +250,17 @@ class CudaKernels:
         of the memory), the merge kernel 2.5 us.  The split count with the least modelled time is
         taken: it fills one wave when the batch is small and keeps the last wave full when it is
         large."""
+        self_max_splits = 64          # a long context at a small batch still fills the GPU (one sequence of 32,768 keys: 55)
         group = num_heads // num_kv_heads
         ctas = meta.num_seqs * num_kv_heads * ((group + 15) // 16)
         tiles = max(1, (meta.max_ctx_len + 63) // 64)
         best, best_t = 1, float("inf")
-        for s in range(1, min(16, tiles) + 1):
+        for s in range(1, min(self_max_splits, tiles) + 1):
             per = -(-tiles // s)
             if s > 1 and per < 2:
                 break
-            t = -(-ctas * s // 444) * (4.0 + 2.25 * per) + (2.5 if s > 1 else 0.0)
+            # (the merge kernel reads eight splits per round trip)
+            t = -(-ctas * s // 444) * (4.0 + 2.25 * per) + (2.0 + 0.5 * -(-s // 8) if s > 1 else 0.0)
             if t < best_t - 1e-9:
                 best, best_t = s, t
         return best
