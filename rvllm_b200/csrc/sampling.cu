@@ -130,10 +130,20 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
         const float4* r4 = reinterpret_cast<const float4*>(row);
         float p1 = 0.f;
-        for (int i = threadIdx.x; i < (V >> 2); i += blockDim.x) {
-            const float4 a = r4[i];
-            part += expf((a.x - m) * inv_t) + expf((a.y - m) * inv_t);
-            p1 += expf((a.z - m) * inv_t) + expf((a.w - m) * inv_t);
+        // (four loads in flight per thread; every thread adds its elements in the same order as before)
+        for (int i0 = threadIdx.x; i0 < (V >> 2); i0 += 4 * blockDim.x) {
+            float4 a[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = i0 + j * blockDim.x;
+                a[j] = i < (V >> 2) ? r4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (i0 + j * (int)blockDim.x >= (V >> 2)) break;
+                part += expf((a[j].x - m) * inv_t) + expf((a[j].y - m) * inv_t);
+                p1 += expf((a[j].z - m) * inv_t) + expf((a[j].w - m) * inv_t);
+            }
         }
         part += p1;
     } else {
@@ -141,27 +151,92 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     }
     const float total = rv_block_sum(part, s_val);
 
-    // threshold key: keep tokens whose order key is >= tau
+    // threshold key: keep tokens whose order key is >= tau.  tau is the largest key c with
+    // count(key >= c) >= k (top-k), or with mass(key >= c) >= top_p * total (top-p); it is found
+    // four bits at a time, eight passes over the row: every thread counts its tokens (and adds
+    // their mass) by the next four bits of the key in 16 slots of its own in shared memory, for the
+    // tokens that agree with the bits decided so far; the block adds the slots up in a fixed order
+    // and takes the largest digit that still satisfies the condition.  NaN is never kept.
     uint32_t tau = 0;
     const int k = top_k ? top_k[r] : 0;
     const float pp = top_p ? top_p[r] : 1.0f;
-    const bool use_k = k > 0 && k < V;
-    const bool use_p = pp < 1.0f;
+    bool use_k = k > 0 && k < V;
+    bool use_p = pp < 1.0f;
     if (use_k || use_p) {
-        uint32_t tau_k = 0, tau_p = 0;
-        for (int bit = 31; bit >= 0; --bit) {
-            const uint32_t ck = tau_k | (1u << bit), cp = tau_p | (1u << bit);
-            float cnt = 0.f, mass = 0.f;
-            for (int i = threadIdx.x; i < V; i += blockDim.x) {
-                const float v = row[i];
-                const uint32_t key = order_key(v);
-                if (use_k && key >= ck) cnt += 1.f;
-                if (use_p && key >= cp) mass += expf((v - m) * inv_t);
+        extern __shared__ __align__(16) unsigned char s_dyn[];
+        int* h_cnt = reinterpret_cast<int*>(s_dyn);                                   // [16][SAMPLE_THREADS]
+        float* h_mass = reinterpret_cast<float*>(s_dyn) + 16 * SAMPLE_THREADS;       // [16][SAMPLE_THREADS]
+        __shared__ int s_cnt[2][16];
+        __shared__ float s_mass[2][16];
+        const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+        uint32_t pre_k = 0, pre_p = 0;        // the bits decided so far
+        int above_cnt = 0;                    // tokens whose decided bits are greater than pre_k
+        float above_mass = 0.f;               // mass of the tokens whose decided bits are greater than pre_p
+        const float target = pp * total;
+        for (int shift = 28; shift >= 0; shift -= 4) {
+#pragma unroll
+            for (int d = 0; d < 16; ++d) { h_cnt[d * SAMPLE_THREADS + tid] = 0; h_mass[d * SAMPLE_THREADS + tid] = 0.f; }
+            // eight loads in flight per thread: one block reads the row at the speed its loads in flight allow
+            for (int i0 = tid; i0 < V; i0 += 8 * SAMPLE_THREADS) {
+                float vs[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int i = i0 + j * SAMPLE_THREADS;
+                    vs[j] = i < V ? row[i] : __int_as_float(0x7fc00000);      // NaN: skipped below
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float v = vs[j];
+                    if (v != v) continue;
+                    const uint32_t key = order_key(v);
+                    const int d = (int)((key >> shift) & 15u);
+                    const bool top = shift == 28;
+                    if (use_k && (top || (key >> (shift + 4)) == (pre_k >> (shift + 4)))) h_cnt[d * SAMPLE_THREADS + tid] += 1;
+                    if (use_p && (top || (key >> (shift + 4)) == (pre_p >> (shift + 4)))) h_mass[d * SAMPLE_THREADS + tid] += expf((v - m) * inv_t);
+                }
             }
-            if (use_k) { cnt = rv_block_sum(cnt, s_val); if (cnt >= (float)k) tau_k = ck; }
-            if (use_p) { mass = rv_block_sum(mass, s_val); if (mass >= pp * total) tau_p = cp; }
+            __syncthreads();
+            {   // warp w adds digit w % 16 over one half of the threads, lanes in a fixed order
+                const int d = warp & 15, part = warp >> 4;
+                int c = 0;
+                float ms = 0.f;
+                for (int j = lane; j < SAMPLE_THREADS / 2; j += 32) {
+                    c += h_cnt[d * SAMPLE_THREADS + part * (SAMPLE_THREADS / 2) + j];
+                    ms += h_mass[d * SAMPLE_THREADS + part * (SAMPLE_THREADS / 2) + j];
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    c += __shfl_xor_sync(0xffffffffu, c, o);
+                    ms += __shfl_xor_sync(0xffffffffu, ms, o);
+                }
+                if (lane == 0) { s_cnt[part][d] = c; s_mass[part][d] = ms; }
+            }
+            __syncthreads();
+            // every thread takes the same decision from the same sums
+            if (use_k) {
+                int run = above_cnt, found = -1;
+                for (int d = 15; d >= 0; --d) {
+                    const int c = s_cnt[0][d] + s_cnt[1][d];
+                    if (run + c >= k) { found = d; break; }
+                    run += c;
+                }
+                if (found < 0) { use_k = false; pre_k = 0; }          // fewer than k tokens (NaN rows): keep all
+                else { pre_k |= (uint32_t)found << shift; above_cnt = run; }
+            }
+            if (use_p) {
+                float run = above_mass;
+                int found = -1;
+                for (int d = 15; d >= 0; --d) {
+                    const float c = s_mass[0][d] + s_mass[1][d];
+                    if (run + c >= target) { found = d; break; }
+                    run += c;
+                }
+                if (found < 0) { use_p = false; pre_p = 0; }          // rounding left the sum just below the target: keep all
+                else { pre_p |= (uint32_t)found << shift; above_mass = run; }
+            }
+            if (!use_k && !use_p) break;
         }
-        tau = tau_k > tau_p ? tau_k : tau_p;
+        tau = pre_k > pre_p ? pre_k : pre_p;
     }
 
     // inverse CDF in vocabulary order: thread t owns the contiguous chunk [t*C, (t+1)*C)
@@ -240,6 +315,14 @@ RV_EXPORT int rv_sample(const float* logits, const float* temperature, const int
     if (n_rows < 0 || vocab <= 0) return RV_ERR_BAD_SIZE;
     if (n_rows == 0) return RV_OK;
     if (temperature && (!seeds || !draw_index)) return RV_ERR_BAD_SIZE;
-    RV_LAUNCH_ST = rv_launch(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, temperature, top_k, top_p, seeds, draw_index, out, vocab);
+    // the threshold search of top-k / top-p keeps 16 counters and 16 sums per thread in shared memory
+    const size_t smem = (temperature && (top_k || top_p)) ? (size_t)2 * 16 * SAMPLE_THREADS * 4 : 0;
+    static bool configured = false;
+    if (smem && !configured) {
+        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * 16 * SAMPLE_THREADS * 4));
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    RV_LAUNCH_ST = rv_launch(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), smem, stream, logits, temperature, top_k, top_p, seeds, draw_index, out, vocab);
     return rv_launch_status();
 }
