@@ -101,168 +101,72 @@ __device__ int block_argmax(const float* row, int V, float* s_val, int* s_idx) {
     return s_idx[0];
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
-              const int* __restrict__ top_k, const float* __restrict__ top_p,
-              const unsigned long long* __restrict__ seeds, const long long* __restrict__ draw_index,
-              int* __restrict__ out, int V) {
-    rv_pdl_launch_dependents();
-    rv_pdl_wait();
-    __shared__ float s_val[33];
-    __shared__ int s_idx[33];
-    __shared__ float s_scan[SAMPLE_THREADS / 32 + 1];
-    __shared__ int s_result;
-    __shared__ float s_incl[SAMPLE_THREADS];
-    const int r = blockIdx.x;
-    const float* row = logits + (size_t)r * V;
-    const float T = temperature ? temperature[r] : 0.f;
-    const int best = block_argmax(row, V, s_val, s_idx);
-    if (!(T > 0.f)) {
-        if (threadIdx.x == 0) out[r] = best;
-        return;
-    }
-    const float m = s_val[0];
-    const float inv_t = 1.0f / T;
-    __syncthreads();
+// ---------------------------------------------------------------------------------------------
+// One to eight CTAs per row.  A row is always cut into SAMPLE_SLICES contiguous slices of the
+// vocabulary; every reduction over the row (arg-max, mass, the 16 + 16 sums of a pass of the
+// threshold search, the kept mass) is done slice by slice by one block of SAMPLE_THREADS threads and
+// the slices' results are combined in slice order.  With several CTAs per row (a thread-block
+// cluster; each CTA owns SAMPLE_SLICES / CTAs neighbouring slices) each CTA writes its slices'
+// results into every CTA's shared memory (st.shared::cluster), and one cluster barrier later all CTAs
+// combine the same numbers in the same order and take the same decision.  So the sampled token does
+// not depend on how many CTAs share the row, which the host chooses by the number of rows: one block
+// per row is bound by its own instruction rate (125 tokens per thread and pass at a vocabulary of
+// 128,256), eight CTAs make a pass eight times shorter.  The exchange buffers alternate between two
+// copies, so that a CTA that is one step ahead never overwrites what a slower one still reads.
+#define SAMPLE_SLICES 8
 
-    // mass of everything
-    float part = 0.f;
-    if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
-        const float4* r4 = reinterpret_cast<const float4*>(row);
-        float p1 = 0.f;
-        // (four loads in flight per thread; every thread adds its elements in the same order as before)
-        for (int i0 = threadIdx.x; i0 < (V >> 2); i0 += 4 * blockDim.x) {
-            float4 a[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int i = i0 + j * blockDim.x;
-                a[j] = i < (V >> 2) ? r4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (i0 + j * (int)blockDim.x >= (V >> 2)) break;
-                part += expf((a[j].x - m) * inv_t) + expf((a[j].y - m) * inv_t);
-                p1 += expf((a[j].z - m) * inv_t) + expf((a[j].w - m) * inv_t);
-            }
-        }
-        part += p1;
-    } else {
-        for (int i = threadIdx.x; i < V; i += blockDim.x) part += expf((row[i] - m) * inv_t);
-    }
-    const float total = rv_block_sum(part, s_val);
+__device__ __forceinline__ uint32_t sc_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t sc_map(const void* p, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"((uint32_t)__cvta_generic_to_shared(p)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void sc_store(uint32_t addr, float v) { asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+__device__ __forceinline__ void sc_store(uint32_t addr, int v) { asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+__device__ __forceinline__ void sc_sync() {
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
 
-    // threshold key: keep tokens whose order key is >= tau.  tau is the largest key c with
-    // count(key >= c) >= k (top-k), or with mass(key >= c) >= top_p * total (top-p); it is found
-    // four bits at a time, eight passes over the row: every thread counts its tokens (and adds
-    // their mass) by the next four bits of the key in 16 slots of its own in shared memory, for the
-    // tokens that agree with the bits decided so far; the block adds the slots up in a fixed order
-    // and takes the largest digit that still satisfies the condition.  NaN is never kept.
-    uint32_t tau = 0;
-    const int k = top_k ? top_k[r] : 0;
-    const float pp = top_p ? top_p[r] : 1.0f;
-    bool use_k = k > 0 && k < V;
-    bool use_p = pp < 1.0f;
-    if (use_k || use_p) {
-        extern __shared__ __align__(16) unsigned char s_dyn[];
-        int* h_cnt = reinterpret_cast<int*>(s_dyn);                                   // [16][SAMPLE_THREADS]
-        float* h_mass = reinterpret_cast<float*>(s_dyn) + 16 * SAMPLE_THREADS;       // [16][SAMPLE_THREADS]
-        __shared__ int s_cnt[2][16];
-        __shared__ float s_mass[2][16];
-        const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-        uint32_t pre_k = 0, pre_p = 0;        // the bits decided so far
-        int above_cnt = 0;                    // tokens whose decided bits are greater than pre_k
-        float above_mass = 0.f;               // mass of the tokens whose decided bits are greater than pre_p
-        const float target = pp * total;
-        for (int shift = 28; shift >= 0; shift -= 4) {
-#pragma unroll
-            for (int d = 0; d < 16; ++d) { h_cnt[d * SAMPLE_THREADS + tid] = 0; h_mass[d * SAMPLE_THREADS + tid] = 0.f; }
-            // eight loads in flight per thread: one block reads the row at the speed its loads in flight allow
-            for (int i0 = tid; i0 < V; i0 += 8 * SAMPLE_THREADS) {
-                float vs[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int i = i0 + j * SAMPLE_THREADS;
-                    vs[j] = i < V ? row[i] : __int_as_float(0x7fc00000);      // NaN: skipped below
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float v = vs[j];
-                    if (v != v) continue;
-                    const uint32_t key = order_key(v);
-                    const int d = (int)((key >> shift) & 15u);
-                    const bool top = shift == 28;
-                    if (use_k && (top || (key >> (shift + 4)) == (pre_k >> (shift + 4)))) h_cnt[d * SAMPLE_THREADS + tid] += 1;
-                    if (use_p && (top || (key >> (shift + 4)) == (pre_p >> (shift + 4)))) h_mass[d * SAMPLE_THREADS + tid] += expf((v - m) * inv_t);
-                }
-            }
-            __syncthreads();
-            {   // warp w adds digit w % 16 over one half of the threads, lanes in a fixed order
-                const int d = warp & 15, part = warp >> 4;
-                int c = 0;
-                float ms = 0.f;
-                for (int j = lane; j < SAMPLE_THREADS / 2; j += 32) {
-                    c += h_cnt[d * SAMPLE_THREADS + part * (SAMPLE_THREADS / 2) + j];
-                    ms += h_mass[d * SAMPLE_THREADS + part * (SAMPLE_THREADS / 2) + j];
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    c += __shfl_xor_sync(0xffffffffu, c, o);
-                    ms += __shfl_xor_sync(0xffffffffu, ms, o);
-                }
-                if (lane == 0) { s_cnt[part][d] = c; s_mass[part][d] = ms; }
-            }
-            __syncthreads();
-            // every thread takes the same decision from the same sums
-            if (use_k) {
-                int run = above_cnt, found = -1;
-                for (int d = 15; d >= 0; --d) {
-                    const int c = s_cnt[0][d] + s_cnt[1][d];
-                    if (run + c >= k) { found = d; break; }
-                    run += c;
-                }
-                if (found < 0) { use_k = false; pre_k = 0; }          // fewer than k tokens (NaN rows): keep all
-                else { pre_k |= (uint32_t)found << shift; above_cnt = run; }
-            }
-            if (use_p) {
-                float run = above_mass;
-                int found = -1;
-                for (int d = 15; d >= 0; --d) {
-                    const float c = s_mass[0][d] + s_mass[1][d];
-                    if (run + c >= target) { found = d; break; }
-                    run += c;
-                }
-                if (found < 0) { use_p = false; pre_p = 0; }          // rounding left the sum just below the target: keep all
-                else { pre_p |= (uint32_t)found << shift; above_mass = run; }
-            }
-            if (!use_k && !use_p) break;
-        }
-        tau = pre_k > pre_p ? pre_k : pre_p;
-    }
+// What the CTAs of a row tell one another, per slice; two copies, used in turn.
+struct SampleExchange {
+    float val[SAMPLE_SLICES];                // arg-max value / mass / kept mass of a slice
+    int idx[SAMPLE_SLICES];                  // arg-max index / last kept token of a slice
+    int cnt[SAMPLE_SLICES][16];              // a pass of the threshold search: tokens per digit
+    float mass[SAMPLE_SLICES][16];           // ... and their mass
+};
 
-    // inverse CDF in vocabulary order: thread t owns the contiguous chunk [t*C, (t+1)*C)
-    const int C = (V + blockDim.x - 1) / blockDim.x;
-    const int lo = threadIdx.x * C;
-    const int hi = min(V, lo + C);
+// Kept mass of a slice in vocabulary order: thread t owns the contiguous chunk [lo, hi) of the slice;
+// on return excl / upto are the kept mass before and up to the end of its chunk, s_incl[last] the
+// slice's kept mass and *s_last its last kept token (-1: none).
+__device__ __forceinline__ void slice_scan(const float* row, int lo_s, int hi_s, uint32_t tau, float m, float inv_t, float* s_scan,
+                           float* s_incl, int* s_last, int& lo, int& hi, int& last_kept, float& excl, float& upto) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int C = (hi_s - lo_s + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+    lo = min(hi_s, lo_s + tid * C);
+    hi = min(hi_s, lo + C);
     float local = 0.f;
-    int last_kept = -1;
+    last_kept = -1;
     for (int i = lo; i < hi; ++i) {
         const float v = row[i];
         if (order_key(v) >= tau && !(v != v)) { local += expf((v - m) * inv_t); last_kept = i; }
     }
-    // exclusive scan of `local` over the block
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float incl = local;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         const float n = __shfl_up_sync(0xffffffffu, incl, o);
         if (lane >= o) incl += n;
     }
-    if (threadIdx.x == 0) s_result = -1;
-    __syncthreads();
+    __syncthreads();                                   // the previous use of the shared arrays is over
+    if (tid == 0) *s_last = -1;
     if (lane == 31) s_scan[warp] = incl;
     __syncthreads();
+    if (last_kept >= 0) atomicMax(s_last, last_kept);
     if (warp == 0) {
-        const int nw = blockDim.x >> 5;
+        const int nw = SAMPLE_THREADS >> 5;
         float w = lane < nw ? s_scan[lane] : 0.f;
         float wi = w;
 #pragma unroll
@@ -275,37 +179,239 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     __syncthreads();
     // inclusive prefixes in shared memory, so that neighbouring chunks tile [0, kept mass)
     // without gaps or overlaps whatever the rounding
-    s_incl[threadIdx.x] = s_scan[warp] + incl;
+    s_incl[tid] = s_scan[warp] + incl;
     __syncthreads();
-    const float excl = threadIdx.x > 0 ? s_incl[threadIdx.x - 1] : 0.f;
-    const float upto = s_incl[threadIdx.x];
-    const float kept_total = s_incl[blockDim.x - 1];
-
-    uint32_t c[4] = {(uint32_t)(draw_index[r] & 0xffffffffll), (uint32_t)((unsigned long long)draw_index[r] >> 32), 0u, 0u};
-    philox4x32_10(c, (uint32_t)(seeds[r] & 0xffffffffull), (uint32_t)(seeds[r] >> 32));
-    const float u = (float)(c[0] >> 8) * (1.0f / 16777216.0f);
-    const float target = u * kept_total;
-
-    if (upto > excl && excl <= target && target < upto) {
-        float run = excl;
-        int pick = last_kept;
-        for (int i = lo; i < hi; ++i) {
-            const float v = row[i];
-            if (order_key(v) >= tau && !(v != v)) {
-                run += expf((v - m) * inv_t);
-                if (run > target) { pick = i; break; }
-            }
-        }
-        atomicMax(&s_result, pick);   // at most one thread matches; max is only a tie guard
-    }
-    __syncthreads();
-    if (s_result < 0) {
-        // rounding put the target at or beyond the kept mass: take the last kept token
-        atomicMax(&s_result, last_kept);
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) out[r] = s_result >= 0 ? s_result : best;
+    excl = tid > 0 ? s_incl[tid - 1] : 0.f;
+    upto = s_incl[tid];
 }
+
+__global__ void __launch_bounds__(SAMPLE_THREADS, 1)
+sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const unsigned long long* __restrict__ seeds, const long long* __restrict__ draw_index,
+              int* __restrict__ out, int V) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    __shared__ float s_val[33];
+    __shared__ int s_idx[33];
+    __shared__ float s_scan[SAMPLE_THREADS / 32 + 1];
+    __shared__ int s_result, s_last;
+    __shared__ float s_incl[SAMPLE_THREADS];
+    __shared__ int s_cnt[2][16];
+    __shared__ float s_mass[2][16];
+    __shared__ SampleExchange xch[2];
+    // gridDim.x CTAs (1, 2, 4 or 8: the cluster) share row blockIdx.y; this one owns the slices [first, first + per)
+    const int CL = gridDim.x, rank = (int)sc_rank(), tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per = SAMPLE_SLICES / CL, first = rank * per;
+    const int r = blockIdx.y;
+    const float* row = logits + (size_t)r * V;
+    const int S = (((V + SAMPLE_SLICES - 1) / SAMPLE_SLICES) + 3) & ~3;     // slices of an aligned row start on 16-byte boundaries
+    const float T = temperature ? temperature[r] : 0.f;
+    int turn = 0;                                        // which copy of the exchange buffers is written next
+    sc_sync();                                           // every CTA of the cluster runs before its memory is written
+
+    // ---- arg-max of the row
+    for (int sl = first; sl < first + per; ++sl) {
+        const int lo_s = min(V, sl * S), n_s = min(V, lo_s + S) - lo_s;
+        int bi = lo_s;
+        float bv = -INFINITY;
+        if (n_s > 0) { bi = lo_s + block_argmax(row + lo_s, n_s, s_val, s_idx); bv = s_val[0]; }
+        if (tid < CL) {
+            sc_store(sc_map(&xch[turn].val[sl], tid), bv);
+            sc_store(sc_map(&xch[turn].idx[sl], tid), bi);
+        }
+    }
+    sc_sync();
+    float m = -INFINITY;
+    int best = 0x7fffffff;
+    for (int sl = 0; sl < SAMPLE_SLICES; ++sl) argmax_combine(m, best, xch[turn].val[sl], xch[turn].idx[sl]);   // larger value, then lower index
+    if (best == 0x7fffffff) best = 0;
+    turn ^= 1;
+    if (!(T > 0.f)) {
+        if (rank == 0 && tid == 0) out[r] = best;
+        return;
+    }
+    const float inv_t = 1.0f / T;
+
+    // ---- mass of everything
+    for (int sl = first; sl < first + per; ++sl) {
+        const int lo_s = min(V, sl * S), hi_s = min(V, lo_s + S);
+        float part = 0.f;
+        for (int i = lo_s + tid; i < hi_s; i += SAMPLE_THREADS) part += expf((row[i] - m) * inv_t);
+        part = rv_block_sum(part, s_val);
+        if (tid < CL) sc_store(sc_map(&xch[turn].val[sl], tid), part);
+    }
+    sc_sync();
+    float total = 0.f;
+    for (int sl = 0; sl < SAMPLE_SLICES; ++sl) total += xch[turn].val[sl];
+    turn ^= 1;
+
+    // ---- threshold key: keep tokens whose order key is >= tau.  tau is the largest key c with
+    // count(key >= c) >= k (top-k), or with mass(key >= c) >= top_p * total (top-p); it is found four
+    // bits at a time, eight passes over the row: every thread counts its tokens (and adds their mass)
+    // by the next four bits of the key in 16 slots of its own in shared memory, for the tokens that
+    // agree with the bits decided so far; the block adds the slots up in a fixed order, the slices'
+    // sums are added in slice order, and the largest digit that still satisfies the condition is
+    // taken.  No atomics: the same result in every run.  NaN is never kept.
+    uint32_t tau = 0;
+    const int k = top_k ? top_k[r] : 0;
+    const float pp = top_p ? top_p[r] : 1.0f;
+    bool use_k = k > 0 && k < V;
+    bool use_p = pp < 1.0f;
+    if (use_k || use_p) {
+        extern __shared__ __align__(16) unsigned char s_dyn[];
+        int* h_cnt = reinterpret_cast<int*>(s_dyn);                                   // [16][SAMPLE_THREADS]
+        float* h_mass = reinterpret_cast<float*>(s_dyn) + 16 * SAMPLE_THREADS;       // [16][SAMPLE_THREADS]
+        uint32_t pre_k = 0, pre_p = 0;        // the bits decided so far
+        int above_cnt = 0;                    // tokens whose decided bits are greater than pre_k
+        float above_mass = 0.f;               // mass of the tokens whose decided bits are greater than pre_p
+        const float target = pp * total;
+        for (int shift = 28; shift >= 0; shift -= 4) {
+            for (int sl = first; sl < first + per; ++sl) {
+                const int lo_s = min(V, sl * S), hi_s = min(V, lo_s + S);
+#pragma unroll
+                for (int d = 0; d < 16; ++d) { h_cnt[d * SAMPLE_THREADS + tid] = 0; h_mass[d * SAMPLE_THREADS + tid] = 0.f; }
+                // four loads in flight per thread
+                for (int i0 = lo_s + tid; i0 < hi_s; i0 += 4 * SAMPLE_THREADS) {
+                    float vs[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int i = i0 + j * SAMPLE_THREADS;
+                        vs[j] = i < hi_s ? row[i] : __int_as_float(0x7fc00000);      // NaN: skipped below
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float v = vs[j];
+                        if (v != v) continue;
+                        const uint32_t key = order_key(v);
+                        const int d = (int)((key >> shift) & 15u);
+                        const bool top = shift == 28;
+                        if (use_k && (top || (key >> (shift + 4)) == (pre_k >> (shift + 4)))) h_cnt[d * SAMPLE_THREADS + tid] += 1;
+                        if (use_p && (top || (key >> (shift + 4)) == (pre_p >> (shift + 4)))) h_mass[d * SAMPLE_THREADS + tid] += expf((v - m) * inv_t);
+                    }
+                }
+                __syncthreads();
+                {   // warp w adds digit w % 16 over one half of the threads, lanes in a fixed order
+                    const int d = warp & 15, half = warp >> 4;
+                    int c = 0;
+                    float ms = 0.f;
+                    for (int j = lane; j < SAMPLE_THREADS / 2; j += 32) {
+                        c += h_cnt[d * SAMPLE_THREADS + half * (SAMPLE_THREADS / 2) + j];
+                        ms += h_mass[d * SAMPLE_THREADS + half * (SAMPLE_THREADS / 2) + j];
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        c += __shfl_xor_sync(0xffffffffu, c, o);
+                        ms += __shfl_xor_sync(0xffffffffu, ms, o);
+                    }
+                    if (lane == 0) { s_cnt[half][d] = c; s_mass[half][d] = ms; }
+                }
+                __syncthreads();
+                // this slice's 16 + 16 sums go to every CTA of the row
+                if (tid < 16 * CL) {
+                    const int d = tid & 15, to = tid >> 4;
+                    sc_store(sc_map(&xch[turn].cnt[sl][d], to), s_cnt[0][d] + s_cnt[1][d]);
+                    sc_store(sc_map(&xch[turn].mass[sl][d], to), s_mass[0][d] + s_mass[1][d]);
+                }
+            }
+            sc_sync();
+            // every thread of every CTA takes the same decision from the same sums
+            if (use_k) {
+                int run = above_cnt, found = -1;
+                for (int d = 15; d >= 0; --d) {
+                    int c = 0;
+                    for (int sl = 0; sl < SAMPLE_SLICES; ++sl) c += xch[turn].cnt[sl][d];
+                    if (run + c >= k) { found = d; break; }
+                    run += c;
+                }
+                if (found < 0) { use_k = false; pre_k = 0; }          // fewer than k tokens (NaN rows): keep all
+                else { pre_k |= (uint32_t)found << shift; above_cnt = run; }
+            }
+            if (use_p) {
+                float run = above_mass;
+                int found = -1;
+                for (int d = 15; d >= 0; --d) {
+                    float c = 0.f;
+                    for (int sl = 0; sl < SAMPLE_SLICES; ++sl) c += xch[turn].mass[sl][d];
+                    if (run + c >= target) { found = d; break; }
+                    run += c;
+                }
+                if (found < 0) { use_p = false; pre_p = 0; }          // rounding left the sum just below the target: keep all
+                else { pre_p |= (uint32_t)found << shift; above_mass = run; }
+            }
+            turn ^= 1;
+            if (!use_k && !use_p) break;
+        }
+        tau = pre_k > pre_p ? pre_k : pre_p;
+    }
+
+    // ---- kept mass and last kept token of every slice, to every CTA
+    int lo, hi, last_kept;
+    float excl, upto;
+    for (int sl = first; sl < first + per; ++sl) {
+        const int lo_s = min(V, sl * S), hi_s = min(V, lo_s + S);
+        slice_scan(row, lo_s, hi_s, tau, m, inv_t, s_scan, s_incl, &s_last, lo, hi, last_kept, excl, upto);
+        if (tid < CL) {
+            sc_store(sc_map(&xch[turn].val[sl], tid), s_incl[SAMPLE_THREADS - 1]);
+            sc_store(sc_map(&xch[turn].idx[sl], tid), s_last);
+        }
+    }
+    sc_sync();
+    float kept_total = 0.f;
+    for (int sl = 0; sl < SAMPLE_SLICES; ++sl) kept_total += xch[turn].val[sl];
+
+    // ---- the draw: the first token, in vocabulary order, whose cumulated kept mass exceeds u * (kept mass)
+    uint32_t c4[4] = {(uint32_t)(draw_index[r] & 0xffffffffll), (uint32_t)((unsigned long long)draw_index[r] >> 32), 0u, 0u};
+    philox4x32_10(c4, (uint32_t)(seeds[r] & 0xffffffffull), (uint32_t)(seeds[r] >> 32));
+    const float u = (float)(c4[0] >> 8) * (1.0f / 16777216.0f);
+    const float target = u * kept_total;
+    // the slice the target falls into (the same arithmetic in every CTA); if rounding put the target at
+    // or beyond the kept mass, the slice of the last kept token
+    int resp = -1;
+    float off = 0.f, resp_off = 0.f;
+    for (int sl = 0; sl < SAMPLE_SLICES; ++sl) {
+        const float kc = xch[turn].val[sl];
+        if (resp < 0 && kc > 0.f && target < off + kc) { resp = sl; resp_off = off; }
+        off += kc;
+    }
+    bool beyond = false;
+    if (resp < 0) {
+        beyond = true;
+        for (int sl = SAMPLE_SLICES - 1; sl >= 0; --sl)
+            if (xch[turn].idx[sl] >= 0) { resp = sl; break; }
+    }
+    if (resp < 0) {                                       // nothing was kept at all (a row of NaN): the arg-max
+        if (rank == 0 && tid == 0) out[r] = best;
+        return;
+    }
+    if (resp / per != rank) return;                       // (nothing of another CTA is touched after the barrier above)
+    {
+        const int lo_s = min(V, resp * S), hi_s = min(V, lo_s + S);
+        slice_scan(row, lo_s, hi_s, tau, m, inv_t, s_scan, s_incl, &s_last, lo, hi, last_kept, excl, upto);
+        if (tid == 0) s_result = -1;
+        __syncthreads();
+        const float t_loc = target - resp_off;
+        if (!beyond && upto > excl && excl <= t_loc && t_loc < upto) {
+            float run = excl;
+            int pick = last_kept;
+            for (int i = lo; i < hi; ++i) {
+                const float v = row[i];
+                if (order_key(v) >= tau && !(v != v)) {
+                    run += expf((v - m) * inv_t);
+                    if (run > t_loc) { pick = i; break; }
+                }
+            }
+            atomicMax(&s_result, pick);   // at most one thread matches; max is only a tie guard
+        }
+        __syncthreads();
+        // no chunk took it (rounding): the last kept token of the slice
+        if (tid == 0) out[r] = s_result >= 0 ? s_result : (s_last >= 0 ? s_last : best);
+    }
+}
+
+static int g_sample_cluster = 0;
+// CTAs per row: 0 chosen by the number of rows, else 1, 2, 4 or 8 (for tests: the result is the same).
+RV_EXPORT void rv_sample_set_cluster(int ctas_per_row) { g_sample_cluster = ctas_per_row; }
 
 // temperature, top_k, top_p may be null (greedy / disabled).  seeds and draw_index are read
 // only for rows with temperature > 0.
@@ -323,6 +429,11 @@ RV_EXPORT int rv_sample(const float* logits, const float* temperature, const int
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    RV_LAUNCH_ST = rv_launch(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), smem, stream, logits, temperature, top_k, top_p, seeds, draw_index, out, vocab);
+    if (n_rows > 65535) return RV_ERR_BAD_SIZE;
+    // CTAs per row: as many (8, 4, 2 or 1) as keep rows x CTAs within the SMs; the result is the same for each
+    int cl = g_sample_cluster > 0 ? g_sample_cluster : (n_rows <= 18 ? 8 : (n_rows <= 37 ? 4 : (n_rows <= 74 ? 2 : 1)));
+    if (cl != 1 && cl != 2 && cl != 4 && cl != 8) return RV_ERR_BAD_SIZE;
+    RV_LAUNCH_ST = rv_launch_cluster(sample_kernel, dim3(cl, n_rows), dim3(SAMPLE_THREADS), smem, stream, (unsigned)cl,
+                                     logits, temperature, top_k, top_p, seeds, draw_index, out, vocab);
     return rv_launch_status();
 }

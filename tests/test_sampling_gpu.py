@@ -89,3 +89,41 @@ def test_sampler_object_and_parameter_checks(K):
             SamplingParams(**bad)
     with pytest.raises(SamplingError):
         s.sample(logits, [SamplingParams()], [0], [0])
+
+
+@pytest.mark.parametrize("vocab", [5, 31, 383, 5000, 128256])
+def test_the_token_does_not_depend_on_how_many_ctas_share_a_row(K, vocab):
+    """A row is cut into eight slices whatever the launch; one, two, four or eight CTAs (a thread-block
+    cluster, results exchanged through distributed shared memory) work through them: the same
+    arithmetic in the same order, so the same tokens bit for bit - greedy, temperature, top-k, top-p,
+    rows of NaN and rows of equal logits included."""
+    from ctypes import c_int
+    torch.manual_seed(vocab)
+    R = 7
+    logits = torch.randn(R, vocab) * 4
+    logits[1] = 2.0                                       # all equal
+    logits[2] = float("nan")                              # nothing to keep: the arg-max rule (index 0)
+    if vocab > 20:
+        logits[3, 7] = logits[3, vocab - 2] = 30.0        # a tie across slices
+    temps = torch.tensor([0.8, 1.0, 0.9, 0.7, 0.0, 1.3, 0.6])
+    seeds = torch.arange(5, 5 + R, dtype=torch.int64)
+    draws = torch.arange(R, dtype=torch.int64) * 3
+    tk = torch.tensor([0, 3, 2, 0, 5, min(40, vocab - 1), 1], dtype=torch.int32)
+    tp = torch.tensor([1.0, 0.9, 0.5, 0.95, 0.8, 0.7, 1.0])
+    lib = K._lib("sampling.cu")
+    results = []
+    try:
+        for cl in (1, 2, 4, 8):
+            lib.rv_sample_set_cluster(c_int(cl))
+            g = logits.cuda()
+            results.append((K.sample(g).tolist(),
+                            K.sample(g, temps.cuda(), None, None, seeds.cuda(), draws.cuda()).tolist(),
+                            K.sample(g, temps.cuda(), tk.cuda(), None, seeds.cuda(), draws.cuda()).tolist(),
+                            K.sample(g, temps.cuda(), tk.cuda(), tp.cuda(), seeds.cuda(), draws.cuda()).tolist()))
+    finally:
+        lib.rv_sample_set_cluster(c_int(0))
+    assert all(r == results[0] for r in results[1:]), results
+    greedy = results[0][0]
+    assert greedy[1] == 0 and greedy[2] == 0 and (vocab <= 20 or greedy[3] == 7)
+    assert results[0][3][6] == greedy[6]                  # top-k of one: the most likely token
+    assert results[0][1][4] == greedy[4]                  # temperature 0 among sampled rows
