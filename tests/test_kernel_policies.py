@@ -74,3 +74,11 @@ def test_key_splits_of_decode_attention_follow_the_wave_model():
             assert 1 <= s <= 64 and (s == 1 or -(-tiles // s) >= 2)
     assert CudaKernels.decode_splits(meta(1, 32768), 32, 8) >= 40         # a long context alone still fills the GPU
     assert CudaKernels.decode_splits(meta(4, 64), 32, 8) == 1             # one tile: nothing to split
+
+
+def test_the_build_check_compiles_both_builds_of_the_prefill_gemm():
+    from rvllm_b200.kernels.variants import all_variants
+    jobs = [(src, tuple(defs)) for src, defs in all_variants()]
+    assert ("gemm_tcgen05.cu", ()) in jobs and ("gemm_tcgen05.cu", ("-DRV_PAIR=1",)) in jobs
+    assert ("sampling.cu", ()) in jobs and ("gemm_tcgen05_decode.cu", ()) in jobs
+    assert len(jobs) == len(set(jobs))
