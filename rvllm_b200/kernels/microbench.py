@@ -4,6 +4,7 @@
     python -m rvllm_b200.kernels.microbench prefill_gemm --m 2048 --n 6144 --k 4096 [--gated]
     python -m rvllm_b200.kernels.microbench decode_attention  --batch 32 --ctx 2048
     python -m rvllm_b200.kernels.microbench prefill_attention --tokens 2048
+    python -m rvllm_b200.kernels.microbench sampling --batch 8 --n 128256
 
 Used for timing a kernel in isolation (CUDA events, warm-up, inputs rotated so that L2 does not
 help) and as the small, self-ending workload of a profiler capture.
@@ -32,7 +33,7 @@ def timed(fns, iters: int, warmup: int = 3):
 def main(argv=None) -> int:
     from . import AttentionMeta, get_library
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["decode_gemm", "prefill_gemm", "decode_attention", "prefill_attention"])
+    ap.add_argument("kernel", choices=["decode_gemm", "prefill_gemm", "decode_attention", "prefill_attention", "sampling"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=28672)
     ap.add_argument("--k", type=int, default=4096)
@@ -51,6 +52,25 @@ def main(argv=None) -> int:
     torch.manual_seed(0)
     dev = "cuda"
     out = {"kernel": args.kernel}
+    if args.kernel == "sampling":
+        # temperature + top-k + top-p over `--batch` rows of `--n` logits; several sets of logits in turn
+        R, V = args.batch, args.n
+        sets = [torch.randn(R, V, device=dev) * 4 for _ in range(max(2, int(300e6 // (R * V * 4)) + 1))]
+        t = torch.full((R,), 0.8, device=dev); tk = torch.full((R,), 50, device=dev, dtype=torch.int32)
+        tp = torch.full((R,), 0.95, device=dev)
+        seeds = torch.arange(R, device=dev, dtype=torch.int64); di = torch.zeros(R, device=dev, dtype=torch.int64)
+        graphs = []
+        for lg in sets:                       # one CUDA graph per set: device time without the host's launch cost
+            K.sample(lg, t, tk, tp, seeds, di)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                K.sample(lg, t, tk, tp, seeds, di)
+            graphs.append(g)
+        ms = timed([g.replay for g in graphs], args.iters)
+        out.update(rows=R, vocab=V, us=round(ms * 1e3, 2))
+        print(json.dumps(out))
+        return 0
     if args.kernel in ("decode_gemm", "prefill_gemm"):
         copies = max(2, int(300e6 // (args.n * args.k * 2)) + 1)
         ws = [(torch.randn(args.n, args.k, device=dev) * 0.02).bfloat16() for _ in range(copies)]
