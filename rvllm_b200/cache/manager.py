@@ -99,6 +99,22 @@ class CacheManager:
     def blocks_for(self, num_tokens: int) -> int:
         return (num_tokens + self.page_size - 1) // self.page_size
 
+    def peak_pages(self, num_tokens: int, largest_portion: int) -> List[int]:
+        """Per group, the most pages a request of `num_tokens` tokens holds at any one time when no
+        step brings it more than `largest_portion` tokens.  A group that keeps every key needs the
+        pages of all its tokens; a window group holds the window behind the first token of a step
+        plus the step's own tokens (what lies below is given back after each step)."""
+        out = []
+        for g in self.groups:
+            full = self.blocks_for(num_tokens)
+            w = g.need.window
+            if w is None:
+                out.append(full)
+            else:
+                # keys [first - w + 1, first + portion) straddle at most one page more than their count fills
+                out.append(min(full, self.blocks_for(w - 1 + max(1, largest_portion)) + 1))
+        return out
+
     # ---- requests ---------------------------------------------------------------------------
     def has(self, req: Hashable) -> bool:
         return req in self.requests

@@ -114,7 +114,7 @@ class DenseDecoderConfig:
     rms_norm_eps: float
     rope_theta: float
     rope_scaling: Optional[RopeScaling]
-    attention_bias: bool                       # bias on q, k and v (never on o or the MLP)
+    attention_bias: bool                       # bias on q, k and v (Llama: on o as well; never on the MLP)
     tie_word_embeddings: bool
     hidden_act: str
     layer_windows: Tuple[Optional[int], ...]   # per layer: None = all keys, W = the last W keys
@@ -125,6 +125,7 @@ class DenseDecoderConfig:
 
     ARCHITECTURE = ""              # set by subclasses
     BIAS_DEFAULT = False           # default of `attention_bias`
+    OUT_BIAS_FOLLOWS = False       # whether `attention_bias` also puts a bias on the output projection
 
     # ---- reading -----------------------------------------------------------------------
     @classmethod
@@ -160,6 +161,8 @@ class DenseDecoderConfig:
             p.append(f"`torch_dtype` = {dtype!r} is not supported (known: bfloat16, float16, float32)")
 
         bias = cls._read_bias(r)
+        if r.boolean("mlp_bias", default=False):
+            p.append("`mlp_bias` = true is not supported: the gated MLP of this engine has no bias")
         windows = cls._read_windows(r, obj, L or 0)
         eos = obj.get("eos_token_id")
         if eos is None:
@@ -244,7 +247,7 @@ class DenseDecoderConfig:
                 "num_kv_heads": self.num_key_value_heads,
                 "head_dim": self.head_dim,
                 "qkv_bias": self.attention_bias,
-                "out_bias": False,
+                "out_bias": self.attention_bias and self.OUT_BIAS_FOLLOWS,
                 "scale": self.head_dim ** -0.5,
                 "window": self.layer_windows[i],
                 "position": "rope",
@@ -254,7 +257,7 @@ class DenseDecoderConfig:
                 "intermediate_size": self.intermediate_size,
                 "activation": self.hidden_act,
             })
-            layers.append(LayerSpec(
+            layers.append(LayerSpec.standard(
                 prefix=f"model.layers.{i}.", block=PartSpec("prenorm_residual"),
                 mixer=mixer, feed_forward=ffn, mixer_norm=norm, feed_forward_norm=norm,
                 names={"mixer": "self_attn.", "feed_forward": "mlp.",
@@ -277,9 +280,11 @@ class DenseDecoderConfig:
 
 @dataclass(frozen=True)
 class LlamaConfig(DenseDecoderConfig):
-    """`LlamaForCausalLM`: no bias unless `attention_bias`, no window."""
+    """`LlamaForCausalLM`: no bias unless `attention_bias`, which then puts one on q, k, v and o
+    (the checkpoints of this architecture that have biases carry `o_proj.bias` too); no window."""
     ARCHITECTURE = "LlamaForCausalLM"
     BIAS_DEFAULT = False
+    OUT_BIAS_FOLLOWS = True
 
 
 @dataclass(frozen=True)

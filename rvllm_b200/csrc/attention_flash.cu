@@ -754,24 +754,11 @@ RV_EXPORT int rv_flash_decode_balanced(const void* q, const void* cache, const i
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.window = window;
-    if (ctas <= 0) {
-        static int sms = 0;
-        if (sms == 0) {
-            int dev = 0;
-            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-                sms = 148;
-        }
-        ctas = 3 * sms;
-    }
+    if (ctas <= 0) ctas = 3 * rv_sm_count();
     const int merge_bytes = 4 * 16 * (HEAD_DIM + 2) * 4;
     const int smem = max(DECODE_STAGES * 2 * TILE_BYTES, merge_bytes);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(flash_decode_balanced_kernel<DECODE_STAGES>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static RvPerDevice configured;
+    if (int e = rv_configure_smem(configured, flash_decode_balanced_kernel<DECODE_STAGES>, smem)) return e;
     RV_LAUNCH_ST = rv_launch(flash_decode_balanced_kernel<DECODE_STAGES>, dim3(ctas), dim3(128), smem, stream, p);
     int st = rv_launch_status();
     if (st != RV_OK) return st;
@@ -785,13 +772,8 @@ template <int WARPS_M, int WARPS_N, int NSTAGES>
 static int launch_flash(const FlashParams& p, int num_seqs, cudaStream_t stream) {
     const int merge_bytes = WARPS_N > 1 ? WARPS_N * 16 * (HEAD_DIM + 2) * 4 : 0;
     const int smem = max(NSTAGES * 2 * TILE_BYTES, merge_bytes);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(flash_paged_kernel<WARPS_M, WARPS_N, NSTAGES>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static RvPerDevice configured;
+    if (int e = rv_configure_smem(configured, flash_paged_kernel<WARPS_M, WARPS_N, NSTAGES>, smem)) return e;
     const dim3 grid(p.row_tiles * p.num_splits, p.nkv, num_seqs);
     RV_LAUNCH_ST = rv_launch(flash_paged_kernel<WARPS_M, WARPS_N, NSTAGES>, dim3(grid), dim3(WARPS_M * WARPS_N * 32), smem, stream, p);
     return rv_launch_status();

@@ -443,12 +443,8 @@ RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long n
     p.scale_log2e = scale * 1.4426950408889634f;
     p.window = window;
     const int smem = Q_BYTES + 4 * KV_BYTES + P_BYTES + 256;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static RvPerDevice configured;
+    if (int e = rv_configure_smem(configured, attention_tcgen05_kernel, smem)) return e;
     const dim3 grid(nkv, num_seqs, (max_q_len * G + ROWS - 1) / ROWS);
     if (grid.y > 65535 || grid.z > 65535) return RV_ERR_UNSUPPORTED;
     RV_LAUNCH_ST = rv_launch(attention_tcgen05_kernel, grid, dim3(NUM_THREADS), smem, stream, map_q, map_kv, p);

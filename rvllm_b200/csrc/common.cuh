@@ -67,6 +67,45 @@ static inline int rv_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     return RV_OK;
 }
 
+// ---- per-device set-up -----------------------------------------------------------------------
+// cudaFuncSetAttribute and the number of SMs belong to a device, not to the process: a library
+// used on a second GPU has to set its kernels up there as well.  `RvPerDevice` remembers, per
+// device ordinal, that a one-time set-up ran (two host threads that meet in a first call both
+// run it and store the same value).
+#define RV_MAX_DEVICES 64
+struct RvPerDevice { bool done[RV_MAX_DEVICES]; };
+
+static inline int rv_current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= RV_MAX_DEVICES) return -1;
+    return dev;
+}
+
+// Raises the dynamic shared memory limit of `kernel` to `bytes` once per device.
+template <typename K>
+static inline int rv_configure_smem(RvPerDevice& once, K kernel, int bytes) {
+    const int dev = rv_current_device();
+    if (dev >= 0 && once.done[dev]) return RV_OK;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+    if (dev >= 0) once.done[dev] = true;
+    return RV_OK;
+}
+
+// The number of SMs of the current device (asked once per device).
+static inline int rv_sm_count() {
+    static int sms[RV_MAX_DEVICES];
+    const int dev = rv_current_device();
+    if (dev >= 0 && sms[dev] > 0) return sms[dev];
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev < 0 ? 0 : dev) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        return 148;
+    }
+    if (dev >= 0) sms[dev] = n;
+    return n;
+}
+
 // the status of the most recent rv_launch of this thread (launchers write RV_LAUNCH_ST = rv_launch(...))
 static thread_local int rv_launch_st = 0;
 #define RV_LAUNCH_ST rv_launch_st

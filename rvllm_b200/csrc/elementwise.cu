@@ -197,20 +197,22 @@ RV_EXPORT int rv_rmsnorm(const void* x, const void* gamma, int gamma_dtype, void
 // (token, head).  q heads: add bias, rotate, write to q_out [T, nh*hd].  k heads: add bias,
 // rotate, write into the page of the token's slot.  v heads: add bias, write into the page.
 // Cache layer layout: [num_pages, 2 (k, v), nkv, page_size, hd].
-// cos/sin: float [table_rows, hd/2]; null pointers mean "no rotation".  With write_kv = 0 the
-// rows hold q alone (row_stride = nh*hd) and nothing is written to the cache.
-template <typename T>
-__global__ void rope_cache_write_kernel(const T* __restrict__ qkv, const void* __restrict__ bias, int bias_dtype,
+// cos/sin: float [table_rows, rot/2]; null pointers mean "no rotation".  `rot` <= hd is the number
+// of leading elements of a head that are rotated, in pairs (i, i + rot/2); the rest of the head
+// passes through (with its bias).  With write_kv = 0 the rows hold q alone (row_stride = nh*hd)
+// and nothing is written to the cache.
+template <typename T, typename TIn = T>
+__global__ void rope_cache_write_kernel(const TIn* __restrict__ qkv, const void* __restrict__ bias, int bias_dtype,
                                         const int* __restrict__ positions, const float* __restrict__ cos_t,
                                         const float* __restrict__ sin_t, const int* __restrict__ slot_mapping,
                                         T* __restrict__ cache, T* __restrict__ q_out, int nh, int nkv, int hd,
-                                        int page_size, int write_kv, int table_rows, int row_stride) {
+                                        int page_size, int write_kv, int table_rows, int row_stride, int rot) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
     const int t = blockIdx.x;
     const int head = blockIdx.y;
-    const int half = hd >> 1;
-    const T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
+    const int half = rot >> 1;
+    const TIn* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
     const int col0 = head * hd;
     int pos = positions[t];
     if (pos < 0) pos = 0;
@@ -243,6 +245,11 @@ __global__ void rope_cache_write_kernel(const T* __restrict__ qkv, const void* _
             }
             dst[i] = rv_from_float<T>(a * c - b * s);
             dst[i + half] = rv_from_float<T>(a * s + b * c);
+        }
+        for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) {       // the part of the head that is not rotated
+            float a = rv_to_float(src[i]);
+            if (bias) a += rv_load_param(bias, bias_dtype, col0 + i);
+            dst[i] = rv_from_float<T>(a);
         }
     } else {
         for (int i = threadIdx.x; i < hd; i += blockDim.x) {
@@ -330,13 +337,24 @@ RV_EXPORT int rv_rope_cache_write(const void* qkv, const void* bias, int bias_dt
                                   const float* cos_t, const float* sin_t, const int* slot_mapping,
                                   void* cache, void* q_out, int n_tokens, int nh, int nkv, int hd,
                                   int page_size, int write_kv, int table_rows, int row_stride,
-                                  int dtype, cudaStream_t stream) {
+                                  int dtype, int rot, int in_dtype, cudaStream_t stream) {
     if (n_tokens < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || (hd & 1) || page_size <= 0 || table_rows <= 0)
         return RV_ERR_BAD_SIZE;
+    if (rot <= 0 || rot > hd || (rot & 1)) return RV_ERR_BAD_SIZE;
     if ((cos_t == nullptr) != (sin_t == nullptr)) return RV_ERR_BAD_SIZE;
     if (row_stride < (write_kv ? nh + 2 * nkv : nh) * hd) return RV_ERR_BAD_SIZE;
     if (n_tokens == 0) return RV_OK;
-    if (dtype == RV_DTYPE_BF16 && hd % 16 == 0 && row_stride % 8 == 0 &&
+    if (in_dtype != dtype) {
+        // a float32 product, rotated and stored as bfloat16: the values are rounded once
+        if (in_dtype != RV_DTYPE_F32 || dtype != RV_DTYPE_BF16) return RV_ERR_BAD_DTYPE;
+        const dim3 grid(n_tokens, write_kv ? nh + 2 * nkv : nh);
+        const int threads = hd / 2 >= 128 ? 128 : (hd / 2 >= 64 ? 64 : 32);
+        RV_LAUNCH_ST = rv_launch(rope_cache_write_kernel<__nv_bfloat16, float>, dim3(grid), dim3(threads), 0, stream,
+            (const float*)qkv, bias, bias_dtype, positions, cos_t, sin_t, slot_mapping, (__nv_bfloat16*)cache,
+            (__nv_bfloat16*)q_out, nh, nkv, hd, page_size, write_kv, table_rows, row_stride, rot);
+        return rv_launch_status();
+    }
+    if (dtype == RV_DTYPE_BF16 && rot == hd && hd % 16 == 0 && row_stride % 8 == 0 &&
         (reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(cache)) % 16 == 0) {
         const int items = (write_kv ? nh + nkv : nh) * (hd / 16);
         int threads = 32;
@@ -351,11 +369,11 @@ RV_EXPORT int rv_rope_cache_write(const void* qkv, const void* bias, int bias_dt
     if (dtype == RV_DTYPE_F32)
         RV_LAUNCH_ST = rv_launch(rope_cache_write_kernel<float>, dim3(grid), dim3(threads), 0, stream, 
             (const float*)qkv, bias, bias_dtype, positions, cos_t, sin_t, slot_mapping, (float*)cache,
-            (float*)q_out, nh, nkv, hd, page_size, write_kv, table_rows, row_stride);
+            (float*)q_out, nh, nkv, hd, page_size, write_kv, table_rows, row_stride, rot);
     else if (dtype == RV_DTYPE_BF16)
         RV_LAUNCH_ST = rv_launch(rope_cache_write_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, 
             (const __nv_bfloat16*)qkv, bias, bias_dtype, positions, cos_t, sin_t, slot_mapping,
-            (__nv_bfloat16*)cache, (__nv_bfloat16*)q_out, nh, nkv, hd, page_size, write_kv, table_rows, row_stride);
+            (__nv_bfloat16*)cache, (__nv_bfloat16*)q_out, nh, nkv, hd, page_size, write_kv, table_rows, row_stride, rot);
     else
         return RV_ERR_BAD_DTYPE;
     return rv_launch_status();
@@ -411,13 +429,13 @@ RV_EXPORT int rv_silu_mul(const void* gate_up, void* out, int n_rows, int inter,
         (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
         const size_t total_vec = total / 8;
         size_t vb = (total_vec + threads - 1) / threads;
-        if (vb > 148 * 32) vb = 148 * 32;
+        if (vb > (size_t)rv_sm_count() * 32) vb = (size_t)rv_sm_count() * 32;
         RV_LAUNCH_ST = rv_launch(silu_mul_bf16_vec_kernel, dim3((int)vb), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
                                                                  inter, total_vec);
         return rv_launch_status();
     }
     size_t blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > (size_t)rv_sm_count() * 16) blocks = (size_t)rv_sm_count() * 16;
     if (dtype == RV_DTYPE_F32)
         RV_LAUNCH_ST = rv_launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, total);
     else if (dtype == RV_DTYPE_BF16)

@@ -125,8 +125,9 @@ __device__ __forceinline__ void store_rope_pair(const GemmParams& p, int m, int 
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int e = v * 8 + j;
-            float a = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ra[e])));
-            float b = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rb[e])));
+            // the float accumulators go into bias and rotation as they are: one rounding, at the store
+            float a = __uint_as_float(ra[e]);
+            float b = __uint_as_float(rb[e]);
             if (p.bias) {
                 a += rv_load_param(p.bias, p.bias_dtype, n_a + e);
                 b += rv_load_param(p.bias, p.bias_dtype, n_b + e);
@@ -453,14 +454,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // One CTA per tile and SM, or (RV_PAIR) one cluster of two CTAs per tile and pair of SMs.
 static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, int max_ctas, cudaStream_t stream) {
     const int smem = STAGES * STAGE_BYTES + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static RvPerDevice configured;
+    if (int e = rv_configure_smem(configured, gemm_tcgen05_kernel, smem)) return e;
     int workers = p.m_tiles * p.n_tiles;
-    const int limit = (max_ctas > 0 ? max_ctas : 148) / (RV_PAIR ? 2 : 1);
+    const int limit = (max_ctas > 0 ? max_ctas : rv_sm_count()) / (RV_PAIR ? 2 : 1);
     if (workers > limit) workers = limit;
     if (workers < 1) workers = 1;
 #if RV_PAIR

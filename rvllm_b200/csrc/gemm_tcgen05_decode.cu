@@ -184,7 +184,7 @@ __device__ __forceinline__ void finish_from_parts(const DecodeGemmParams& p, int
                 float own[4] = {acc[j].x, acc[j].y, acc[j].z, acc[j].w}, other[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    own[e] = __bfloat162float(__float2bfloat16_rn(own[e])) + bias4[e];
+                    own[e] = own[e] + bias4[e];                       // float sums throughout: one rounding, at the store
                     other[e] = __shfl_xor_sync(0xffffffffu, own[e], hd >> 3);
                 }
                 if (!row_ok || !live) continue;
@@ -596,10 +596,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                             for (int j = 0; j < 4; ++j) {
                                 const int m = m0 + j;
                                 if (m >= p.M) break;
-                                const float own = __bfloat162float(__float2bfloat16_rn(fin[et * (MB + 1) + m])) + b;
+                                const float own = fin[et * (MB + 1) + m] + b;
                                 float v = own;
                                 if (is_q || is_k) {
-                                    const float other = __bfloat162float(__float2bfloat16_rn(fin[pe * (MB + 1) + m])) + bp;
+                                    const float other = fin[pe * (MB + 1) + m] + bp;
                                     v = first ? own * c[j] - other * sn[j] : other * sn[j] + own * c[j];
                                 }
                                 if (is_q) {
@@ -661,13 +661,8 @@ static int launch_decode(const CUtensorMap& mw, const CUtensorMap& mx, const Dec
     const int stage = A_BYTES + MB * BK * 2;
     const int fin = TILE_F * (MB + 1) * 4;
     int smem = (STAGES * stage > fin ? STAGES * stage : fin) + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             smem + MAX_NORM_K * 4 + (64 + 8) * TILE_F * 4);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static RvPerDevice configured;
+    if (int e = rv_configure_smem(configured, gemm_decode_kernel<MB>, smem + MAX_NORM_K * 4 + (64 + 8) * TILE_F * 4)) return e;
     if (p.norm_gamma || p.cluster) {
         const int num_kb = (p.K + BK - 1) / BK;
         smem = STAGES * stage + 1024;

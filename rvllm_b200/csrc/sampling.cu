@@ -423,15 +423,14 @@ RV_EXPORT int rv_sample(const float* logits, const float* temperature, const int
     if (temperature && (!seeds || !draw_index)) return RV_ERR_BAD_SIZE;
     // the threshold search of top-k / top-p keeps 16 counters and 16 sums per thread in shared memory
     const size_t smem = (temperature && (top_k || top_p)) ? (size_t)2 * 16 * SAMPLE_THREADS * 4 : 0;
-    static bool configured = false;
-    if (smem && !configured) {
-        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * 16 * SAMPLE_THREADS * 4));
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
+    static RvPerDevice configured;
+    if (smem) {
+        if (int e = rv_configure_smem(configured, sample_kernel, (int)(2 * 16 * SAMPLE_THREADS * 4))) return e;
     }
     if (n_rows > 65535) return RV_ERR_BAD_SIZE;
     // CTAs per row: as many (8, 4, 2 or 1) as keep rows x CTAs within the SMs; the result is the same for each
-    int cl = g_sample_cluster > 0 ? g_sample_cluster : (n_rows <= 18 ? 8 : (n_rows <= 37 ? 4 : (n_rows <= 74 ? 2 : 1)));
+    const int sms = rv_sm_count();
+    int cl = g_sample_cluster > 0 ? g_sample_cluster : (n_rows * 8 <= sms ? 8 : (n_rows * 4 <= sms ? 4 : (n_rows * 2 <= sms ? 2 : 1)));
     if (cl != 1 && cl != 2 && cl != 4 && cl != 8) return RV_ERR_BAD_SIZE;
     RV_LAUNCH_ST = rv_launch_cluster(sample_kernel, dim3(cl, n_rows), dim3(SAMPLE_THREADS), smem, stream, (unsigned)cl,
                                      logits, temperature, top_k, top_p, seeds, draw_index, out, vocab);

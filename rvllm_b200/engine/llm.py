@@ -31,6 +31,7 @@ class _Flight:
     ids: Optional[torch.Tensor] = None
     host_ids: Optional[torch.Tensor] = None
     ready: Optional[object] = None
+    host_status: Optional[torch.Tensor] = None      # the kernels' status word, copied with the ids
 
 
 @dataclass
@@ -142,11 +143,15 @@ class LLM:
             if flight.ids.is_cuda:
                 host = self._id_buffers[self._id_next]
                 self._id_next ^= 1
-                if host is None or host.numel() < len(rows):
-                    host = torch.empty((max(len(rows), self.config.max_num_seqs),), dtype=torch.int32, pin_memory=True)
+                if host is None or host.numel() < len(rows) + 1:
+                    host = torch.empty((max(len(rows), self.config.max_num_seqs) + 1,), dtype=torch.int32, pin_memory=True)
                     self._id_buffers[self._id_next ^ 1] = host
                 flight.host_ids = host[:len(rows)]
                 flight.host_ids.copy_(flight.ids, non_blocking=True)
+                status = getattr(self.engine.kernels, "status_word", None)
+                if status is not None:        # the last element carries the kernels' status word of this step
+                    flight.host_status = host[-1:]
+                    flight.host_status.copy_(status, non_blocking=True)
                 flight.ready = torch.cuda.Event()
                 flight.ready.record()
             else:
@@ -160,6 +165,9 @@ class LLM:
         if flight.host_ids is not None:
             if flight.ready is not None:
                 flight.ready.synchronize()
+            if flight.host_status is not None and int(flight.host_status[0]) != 0:
+                # a kernel of this step gave up a bounded wait: its ids are not results
+                self.engine.kernels.raise_on_abort(int(flight.host_status[0]))
             ids = flight.host_ids.tolist()
             sampled = {rid: ids[i] for rid, i in flight.row_of.items()}
         return self.scheduler.resolve(flight.batch, sampled)

@@ -126,10 +126,15 @@ class Scheduler:
             raise SchedulerError(f"request {req.req_id!r}: a prompt of {len(req.prompt)} tokens exceeds "
                                  f"max_num_batched_tokens {self.max_num_batched_tokens} and chunking is off")
         longest = min(len(req.prompt) + req.params.max_tokens, self.max_model_len)
-        need = self.cache.blocks_for(longest)
-        if need > self.cache.num_pages:
-            raise KvExhausted(need, self.cache.num_pages, f"request {req.req_id!r} can never fit: "
-                              f"{longest} tokens need {need} pages of {self.cache.page_size}")
+        # the most pages it will hold at once, group by group: all its tokens where every key is
+        # kept, a window plus one step's portion where pages are given back behind the window
+        portion = len(req.prompt)
+        if self.enable_chunked_prefill:
+            portion = min(portion, self.max_num_batched_tokens, self.max_prefill_chunk or portion)
+        for gi, need in enumerate(self.cache.peak_pages(longest, portion)):
+            if need > self.cache.num_pages:
+                raise KvExhausted(need, self.cache.num_pages, f"request {req.req_id!r} can never fit: {longest} tokens "
+                                  f"need {need} pages of {self.cache.page_size} at once in cache group {gi}")
         req.arrival = self._arrivals
         self._arrivals += 1
         req.state = WAITING

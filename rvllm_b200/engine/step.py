@@ -342,6 +342,8 @@ class ModelRunner:
         wants its logits, and a bucket is large enough."""
         if not self.graph_batch_sizes or self.device.type != "cuda":
             return None
+        if not getattr(self.model, "graph_safe", True):
+            return None                       # a part of this model cannot be captured: every step runs eagerly
         for e in entries:
             if len(e.tokens) != 1 or len(e.want) != 1:
                 return None
@@ -404,7 +406,7 @@ class ModelRunner:
         every context bucket up to `max_context` (default: max_model_len), so that no step of a
         running service pays for a capture.  A graph is captured on a batch of padding rows, which
         write nothing, so live requests are not disturbed.  Returns the number of graphs captured."""
-        if not self.graph_batch_sizes or self.device.type != "cuda":
+        if not self.graph_batch_sizes or self.device.type != "cuda" or not getattr(self.model, "graph_safe", True):
             return 0
         limit = min(max_context or self.max_model_len, self.max_model_len)
         ctx_buckets, b = [], self._ctx_bucket(1)

@@ -28,7 +28,10 @@ ROUND_TO = 64   # a request's tokens are counted in multiples of this when sizin
 
 
 def build_engine(model_dir: str, dtype: str, max_tokens: int, block_size: int = 16, device: str = "cuda:0",
-                 max_live: int = 4) -> Engine:
+                 max_live: int = 4, graphs: bool = False) -> Engine:
+    """The engine a replay runs on: a pool of exactly `max_tokens` (rounded up) tokens, `max_live`
+    request slots.  `graphs`: decode-only steps are replayed from CUDA graphs, as generation does by
+    default; otherwise every step is launched kernel by kernel."""
     if ROUND_TO % block_size and block_size % ROUND_TO:
         raise ValueError(f"block_size {block_size} neither divides nor is a multiple of {ROUND_TO}")
     cfg = load_config(model_dir)
@@ -37,7 +40,7 @@ def build_engine(model_dir: str, dtype: str, max_tokens: int, block_size: int = 
     ec = EngineConfig(dtype=dtype, block_size=block_size, num_blocks=max(1, pool_tokens // block_size),
                       max_model_len=min(cfg.to_spec().max_position_embeddings, pool_tokens),
                       max_num_seqs=max_live, max_num_batched_tokens=max(pool_tokens, max_live),
-                      enforce_eager=True, device=device)
+                      enforce_eager=not graphs, device=device)
     return Engine(model_dir, engine_config=ec)
 
 
@@ -54,6 +57,9 @@ def replay(engine: Engine, lines: IO[str], out_dir: str, echo: Optional[IO[str]]
         logits = engine.runner.step(entries) if entries else None
         if logits is not None:
             arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
+            check = getattr(engine.kernels, "raise_on_abort", None)
+            if check is not None:
+                check()      # a kernel that gave up a bounded wait has written no result: fail, write nothing
             arr.tofile(os.path.join(out_dir, f"{step}.f32"))
         for rid in rec.get("end", ()):
             engine.runner.finish(rid)
@@ -74,7 +80,11 @@ def main(argv=None) -> int:
                     help="most tokens live requests hold at any time (each request rounded up to 64)")
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--max-live", type=int, default=4, help="most requests live at a time (request slots)")
+    ap.add_argument("--graphs", action="store_true",
+                    help="replay decode-only steps from CUDA graphs, as generation does (default: every step eager)")
     args = ap.parse_args(argv)
-    engine = build_engine(args.model, args.dtype, args.max_tokens, args.block_size, args.device)
+    engine = build_engine(args.model, args.dtype, args.max_tokens, args.block_size, args.device,
+                          max_live=args.max_live, graphs=args.graphs)
     replay(engine, sys.stdin, args.out, sys.stdout)
     return 0

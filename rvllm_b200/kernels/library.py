@@ -68,7 +68,6 @@ class AttentionMeta:
 
 
 class CudaKernels:
-    SKINNY_MAX_ROWS = 0     # rows up to which the weight-streaming GEMM replaces the library GEMM (0: off)
     TCGEN05_MIN_ROWS = 128  # rows from which the tcgen05 GEMM of this project is used for bfloat16 ...
     TCGEN05_MIN_FILL = 0.0  # ... where its tiles keep its persistent workers busy for this share of their rounds
                             # (0: always.  With 0.8 the library's GEMM takes the partly filled shapes and is 20-140 %
@@ -89,6 +88,7 @@ class CudaKernels:
     FUSED_NORM_MAX_ROWS = 0 # rows up to which an RMSNorm is applied inside the decode GEMM that consumes it
     FUSED_QKV_MAX_ROWS = 32 # rows up to which q/k/v product, rotation and cache write are one kernel
     pdl = os.environ.get("RVLLM_NO_PDL") != "1"   # programmatic dependent launch between kernels
+    num_sms = 148           # SMs of the device; asked from the device when the library is made
 
     def __init__(self, device="cuda:0"):
         if not torch.cuda.is_available():
@@ -100,8 +100,12 @@ class CudaKernels:
         # the float32 path must never round operands to TF32 inside a library product
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
+        self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._libs = {}
         self._decode_counters = None
+        # one status word for every tcgen05 launch of the engine: a kernel whose bounded wait on an
+        # mbarrier gave up writes a non-zero code here instead of hanging (see `raise_on_abort`)
+        self._status = torch.zeros((1,), dtype=torch.int32, device=self.device)
 
     # ------------------------------------------------------------------ plumbing
     def _lib(self, source: str, defines=()):
@@ -125,6 +129,30 @@ class CudaKernels:
             return _DT[t.dtype]
         except KeyError:
             raise KernelError(f"{name}: dtype {t.dtype} is not supported (float32, bfloat16)") from None
+
+    # ------------------------------------------------------------------ aborted kernels
+    @property
+    def status_word(self) -> torch.Tensor:
+        """int32 [1] on the device: 0, or the code of the first bounded wait that gave up in a tcgen05
+        kernel launched without a status tensor of the caller's own."""
+        return self._status
+
+    def raise_on_abort(self, value: Optional[int] = None) -> None:
+        """Raise `KernelError` if a kernel gave up a bounded wait since the last check: what it
+        wrote is then not a result.  `value` is the status word as the caller has already read it
+        (for instance copied to the host beside a step's sampled ids); None reads it now, which
+        waits for the device.  After a non-zero value the word and the arrival counters of the
+        split-K products are cleared, so that the next launches start clean (an aborted CTA skips
+        its arrival, which would make a later launch take the wrong CTA for the last one)."""
+        if value is None:
+            value = int(self._status.item())
+        if value == 0:
+            return
+        self._status.zero_()
+        if self._decode_counters is not None:
+            self._decode_counters.zero_()
+        raise KernelError(f"a tcgen05 kernel gave up a bounded wait on an mbarrier (wait number {value} of the kernel's "
+                          "source); what that step wrote is not a result")
 
     # ------------------------------------------------------------------ row kernels
     def gather_rows(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
@@ -173,34 +201,39 @@ class CudaKernels:
         return out
 
     def rope_cache_write(self, qkv, bias, positions, cos, sin, slot_mapping, cache_layer,
-                         num_heads, num_kv_heads, head_dim, write_kv=True) -> torch.Tensor:
+                         num_heads, num_kv_heads, head_dim, write_kv=True, out_dtype=None) -> torch.Tensor:
         """Add the q/k/v bias, rotate q and k, write k and v into their cache pages, return q
         [T, num_heads * head_dim].  qkv rows are [q | k | v], or q alone when `write_kv` is False.
-        cache_layer: [num_pages, 2, num_kv_heads, page_size, head_dim]."""
+        cache_layer: [num_pages, 2, num_kv_heads, page_size, head_dim].  `out_dtype` bfloat16 with
+        float32 rows: the product stays in float until it has been biased and rotated."""
         _need(qkv, "qkv", dims=2); _need(positions, "positions", torch.int32, 1)
+        out_dtype = out_dtype or qkv.dtype
         T = qkv.shape[0]
         width = (num_heads + (2 * num_kv_heads if write_kv else 0)) * head_dim
         if qkv.shape[1] != width:
             raise KernelError(f"rope_cache_write: qkv rows have {qkv.shape[1]} columns, expected {width}")
         if write_kv:
-            _need(cache_layer, "cache_layer", qkv.dtype, 5); _need(slot_mapping, "slot_mapping", torch.int32, 1)
+            _need(cache_layer, "cache_layer", out_dtype, 5); _need(slot_mapping, "slot_mapping", torch.int32, 1)
             if tuple(cache_layer.shape[1:3]) != (2, num_kv_heads) or cache_layer.shape[4] != head_dim:
                 raise KernelError(f"rope_cache_write: cache layer of shape {tuple(cache_layer.shape)} does not "
                                   f"fit {num_kv_heads} kv heads of {head_dim}")
+        rot = head_dim
         if cos is not None:
             _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
-            if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
-                raise KernelError("rope_cache_write: cos/sin tables must be [rows, head_dim/2]")
+            rot = 2 * cos.shape[1]            # the leading `rot` elements of a head are rotated, the rest pass through
+            if not 0 < rot <= head_dim or sin.shape != cos.shape:
+                raise KernelError(f"rope_cache_write: cos/sin tables must be [rows, rotary_dim/2] with rotary_dim <= "
+                                  f"head_dim {head_dim}, got {tuple(cos.shape)} and {tuple(sin.shape)}")
         if bias is not None:
             _need(bias, "bias", dims=1)
-        q = torch.empty((T, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        q = torch.empty((T, num_heads * head_dim), dtype=out_dtype, device=qkv.device)
         page = cache_layer.shape[3] if write_kv else 1
         st = self._lib("elementwise.cu").rv_rope_cache_write(
             _ptr(qkv), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0), _ptr(positions),
             _ptr(cos), _ptr(sin), _ptr(slot_mapping if write_kv else None), _ptr(cache_layer if write_kv else None),
             _ptr(q), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page),
             c_int(1 if write_kv else 0), c_int(cos.shape[0] if cos is not None else 1), c_int(qkv.shape[1]),
-            c_int(self._dt(qkv, "qkv")), self._stream())
+            c_int(_DT[out_dtype]), c_int(rot), c_int(self._dt(qkv, "qkv")), self._stream())
         _check("rope_cache_write", st)
         return q
 
@@ -242,10 +275,9 @@ class CudaKernels:
                                  mode=1, q_filter=1, max_q_len=1)
         return out
 
-    @staticmethod
-    def decode_splits(meta: AttentionMeta, num_heads: int, num_kv_heads: int) -> int:
+    def decode_splits(self, meta: AttentionMeta, num_heads: int, num_kv_heads: int) -> int:
         """Into how many CTAs the keys of a sequence are split in a decode step.  Three CTAs of
-        the kernel fit an SM (444 on the GPU) and run in waves; a CTA costs about 4 us plus 2.25 us
+        the kernel fit an SM (444 on a GPU of 148 SMs) and run in waves; a CTA costs about 4 us plus 2.25 us
         per 64-key tile (measured with all slots busy, where the tiles' bytes arrive at the speed
         of the memory), the merge kernel 2.5 us.  The split count with the least modelled time is
         taken: it fills one wave when the batch is small and keeps the last wave full when it is
@@ -260,7 +292,7 @@ class CudaKernels:
             if s > 1 and per < 2:
                 break
             # (the merge kernel reads eight splits per round trip)
-            t = -(-ctas * s // 444) * (4.0 + 2.25 * per) + (2.0 + 0.5 * -(-s // 8) if s > 1 else 0.0)
+            t = -(-ctas * s // (3 * self.num_sms)) * (4.0 + 2.25 * per) + (2.0 + 0.5 * -(-s // 8) if s > 1 else 0.0)
             if t < best_t - 1e-9:
                 best, best_t = s, t
         return best
@@ -279,7 +311,7 @@ class CudaKernels:
         _need(q, "q", torch.bfloat16, 2); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
         lib = self._lib("attention_flash.cu", (f"-DHEAD_DIM={head_dim}",))
         T = q.shape[0]
-        grid = ctas or 444
+        grid = ctas or 3 * self.num_sms
         pieces = lib.rv_flash_balanced_max_pieces(c_int(meta.max_ctx_len), c_int(num_kv_heads), c_int(grid))
         scratch = torch.empty((pieces * T * num_heads * (head_dim + 2),), dtype=torch.float32, device=q.device)
         counts = torch.empty((meta.num_seqs * num_kv_heads,), dtype=torch.int32, device=q.device)
@@ -316,7 +348,7 @@ class CudaKernels:
             _ptr(q), _ptr(cache_layer), ctypes.c_longlong(cache_layer.shape[0]), _ptr(meta.block_tables),
             _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens), _ptr(out), c_int(q.shape[0]), c_int(meta.num_seqs),
             c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]), c_int(meta.max_blocks),
-            c_float(scale), c_int(window or 0), c_int(meta.max_q_len), _ptr(status), self._stream())
+            c_float(scale), c_int(window or 0), c_int(meta.max_q_len), _ptr(status if status is not None else self._status), self._stream())
         _check("attention_tcgen05", st)
         return out
 
@@ -375,9 +407,6 @@ class CudaKernels:
         if self._use_decode_gemm(M, weight.shape[0], K, False) and out_dtype in (torch.bfloat16, torch.float32) \
                 and (residual is None or (residual.dtype == torch.bfloat16 and out_dtype == torch.bfloat16)):
             return self.linear_decode(x, weight, bias, residual, out_dtype)
-        if 0 < M <= self.SKINNY_MAX_ROWS and K % 8 == 0 and out_dtype in (torch.bfloat16, torch.float32) \
-                and (residual is None or (residual.dtype == torch.bfloat16 and out_dtype == torch.bfloat16)):
-            return self.linear_skinny(x, weight, bias, residual, out_dtype)
         if self._tcgen05_fills(M, weight.shape[0]) and K % 8 == 0 and bias is None and out_dtype in (torch.bfloat16, torch.float32) \
                 and (residual is None or (residual.dtype == torch.bfloat16 and out_dtype == torch.bfloat16)):
             return self.linear_tcgen05(x, weight, residual, out_dtype)
@@ -390,40 +419,24 @@ class CudaKernels:
             return out
         if residual is not None and bias is None:
             return torch.addmm(residual, x, weight.t())
-        out = torch.nn.functional.linear(x, weight, bias.to(x.dtype) if bias is not None else None)
         if residual is not None:
-            out += residual
-        return out
-
-    def linear_skinny(self, x, weight, bias=None, residual=None, out_dtype=None, gated=False, tiles_per_cta=0):
-        """The weight-streaming tensor-core GEMM for at most 64 rows of bfloat16 activations.
-        gated: weight rows are [gate | up]; returns silu(x gate^T) * (x up^T)."""
-        _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
-        M, K = x.shape
-        N = weight.shape[0]
-        out_dtype = out_dtype or torch.bfloat16
-        out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
-        if bias is not None:
-            _need(bias, "bias", dims=1)
-        if residual is not None:
-            _need(residual, "residual", torch.bfloat16, 2)
-        st = self._lib("gemm_skinny.cu").rv_gemm_skinny_bf16(
-            _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0),
-            _ptr(residual), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0), c_int(M), c_int(N), c_int(K),
-            c_int(1 if gated else 0), c_int(tiles_per_cta), self._stream())
-        _check("gemm_skinny", st)
-        return out
+            # bias and residual: the sum is formed in float and rounded once
+            out = torch.mm(x, weight.t(), out_dtype=torch.float32)
+            out += bias.float()
+            out += residual.float()
+            return out.to(out_dtype)
+        return torch.nn.functional.linear(x, weight, bias.to(x.dtype) if bias is not None else None)
 
     def _tcgen05_fills(self, M: int, N: int, gated: bool = False) -> bool:
         """Whether this project's tcgen05 GEMM is the one to use for M rows and N weight rows: from
-        `TCGEN05_MIN_ROWS` rows on, and only where its persistent workers (148 CTAs, or 74 pairs on
+        `TCGEN05_MIN_ROWS` rows on, and only where its persistent workers (one CTA per SM, or one pair per two SMs on
         tiles of 256 rows) are busy for at least `TCGEN05_MIN_FILL` of their rounds.  Where a last
         round stays mostly empty the library's GEMM, which cuts such shapes differently, measured
         20 to 140 % faster (o_proj at 512 rows: 22.6 against 41 us)."""
         if M < self.TCGEN05_MIN_ROWS:
             return False
         pair = self.PAIR_GEMM and (M % 256 == 0 or M % 256 > 128)
-        rows, workers = (256, 74) if pair else (128, 148)
+        rows, workers = (256, self.num_sms // 2) if pair else (128, self.num_sms)
         tiles = -(-M // rows) * (-(-(N // 2) // 128) if gated else -(-N // 256))
         rounds = -(-tiles // workers)
         return tiles >= self.TCGEN05_MIN_FILL * rounds * workers
@@ -450,7 +463,7 @@ class CudaKernels:
         epilogue = 2 if gated else (1 if residual is not None else 0)
         st = self._prefill_gemm_lib(M, pair).rv_gemm_tcgen05_bf16(
             _ptr(x), _ptr(weight), _ptr(residual), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0),
-            c_int(M), c_int(N), c_int(K), c_int(epilogue), _ptr(status), c_int(max_ctas), self._stream())
+            c_int(M), c_int(N), c_int(K), c_int(epilogue), _ptr(status if status is not None else self._status), c_int(max_ctas), self._stream())
         _check("gemm_tcgen05", st)
         return out
 
@@ -469,7 +482,7 @@ class CudaKernels:
         at least four 64-wide k blocks each, three per SM where that still leaves sixteen (measured:
         cutting finer costs more in the merge than it gains in bandwidth)."""
         num_kb = (K + 63) // 64
-        two, three = 296 // max(n_tiles, 1), 444 // max(n_tiles, 1)
+        two, three = 2 * self.num_sms // max(n_tiles, 1), 3 * self.num_sms // max(n_tiles, 1)
         if three > two and num_kb // three >= 16:
             return min(three, 32)
         return max(1, min(two, num_kb // 4, 32))
@@ -532,7 +545,7 @@ class CudaKernels:
             _ptr(out), c_int(1 if out_dtype == torch.float32 else 0), c_int(M), c_int(N), c_int(K),
             c_int(1 if gated else 0), c_int(splits), c_int(1 if cluster else 0), _ptr(scratch),
             _ptr(self._decode_counters if splits > 1 else None),
-            _ptr(status), *self._norm_args(norm, K), self._stream())
+            _ptr(status if status is not None else self._status), *self._norm_args(norm, K), self._stream())
         _check("gemm_tcgen05_decode", st)
         return out
 
@@ -541,10 +554,12 @@ class CudaKernels:
         """The q/k/v product of the step's rows, then bias, rotation of q and k and the write of k
         and v into the rows' cache slots; returns q [T, num_heads * head_dim].  For few bfloat16
         rows this is one kernel (the decode GEMM's rotary epilogue); otherwise the product and
-        `rope_cache_write` run one after the other, with the same result.
+        `rope_cache_write` run one after the other, with the same result.  Tables narrower than
+        head_dim / 2 (a rotation of the leading part of each head only) always take the latter.
         norm = (gamma, eps): x is normalised first (RMSNorm), inside the fused kernel where that runs."""
         M, K = x.shape
-        if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < M <= self.FUSED_QKV_MAX_ROWS
+        full_rotation = cos is None or cos.shape[1] == head_dim // 2      # the rotary epilogues rotate whole heads
+        if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < M <= self.FUSED_QKV_MAX_ROWS and full_rotation
                 and 128 % head_dim == 0 and K % 8 == 0 and weight.shape[0] == (num_heads + 2 * num_kv_heads) * head_dim):
             if norm is not None and not self._can_fuse_norm(x, norm):
                 x, norm = self.rmsnorm(x, *norm), None
@@ -552,14 +567,15 @@ class CudaKernels:
                                         num_heads, num_kv_heads, head_dim, norm=norm)
         if norm is not None:
             x = self.rmsnorm(x, *norm)
-        if (self.FUSED_QKV_PREFILL and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+        if (self.FUSED_QKV_PREFILL and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and full_rotation
                 and self._tcgen05_fills(M, weight.shape[0]) and head_dim in (64, 128, 256) and K % 8 == 0
                 and weight.shape[0] == (num_heads + 2 * num_kv_heads) * head_dim):
             return self._qkv_rope_tcgen05(x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
                                           num_heads, num_kv_heads, head_dim)
-        qkv = self.linear(x, weight)
+        # the product leaves its kernel in float and is rounded once, after bias and rotation
+        qkv = self.linear(x, weight, out_dtype=torch.float32)
         return self.rope_cache_write(qkv, bias, positions, cos, sin, slot_mapping, cache_layer,
-                                     num_heads, num_kv_heads, head_dim)
+                                     num_heads, num_kv_heads, head_dim, out_dtype=x.dtype)
 
     def _qkv_rope_tcgen05(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
                           num_heads, num_kv_heads, head_dim, status=None, max_ctas=0, pair=None):
@@ -584,7 +600,7 @@ class CudaKernels:
             _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0),
             _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(cache_layer), _ptr(q), c_int(M), c_int(K),
             c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]),
-            c_int(cos.shape[0] if cos is not None else 1), _ptr(status), c_int(max_ctas), self._stream())
+            c_int(cos.shape[0] if cos is not None else 1), _ptr(status if status is not None else self._status), c_int(max_ctas), self._stream())
         _check("gemm_tcgen05_qkv_rope", st)
         return q
 
@@ -625,7 +641,7 @@ class CudaKernels:
             _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(cache_layer), _ptr(q), c_int(M), c_int(K),
             c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]),
             c_int(cos.shape[0] if cos is not None else 1), c_int(splits), c_int(1 if cluster else 0), _ptr(scratch),
-            _ptr(self._decode_counters if splits > 1 else None), _ptr(status), *self._norm_args(norm, K), self._stream())
+            _ptr(self._decode_counters if splits > 1 else None), _ptr(status if status is not None else self._status), *self._norm_args(norm, K), self._stream())
         _check("gemm_decode_qkv_rope", st)
         return q
 
@@ -641,9 +657,6 @@ class CudaKernels:
             return self.linear_decode(x, weight, gated=True, norm=norm)
         if norm is not None:
             x = self.rmsnorm(x, *norm)
-        if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < M <= self.SKINNY_MAX_ROWS \
-                and K % 8 == 0 and weight.shape[0] % 2 == 0:
-            return self.linear_skinny(x, weight, gated=True)
         if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and self._tcgen05_fills(M, weight.shape[0], True) \
                 and K % 8 == 0 and weight.shape[0] % 2 == 0:
             return self.linear_tcgen05(x, weight, gated=True)

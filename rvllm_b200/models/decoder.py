@@ -15,34 +15,36 @@ import torch
 
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
 from ..errors import ConfigError
-from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, KvCacheNeed, StateNeed,
-                          TensorSpec)
+from ..parts.base import BLOCKS, FAMILIES, HOOKS, NORMS, POSITION_ENCODINGS, TensorSpec
 from ..parts.linear import Linear
 
 
 class _Layer:
     def __init__(self, spec: LayerSpec, position_encodings: Dict[str, object]):
-        mp = dict(spec.mixer.params)
-        if "position" in mp:
-            key = mp["position"]
-            if key is not None and key not in position_encodings:
-                raise ConfigError(f"layer {spec.prefix!r} names position encoding {key!r}, which the model does not define")
-            mp["position"] = position_encodings.get(key) if key is not None else None
         self.spec = spec
-        self.mixer = MIXERS.build(spec.mixer.kind, **mp)
-        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward.kind, **spec.feed_forward.params)
-        self.mixer_norm = NORMS.build(spec.mixer_norm.kind, **spec.mixer_norm.params)
-        self.feed_forward_norm = NORMS.build(spec.feed_forward_norm.kind, **spec.feed_forward_norm.params)
-        self.block = BLOCKS.build(spec.block.kind, mixer=self.mixer, feed_forward=self.feed_forward,
-                                  mixer_norm=self.mixer_norm, feed_forward_norm=self.feed_forward_norm,
-                                  **spec.block.params)
+        self.parts: Dict[str, object] = {}
+        self.mixer = None                  # the part that owns the run entry's cache slot, if the layer has one
+        for role, ps in spec.parts.items():
+            params = dict(ps.params)
+            if ps.family == "mixer" and "position" in params:
+                key = params["position"]
+                if key is not None and key not in position_encodings:
+                    raise ConfigError(f"layer {spec.prefix!r} names position encoding {key!r}, which the model does not define")
+                params["position"] = position_encodings.get(key) if key is not None else None
+            if ps.family not in FAMILIES:
+                raise ConfigError(f"layer {spec.prefix!r}: part {role!r} has family {ps.family!r} (known: {', '.join(FAMILIES)})")
+            part = FAMILIES[ps.family].build(ps.kind, **params)
+            self.parts[role] = part
+            if ps.family == "mixer":
+                self.mixer = part
+        self.block = BLOCKS.build(spec.block.kind, parts=self.parts, **spec.block.params)
+
+    def cache_need(self):
+        return self.mixer.cache_need() if self.mixer is not None else None
 
     def named_parts(self):
         n = self.spec.names
-        return [(self.spec.prefix + n.get("mixer", "mixer."), self.mixer),
-                (self.spec.prefix + n.get("feed_forward", "feed_forward."), self.feed_forward),
-                (self.spec.prefix + n.get("mixer_norm", "mixer_norm."), self.mixer_norm),
-                (self.spec.prefix + n.get("feed_forward_norm", "feed_forward_norm."), self.feed_forward_norm)]
+        return [(self.spec.prefix + n.get(role, role + "."), part) for role, part in self.parts.items()]
 
 
 class DecoderModel:
@@ -55,6 +57,8 @@ class DecoderModel:
                                    for k, p in spec.position_encodings.items()}
         self.layers: List[_Layer] = [_Layer(ls, self.position_encodings) for ls in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm.kind, **spec.final_norm.params)
+        self.embedding_hooks = [HOOKS.build(h.kind, **h.params) for h in spec.embedding_hooks]
+        self.logit_hooks = [HOOKS.build(h.kind, **h.params) for h in spec.logit_hooks]
         self.embedding: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
         self.dtype = None
@@ -68,7 +72,16 @@ class DecoderModel:
         out.append((self.spec.final_norm_prefix, self.final_norm))
         for key, pe in self.position_encodings.items():
             out.append((f"position.{key}.", pe))
+        out.extend((f"hooks.embedding.{i}.", h) for i, h in enumerate(self.embedding_hooks))
+        out.extend((f"hooks.logits.{i}.", h) for i, h in enumerate(self.logit_hooks))
         return out
+
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step of this model may be captured in a CUDA graph: every part (and
+        block arrangement) allows it."""
+        things = [part for _, part in self.named_parts()] + [layer.block for layer in self.layers]
+        return all(getattr(t, "graph_safe", True) for t in things)
 
     def expected_tensors(self) -> Dict[str, TensorSpec]:
         s = self.spec
@@ -95,12 +108,12 @@ class DecoderModel:
         """cache slot -> KvCacheNeed | StateNeed | None, taken from the entry that writes it."""
         needs = {}
         for e in self.spec.run_order:
-            need = self.layers[e.layer].mixer.cache_need()
+            need = self.layers[e.layer].cache_need()
             if e.writes_cache:
                 needs[e.cache] = need
         for e in self.spec.run_order:
             if not e.writes_cache:
-                need = self.layers[e.layer].mixer.cache_need()
+                need = self.layers[e.layer].cache_need()
                 if need != needs.get(e.cache):
                     raise ConfigError(f"layer {e.layer} reads cache slot {e.cache} but needs {need}, "
                                       f"while its writer provides {needs.get(e.cache)}")
@@ -113,6 +126,8 @@ class DecoderModel:
             x = x.to(self.dtype)       # a table the checkpoint keeps in 32 bits; activations have the engine's type
         for pe in self.position_encodings.values():
             x = pe.on_embeddings(x, ctx)
+        for hook in self.embedding_hooks:
+            x = hook(x, ctx)
         for e in self.spec.run_order:
             x = self.layers[e.layer].block(x, ctx, caches.view(e.cache), e.writes_cache)
         return x
@@ -121,8 +136,12 @@ class DecoderModel:
         """float32 logits [R, vocab] at the rows `ctx.logit_rows` of the step."""
         rows = ctx.kernels.gather_rows(hidden, ctx.logit_rows)
         if hasattr(self.final_norm, "as_rms"):       # the LM head's product applies the norm itself for few rows
-            return ctx.kernels.linear(rows, self.lm_head, None, None, torch.float32, norm=self.final_norm.as_rms())
-        return ctx.kernels.linear(self.final_norm(rows, ctx), self.lm_head, None, None, torch.float32)
+            logits = ctx.kernels.linear(rows, self.lm_head, None, None, torch.float32, norm=self.final_norm.as_rms())
+        else:
+            logits = ctx.kernels.linear(self.final_norm(rows, ctx), self.lm_head, None, None, torch.float32)
+        for hook in self.logit_hooks:
+            logits = hook(logits, ctx)
+        return logits
 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:

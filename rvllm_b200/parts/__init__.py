@@ -1,5 +1,5 @@
 from .base import (Part, TensorSpec, KvCacheNeed, StateNeed, Registry, MIXERS, FEED_FORWARDS, NORMS,
-                   POSITION_ENCODINGS, BLOCKS)
+                   POSITION_ENCODINGS, BLOCKS, HOOKS, FAMILIES)
 from .linear import Linear
 from .norm import RMSNorm
 from .rope import RotaryEncoding, inverse_frequencies

@@ -10,6 +10,8 @@ from __future__ import annotations
 
 from typing import Optional
 
+import torch
+
 from .base import MIXERS, KvCacheNeed, Part
 from .linear import Linear
 
@@ -56,10 +58,10 @@ class PagedAttention(Part):
         else:                             # a layer that reads another layer's cache needs its queries only
             if input_norm is not None:
                 x = k.rmsnorm(x, *input_norm)
-            q_rows = self.qkv(x, ctx, with_bias=False, rows=self.q_dim)
+            q_rows = self.qkv(x, ctx, with_bias=False, rows=self.q_dim, out_dtype=torch.float32)   # rounded once, after the rotation
             q = k.rope_cache_write(q_rows, bias[:self.q_dim] if bias is not None else None, ctx.positions, cos, sin,
                                    meta.slot_mapping, cache.kv, self.num_heads, self.num_kv_heads, self.head_dim,
-                                   write_kv=False)
+                                   write_kv=False, out_dtype=x.dtype)
         o = k.paged_attention(q, cache.kv, meta, self.num_heads, self.num_kv_heads, self.head_dim,
                               self.scale, self.window)
         return self.out(o, ctx, residual=residual)

@@ -12,7 +12,13 @@ tensors it owns (`tensor_specs`, names relative to its prefix) and receives them
   `__call__(x, ctx, cache, residual, write_cache)` -> residual + mixed x.  `cache` is the
   `CacheView` of the run entry's cache slot.
 * feed-forward: `__call__(x, ctx, residual)` -> residual + f(x).
-* block: built from the four parts of a layer; `__call__(x, ctx, cache, write_cache)` -> x.
+* block: built from `parts`, the layer's built parts by role name (which roles it needs is the
+  block's own matter), plus its parameters; `__call__(x, ctx, cache, write_cache)` -> x.
+* hook: `__call__(x, ctx)` -> x, on the embedded tokens or on the float32 logits.
+
+A part whose step cannot be recorded into a CUDA graph (it reads device values on the host, or
+launches a number of kernels that depends on the data) sets `graph_safe = False`; a model with
+such a part runs its decode steps eagerly.
 
 `ctx` is the step's `StepContext` (tokens' positions, the attention metadata of each cache
 group, state slots, the kernel library).
@@ -47,6 +53,8 @@ class StateNeed:
 
 
 class Part:
+    graph_safe = True      # whether the part's work in a decode step may be captured in a CUDA graph
+
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         return {}
 
@@ -80,3 +88,5 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block arrangement")
+HOOKS = Registry("hook")
+FAMILIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS}

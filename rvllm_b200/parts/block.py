@@ -14,9 +14,14 @@ from .base import BLOCKS
 
 
 class PreNormResidualBlock:
-    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm):
-        self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+    ROLES = ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")
+
+    def __init__(self, parts):
+        from ..errors import ConfigError
+        if sorted(parts) != sorted(self.ROLES):
+            raise ConfigError(f"the pre-norm residual block arranges the parts {', '.join(self.ROLES)}; got {', '.join(sorted(parts))}")
+        self.mixer, self.feed_forward = parts["mixer"], parts["feed_forward"]
+        self.mixer_norm, self.feed_forward_norm = parts["mixer_norm"], parts["feed_forward_norm"]
 
     @staticmethod
     def _handed_over(part, norm):

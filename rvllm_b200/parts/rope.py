@@ -39,15 +39,23 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[dict]) ->
 
 
 class RotaryEncoding(Part):
-    def __init__(self, head_dim: int, theta: float, scaling: Optional[dict] = None):
+    """`rotary_dim` (default: head_dim) is the number of leading elements of a head that are
+    rotated, in pairs (i, i + rotary_dim/2) with frequencies theta^(-2i/rotary_dim); the rest of
+    the head passes through.  The tables then have rotary_dim/2 columns, and the kernels that
+    rotate in a GEMM's epilogue (whole heads only) leave such a model to the rotary kernel."""
+
+    def __init__(self, head_dim: int, theta: float, scaling: Optional[dict] = None, rotary_dim: Optional[int] = None):
         if head_dim % 2:
             raise ConfigError(f"rotary encoding needs an even head_dim, got {head_dim}")
-        self.head_dim, self.theta, self.scaling = head_dim, theta, scaling
-        self.inv_freq = inverse_frequencies(head_dim, theta, scaling)
+        rotary_dim = head_dim if rotary_dim is None else rotary_dim
+        if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
+            raise ConfigError(f"rotary_dim must be even and in (0, head_dim = {head_dim}], got {rotary_dim}")
+        self.head_dim, self.theta, self.scaling, self.rotary_dim = head_dim, theta, scaling, rotary_dim
+        self.inv_freq = inverse_frequencies(rotary_dim, theta, scaling)
         self.cos = self.sin = None
 
     def prepare(self, max_len: int, device) -> None:
-        cos = torch.empty((max_len, self.head_dim // 2), dtype=torch.float32)
+        cos = torch.empty((max_len, self.rotary_dim // 2), dtype=torch.float32)
         sin = torch.empty_like(cos)
         inv = self.inv_freq.to(torch.float64)
         step = 16384

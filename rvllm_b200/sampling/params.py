@@ -5,6 +5,15 @@ Fields as the reference's `SamplingParams {temperature, top_k, top_p, seed}`
 `stop_token_ids` and `ignore_eos` are what its evaluation loop takes from the environment
 (RVLLM_MAX_TOKENS default 256, RVLLM_EOS; v3/crates/rvllm-bench/src/bin/rvllm_eval.rs:83-86,
 624-629).
+
+What the filters keep (the reference defines `top_k` and `top_p` as fields only and samples
+greedily, so the rule is this project's): both act on softmax(logits / temperature) of the whole
+vocabulary.  `top_k` keeps the k most likely tokens, `top_p` the smallest set of most likely tokens
+whose probability reaches top_p, in both cases with every token as likely as the last kept one.
+With both set, a token is kept if BOTH keep it: the top-p mass is counted on the whole
+distribution, not on the one renormalised after top-k (libraries that apply the filters one after
+the other keep fewer tokens when k cuts off much mass).  The draw is then made from the kept
+tokens, renormalised, by inverse CDF in vocabulary order.
 """
 from __future__ import annotations
 

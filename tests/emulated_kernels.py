@@ -33,26 +33,27 @@ class EmulatedKernels:
         return (g / (1.0 + torch.exp(-g)) * u).to(gate_up.dtype)
 
     def rope_cache_write(self, qkv, bias, positions, cos, sin, slot_mapping, cache_layer,
-                         num_heads, num_kv_heads, head_dim, write_kv=True):
+                         num_heads, num_kv_heads, head_dim, write_kv=True, out_dtype=None):
+        out_dtype = out_dtype or qkv.dtype
         T = qkv.shape[0]
         x = qkv.float()
         if bias is not None:
             x = x + bias.float()
-        half = head_dim // 2
         pos = positions.long()
 
-        def rot(t):   # [T, heads, hd]
+        def rot(t):   # [T, heads, hd]; the tables' width says how much of a head is rotated
             if cos is None:
                 return t
+            half = cos.shape[1]
             c, s = cos[pos][:, None, :], sin[pos][:, None, :]
-            a, b = t[..., :half], t[..., half:]
-            return torch.cat([a * c - b * s, a * s + b * c], -1)
+            a, b, rest = t[..., :half], t[..., half:2 * half], t[..., 2 * half:]
+            return torch.cat([a * c - b * s, a * s + b * c, rest], -1)
 
         q_dim, kv_dim = num_heads * head_dim, num_kv_heads * head_dim
         q = rot(x[:, :q_dim].view(T, num_heads, head_dim))
         if write_kv:
-            k = rot(x[:, q_dim:q_dim + kv_dim].view(T, num_kv_heads, head_dim)).to(qkv.dtype)
-            v = x[:, q_dim + kv_dim:].view(T, num_kv_heads, head_dim).to(qkv.dtype)
+            k = rot(x[:, q_dim:q_dim + kv_dim].view(T, num_kv_heads, head_dim)).to(out_dtype)
+            v = x[:, q_dim + kv_dim:].view(T, num_kv_heads, head_dim).to(out_dtype)
             ps = cache_layer.shape[3]
             for t in range(T):
                 slot = int(slot_mapping[t])
@@ -60,7 +61,7 @@ class EmulatedKernels:
                     continue
                 cache_layer[slot // ps, 0, :, slot % ps, :] = k[t]
                 cache_layer[slot // ps, 1, :, slot % ps, :] = v[t]
-        return q.reshape(T, q_dim).to(qkv.dtype)
+        return q.reshape(T, q_dim).to(out_dtype)
 
     def qkv_rope_cache_write(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
                              num_heads, num_kv_heads, head_dim, norm=None):

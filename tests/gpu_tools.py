@@ -10,11 +10,13 @@ from rvllm_b200.kernels import AttentionMeta
 
 
 def paged_setup(k_seqs: Sequence[torch.Tensor], v_seqs: Sequence[torch.Tensor], q_lens: Sequence[int],
-                page_size: int, dtype, seed: int = 0, spare_pages: int = 3):
+                page_size: int, dtype, seed: int = 0, spare_pages: int = 3, window: Optional[int] = None):
     """Scatter whole-sequence keys/values [ctx, nkv, hd] into shuffled pages.
 
     Returns (cache layer [pages, 2, nkv, page, hd], AttentionMeta).  The last q_len tokens of every
-    sequence are the step's tokens."""
+    sequence are the step's tokens.  With `window`, the pages that lie wholly below the window of a
+    sequence's first query have been given back, as the cache manager does while a request runs:
+    their block-table entries are -1 and their keys are nowhere in the cache."""
     dev = "cuda"
     B = len(k_seqs)
     nkv, hd = k_seqs[0].shape[1:]
@@ -28,7 +30,10 @@ def paged_setup(k_seqs: Sequence[torch.Tensor], v_seqs: Sequence[torch.Tensor], 
     table = torch.full((B, MB), -1, dtype=torch.int32)
     nxt = 0
     for b in range(B):
+        first_seen = (ctx_lens[b] - q_lens[b]) - window + 1 if window else 0      # first key the first query sees
         for blk in range(blocks[b]):
+            if (blk + 1) * page_size <= first_seen:
+                continue                                                           # given back: the entry stays -1
             page = perm[nxt]
             nxt += 1
             table[b, blk] = page

@@ -1,7 +1,8 @@
 """Plain, slow implementation of the Llama / Qwen2 dense decoder, used as the oracle.
 
 Whole sequences only, no cache, no batching, one function per part, torch used
-purely as an array library on the CPU.  It shares no code with the engine under
+purely as an array library (float64; on the CPU, or, for the models of real layer widths whose
+float64 products would take minutes there, on the device the weights were read to).  It shares no code with the engine under
 ``rvllm_b200``: it reads config.json with ``json`` and model.safetensors with the
 ``safetensors`` package, and restates every formula from the reference's files
 (paths are relative to the reference project's root).
@@ -31,14 +32,14 @@ DEFAULT_DTYPE = torch.float64
 
 # --------------------------------------------------------------------------- model folder
 
-def read_model_folder(path: str, dtype=DEFAULT_DTYPE):
-    """config.json as a dict and every tensor of model.safetensors converted to `dtype`."""
+def read_model_folder(path: str, dtype=DEFAULT_DTYPE, device="cpu"):
+    """config.json as a dict and every tensor of model.safetensors converted to `dtype` on `device`."""
     from safetensors.torch import load_file
 
     with open(os.path.join(path, "config.json")) as f:
         cfg = json.load(f)
     raw = load_file(os.path.join(path, "model.safetensors"))
-    weights = {k: v.to(dtype) for k, v in raw.items()}
+    weights = {k: v.to(device=device, dtype=dtype) for k, v in raw.items()}
     return cfg, weights
 
 
@@ -52,7 +53,7 @@ def embedding(ids: Sequence[int], table: torch.Tensor) -> torch.Tensor:
     """
     ids = list(ids)
     assert all(0 <= i < table.shape[0] for i in ids), "token id out of vocabulary"
-    return table[torch.tensor(ids, dtype=torch.long)]
+    return table[torch.tensor(ids, dtype=torch.long, device=table.device)]
 
 
 def rms_norm(x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
@@ -116,10 +117,10 @@ def apply_rope(x: torch.Tensor, positions: Sequence[int], inv_freq: torch.Tensor
     rvllm-fused/src/reference.rs:177-203.
     """
     half = x.shape[-1] // 2
-    pos = torch.tensor(list(positions), dtype=torch.float64)
+    pos = torch.tensor(list(positions), dtype=torch.float64, device=x.device)
     # the engine keeps inv_freq as float32; use the same rounded frequencies so that the
     # comparison measures the rotation, not a difference in the table's last bit
-    ang = pos[:, None] * inv_freq.to(torch.float32).to(torch.float64)[None, :]
+    ang = pos[:, None] * inv_freq.to(torch.float32).to(device=x.device, dtype=torch.float64)[None, :]
     cos = torch.cos(ang).to(x.dtype)[:, None, :]
     sin = torch.sin(ang).to(x.dtype)[:, None, :]
     a, b = x[..., :half], x[..., half:]
@@ -127,7 +128,7 @@ def apply_rope(x: torch.Tensor, positions: Sequence[int], inv_freq: torch.Tensor
 
 
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
-                     window: Optional[int] = None) -> torch.Tensor:
+                     window: Optional[int] = None, store=None) -> torch.Tensor:
     """GQA attention over one whole sequence.  q [T, nh, hd], k/v [T, nkv, hd].
 
     kv_head = h * nkv / nh; score = (q . k) * scale; query t sees keys j <= t and,
@@ -139,7 +140,7 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     T, nh, hd = q.shape
     nkv = k.shape[1]
     out = torch.zeros_like(q)
-    t_idx = torch.arange(T)
+    t_idx = torch.arange(T, device=q.device)
     allowed = t_idx[None, :] <= t_idx[:, None]
     if window is not None:
         allowed = allowed & (t_idx[None, :] > t_idx[:, None] - window)
@@ -148,6 +149,11 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
         s = (q[:, h, :] @ k[:, g, :].t()) * scale
         s = s.masked_fill(~allowed, float("-inf"))
         p = torch.softmax(s, dim=-1)
+        if store is not None:
+            # a tensor-core attention multiplies probabilities as 16-bit operands: exp(s - max) is
+            # rounded (the row's sum is not), which is the same as rounding p up to the common factor
+            e = torch.exp(s - s.amax(dim=-1, keepdim=True))
+            p = store(e) / e.sum(dim=-1, keepdim=True)
         out[:, h, :] = p @ v[:, g, :]
     return out
 
@@ -194,10 +200,23 @@ def has_qkv_bias(cfg: dict) -> bool:
     return bool(cfg.get("attention_bias", False))
 
 
+def has_out_bias(cfg: dict) -> bool:
+    """A Llama checkpoint with `attention_bias` carries a bias on o_proj as well; Qwen2 never does."""
+    return cfg["architectures"][0] == "LlamaForCausalLM" and bool(cfg.get("attention_bias", False))
+
+
 # --------------------------------------------------------------------------- whole model
 
-def decoder_layer(x, positions, cfg, w: Dict[str, torch.Tensor], prefix: str, inv_freq, window):
-    """x + attn(norm(x)), then + mlp(norm(.)) — v3/crates/rvllm-runtime/src/layer_exec.rs:162-529."""
+def _keep(t):
+    return t
+
+
+def decoder_layer(x, positions, cfg, w: Dict[str, torch.Tensor], prefix: str, inv_freq, window, store=_keep):
+    """x + attn(norm(x)), then + mlp(norm(.)) — v3/crates/rvllm-runtime/src/layer_exec.rs:162-529.
+
+    `store` is applied to every tensor that an engine would write to memory between two kernels
+    (default: nothing); with a rounding to bfloat16 it shows how much error that precision alone
+    causes, whatever the kernels (see `forward`)."""
     nh = cfg["num_attention_heads"]
     nkv = cfg.get("num_key_value_heads", nh)
     hd = cfg.get("head_dim") or cfg["hidden_size"] // nh
@@ -205,27 +224,38 @@ def decoder_layer(x, positions, cfg, w: Dict[str, torch.Tensor], prefix: str, in
     bias = has_qkv_bias(cfg)
     T = x.shape[0]
 
-    a = rms_norm(x, w[prefix + "input_layernorm.weight"], eps)
+    a = store(rms_norm(x, w[prefix + "input_layernorm.weight"], eps))
     sa = prefix + "self_attn."
     q = linear(a, w[sa + "q_proj.weight"], w[sa + "q_proj.bias"] if bias else None).view(T, nh, hd)
     k = linear(a, w[sa + "k_proj.weight"], w[sa + "k_proj.bias"] if bias else None).view(T, nkv, hd)
-    v = linear(a, w[sa + "v_proj.weight"], w[sa + "v_proj.bias"] if bias else None).view(T, nkv, hd)
-    q = apply_rope(q, positions, inv_freq)
-    k = apply_rope(k, positions, inv_freq)
-    o = causal_attention(q, k, v, 1.0 / math.sqrt(hd), window).reshape(T, nh * hd)
-    x = x + linear(o, w[sa + "o_proj.weight"])
+    v = store(linear(a, w[sa + "v_proj.weight"], w[sa + "v_proj.bias"] if bias else None).view(T, nkv, hd))
+    q = store(apply_rope(q, positions, inv_freq))
+    k = store(apply_rope(k, positions, inv_freq))
+    o = store(causal_attention(q, k, v, 1.0 / math.sqrt(hd), window, None if store is _keep else store).reshape(T, nh * hd))
+    x = store(x + linear(o, w[sa + "o_proj.weight"], w[sa + "o_proj.bias"] if has_out_bias(cfg) else None))
 
-    m = rms_norm(x, w[prefix + "post_attention_layernorm.weight"], eps)
+    m = store(rms_norm(x, w[prefix + "post_attention_layernorm.weight"], eps))
     mp = prefix + "mlp."
-    x = x + gated_mlp(m, w[mp + "gate_proj.weight"], w[mp + "up_proj.weight"], w[mp + "down_proj.weight"])
-    return x
+    if store is _keep:
+        return x + gated_mlp(m, w[mp + "gate_proj.weight"], w[mp + "up_proj.weight"], w[mp + "down_proj.weight"])
+    g, u = linear(m, w[mp + "gate_proj.weight"]), linear(m, w[mp + "up_proj.weight"])
+    h = store(g / (1.0 + torch.exp(-g)) * u)
+    return store(x + linear(h, w[mp + "down_proj.weight"]))
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], token_ids: Sequence[int]) -> torch.Tensor:
+def round_to_bfloat16(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.bfloat16).to(t.dtype)
+
+
+def forward(cfg: dict, w: Dict[str, torch.Tensor], token_ids: Sequence[int], store=_keep) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence starting at position 0.
 
     Skeleton: v3/crates/rvllm-runtime/src/bring_up.rs:535-669; the LM head is the
     embedding matrix when `tie_word_embeddings` (rvllm-loader/src/load.rs:310-311,351-363).
+
+    With `store=round_to_bfloat16` every tensor that passes between two parts is rounded to
+    bfloat16 while all arithmetic stays float64: the difference to the plain logits is the error
+    that storing activations in that precision causes by itself, the yardstick for a bfloat16 engine.
     """
     nh = cfg["num_attention_heads"]
     hd = cfg.get("head_dim") or cfg["hidden_size"] // nh
@@ -234,8 +264,8 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], token_ids: Sequence[int]) -> 
     positions = list(range(len(token_ids)))
     x = embedding(token_ids, w["model.embed_tokens.weight"])
     for l in range(cfg["num_hidden_layers"]):
-        x = decoder_layer(x, positions, cfg, w, f"model.layers.{l}.", inv_freq, windows[l])
-    y = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+        x = decoder_layer(x, positions, cfg, w, f"model.layers.{l}.", inv_freq, windows[l], store)
+    y = store(rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]))
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return linear(y, head)
 

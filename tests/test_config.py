@@ -121,11 +121,11 @@ def test_config_json_round_trip(tmp_path):
 
 def test_spec_carries_the_sizes_layer_by_layer():
     spec = config_from_dict(tiny_configs.get("tiny_qwen2")).to_spec()
-    assert [l.mixer.params["window"] for l in spec.layers] == [None, 40, 40]
-    assert all(l.mixer.params["qkv_bias"] for l in spec.layers)
+    assert [l.parts["mixer"].params["window"] for l in spec.layers] == [None, 40, 40]
+    assert all(l.parts["mixer"].params["qkv_bias"] for l in spec.layers)
     assert spec.lm_head_name is None and spec.layers[1].prefix == "model.layers.1."
     assert [(e.layer, e.cache) for e in spec.run_order] == [(0, 0), (1, 1), (2, 2)]
-    assert spec.layers[0].mixer_norm.params == {"size": 96, "eps": 1e-6}
+    assert spec.layers[0].parts["mixer_norm"].params == {"size": 96, "eps": 1e-6}
 
 
 def test_registry_accepts_new_architectures():
@@ -154,3 +154,18 @@ def test_engine_options_are_validated_together():
     assert len(e.value.reasons) >= 5
     ok = EngineConfig(dtype="bf16", max_model_len=None).validated(512)
     assert ok.dtype == "bfloat16" and ok.max_model_len == 512
+
+
+def test_llama_attention_bias_reaches_the_output_projection_and_mlp_bias_is_refused():
+    from rvllm_b200.models.decoder import expected_tensors
+    d = tiny_configs.get("baseline0")
+    d["attention_bias"] = True
+    names = expected_tensors(config_from_dict(d).to_spec())
+    for proj in ("q_proj", "k_proj", "v_proj", "o_proj"):
+        assert f"model.layers.1.self_attn.{proj}.bias" in names
+    assert not any("mlp" in n and n.endswith(".bias") for n in names)
+    q = expected_tensors(config_from_dict(tiny_configs.get("baseline1")).to_spec())
+    assert "model.layers.0.self_attn.q_proj.bias" in q and "model.layers.0.self_attn.o_proj.bias" not in q
+    d["mlp_bias"] = True
+    with pytest.raises(ConfigError, match="mlp_bias"):
+        config_from_dict(d)

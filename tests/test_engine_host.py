@@ -56,6 +56,8 @@ def test_replay_matches_plain_under_every_cut(emulated, tmp_path, name, schedule
         assert max(len(s["entries"]) for s in trace.steps) == 4
         assert any(len({len(e["tokens"]) == 1 for e in s["entries"]}) == 2 for s in trace.steps), \
             "portions beside single tokens"
+        assert trace.preemptions == 1 and any(label.endswith("#0") for rows in trace.rows.values() for label, _ in rows), \
+            "one live request is ended and fed again from position 0"
     engine = trace_mod.build_engine(folder, "float32", trace.max_tokens, block_size=8, device="cpu")
     pages = engine.cache.num_pages
     assert pages * 8 == trace.max_tokens                       # so few pages that they are used again

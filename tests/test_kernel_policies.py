@@ -65,15 +65,15 @@ def test_the_prefill_gemm_and_its_build_are_chosen_by_rows():
 
 def test_key_splits_of_decode_attention_follow_the_wave_model():
     meta = lambda seqs, ctx: SimpleNamespace(num_seqs=seqs, max_ctx_len=ctx)
-    assert CudaKernels.decode_splits(meta(8, 2088), 32, 8) == 6           # 384 CTAs: one wave of 444
-    assert CudaKernels.decode_splits(meta(1, 2048), 32, 8) == 16          # two tiles per CTA at least
+    assert _k().decode_splits(meta(8, 2088), 32, 8) == 6           # 384 CTAs: one wave of 444
+    assert _k().decode_splits(meta(1, 2048), 32, 8) == 16          # two tiles per CTA at least
     for seqs in (1, 2, 3, 5, 8, 13, 24, 31):                              # never a split of fewer than two tiles, never more than 64
         for ctx in (1, 64, 65, 300, 1000, 4096, 100000):
-            s = CudaKernels.decode_splits(meta(seqs, ctx), 32, 8)
+            s = _k().decode_splits(meta(seqs, ctx), 32, 8)
             tiles = (ctx + 63) // 64
             assert 1 <= s <= 64 and (s == 1 or -(-tiles // s) >= 2)
-    assert CudaKernels.decode_splits(meta(1, 32768), 32, 8) >= 40         # a long context alone still fills the GPU
-    assert CudaKernels.decode_splits(meta(4, 64), 32, 8) == 1             # one tile: nothing to split
+    assert _k().decode_splits(meta(1, 32768), 32, 8) >= 40         # a long context alone still fills the GPU
+    assert _k().decode_splits(meta(4, 64), 32, 8) == 1             # one tile: nothing to split
 
 
 def test_the_build_check_compiles_both_builds_of_the_prefill_gemm():

@@ -31,6 +31,7 @@ ODD = {
     "hd128_group8_window": cfg("Qwen2ForCausalLM", 256, 3, 8, 1, 128, 512, 1000, use_sliding_window=True, sliding_window=48,
                                layer_types=["sliding_attention", "full_attention", "sliding_attention"]),
     "hd16_group20": cfg("LlamaForCausalLM", 96, 2, 20, 1, 16, 172, 261),
+    "llama_with_biases": cfg("LlamaForCausalLM", 128, 2, 4, 2, 32, 172, 261, attention_bias=True),   # q, k, v and o
     "width100_group5": cfg("LlamaForCausalLM", 100, 2, 10, 2, 112, 172, 333, rope_theta=500000.0),
     "hd64_many_heads": cfg("LlamaForCausalLM", 192, 2, 12, 4, 64, 344, 640,
                            rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,

@@ -123,7 +123,7 @@ def test_block_equals_plain_decoder_layer(dtype):
                        qkv_bias=True, position=rope)
     mlp = FEED_FORWARDS.build("gated_mlp", hidden_size=56, intermediate_size=100)
     n1, n2 = NORMS.build("rmsnorm", size=56, eps=2e-5), NORMS.build("rmsnorm", size=56, eps=2e-5)
-    block = BLOCKS.build("prenorm_residual", mixer=att, feed_forward=mlp, mixer_norm=n1, feed_forward_norm=n2)
+    block = BLOCKS.build("prenorm_residual", parts={"mixer": att, "feed_forward": mlp, "mixer_norm": n1, "feed_forward_norm": n2})
     w = {}
     for prefix, part, seed in (("self_attn.", att, 1), ("mlp.", mlp, 2), ("input_layernorm.", n1, 3),
                                ("post_attention_layernorm.", n2, 4)):

@@ -10,11 +10,34 @@ from model_tools import model_folder
 
 
 def test_rms_norm_hand_value():
-    # x = [3, 4]: mean square 12.5; the reference's own unit test uses the same numbers
-    # (v3/crates/rvllm-fused/src/reference.rs:248-259)
+    # own numbers: x = [3, 4], gamma = [1, 2]: mean square 12.5
     y = P.rms_norm(torch.tensor([[3.0, 4.0]], dtype=torch.float64), torch.tensor([1.0, 2.0], dtype=torch.float64), 0.0)
     r = 1.0 / math.sqrt(12.5)
     assert torch.allclose(y, torch.tensor([[3 * r, 8 * r]], dtype=torch.float64))
+
+
+def test_the_reference_s_own_literal_vectors():
+    """The only literal numbers the reference's code carries: the unit tests of its float oracle
+    (v3/crates/rvllm-fused/src/reference.rs:247-304), restated here."""
+    # rmsnorm_matches_hand_calc (:247-259): x = [1, 2, 3], gamma = 1, eps = 0 -> x / sqrt(14 / 3)
+    x = torch.tensor([[1.0, 2.0, 3.0]], dtype=torch.float64)
+    y = P.rms_norm(x, torch.ones(3, dtype=torch.float64), 0.0)
+    assert (y - x / math.sqrt(14.0 / 3.0)).abs().max() < 1e-6
+    # argmax_returns_largest (:261-268): rows [0.1, 0.9, 0.3] -> 1 and [0.5, -1.0, 0.8] -> 2
+    assert P.argmax_lowest(torch.tensor([0.1, 0.9, 0.3])) == 1
+    assert P.argmax_lowest(torch.tensor([0.5, -1.0, 0.8])) == 2
+    # embedding_gather_picks_row (:284-293): a 3 x 2 table, ids [2, 0]
+    table = torch.tensor([[10.0, 11.0], [20.0, 21.0], [30.0, 31.0]], dtype=torch.float64)
+    assert P.embedding([2, 0], table).tolist() == [[30.0, 31.0], [10.0, 11.0]]
+    # rope_is_orthogonal_preserving (:295-304): one token at position 0, one head of 4 (cos 1, sin 0)
+    q = torch.tensor([[[1.0, 0.0, 0.0, 1.0]]], dtype=torch.float64)
+    assert P.apply_rope(q, [0], P.rope_inv_freq(4, 10000.0, None)).tolist() == q.tolist()
+    # silu_mul (:270-282 gives gate [0, 1, -1, 2], up 1 and checks only that something is non-zero):
+    # silu(0) = 0, silu(1) = 1 / (1 + e^-1)
+    g = torch.tensor([[0.0, 1.0, -1.0, 2.0]], dtype=torch.float64)
+    eye = torch.eye(4, dtype=torch.float64)
+    h = P.gated_mlp(torch.ones(1, 4, dtype=torch.float64) , torch.diag(g[0]), eye, eye)
+    assert abs(float(h[0, 0])) == 0.0 and abs(float(h[0, 1]) - 1.0 / (1.0 + math.exp(-1.0))) < 1e-12
 
 
 def test_rope_pairs_are_half_split_and_keep_norms():

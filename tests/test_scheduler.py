@@ -210,3 +210,32 @@ def test_two_halves_of_the_accounting_let_a_step_run_ahead():
     assert not s.has_unfinished() and not cache.requests
     cache.check()
     assert cache.num_free_pages() == [64]
+
+
+def test_a_window_only_model_admits_requests_longer_than_its_pool():
+    """Every group of this cache keeps a window of 16 keys: a request holds the window plus one
+    step's portion at most, so a request of 200 tokens fits a pool of 10 pages of 4 - and runs to
+    its end with pages coming back behind the window.  With a group that keeps every key beside it
+    the same request can never fit, and the error names that group."""
+    def run(needs, budget, num_pages=10):
+        cache = CacheManager(needs, num_pages, 4, 2, allocate=False)
+        s = Scheduler(cache, 2, budget, 256, None, True, ())
+        s.add_request(req("long", 150, max_tokens=50))
+        peak = 0
+        while s.has_unfinished():
+            batch = s.schedule()
+            assert not batch.preempted
+            for e in batch.entries:
+                cache.append(e.request.req_id, e.num_tokens)
+            peak = max(peak, num_pages - min(cache.num_free_pages()))
+            for e in batch.entries:
+                cache.release_passed(e.request.req_id)          # as the step function does after the model ran
+            s.update(batch, {e.request.req_id: 7 for e in batch.entries if e.samples})
+            cache.check()
+        return cache, peak
+    cache, peak = run({0: KvCacheNeed(1, 16, 16), 1: KvCacheNeed(1, 16, 16)}, budget=8)
+    assert cache.peak_pages(200, 8) == [7] and peak <= 7 and cache.num_free_pages() == [10]
+    with pytest.raises(KvExhausted, match="never fit.*group 1"):
+        run({0: KvCacheNeed(1, 16, 16), 1: KvCacheNeed(1, 16, None)}, budget=8)
+    with pytest.raises(KvExhausted, match="never fit.*group 0"):
+        run({0: KvCacheNeed(1, 16, 16)}, budget=64)                 # portions of 64 tokens do not fit 10 pages

@@ -1,7 +1,11 @@
 """Toy parts defined here - a mixer with state of its own, a feed-forward with a router, a position
-encoding added to the embeddings - are registered, built into a model through a toy architecture,
-loaded from a random-weights folder and stepped - prompts cut into portions, decoding, several
-live requests, slots used again - without touching the framework's files.
+encoding added to the embeddings, a block arrangement with four norms, hooks on the embeddings and
+on the logits - are registered, built into a model through a toy architecture, loaded from a
+random-weights folder and stepped - prompts cut into portions, decoding, several live requests,
+slots used again - without touching the framework's files.  The attention layers of the toy
+rotate only the first half of each head (a rotary_dim below head_dim), and the state mixer says
+that it cannot be captured in a CUDA graph, so the engine runs the toy's decode steps eagerly
+even with graphs switched on.
 
 The toy mixer keeps a running, decayed sum of projected inputs per request:
     s_t = decay * s_{t-1} + x_t W^T ;  y_t = s_t
@@ -19,12 +23,17 @@ import torch
 
 from rvllm_b200 import config_from_dict, kernels as kernel_pkg, register_architecture, write_random_model
 from rvllm_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry, unregister_architecture
-from rvllm_b200.parts import FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, Part, StateNeed, TensorSpec
+from rvllm_b200.parts import BLOCKS, FEED_FORWARDS, HOOKS, MIXERS, POSITION_ENCODINGS, Part, StateNeed, TensorSpec
 
 DECAY = 0.9
+SOFTCAP = 5.0
+EMBED_SCALE = 1.5
+ROTARY_DIM = 8         # of a head of 16
 
 
 class RunningSumMixer(Part):
+    graph_safe = False     # it reads the state slots on the host: its steps cannot be captured
+
     def __init__(self, hidden_size: int, state_size: int):
         self.hidden_size, self.state_size = hidden_size, state_size
         self.w_in = self.w_out = None
@@ -114,6 +123,39 @@ class LearnedPositions(Part):
         return x + self.weight[ctx.positions.long()].to(x.dtype)
 
 
+class SandwichBlock:
+    """x + norm(mixer(norm(x))), then + norm(feed_forward(norm(.))): four norms, each with a weight
+    of its own, around the two parts."""
+    ROLES = ("mixer", "feed_forward", "pre_mixer_norm", "post_mixer_norm", "pre_ffn_norm", "post_ffn_norm")
+
+    def __init__(self, parts):
+        assert sorted(parts) == sorted(self.ROLES)
+        self.p = parts
+
+    def __call__(self, x, ctx, cache, write_cache=True):
+        p = self.p
+        h = p["mixer"](p["pre_mixer_norm"](x, ctx), ctx, cache, residual=None, write_cache=write_cache)
+        x = x + p["post_mixer_norm"](h, ctx)
+        h = p["feed_forward"](p["pre_ffn_norm"](x, ctx), ctx, residual=None)
+        return x + p["post_ffn_norm"](h, ctx)
+
+
+class Scale(Part):
+    def __init__(self, factor: float):
+        self.factor = factor
+
+    def __call__(self, x, ctx):
+        return x * self.factor
+
+
+class SoftCap(Part):
+    def __init__(self, cap: float):
+        self.cap = cap
+
+    def __call__(self, logits, ctx):
+        return torch.tanh(logits / self.cap) * self.cap
+
+
 @dataclass(frozen=True)
 class ToyConfig:
     hidden_size: int
@@ -142,18 +184,30 @@ class ToyConfig:
             # even layers have the routed feed-forward, odd ones the gated MLP
             ffn = (PartSpec("gated_mlp", {"hidden_size": self.hidden_size, "intermediate_size": 40}) if i % 2 else
                    PartSpec("routed_experts", {"hidden_size": self.hidden_size, "expert_size": 12, "num_experts": 3}))
-            layers.append(LayerSpec(prefix=f"layers.{i}.", block=PartSpec("prenorm_residual"), mixer=mixer,
-                                    feed_forward=ffn,
-                                    mixer_norm=norm, feed_forward_norm=norm,
-                                    names={"mixer": "mixer.", "feed_forward": "ffn.", "mixer_norm": "norm1.", "feed_forward_norm": "norm2."}))
+            if i % 2:
+                # the attention layers use the block with four norms, named part by part
+                n = PartSpec("rmsnorm", norm.params, "norm")
+                layers.append(LayerSpec(prefix=f"layers.{i}.", block=PartSpec("sandwich"),
+                                        parts={"mixer": PartSpec(mixer.kind, mixer.params, "mixer"),
+                                               "feed_forward": PartSpec(ffn.kind, ffn.params, "feed_forward"),
+                                               "pre_mixer_norm": n, "post_mixer_norm": n, "pre_ffn_norm": n, "post_ffn_norm": n},
+                                        names={"feed_forward": "ffn.", "pre_mixer_norm": "norm1.", "post_mixer_norm": "norm1b.",
+                                               "pre_ffn_norm": "norm2.", "post_ffn_norm": "norm2b."}))
+                continue
+            layers.append(LayerSpec.standard(prefix=f"layers.{i}.", block=PartSpec("prenorm_residual"), mixer=mixer,
+                                             feed_forward=ffn, mixer_norm=norm, feed_forward_norm=norm,
+                                             names={"mixer": "mixer.", "feed_forward": "ffn.", "mixer_norm": "norm1.",
+                                                    "feed_forward_norm": "norm2."}))
         # the run order names layer 0 twice (its second run has a state of its own) and lets the
         # last entry read the keys and values that layer 1 wrote
         order = (RunEntry(0, 0), RunEntry(1, 1), RunEntry(0, 2), RunEntry(1, 1, writes_cache=False))
         return ModelSpec(architecture="ToyForCausalLM", hidden_size=self.hidden_size, vocab_size=self.vocab_size,
                          max_position_embeddings=256, embedding_name="embed.weight", layers=tuple(layers),
                          run_order=order, final_norm=norm, final_norm_prefix="final_norm.", lm_head_name=None,
-                         position_encodings={"rope": PartSpec("rotary", {"head_dim": 16, "theta": 10000.0}),
-                                             "abs": PartSpec("learned_positions", {"hidden_size": self.hidden_size, "max_len": 256})})
+                         position_encodings={"rope": PartSpec("rotary", {"head_dim": 16, "theta": 10000.0, "rotary_dim": ROTARY_DIM}),
+                                             "abs": PartSpec("learned_positions", {"hidden_size": self.hidden_size, "max_len": 256})},
+                         embedding_hooks=(PartSpec("scale", {"factor": EMBED_SCALE}),),
+                         logit_hooks=(PartSpec("softcap", {"cap": SOFTCAP}),))
 
 
 TOY = {"architectures": ["ToyForCausalLM"], "hidden_size": 24, "state_size": 10, "vocab_size": 50, "num_layers": 2}
@@ -164,8 +218,14 @@ def toy_registered():
     MIXERS.register("running_sum", RunningSumMixer)
     FEED_FORWARDS.register("routed_experts", RoutedExperts)
     POSITION_ENCODINGS.register("learned_positions", LearnedPositions)
+    BLOCKS.register("sandwich", SandwichBlock)
+    HOOKS.register("scale", Scale)
+    HOOKS.register("softcap", SoftCap)
     register_architecture("ToyForCausalLM", ToyConfig)
     yield
+    BLOCKS.unregister("sandwich")
+    HOOKS.unregister("scale")
+    HOOKS.unregister("softcap")
     MIXERS.unregister("running_sum")
     FEED_FORWARDS.unregister("routed_experts")
     POSITION_ENCODINGS.unregister("learned_positions")
@@ -178,9 +238,12 @@ def reference_logits(folder, tokens):
     from safetensors.torch import load_file
     w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
     T = len(tokens)
-    x = w["embed.weight"][torch.tensor(tokens)] + w["position.abs.weight"][:T]
-    inv = P.rope_inv_freq(16, 10000.0, None)
+    x = (w["embed.weight"][torch.tensor(tokens)] + w["position.abs.weight"][:T]) * EMBED_SCALE
+    inv = P.rope_inv_freq(ROTARY_DIM, 10000.0, None)
     kv = {}
+
+    def rope(t):       # only the first ROTARY_DIM elements of each head turn
+        return torch.cat([P.apply_rope(t[..., :ROTARY_DIM], range(T), inv), t[..., ROTARY_DIM:]], -1)
 
     def running_sum(h, p):
         u = h @ w[p + "mixer.in_proj.weight"].t()
@@ -193,9 +256,9 @@ def reference_logits(folder, tokens):
 
     def attention(h, p, reuse):
         q = (h @ w[p + "mixer.q_proj.weight"].t()).view(T, 2, 16)
-        q = P.apply_rope(q, range(T), inv)
+        q = rope(q)
         if not reuse:
-            k = P.apply_rope((h @ w[p + "mixer.k_proj.weight"].t()).view(T, 1, 16), range(T), inv)
+            k = rope((h @ w[p + "mixer.k_proj.weight"].t()).view(T, 1, 16))
             v = (h @ w[p + "mixer.v_proj.weight"].t()).view(T, 1, 16)
             kv["k"], kv["v"] = k, v
         o = P.causal_attention(q, kv["k"], kv["v"], 0.25).reshape(T, 32)
@@ -204,22 +267,28 @@ def reference_logits(folder, tokens):
     for layer, reuse in ((0, False), (1, False), (0, False), (1, True)):
         p = f"layers.{layer}."
         h = P.rms_norm(x, w[p + "norm1.weight"], 1e-5)
-        x = x + (running_sum(h, p) if layer == 0 else attention(h, p, reuse))
+        if layer == 0:
+            x = x + running_sum(h, p)
+        else:              # the block with four norms
+            x = x + P.rms_norm(attention(h, p, reuse), w[p + "norm1b.weight"], 1e-5)
         h = P.rms_norm(x, w[p + "norm2.weight"], 1e-5)
         if layer == 0:
             gate = torch.softmax(h @ w[p + "ffn.router.weight"].t() * 8.0, dim=-1)
             for e in range(3):
                 x = x + gate[:, e:e + 1] * (torch.relu(h @ w[p + f"ffn.experts.{e}.up.weight"].t()) @ w[p + f"ffn.experts.{e}.down.weight"].t())
         else:
-            x = x + P.gated_mlp(h, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
-    return P.rms_norm(x, w["final_norm.weight"], 1e-5) @ w["embed.weight"].t()
+            m = P.gated_mlp(h, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
+            x = x + P.rms_norm(m, w[p + "norm2b.weight"], 1e-5)
+    logits = P.rms_norm(x, w["final_norm.weight"], 1e-5) @ w["embed.weight"].t()
+    return torch.tanh(logits / SOFTCAP) * SOFTCAP
 
 
-def run_toy(tmp_path, device, dtype, tol):
+def run_toy(tmp_path, device, dtype, tol, graphs=False):
     from rvllm_b200.engine import StepEntry
     from rvllm_b200.engine.trace import build_engine
     folder = write_random_model(config_from_dict(TOY), str(tmp_path / "toy"), seed=2, dtype="float32")
-    eng = build_engine(folder, dtype, 3 * 64, block_size=8, device=device, max_live=3)
+    eng = build_engine(folder, dtype, 3 * 64, block_size=8, device=device, max_live=3, graphs=graphs)
+    assert not eng.model.graph_safe                 # because of the state mixer
     assert len(eng.cache.groups) == 1 and sorted(eng.cache._state) == [0, 2]        # two states, one kv group
     g = torch.Generator().manual_seed(0)
     seqs = {r: torch.randint(0, 50, (n,), generator=g).tolist() for r, n in (("a", 30), ("b", 21), ("c", 17), ("d", 26))}
@@ -250,6 +319,8 @@ def run_toy(tmp_path, device, dtype, tol):
         err = float((full - ref[r]).abs().max() / ref[r].abs().max())
         assert err < tol, f"request {r}: {err:.2e}"
     eng.cache.check()
+    assert not eng.runner._graphs                   # no step of this model was captured
+    return eng
 
 
 def test_toy_state_mixer_on_cpu_with_emulated_kernels(tmp_path, toy_registered):
@@ -265,3 +336,35 @@ def test_toy_state_mixer_on_cpu_with_emulated_kernels(tmp_path, toy_registered):
 @pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("bfloat16", 3e-2)])
 def test_toy_state_mixer_on_gpu(tmp_path, toy_registered, dtype, tol):
     run_toy(tmp_path, "cuda:0", dtype, tol)
+
+
+@pytest.mark.gpu
+def test_a_part_that_cannot_be_captured_keeps_the_model_out_of_cuda_graphs(tmp_path, toy_registered):
+    """With graphs switched on, the toy's decode steps (which call .tolist() inside the state
+    mixer) still run, eagerly, and give the same logits; a model of the framework's own parts is
+    captured as before."""
+    eng = run_toy(tmp_path, "cuda:0", "float32", 1e-4, graphs=True)
+    assert eng.runner.graph_batch_sizes and eng.runner.capture_decode_graphs() == 0
+    from model_tools import model_folder
+    from rvllm_b200.engine.trace import build_engine
+    plain = build_engine(model_folder("tiny_llama"), "float32", 128, graphs=True)
+    assert plain.model.graph_safe and plain.runner.capture_decode_graphs(batch_sizes=(1,)) > 0
+
+
+def test_the_toy_s_spec_is_checked(toy_registered):
+    """Named parts: an unknown family, two mixers in a layer and roles a block does not know are
+    refused with a message."""
+    from rvllm_b200 import ConfigError
+    from rvllm_b200.models import DecoderModel
+    spec = config_from_dict(TOY).to_spec()
+    layer = spec.layers[1]
+    import dataclasses
+    two = dataclasses.replace(layer, parts={**layer.parts, "second": layer.parts["mixer"]})
+    with pytest.raises(ConfigError, match="more than one mixer"):
+        DecoderModel(dataclasses.replace(spec, layers=(spec.layers[0], two)))
+    odd = dataclasses.replace(layer, parts={**layer.parts, "mixer": PartSpec("paged_attention", layer.parts["mixer"].params, "gizmo")})
+    with pytest.raises(ConfigError, match="family 'gizmo'"):
+        DecoderModel(dataclasses.replace(spec, layers=(spec.layers[0], odd)))
+    wrong = dataclasses.replace(spec.layers[0], parts={k: v for k, v in spec.layers[0].parts.items() if k != "mixer_norm"})
+    with pytest.raises(ConfigError, match="arranges the parts"):
+        DecoderModel(dataclasses.replace(spec, layers=(wrong, spec.layers[1])))
