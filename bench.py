@@ -15,7 +15,9 @@ A "step" is one decode step of the whole batch.  One JSON line is printed:
   prefill      one 2,048-token prompt: tokens per second, milliseconds, fraction of the bf16 peak
   roofline     bytes a decode step has to read (every weight once + the live requests' cache)
                over its time, against the measured copy bandwidth
-  points       decode tokens per second at batch 1 and 64
+  points       decode tokens per second at batch 1 and 64 with their fractions of the HBM roofline,
+               the end-to-end figure at batch 64, and the output tokens per second of the continuous
+               batching workload at Qwen2.5-7B sizes (64 requests, prompts 128..4,096, 256 tokens each)
 
 The reference arm (--impl reference) reports that the reference cannot be installed here: it is
 a Rust workspace built with maturin and cargo, neither of which exists in this image.
@@ -115,6 +117,18 @@ class ClockSampler:
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def ensure_built():
+    """Compile whatever kernel library is missing before anything is timed (a library is otherwise
+    compiled when a step first needs it, which may be inside a timed region)."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from rvllm_b200.kernels import build as kb
+    from rvllm_b200.kernels.variants import all_variants
+    jobs = all_variants()
+    with ThreadPoolExecutor(max_workers=8) as pool:
+        list(pool.map(lambda j: kb.compile_library(j[0], j[1]), jobs))
 
 
 def weight_bytes_per_step(cfg, layers, el=2):
@@ -241,18 +255,41 @@ def run_ours(args):
             llm.scheduler.abort(r.req_id)
         return b * steps / dt, h2d, b * 4
 
+    def hbm_gbs(b, ms, ctx):
+        """Bytes a decode step of b requests has to read (weights once, the requests' cache) over its time."""
+        step_bytes = weight_bytes_per_step(cfg_dict, args.layers) + b * ctx * kv_bytes_per_token(cfg_dict, args.layers)
+        return step_bytes / (ms / 1e3) / 1e9
+
     points = {}
     main = None
     for b in batches:
         ms, ctx, launches, ck = decode_device(b, args.steps, args.warmup, sample_clocks=(b == args.batch))
         tps = b / (ms / 1e3)
-        points[f"decode_b{b}"] = round(tps, 1)
+        if b != args.batch or b in (1, 64):
+            points[f"decode_b{b}"] = round(tps, 1)
+            points[f"decode_b{b}_hbm_frac"] = round(hbm_gbs(b, ms, ctx) / peaks["hbm_gbs"], 4)
         if b == args.batch:
             main = (ms, ctx, launches, ck, tps)
     ms, ctx, launches, ck, tps = main
     e2e_tps, h2d, d2h = decode_e2e(args.batch, args.steps, args.warmup)
-    step_bytes = weight_bytes_per_step(cfg_dict, args.layers) + args.batch * ctx * kv_bytes_per_token(cfg_dict, args.layers)
-    achieved = step_bytes / (ms / 1e3) / 1e9
+    if 64 in batches and args.batch != 64:
+        points["e2e_b64"] = round(decode_e2e(64, args.steps, args.warmup)[0], 1)
+    achieved = hbm_gbs(args.batch, ms, ctx)
+    if not args.no_points and args.shape == "llama-3.1-8b" and args.layers == full_layers:
+        # continuous batching at Qwen2.5-7B sizes (64 requests, prompts 128..4,096, 256 tokens each, 2,048 tokens
+        # a step): output tokens per second, measured with a model of its own after this one is gone
+        del runner, kernels
+        llm = None
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            sv = serve_workload("qwen2.5-7b", None, 64, 256, 2048, args.eager)
+            points["serve_qwen2.5-7b_output_tok_s"] = sv["value"]
+            points["serve_qwen2.5-7b_seconds"] = sv["seconds"]
+        except Exception as exc:     # the decode line stands on its own
+            points["serve_qwen2.5-7b_output_tok_s"] = None
+            points["serve_error"] = f"{type(exc).__name__}: {exc}"[:200]
     line = {
         "metric": f"decode tokens/s ({args.shape} layer sizes, bf16, random weights, {PROMPT_LEN}-token prompts)",
         "value": round(tps, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
@@ -271,35 +308,35 @@ def run_ours(args):
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks["source"]},
-        "points": {k: v for k, v in points.items() if k != f"decode_b{args.batch}" or args.batch in (1, 64)},
+        "points": points,
         "clocks": ck,
     }
     print(json.dumps(line))
 
 
-def run_serve(args):
-    """Continuous batching through the entry point: --requests prompts of uneven length arrive at once,
+def serve_workload(shape_name, layers, requests, output_len, budget, eager):
+    """Continuous batching through the entry point: `requests` prompts of uneven length arrive at once,
     prompts are cut into portions under a token budget and run beside the decoding requests."""
     import torch
 
     from rvllm_b200 import LLM, SamplingParams, config_from_dict
     from rvllm_b200.kernels.library import COUNTERS
 
-    shape, _, context = SHAPES[args.shape]
+    shape, _, context = SHAPES[shape_name]
     cfg_dict = dict(shape)
     full_layers = cfg_dict["num_hidden_layers"]
-    cfg_dict["num_hidden_layers"] = args.layers or full_layers
+    cfg_dict["num_hidden_layers"] = layers or full_layers
     gen = torch.Generator().manual_seed(0)
-    lo, hi = 128, min(4096, context - args.output_len)
-    lengths = torch.randint(lo, hi + 1, (args.requests,), generator=gen).tolist()
+    lo, hi = 128, min(4096, context - output_len)
+    lengths = torch.randint(lo, hi + 1, (requests,), generator=gen).tolist()
     prompts = [torch.randint(0, cfg_dict["vocab_size"], (n,), generator=gen).tolist() for n in lengths]
-    pages = sum((n + args.output_len + 15) // 16 + 1 for n in lengths)
+    pages = sum((n + output_len + 15) // 16 + 1 for n in lengths)
     llm = LLM(config=config_from_dict(cfg_dict), random_weights=True, seed=0, dtype="bfloat16", block_size=16,
-              num_blocks=pages + 8, max_model_len=context, max_num_seqs=args.requests,
-              max_num_batched_tokens=args.budget, enforce_eager=args.eager)
-    sp = SamplingParams(temperature=0.0, max_tokens=args.output_len, ignore_eos=True)
+              num_blocks=pages + 8, max_model_len=context, max_num_seqs=requests,
+              max_num_batched_tokens=budget, enforce_eager=eager)
+    sp = SamplingParams(temperature=0.0, max_tokens=output_len, ignore_eos=True)
     llm.generate(prompts[:2], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))     # warm-up
-    graphs = llm.capture_graphs(hi + args.output_len)      # as a service does when it starts, not while it serves
+    graphs = llm.capture_graphs(hi + output_len)      # as a service does when it starts, not while it serves
     clocks = ClockSampler()
     clocks.start()
     COUNTERS["launches"] = 0
@@ -310,18 +347,22 @@ def run_serve(args):
     dt = time.perf_counter() - t0
     ck = clocks.stop()
     n_out = sum(len(o.outputs[0].token_ids) for o in outs)
-    print(json.dumps({
-        "metric": f"continuous batching, output tokens/s ({args.shape} layer sizes, bf16, random weights)",
+    return {
+        "metric": f"continuous batching, output tokens/s ({shape_name} layer sizes, bf16, random weights)",
         "value": round(n_out / dt, 1), "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
         "impl": "ours", "data": "synthetic: random weights, uniform random token ids, all requests arrive at once",
         "seconds": round(dt, 3), "prompt_tokens": sum(lengths), "output_tokens": n_out,
         "total_tokens_per_s": round((sum(lengths) + n_out) / dt, 1),
         "preemptions": sum(o.num_preemptions for o in outs), "gpu_launches": COUNTERS["launches"],
-        "config": {"model": f"{args.shape}-shape", "layers": cfg_dict["num_hidden_layers"], "layers_full": full_layers,
-                   "requests": args.requests, "prompt_len": f"uniform {lo}..{hi}", "output_len": args.output_len,
-                   "token_budget": args.budget, "seq_len": context, "block_size": 16, "cuda_graph": not args.eager,
+        "config": {"model": f"{shape_name}-shape", "layers": cfg_dict["num_hidden_layers"], "layers_full": full_layers,
+                   "requests": requests, "prompt_len": f"uniform {lo}..{hi}", "output_len": output_len,
+                   "token_budget": budget, "seq_len": context, "block_size": 16, "cuda_graph": not eager,
                    "graphs_captured_before": graphs},
-        "clocks": ck}))
+        "clocks": ck}
+
+
+def run_serve(args):
+    print(json.dumps(serve_workload(args.shape, args.layers, args.requests, args.output_len, args.budget, args.eager)))
 
 
 def main():
@@ -350,6 +391,7 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    ensure_built()
     if args.workload == "serve":
         run_serve(args)
     else:

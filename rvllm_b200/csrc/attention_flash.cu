@@ -887,8 +887,9 @@ RV_EXPORT int rv_flash_attention_static(const void* q, const void* cache, const 
         }
         g_static_scratch_addr[device] = addr;
     }
-    // Nothing in the scratch has to be zero at entry: every element the merge kernel reads was
-    // written by the attention kernel of the same call (empty key ranges write m = -inf, l = 0).
+    // Nothing in the scratch has to be zero at entry: for every row that the sequences cover, every
+    // element the merge kernel reads was written by the attention kernel of the same call (empty key
+    // ranges write m = -inf, l = 0).  Rows outside the sequences are undefined (see the header).
     const int st = rv_flash_attention(q, cache, block_tables, cu_seqlens, ctx_lens, out,
                                       num_splits > 1 ? g_static_scratch_addr[device] : nullptr, n_tokens, num_seqs,
                                       nh, nkv, hd, page_size, max_blocks, scale, window, mode, max_q_len, num_splits,

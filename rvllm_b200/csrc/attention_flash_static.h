@@ -24,8 +24,14 @@
 //   * The function calls no cudaMalloc, cudaFree or any allocating routine.  Inputs and outputs
 //     are the caller's, exactly as for rv_flash_attention (q_filter is always 0: every sequence).
 //   * The first call on a device looks up the array's device address
-//     (cudaGetSymbolAddress, with that device current) and remembers it.  Make that first call
-//     before any stream capture on that device.
+//     (cudaGetSymbolAddress, with that device current) and remembers it, and raises the kernels'
+//     shared-memory limit on that device.  Make that first call before any stream capture on that
+//     device.  The remembered address is kept per device without a lock: two host threads that
+//     make the first call on a device at the same moment both look it up and store the same value.
+//   * n_tokens must be the number of rows that the sequences cover (cu_seqlens[num_seqs]) and
+//     max_q_len at least the longest sequence's rows.  Output rows beyond the sequences, or beyond
+//     an understated max_q_len, are undefined: with key splits they are merged from whatever an
+//     earlier call left in the shared array.
 //   * All calls share the one array, which keeps whatever the last call left in it.  Nothing in
 //     it has to be zero: each call overwrites every element it later reads.  Two calls that
 //     overlap on the GPU (different streams, no ordering between them) race on it - order them.

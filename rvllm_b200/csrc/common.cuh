@@ -118,6 +118,18 @@ static inline int rv_launch_status() {
     return e == cudaSuccess ? RV_OK : (int)e;
 }
 
+// Philox-4x32-10 (Salmon et al., 2011): counter c, key (k0, k1) -> four random words in c.
+__device__ __forceinline__ void philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+        const uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
+        c[0] = n0; c[1] = lo1; c[2] = n2; c[3] = lo0;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+}
+
 __device__ __forceinline__ float rv_to_float(float v) { return v; }
 __device__ __forceinline__ float rv_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -444,3 +444,52 @@ RV_EXPORT int rv_silu_mul(const void* gate_up, void* out, int n_rows, int inter,
         return RV_ERR_BAD_DTYPE;
     return rv_launch_status();
 }
+
+// ------------------------------------------------------------------ random normal fill
+// out[i] = mean + std * z_i with z from a counter-based generator: element i is word (i mod 4) of
+// Philox-4x32-10 at counter (i / 4, stream) under the key `seed`, two words turned into two
+// normals by Box-Muller; so a tensor's values depend on (seed, stream, i) only, not on the launch.
+// The reference fills its benchmark weights on the host (v3/crates/rvllm-bench); here the
+// random-weights mode of the engine fills them where they live.
+template <typename T>
+__global__ void fill_normal_kernel(T* __restrict__ out, long long n, float mean, float std, unsigned long long seed,
+                                   unsigned long long stream) {
+    const long long quads = (n + 3) / 4;
+    for (long long qd = (long long)blockIdx.x * blockDim.x + threadIdx.x; qd < quads; qd += (long long)gridDim.x * blockDim.x) {
+        uint32_t c[4] = {(uint32_t)(qd & 0xffffffffll), (uint32_t)((unsigned long long)qd >> 32),
+                         (uint32_t)(stream & 0xffffffffull), (uint32_t)(stream >> 32)};
+        philox4x32_10(c, (uint32_t)(seed & 0xffffffffull), (uint32_t)(seed >> 32));
+        float z[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float u1 = ((float)(c[2 * h] >> 8) + 0.5f) * (1.0f / 16777216.0f);      // (0, 1)
+            const float u2 = (float)(c[2 * h + 1] >> 8) * (1.0f / 16777216.0f);           // [0, 1)
+            const float r = sqrtf(-2.0f * logf(u1));
+            float sn, cs;
+            sincospif(2.0f * u2, &sn, &cs);
+            z[2 * h] = r * cs;
+            z[2 * h + 1] = r * sn;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const long long i = qd * 4 + j;
+            if (i < n) out[i] = rv_from_float<T>(mean + std * z[j]);
+        }
+    }
+}
+
+RV_EXPORT int rv_fill_normal(void* out, long long n, float mean, float std, unsigned long long seed,
+                             unsigned long long stream_id, int dtype, cudaStream_t stream) {
+    if (n < 0 || !(std >= 0.f)) return RV_ERR_BAD_SIZE;
+    if (n == 0) return RV_OK;
+    const int threads = 256;
+    long long blocks = ((n + 3) / 4 + threads - 1) / threads;
+    if (blocks > (long long)rv_sm_count() * 16) blocks = (long long)rv_sm_count() * 16;
+    if (dtype == RV_DTYPE_F32)
+        RV_LAUNCH_ST = rv_launch(fill_normal_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, (float*)out, n, mean, std, seed, stream_id);
+    else if (dtype == RV_DTYPE_BF16)
+        RV_LAUNCH_ST = rv_launch(fill_normal_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream, (__nv_bfloat16*)out, n, mean, std, seed, stream_id);
+    else
+        return RV_ERR_BAD_DTYPE;
+    return rv_launch_status();
+}

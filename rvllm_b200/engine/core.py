@@ -46,14 +46,24 @@ class Engine:
 
         expected = self.model.expected_tensors()
         if random_weights and model_dir is None:
-            gen = torch.Generator(device=self.device)
-            gen.manual_seed(seed)
+            if hasattr(self.kernels, "fill_normal"):
+                # filled on the device by the counter-based generator: a tensor's values depend on the
+                # seed and on its place among the sorted names only
+                order = {name: i for i, name in enumerate(sorted(expected))}
 
-            def get(name: str) -> torch.Tensor:
-                ts = expected[name]
-                mean, std = INIT_STD[ts.init]
-                t = torch.empty(ts.shape, dtype=torch.float32, device=self.device).normal_(mean, std, generator=gen)
-                return t.to(self.dtype)
+                def get(name: str) -> torch.Tensor:
+                    ts = expected[name]
+                    mean, std = INIT_STD[ts.init]
+                    return self.kernels.fill_normal(ts.shape, self.dtype, mean, std, seed, order[name])
+            else:
+                gen = torch.Generator(device=self.device)
+                gen.manual_seed(seed)
+
+                def get(name: str) -> torch.Tensor:
+                    ts = expected[name]
+                    mean, std = INIT_STD[ts.init]
+                    t = torch.empty(ts.shape, dtype=torch.float32, device=self.device).normal_(mean, std, generator=gen)
+                    return t.to(self.dtype)
         else:
             source = WeightSource(model_dir)
             source.check({n: ts.shape for n, ts in expected.items()}, self.spec.ignored_tensors)

@@ -165,6 +165,17 @@ class CudaKernels:
         _check("gather_rows", st)
         return out
 
+    def fill_normal(self, shape, dtype: torch.dtype, mean: float, std: float, seed: int, stream: int) -> torch.Tensor:
+        """A new tensor of N(mean, std) values from the counter-based generator: element i depends
+        on (seed, stream, i) only.  The engine's random-weights mode gives every tensor a stream of
+        its own (its index among the sorted tensor names)."""
+        out = torch.empty(tuple(shape), dtype=dtype, device=self.device)
+        st = self._lib("elementwise.cu").rv_fill_normal(
+            _ptr(out), ctypes.c_longlong(out.numel()), c_float(mean), c_float(std), ctypes.c_ulonglong(seed & (2 ** 64 - 1)),
+            ctypes.c_ulonglong(stream), c_int(self._dt(out, "out")), self._stream())
+        _check("fill_normal", st)
+        return out
+
     def late_tokens(self, token_ids: torch.Tensor, cu_seqlens: torch.Tensor, source: torch.Tensor,
                     sampled: torch.Tensor) -> None:
         """token_ids[cu_seqlens[i]] = sampled[source[i]] for every sequence i with source[i] >= 0:

@@ -600,3 +600,26 @@ def test_attention_tcgen05_kernel(K, case):
     assert int(status.item()) == 0, "a bounded wait inside the kernel gave up"
     full = K.paged_attention(q, cache, meta, nh, nkv, hd, scale, window)          # with the decode kernel for the rest
     assert rel_err(full.view(-1, nh, hd), ref) < BF16_TOL
+
+
+def test_fill_normal_kernel_is_counter_based_and_normal(K):
+    """The random-weights fill: element i is a function of (seed, stream, i) - checked against the
+    plain Philox and Box-Muller for the first elements -, the same whatever the size of the launch,
+    different for another seed or stream, and normal in its first four moments."""
+    n = 1_000_004
+    a = K.fill_normal((n,), torch.float32, 0.0, 1.0, seed=7, stream=3)
+    assert torch.equal(a[:1001], K.fill_normal((1001,), torch.float32, 0.0, 1.0, seed=7, stream=3))
+    assert not torch.equal(a[:1000], K.fill_normal((1000,), torch.float32, 0.0, 1.0, seed=8, stream=3))
+    assert not torch.equal(a[:1000], K.fill_normal((1000,), torch.float32, 0.0, 1.0, seed=7, stream=4))
+    for qd in (0, 1, 250_000):
+        w = P.philox4x32([qd, 0, 3, 0], [7, 0])
+        for h in range(2):
+            u1, u2 = ((w[2 * h] >> 8) + 0.5) / 16777216.0, (w[2 * h + 1] >> 8) / 16777216.0
+            r = math.sqrt(-2.0 * math.log(u1))
+            assert abs(float(a[4 * qd + 2 * h]) - r * math.cos(2 * math.pi * u2)) < 1e-5
+            assert abs(float(a[4 * qd + 2 * h + 1]) - r * math.sin(2 * math.pi * u2)) < 1e-5
+    d = a.double()
+    assert abs(float(d.mean())) < 5e-3 and abs(float(d.std()) - 1) < 5e-3
+    assert abs(float((d ** 3).mean())) < 2e-2 and abs(float((d ** 4).mean()) - 3) < 5e-2
+    b = K.fill_normal((300, 1000), torch.bfloat16, 1.0, 0.1, seed=1, stream=0).double()
+    assert b.shape == (300, 1000) and abs(float(b.mean()) - 1) < 2e-3 and abs(float(b.std()) - 0.1) < 2e-3

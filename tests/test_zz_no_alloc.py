@@ -29,19 +29,19 @@ def ptr(t):
     return c_void_p(t.data_ptr() if t is not None else 0)
 
 
-def call_static(lib, q, cache, meta, out, nh, nkv, scale, window, splits, err):
+def call_static(lib, q, cache, meta, out, nh, nkv, scale, window, splits, err, mode=1):
     return lib.rv_flash_attention_static(
         ptr(q), ptr(cache), ptr(meta.block_tables), ptr(meta.cu_seqlens), ptr(meta.ctx_lens), ptr(out),
         c_int(q.shape[0]), c_int(meta.num_seqs), c_int(nh), c_int(nkv), c_int(HD), c_int(cache.shape[3]),
-        c_int(meta.max_blocks), c_float(scale), c_int(window), c_int(1), c_int(1), c_int(splits),
+        c_int(meta.max_blocks), c_float(scale), c_int(window), c_int(mode), c_int(meta.max_q_len), c_int(splits),
         c_void_p(torch.cuda.current_stream().cuda_stream), err, c_int(len(err)))
 
 
-def call_ordinary(lib, q, cache, meta, out, scratch, nh, nkv, scale, window, splits):
+def call_ordinary(lib, q, cache, meta, out, scratch, nh, nkv, scale, window, splits, mode=1):
     return lib.rv_flash_attention(
         ptr(q), ptr(cache), ptr(meta.block_tables), ptr(meta.cu_seqlens), ptr(meta.ctx_lens), ptr(out), ptr(scratch),
         c_int(q.shape[0]), c_int(meta.num_seqs), c_int(nh), c_int(nkv), c_int(HD), c_int(cache.shape[3]),
-        c_int(meta.max_blocks), c_float(scale), c_int(window), c_int(1), c_int(1), c_int(splits), c_int(0),
+        c_int(meta.max_blocks), c_float(scale), c_int(window), c_int(mode), c_int(meta.max_q_len), c_int(splits), c_int(0),
         c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
@@ -73,6 +73,36 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row():
         assert diff <= 1e-2 * float(want.float().abs().max()), f"call {call}: differs by {diff}"
         # and against the plain kernel, so that both being wrong together would show
         from rvllm_b200.kernels import get_library
+        plain = get_library("cuda:0").paged_attention_plain(q, cache, meta, nh, nkv, HD, scale, window or None)
+        assert float((got.float() - plain.float()).abs().max()) <= 1e-2 * float(plain.float().abs().max())
+
+
+def test_static_scratch_entry_point_with_the_prefill_tiling():
+    """The header offers both tilings: here prompt portions of several tokens (mode 0, 64 rows per
+    CTA), their keys split over three CTAs, again twice in a row on different inputs."""
+    from rvllm_b200.kernels import build, get_library
+    lib = build.load_library("attention_flash.cu", (f"-DHEAD_DIM={HD}",))
+    lib.rv_flash_scratch_floats.restype = ctypes.c_longlong
+    nh, nkv, page, splits = 8, 2, 16, 3
+    scale = 1 / math.sqrt(HD)
+    err = ctypes.create_string_buffer(256)
+    for call, (q_lens, ctx_lens, window, seed) in enumerate([((40, 7), (100, 300), 0, 5), ((3, 64, 20), (500, 64, 129), 96, 6)]):
+        torch.manual_seed(seed)
+        ks = [torch.randn(c, nkv, HD) for c in ctx_lens]
+        vs = [torch.randn(c, nkv, HD) for c in ctx_lens]
+        cache, meta = paged_setup(ks, vs, list(q_lens), page, torch.bfloat16, seed=seed)
+        T = sum(q_lens)
+        q = torch.randn(T, nh * HD, device="cuda").bfloat16()
+        need = lib.rv_flash_scratch_floats(c_int(T), c_int(nh), c_int(splits))
+        assert 0 < need <= STATIC_FLOATS
+        scratch = torch.empty(need, dtype=torch.float32, device="cuda")
+        want = torch.zeros_like(q)
+        assert call_ordinary(lib, q, cache, meta, want, scratch, nh, nkv, scale, window, splits, mode=0) == 0
+        got = torch.zeros_like(q)
+        assert call_static(lib, q, cache, meta, got, nh, nkv, scale, window, splits, err, mode=0) == 0, err.value.decode()
+        torch.cuda.synchronize()
+        assert err.value == b"" and torch.isfinite(got.float()).all()
+        assert float((got.float() - want.float()).abs().max()) <= 1e-2 * float(want.float().abs().max()), f"call {call}"
         plain = get_library("cuda:0").paged_attention_plain(q, cache, meta, nh, nkv, HD, scale, window or None)
         assert float((got.float() - plain.float()).abs().max()) <= 1e-2 * float(plain.float().abs().max())
 
