@@ -405,6 +405,309 @@ __global__ void flash_combine_kernel(const float* __restrict__ part_o, const flo
 }
 
 // ---------------------------------------------------------------------------------------------
+// Decode attention fed by TMA (head sizes 64 and 128, pages of at least 8 keys).  The decode tiling
+// of the kernel above - 16 rows, four warps that own 16 of a tile's 64 keys each, key splits over
+// CTAs, the same arithmetic in the same order, so the same bits - but the tiles are brought in by
+// a fifth warp with cp.async.bulk.tensor, one box per (page, 64 elements of the head) through the
+// block table, into 128-byte-swizzled stages that mbarriers hand back and forth:
+//   full[stage]   the producer's expect_tx + the boxes' bytes        -> the four consumer warps
+//   empty[stage]  one arrival per consumer warp after its last read  -> the producer
+// The consumer warps issue no address arithmetic or copy instructions at all.  Only the box that
+// holds the sequence's newest key (written by the kernel before this one) has to wait for that
+// kernel; with `early` set, the producer requests all older keys before griddepcontrol.wait, so
+// that they arrive while the predecessor's last CTAs drain.
+// A CTA never returns while one of its copies is in flight: every box that is requested is waited
+// for by the consumers, and after a wait that gave up (bounded, with a status word) the producer
+// waits, again bounded, for what it has requested - shared memory that a later CTA of the grid
+// inherits is never written by a copy of an earlier one.
+#if HEAD_DIM == 64 || HEAD_DIM == 128
+#define RV_HAVE_TMA_DECODE 1
+#include "tcgen05.cuh"
+#define TMA_HALVES (HEAD_DIM / 64)
+#define TMA_SLAB (KV_TILE * 128)                    // one 64-element slab of a tile: 64 keys x 128 bytes
+#define TMA_TILE_BYTES (TMA_HALVES * TMA_SLAB)      // K (or V) of a 64-key tile
+#ifndef TMA_STAGES
+#define TMA_STAGES 2
+#endif
+#define TMA_THREADS 160                             // 4 consumer warps + 1 producer warp
+#ifndef TMA_MIN_CTAS
+#define TMA_MIN_CTAS 3                              // CTAs per SM the register budget is held to
+#endif
+
+// byte offset of element `col` of key `row` inside a tile of 128-byte-swizzled slabs
+__device__ __forceinline__ int tma_swz(int row, int col) {
+    return (col >> 6) * TMA_SLAB + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4);
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int NST>
+__global__ void __launch_bounds__(TMA_THREADS, TMA_MIN_CTAS)
+flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FlashParams p, int* status, int early) {
+    rv_pdl_launch_dependents();
+    constexpr int HD = HEAD_DIM;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* k_s = smem;                                   // [NST][TMA_TILE_BYTES]
+    unsigned char* v_s = smem + NST * TMA_TILE_BYTES;            // [NST][TMA_TILE_BYTES]
+    __shared__ __align__(8) uint64_t bars[2 * NST];
+    __shared__ volatile int abort_flag;
+
+    const int seq = blockIdx.z, kvh = blockIdx.y;
+    const int tile_m = blockIdx.x / p.num_splits, split = blockIdx.x - tile_m * p.num_splits;
+    const int G = p.nh / p.nkv;
+    const int ctx = p.ctx_lens[seq];
+    const int q_start = p.cu_seqlens[seq];
+    const int q_len = p.cu_seqlens[seq + 1] - q_start;
+    const int rows_total = q_len * G;
+    const int row0 = tile_m * 16;
+    if (q_len <= 0 || row0 >= rows_total || (p.q_filter == 1 && q_len != 1) || (p.q_filter == 2 && q_len == 1)) {
+        rv_pdl_wait();
+        return;
+    }
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[NST]);
+
+    // key range of the row tile and this split's share of its key tiles (as in the kernel above)
+    const int last_row = min(rows_total, row0 + 16) - 1;
+    const int pos_first = ctx - q_len + row0 / G, pos_last = ctx - q_len + last_row / G;
+    const int key_lo = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
+    const int key_hi = ctx > 0 ? pos_last + 1 : 0;
+    const int tile_lo = key_lo / KV_TILE, tile_hi = (key_hi + KV_TILE - 1) / KV_TILE;
+    const int per_split = (tile_hi - tile_lo + p.num_splits - 1) / p.num_splits;
+    const int t_begin = tile_lo + split * per_split;
+    const int t_end = min(tile_hi, t_begin + per_split);
+    const int n_tiles = t_end > t_begin ? t_end - t_begin : 0;
+
+    if (tid == 0) {
+        abort_flag = 0;
+#pragma unroll
+        for (int s = 0; s < NST; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // value stages start as zeros: keys of a tile that are not requested (beyond the context, or
+    // below a window) meet a probability of zero, which must not find a NaN left in shared memory
+    for (int i = tid; i < NST * TMA_TILE_BYTES / 16; i += TMA_THREADS) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ producer warp
+        const int* table = p.block_tables + (size_t)seq * p.max_blocks;
+        const int box_keys = p.page_size < KV_TILE ? p.page_size : KV_TILE;
+        const int boxes = KV_TILE / box_keys;
+        bool waited = false;
+        if (!early) { rv_pdl_wait(); waited = true; }
+        int issued = 0;
+        bool ok = true;
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const int t = t_begin + i, stage = i % NST, use = i / NST;
+            if (use > 0) {
+                int ok_l = 1;
+                if (lane == 0) ok_l = mbar_wait(empty0 + 8 * stage, (use - 1) & 1, &abort_flag, 1) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok_l, 0) != 0;
+                if (!ok) break;
+            }
+            // the newest key of the sequence was written by the kernel before this one
+            if (!waited && (t + 1) * KV_TILE >= ctx) { rv_pdl_wait(); waited = true; }
+            const int key = t * KV_TILE + lane * box_keys;
+            int page = -1;
+            if (lane < boxes && key < key_hi && key + box_keys > key_lo) page = __ldg(table + (key >> p.page_shift));
+            const unsigned mask = __ballot_sync(0xffffffffu, page >= 0);
+            const uint32_t bar = full0 + 8 * stage;
+            if (lane == 0) mbar_expect_tx(bar, (uint32_t)__popc(mask) * 2u * TMA_HALVES * (uint32_t)box_keys * 128u);
+            __syncwarp();
+            if (page >= 0) {
+                const int row_k = ((page * 2) * p.nkv + kvh) * p.page_size + (key & (p.page_size - 1));
+                const int row_v = row_k + p.nkv * p.page_size;
+                const uint32_t dk = smem_u32(k_s) + (uint32_t)stage * TMA_TILE_BYTES + (uint32_t)lane * box_keys * 128;
+                const uint32_t dv = smem_u32(v_s) + (uint32_t)stage * TMA_TILE_BYTES + (uint32_t)lane * box_keys * 128;
+#pragma unroll
+                for (int h = 0; h < TMA_HALVES; ++h) {
+                    tma_load_2d(dk + h * TMA_SLAB, &map_kv, h * 64, row_k, bar);
+                    tma_load_2d(dv + h * TMA_SLAB, &map_kv, h * 64, row_v, bar);
+                }
+            }
+            __syncwarp();
+            ++issued;
+        }
+        if (!waited) rv_pdl_wait();
+        if (!ok || abort_flag != 0) {
+            // something gave up: wait (bounded) for the copies still in flight before this CTA's shared memory is given up
+            if (lane == 0) {
+                volatile int ignore = 0;
+                for (int i = max(0, issued - NST); i < issued; ++i)
+                    mbar_wait(full0 + 8 * (i % NST), (i / NST) & 1, &ignore, 0);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ consumer warps
+        const int warp_n = warp;
+        const int quad = lane >> 2, tq = lane & 3;
+        int r[2], pos[2], lo[2], head[2], tok[2];
+        bool valid[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            r[i] = row0 + quad + 8 * i;
+            const bool in_range = r[i] < rows_total;
+            const int t = in_range ? r[i] / G : 0;
+            tok[i] = q_start + t;
+            head[i] = kvh * G + (in_range ? r[i] - t * G : 0);
+            valid[i] = in_range && ctx > 0;
+            pos[i] = valid[i] ? ctx - q_len + t : -1;
+            lo[i] = (p.window > 0 && pos[i] - p.window + 1 > 0) ? pos[i] - p.window + 1 : 0;
+        }
+        float o[HD / 8][4];
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+        rv_pdl_wait();
+        uint32_t qa[HD / 16][4];
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const __nv_bfloat16* qp = p.q + ((size_t)tok[i] * p.nh + head[i]) * HD + ks * 16 + tq * 2;
+                qa[ks][i] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp) : 0u;
+                qa[ks][i + 2] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp + 8) : 0u;
+            }
+        }
+        bool ok = true;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int t = t_begin + it, stage = it % NST;
+            if (!mbar_wait(full0 + 8 * stage, (it / NST) & 1, &abort_flag, 2)) { ok = false; break; }
+            const unsigned char* ks = k_s + (size_t)stage * TMA_TILE_BYTES;
+            const unsigned char* vs = v_s + (size_t)stage * TMA_TILE_BYTES;
+            // S = Q K^T for the rows and this warp's 16 keys of the tile
+            float s[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                uint32_t b[4];
+                const int key_row = warp_n * 16 + (lane >> 4) * 8 + (lane & 7);
+                const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4(b, ks + tma_swz(key_row, col));
+                mma_bf16(s[0], qa[kk], b[0], b[1]);
+                mma_bf16(s[1], qa[kk], b[2], b[3]);
+            }
+            const int key0 = t * KV_TILE + warp_n * 16 + tq * 2;
+            float m_tile[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const int key = key0 + n * 8 + (e & 1);
+                    const bool see = key <= pos[i] && key >= lo[i];
+                    const float v = see ? s[n][e] * p.scale_log2e : -INFINITY;
+                    s[n][e] = v;
+                    m_tile[i] = fmaxf(m_tile[i], v);
+                }
+            }
+            float alpha[2], m_safe[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                m_tile[i] = fmaxf(m_tile[i], __shfl_xor_sync(0xffffffffu, m_tile[i], 1));
+                m_tile[i] = fmaxf(m_tile[i], __shfl_xor_sync(0xffffffffu, m_tile[i], 2));
+                const float m_new = fmaxf(m_run[i], m_tile[i]);
+                m_safe[i] = m_new == -INFINITY ? 0.f : m_new;
+                alpha[i] = exp2f(m_run[i] - m_safe[i]);
+                m_run[i] = m_new;
+            }
+            float l_tile[2] = {0.f, 0.f};
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float pv = exp2f(s[n][e] - m_safe[e >> 1]);
+                    s[n][e] = pv;
+                    l_tile[e >> 1] += pv;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * alpha[i] + l_tile[i];
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) {
+                o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+                o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+            }
+            // O += P V
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[0][0], s[0][1]);
+            pa[1] = pack_bf16(s[0][2], s[0][3]);
+            pa[2] = pack_bf16(s[1][0], s[1][1]);
+            pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+            for (int n2 = 0; n2 < HD / 16; ++n2) {
+                uint32_t b[4];
+                const int key_row = warp_n * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                const int col = n2 * 16 + (lane >> 4) * 8;
+                ldmatrix_x4_trans(b, vs + tma_swz(key_row, col));
+                mma_bf16(o[2 * n2], pa, b[0], b[1]);
+                mma_bf16(o[2 * n2 + 1], pa, b[2], b[3]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * stage);      // this warp has read the stage for the last time
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+            l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+        }
+        // merge the four warps through shared memory (every requested tile has arrived and been read:
+        // no copy is in flight, the stages are free) - unless a wait gave up: then nothing is written
+        consumer_sync();
+        if (abort_flag == 0 && ok) {
+            float* mo = reinterpret_cast<float*>(smem);                 // [4][16][HD]
+            float* mml = mo + 4 * 16 * HD;                              // [4][16][2]
+            const int n_rows = min(16, rows_total - row0);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int row = quad + 8 * i;
+                if (row >= n_rows) continue;
+#pragma unroll
+                for (int n = 0; n < HD / 8; ++n) {
+                    float* dst = mo + ((size_t)warp_n * 16 + row) * HD + n * 8 + tq * 2;
+                    dst[0] = o[n][2 * i]; dst[1] = o[n][2 * i + 1];
+                }
+                if (tq == 0) {
+                    mml[(warp_n * 16 + row) * 2] = m_run[i];
+                    mml[(warp_n * 16 + row) * 2 + 1] = l_run[i];
+                }
+            }
+            consumer_sync();
+            for (int idx = tid; idx < n_rows * HD; idx += 128) {
+                const int row = idx / HD, d = idx - row * HD;
+                float m_all = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) m_all = fmaxf(m_all, mml[(w * 16 + row) * 2]);
+                const float m_s = m_all == -INFINITY ? 0.f : m_all;
+                float l_all = 0.f, acc = 0.f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const float f = exp2f(mml[(w * 16 + row) * 2] - m_s);
+                    l_all += mml[(w * 16 + row) * 2 + 1] * f;
+                    acc += mo[((size_t)w * 16 + row) * HD + d] * f;
+                }
+                const int rr = row0 + row;
+                const int t = rr / G;
+                const size_t row_out = (size_t)(q_start + t) * p.nh + kvh * G + (rr - t * G);
+                if (p.num_splits == 1) {
+                    p.out[row_out * HD + d] = __float2bfloat16_rn(acc * (l_all > 0.f ? 1.f / l_all : 0.f));
+                } else {
+                    const size_t prow = (size_t)split * p.n_tokens * p.nh + row_out;
+                    p.part_o[prow * HD + d] = acc;
+                    if (d == 0) { p.part_ml[prow * 2] = m_all; p.part_ml[prow * 2 + 1] = l_all; }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (tid == 0 && abort_flag != 0 && status) atomicCAS(status, 0, abort_flag);
+}
+#endif   // HEAD_DIM 64 / 128
+
+// ---------------------------------------------------------------------------------------------
 // Decode attention with the work cut evenly: one token per sequence, as the decode tiling above,
 // but the grid is a fixed number of CTAs (as many as stay resident: three per SM) and every CTA
 // takes the same number of 64-key tiles.  The tiles of all (sequence, kv head) pairs form one list,
@@ -825,6 +1128,61 @@ RV_EXPORT int rv_flash_attention(const void* q, const void* cache, const int* bl
         return rv_launch_status();
     }
     return RV_OK;
+}
+
+// The TMA-fed decode kernel for the sequences of a step that bring one token (q_filter 1) or for
+// a step of such sequences only (q_filter 0 with max_q_len 1).  Same arguments as rv_flash_attention
+// plus the number of pages of the cache layer (for the tensor map), the status word of bounded
+// waits and `early` (request keys before griddepcontrol.wait).  Refuses (RV_ERR_UNSUPPORTED) head
+// sizes other than 64 and 128 and pages of fewer than 8 keys: the caller falls back to rv_flash_attention.
+RV_EXPORT int rv_flash_decode_tma(const void* q, const void* cache, long long num_pages, const int* block_tables,
+                                  const int* cu_seqlens, const int* ctx_lens, void* out, float* scratch, int n_tokens,
+                                  int num_seqs, int nh, int nkv, int hd, int page_size, int max_blocks, float scale,
+                                  int window, int max_q_len, int num_splits, int q_filter, int* status, int early,
+                                  cudaStream_t stream) {
+#ifdef RV_HAVE_TMA_DECODE
+    if (hd != HEAD_DIM) return RV_ERR_UNSUPPORTED;
+    if (n_tokens < 0 || num_seqs < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_blocks <= 0 ||
+        max_q_len <= 0 || num_splits < 1 || num_pages <= 0)
+        return RV_ERR_BAD_SIZE;
+    if ((page_size & (page_size - 1)) || page_size < 8) return RV_ERR_UNSUPPORTED;
+    if (num_seqs > 65535 || nkv > 65535) return RV_ERR_BAD_SIZE;
+    if (n_tokens == 0 || num_seqs == 0) return RV_OK;
+    if (num_splits > 1 && scratch == nullptr) return RV_ERR_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) % 16)
+        return RV_ERR_ALIGNMENT;
+    alignas(64) CUtensorMap map_kv;
+    int st = rv_make_bf16_map(&map_kv, cache, num_pages * 2 * nkv * page_size, HEAD_DIM, page_size < KV_TILE ? page_size : KV_TILE);
+    if (st != RV_OK) return st;
+    FlashParams p;
+    p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache;
+    p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.ctx_lens = ctx_lens;
+    p.out = (__nv_bfloat16*)out;
+    p.part_o = scratch;
+    p.part_ml = scratch ? scratch + (size_t)num_splits * n_tokens * nh * HEAD_DIM : nullptr;
+    p.n_tokens = n_tokens; p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.max_blocks = max_blocks;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.scale_log2e = scale * 1.4426950408889634f;
+    p.window = window; p.num_splits = num_splits; p.q_filter = q_filter;
+    const int G = nh / nkv;
+    p.row_tiles = (max_q_len * G + 15) / 16;
+    const int smem = 2 * TMA_STAGES * TMA_TILE_BYTES + 1024;
+    static RvPerDevice configured;
+    if (int e = rv_configure_smem(configured, flash_decode_tma_kernel<TMA_STAGES>, smem)) return e;
+    const dim3 grid(p.row_tiles * p.num_splits, p.nkv, num_seqs);
+    RV_LAUNCH_ST = rv_launch(flash_decode_tma_kernel<TMA_STAGES>, grid, dim3(TMA_THREADS), smem, stream, map_kv, p, status, early);
+    st = rv_launch_status();
+    if (st != RV_OK) return st;
+    if (num_splits > 1) {
+        RV_LAUNCH_ST = rv_launch(flash_combine_kernel, dim3(n_tokens * nh), dim3((HEAD_DIM + 31) / 32 * 32), 0, stream,
+                                 p.part_o, p.part_ml, p.out, n_tokens * nh, num_splits);
+        return rv_launch_status();
+    }
+    return RV_OK;
+#else
+    return RV_ERR_UNSUPPORTED;
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -82,6 +82,8 @@ class CudaKernels:
     DECODE_L2_AHEAD = 6          # k blocks of weights, beyond its stages, that a decode GEMM's CTA asks into L2 before its wait
     CLUSTER_MAX_ROWS = 32        # (with 64 rows one CTA fits an SM and the library's GEMM is faster)
     CLUSTER_TARGET_CTAS = 225    # of such a product, tiles x splits (measured best at 8B, 7B and 32B layer sizes)
+    TMA_DECODE = True       # decode attention's tiles come by TMA (head sizes 64 / 128, pages of 8 keys or more) ...
+    TMA_DECODE_EARLY = True   # ... and keys older than the step's own are requested before the wait for the kernel before
     BALANCED_DECODE = True  # decode attention by the kernel that cuts all tiles evenly over resident CTAs ...
     BALANCED_MIN_PAIRS = 256  # ... from this many (sequence, kv head) pairs on
     FUSED_QKV_PREFILL = True  # from TCGEN05_MIN_ROWS rows on the prefill GEMM rotates and writes the cache in its epilogue
@@ -268,22 +270,46 @@ class CudaKernels:
                 if self._balanced_ok(meta, group, num_kv_heads):
                     self.flash_decode_balanced(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window)
                 else:
-                    self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
-                                         mode=1, q_filter=1, max_q_len=1)
+                    self.decode_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, q_filter=1)
             return out
         if meta.max_q_len == 1:
             if self._balanced_ok(meta, group, num_kv_heads):
                 self.flash_decode_balanced(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window)
             else:
-                self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
-                                     mode=1, num_splits=self.decode_splits(meta, num_heads, num_kv_heads))
+                self.decode_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
+                                      num_splits=self.decode_splits(meta, num_heads, num_kv_heads))
         elif meta.num_decode == 0:
             self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, mode=0)
         else:
             self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
                                  mode=0, q_filter=2)
-            self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
-                                 mode=1, q_filter=1, max_q_len=1)
+            self.decode_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, q_filter=1)
+        return out
+
+    def decode_attention(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
+                         num_splits=1, q_filter=0, status=None, tma=None, early=None):
+        """Attention of the step's one-token sequences (all of them, or with q_filter 1 those among
+        longer ones) with the decode tiling, the keys split over `num_splits` CTAs: the tiles come by
+        TMA where the kernel is built for the sizes (head size 64 or 128, pages of 8 keys or more),
+        by cp.async otherwise; both give the same bits."""
+        tma = self.TMA_DECODE if tma is None else tma
+        if not tma or head_dim not in (64, 128) or cache_layer.shape[3] < 8:
+            return self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
+                                        mode=1, num_splits=num_splits, q_filter=q_filter, max_q_len=1)
+        _need(q, "q", torch.bfloat16, 2); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
+        lib = self._lib("attention_flash.cu", (f"-DHEAD_DIM={head_dim}",))
+        T = q.shape[0]
+        scratch = None
+        if num_splits > 1:
+            scratch = torch.empty((num_splits * T * num_heads * (head_dim + 2),), dtype=torch.float32, device=q.device)
+        early = self.TMA_DECODE_EARLY if early is None else early
+        st = lib.rv_flash_decode_tma(
+            _ptr(q), _ptr(cache_layer), ctypes.c_longlong(cache_layer.shape[0]), _ptr(meta.block_tables), _ptr(meta.cu_seqlens),
+            _ptr(meta.ctx_lens), _ptr(out), _ptr(scratch), c_int(T), c_int(meta.num_seqs), c_int(num_heads), c_int(num_kv_heads),
+            c_int(head_dim), c_int(cache_layer.shape[3]), c_int(meta.max_blocks), c_float(scale), c_int(window or 0), c_int(1),
+            c_int(num_splits), c_int(q_filter), _ptr(status if status is not None else self._status),
+            c_int(1 if (early and self.pdl) else 0), self._stream())
+        _check("flash_decode_tma", st)
         return out
 
     def decode_splits(self, meta: AttentionMeta, num_heads: int, num_kv_heads: int) -> int:

@@ -47,6 +47,7 @@ def main(argv=None) -> int:
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--splits", type=int, default=0, help="key splits of the decode attention (0: the library's choice)")
+    ap.add_argument("--variant", default="", help="decode_attention: tma | cpasync | balanced (default: the library's choice)")
     args = ap.parse_args(argv)
     K = get_library("cuda:0")
     torch.manual_seed(0)
@@ -90,27 +91,37 @@ def main(argv=None) -> int:
         else:
             B, q_lens, ctx = 1, [args.tokens], args.tokens
         MB = (ctx + ps - 1) // ps
-        cache = torch.randn(B * MB, 2, nkv, ps, hd, device=dev).bfloat16()
-        bt = torch.arange(B * MB, dtype=torch.int32, device=dev).view(B, MB)
+        # several copies of the cache in one layer, used in turn, so that L2 does not serve the keys
+        kv_one = B * ctx * 2 * nkv * hd * 2
+        copies = 1 if args.kernel != "decode_attention" else max(2, int(300e6 // kv_one) + 1)
+        cache = torch.randn(copies * B * MB, 2, nkv, ps, hd, device=dev).bfloat16()
+        bts = [(torch.arange(B * MB, dtype=torch.int32, device=dev) + c * B * MB).view(B, MB) for c in range(copies)]
+        bt = bts[0]
         T = sum(q_lens)
         q = torch.randn(T, nh * hd, device=dev).bfloat16()
         cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev)
         ctxs = torch.full((B,), ctx, dtype=torch.int32, device=dev)
         seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(q_lens)]).to(dev)
         meta = AttentionMeta(bt, cu, ctxs, seq, None, B, max(q_lens), ctx, ps, sum(1 for n in q_lens if n == 1))
-        if args.kernel == "decode_attention" and args.splits > 0:
+        metas = [AttentionMeta(b, cu, ctxs, seq, None, B, max(q_lens), ctx, ps, sum(1 for n in q_lens if n == 1)) for b in bts]
+        if args.kernel == "decode_attention" and (args.splits > 0 or args.variant):
             o = torch.empty_like(q)
-            fn = lambda: K.flash_attention(q, cache, meta, o, nh, nkv, hd, hd ** -0.5, None, mode=1, num_splits=args.splits)
+            splits = args.splits or K.decode_splits(meta, nh, nkv)
+            if args.variant == "balanced":
+                fn = lambda m: K.flash_decode_balanced(q, cache, m, o, nh, nkv, hd, hd ** -0.5, None)
+            else:
+                fn = lambda m: K.decode_attention(q, cache, m, o, nh, nkv, hd, hd ** -0.5, None, num_splits=splits,
+                                                  tma=args.variant != "cpasync")
         else:
-            fn = lambda: K.paged_attention(q, cache, meta, nh, nkv, hd, hd ** -0.5, None)
+            fn = lambda m: K.paged_attention(q, cache, m, nh, nkv, hd, hd ** -0.5, None)
         # one CUDA graph of several launches: device time without the host's launch cost
         for _ in range(2):
-            fn()
+            fn(metas[0])
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            for _ in range(4):
-                fn()
+            for i in range(4):
+                fn(metas[i % len(metas)])
         ms = timed([graph.replay], args.iters) / 4
         kv_bytes = B * ctx * 2 * nkv * hd * 2
         out.update(batch=B, ctx=ctx, heads=nh, kv_heads=nkv, head_dim=hd, us=round(ms * 1e3, 2))

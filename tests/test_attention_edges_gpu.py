@@ -242,3 +242,52 @@ def test_prefill_attention_over_long_contexts(K, q_len, ctx, window):
     rows = [0, 1, 31, 32, 127, 128, q_len // 2, q_len - 2, q_len - 1]
     ref = rows_reference(k, v, q[rows], [ctx - q_len + r for r in rows], scale, window, nh)
     assert rel_err(out.view(q_len, nh, hd)[rows], ref) < BF16_TOL
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(32, 8, 128, 16, None), (8, 2, 64, 8, 100), (28, 4, 128, 64, None),
+                                                  (6, 6, 64, 128, 333), (16, 1, 128, 32, None)])
+def test_tma_fed_decode_attention_gives_the_bits_of_the_cp_async_kernel(K, nh, nkv, hd, page, window):
+    """The decode kernel whose tiles come by TMA against the one that copies them with cp.async:
+    the same arithmetic in the same order, so the same bits - for every split count, with and
+    without requesting keys before the wait for the preceding kernel, with pages given back below
+    the window, for one-token sequences among longer ones (q_filter), and with far more CTAs than
+    stay resident at once, so that later CTAs inherit the shared memory of earlier ones."""
+    scale = 1 / math.sqrt(hd)
+    g = torch.Generator().manual_seed(hd + page)
+    contexts = [1, 7, 64, 65, 500, 1027, 2049, 130]
+    ks = [torch.randn(c, nkv, hd, generator=g) for c in contexts]
+    vs = [torch.randn(c, nkv, hd, generator=g) for c in contexts]
+    B = len(contexts)
+    cache, meta = paged_setup(ks, vs, [1] * B, page, torch.bfloat16, window=window)
+    q = torch.randn(B, nh * hd, generator=g).cuda().bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    plain = K.paged_attention_plain(q, cache, meta, nh, nkv, hd, scale, window)
+    for splits in (1, 2, 5, 16, 40):
+        want = K.decode_attention(q, cache, meta, torch.zeros_like(q), nh, nkv, hd, scale, window, num_splits=splits, tma=False)
+        for early in (False, True):
+            got = K.decode_attention(q, cache, meta, torch.full_like(q, 9.0), nh, nkv, hd, scale, window, num_splits=splits,
+                                     tma=True, early=early, status=status)
+            assert torch.equal(got, want), f"{splits} splits, early={early}"
+        assert rel_err(want, plain.double()) < BF16_TOL
+    assert int(status.item()) == 0
+    # one-token sequences among longer ones: only they are touched
+    q_lens = [1, 20, 1, 3, 1]
+    ctxs = [300, 20, 64, 700, 1]
+    ks = [torch.randn(c, nkv, hd, generator=g) for c in ctxs]
+    vs = [torch.randn(c, nkv, hd, generator=g) for c in ctxs]
+    cache, meta = paged_setup(ks, vs, q_lens, page, torch.bfloat16, window=window)
+    q = torch.randn(sum(q_lens), nh * hd, generator=g).cuda().bfloat16()
+    want = K.decode_attention(q, cache, meta, torch.full_like(q, 9.0), nh, nkv, hd, scale, window, q_filter=1, tma=False)
+    got = K.decode_attention(q, cache, meta, torch.full_like(q, 9.0), nh, nkv, hd, scale, window, q_filter=1, tma=True, status=status)
+    assert torch.equal(got, want) and float((got[1:21].float() - 9.0).abs().max()) == 0.0
+    # 2,000 CTAs of two to three tiles each: several waves on every SM
+    many = 250 if nkv >= 4 else 600
+    ctxs = [130 + (37 * i) % 60 for i in range(many)]
+    ks = [torch.randn(c, nkv, hd, generator=g) for c in ctxs]
+    cache, meta = paged_setup(ks, ks, [1] * many, page, torch.bfloat16)
+    q = torch.randn(many, nh * hd, generator=g).cuda().bfloat16()
+    want = K.decode_attention(q, cache, meta, torch.zeros_like(q), nh, nkv, hd, scale, None, tma=False)
+    for _ in range(3):
+        got = K.decode_attention(q, cache, meta, torch.full_like(q, 9.0), nh, nkv, hd, scale, None, tma=True, status=status)
+        assert torch.equal(got, want)
+    assert int(status.item()) == 0
