@@ -5,10 +5,15 @@
 //   S = Q K^T        tcgen05.mma, Q [128 x hd] and K [64 x hd] K-major in shared memory (TMA,
 //                    128-byte swizzle), S [128 x 64] float in tensor memory;
 //   softmax          four warps, one thread per row: tcgen05.ld of the row, scale, causal / window
-//                    mask, running maximum and sum in float, P = exp2(s - m) written as bfloat16
-//                    into shared memory in the swizzled K-major layout;
-//   O += P V         tcgen05.mma, V [64 keys x hd] as the MN-major B operand straight from the
-//                    cache's [key][hd] pages, O [128 x hd] float accumulated in tensor memory.
+//                    mask, running maximum and sum in float, P = exp2(s - m) packed as bfloat16
+//                    pairs and written back into tensor memory (tcgen05.st) over the first half of
+//                    the S buffer it came from;
+//   O += P V         tcgen05.mma with P as the A operand FROM TENSOR MEMORY and V [64 keys x hd] as
+//                    the MN-major B operand straight from the cache's [key][hd] pages, O [128 x hd]
+//                    float accumulated in tensor memory.
+// P never passes through shared memory, and because P(i) lives in S buffer i mod 2, the softmax of
+// tile i + 1 does not have to wait for the P V product of tile i: softmax and tensor core run side
+// by side, the products ordered among themselves by the order in which the one thread issues them.
 // The reference maximum of a row is only raised when the true maximum has grown by more than 2^8
 // (then O is rescaled in tensor memory), so most tiles need no pass over O; the final division
 // by the row sum uses the same reference.  One thread issues all TMA loads and MMAs; pages are
@@ -31,10 +36,9 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "this kernel is built for head 
 #define HALVES (HEAD_DIM / 64)                 // 64-element (128-byte) slabs of the head dimension
 #define Q_BYTES (ROWS * HEAD_DIM * 2)
 #define KV_BYTES (KV_TILE * HEAD_DIM * 2)      // one of K or V for a tile
-#define P_BYTES (ROWS * KV_TILE * 2)
 #define NUM_THREADS 192               // 4 softmax warps, 1 loader warp, 1 MMA warp
 #define TMEM_COLS 256
-#define S_COL 0                   // two S buffers: columns 0-63 and 64-127
+#define S_COL 0                   // two S buffers: columns 0-63 and 64-127; P (bf16 pairs) reuses the first 32 columns of each
 #define O_COL 128
 #define RESCALE_LOG2 8.0f
 
@@ -70,6 +74,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows in the 128 lanes, 16 bf16 of K in 8 columns) from tensor memory
+__device__ __forceinline__ void tcgen05_mma_bf16_ts(uint32_t tmem_c, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                                    uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_c), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // MN-major operand with 128-byte swizzle (V as [key][hd]): 64 consecutive hd elements are one
@@ -94,10 +105,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     unsigned char* q_s = smem_raw;                           // [HALVES][128 rows x 128 B]
     unsigned char* k_s = q_s + Q_BYTES;                      // [2 stages][HALVES][64 keys x 128 B]
     unsigned char* v_s = k_s + 2 * KV_BYTES;                 // [2 stages][HALVES][64 keys x 128 B]
-    unsigned char* p_s = v_s + 2 * KV_BYTES;                 // [128 rows x 128 B]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + P_BYTES);       // 13 barriers
-    uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 13);
-    volatile int& abort_flag = *reinterpret_cast<volatile int*>(bars + 14);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * KV_BYTES);  // 15 barriers
+    uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 15);
+    volatile int& abort_flag = *reinterpret_cast<volatile int*>(bars + 16);
 
     rv_pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -105,7 +115,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const uint32_t bar_v0 = smem_u32(&bars[3]);                                      // v full [2]
     const uint32_t bar_vfree0 = smem_u32(&bars[5]);                                  // v free [2]
     const uint32_t bar_s_full0 = smem_u32(&bars[7]), bar_s_free0 = smem_u32(&bars[9]);   // [2] each
-    const uint32_t bar_p_full = smem_u32(&bars[11]), bar_o_full = smem_u32(&bars[12]);
+    // The P V product of tile i reports on o_full[i mod 2]: a thread that follows every phase of both barriers
+    // in order, and looks at product i - 2 before it lets product i start, is never more than one phase behind
+    // either of them (with one barrier a warp that ran late could not tell phase i - 1 from phase i + 1).
+    // P of tile i is announced on p_full[i mod 2] as well: a softmax warp may run one tile ahead of the
+    // slowest one (it no longer waits for the product of the tile before), and its arrival for tile i + 1
+    // must not be counted among the four of tile i.
+    const uint32_t bar_o_full0 = smem_u32(&bars[11]), bar_p_full0 = smem_u32(&bars[13]);      // o full [2], p full [2]
 
     // Row tiles late in the prompt see the most keys.  CTAs are handed out in the order of their
     // linear index (x fastest), so the row tile is the slowest index, counted down: all heads' and
@@ -137,7 +153,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         mbar_init(bar_s_full0, 1); mbar_init(bar_s_full0 + 8, 1);
         // the softmax warps arrive once per warp (after a warp barrier), not once per thread
         mbar_init(bar_s_free0, 4); mbar_init(bar_s_free0 + 8, 4);
-        mbar_init(bar_p_full, 4); mbar_init(bar_o_full, 1);
+        mbar_init(bar_p_full0, 4); mbar_init(bar_p_full0 + 8, 4); mbar_init(bar_o_full0, 1); mbar_init(bar_o_full0 + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 4) {
@@ -236,15 +252,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
                 if (!(ok = mbar_wait(bar_v0 + 8 * b, (it >> 1) & 1, &abort_flag, 7))) break;
                 // O += P V once the softmax warps have written P (and rescaled O if they had to)
-                if (!(ok = mbar_wait(bar_p_full, it & 1, &abort_flag, 8))) break;
+                if (!(ok = mbar_wait(bar_p_full0 + 8 * b, (it >> 1) & 1, &abort_flag, 8))) break;
                 tcgen05_fence_after();
-                const uint64_t dp = umma_desc(smem_u32(p_s));
+                const uint32_t tp = tmem_base + S_COL + b * KV_TILE;     // P(it): bf16 pairs in the first 32 columns of S buffer b
                 const uint64_t dv = umma_desc_mn(smem_u32(v_s) + b * KV_BYTES, KV_TILE * 128);
 #pragma unroll
-                for (int j = 0; j < KV_TILE / 16; ++j)   // 16 keys per MMA: 32 bytes along P's rows, 2048 bytes down V
-                    tcgen05_mma_bf16(tmem_base + O_COL, dp + (uint64_t)(2 * j), dv + (uint64_t)(128 * j), idesc_o, (it | j) != 0);
+                for (int j = 0; j < KV_TILE / 16; ++j)   // 16 keys per MMA: 8 columns along P's rows, 2048 bytes down V
+                    tcgen05_mma_bf16_ts(tmem_base + O_COL, tp + 8 * j, dv + (uint64_t)(128 * j), idesc_o, (it | j) != 0);
                 tcgen05_commit(bar_vfree0 + 8 * b);
-                tcgen05_commit(bar_o_full);
+                tcgen05_commit(bar_o_full0 + 8 * b);
             }
         }
     } else {
@@ -257,9 +273,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
         const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
         float m_ref = -INFINITY, l_run = 0.f;
-        const int row_local = warp * 32 + lane;
-        unsigned char* p_row0 = p_s + (row_local >> 3) * 1024 + (row_local & 7) * 128;
         bool ok = true;
+        bool prev_waited = false;    // whether this iteration's rescale has already waited for the product of the tile before
         for (int t = t_begin; t < t_end; ++t) {
             const int it = t - t_begin;
             const int sb = it & 1;
@@ -306,17 +321,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 m_ref = m_tile;
                 l_run *= factor;
             }
-            // The P V product of the tile before must be complete before P is overwritten (S of this
-            // tile was produced ahead of it) and before O is rescaled.
+            // P(it) goes into S buffer sb, which no product reads any more (P(it - 2) was consumed before
+            // S(it) was produced), so only a rescale of O has to wait for the P V product of the tile before.
 #ifdef ATTN_TRACE
             if (tr) p.status[8 + it * 5 + 2] = (int)clock64();
 #endif
-            if (it > 0 && !mbar_wait(bar_o_full, (it - 1) & 1, &abort_flag, 11)) { ok = false; break; }
-#ifdef ATTN_TRACE
-            if (tr) p.status[8 + it * 5 + 3] = (int)clock64();
-#endif
+            // product it - 2 (finished before S(it) was produced) is looked at before product it may start,
+            // unless the rescale of the tile before has looked at it already
+            if (it >= 2 && !prev_waited &&
+                !mbar_wait(bar_o_full0 + 8 * (it & 1), ((it - 2) >> 1) & 1, &abort_flag, 12)) { ok = false; break; }
+            prev_waited = false;
             const bool any_raise = __any_sync(0xffffffffu, raise && it > 0);
             if (any_raise) {
+                // O is rescaled: the product of the tile before must have finished
+                if (!mbar_wait(bar_o_full0 + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1, &abort_flag, 11)) { ok = false; break; }
+                prev_waited = true;
                 tcgen05_fence_after();
 #pragma unroll
                 for (int c = 0; c < HEAD_DIM; c += 32) {
@@ -330,37 +349,36 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tmem_st_wait();
                 tcgen05_fence_before();
             }
+#ifdef ATTN_TRACE
+            if (tr) p.status[8 + it * 5 + 3] = (int)clock64();
+#endif
             const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-            unsigned char* p_row = p_row0;
             float l_tile = 0.f, l_tile2 = 0.f;
+            uint32_t pk[32];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {                    // 8 chunks of 8 keys = 16 bytes
-                uint4 v;
-                uint32_t* w = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int e = c * 8 + 2 * j;
-                    const float x0 = fast_exp2(fmaf(__uint_as_float(e < 32 ? s0[e] : s1[e - 32]), p.scale_log2e, neg_m));
-                    const float x1 = fast_exp2(fmaf(__uint_as_float(e + 1 < 32 ? s0[e + 1] : s1[e + 1 - 32]), p.scale_log2e, neg_m));
-                    l_tile += x0;
-                    l_tile2 += x1;
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(x0, x1);
-                    w[j] = *reinterpret_cast<uint32_t*>(&h2);
-                }
-                *reinterpret_cast<uint4*>(p_row + ((c ^ (row_local & 7)) << 4)) = v;
+            for (int j = 0; j < 32; ++j) {                   // keys 2j and 2j + 1 of the tile: one column of P
+                const int e = 2 * j;
+                const float x0 = fast_exp2(fmaf(__uint_as_float(e < 32 ? s0[e] : s1[e - 32]), p.scale_log2e, neg_m));
+                const float x1 = fast_exp2(fmaf(__uint_as_float(e + 1 < 32 ? s0[e + 1] : s1[e + 1 - 32]), p.scale_log2e, neg_m));
+                l_tile += x0;
+                l_tile2 += x1;
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(x0, x1);
+                pk[j] = *reinterpret_cast<uint32_t*>(&h2);
             }
             l_tile += l_tile2;
             l_run += l_tile;
-            fence_async_smem();
+            tmem_st_32x32(t_lane + S_COL + sb * KV_TILE, pk);
+            tmem_st_wait();
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_p_full);
+            if (lane == 0) mbar_arrive(bar_p_full0 + 8 * sb);
 #ifdef ATTN_TRACE
             if (tr) p.status[8 + it * 5 + 4] = (int)clock64();
 #endif
         }
         if (ok) {
-            ok = mbar_wait(bar_o_full, (n_it - 1) & 1, &abort_flag, 10);
+            // the last product (the one before it, on the other barrier, finished earlier: products run in order)
+            ok = mbar_wait(bar_o_full0 + 8 * ((n_it - 1) & 1), ((n_it - 1) >> 1) & 1, &abort_flag, 10);
             tcgen05_fence_after();
             if (ok) {
                 const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -442,7 +460,7 @@ RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long n
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.window = window;
-    const int smem = Q_BYTES + 4 * KV_BYTES + P_BYTES + 256;
+    const int smem = Q_BYTES + 4 * KV_BYTES + 256;
     static RvPerDevice configured;
     if (int e = rv_configure_smem(configured, attention_tcgen05_kernel, smem)) return e;
     const dim3 grid(nkv, num_seqs, (max_q_len * G + ROWS - 1) / ROWS);
