@@ -41,7 +41,9 @@
 
 #define TILE_F 128           // output features per tile (UMMA M)
 #define BK 64
-#define STAGES 4
+// stages of the TMA ring: four, or three for 33 to 64 rows, whose wider activation tiles and cluster buffers
+// would otherwise leave room for only one CTA per SM
+#define STAGES_FOR(MB) ((MB) > 32 && (MB) <= 64 ? 3 : 4)
 #define UMMA_K 16
 #define A_BYTES (TILE_F * BK * 2)
 #define NUM_THREADS 192
@@ -244,9 +246,10 @@ __device__ __forceinline__ void finish_from_parts(const DecodeGemmParams& p, int
 }
 
 template <int MB>
-__global__ void __launch_bounds__(NUM_THREADS, MB <= 16 ? 3 : 2)
+__global__ void __launch_bounds__(NUM_THREADS, (MB <= 16 || MB == 64) ? 3 : 2)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    const DecodeGemmParams p) {
+    constexpr int STAGES = STAGES_FOR(MB);
     constexpr int B_BYTES = MB * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int TMEM_COLS = MB < 32 ? 32 : MB;
@@ -658,6 +661,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 template <int MB>
 static int launch_decode(const CUtensorMap& mw, const CUtensorMap& mx, const DecodeGemmParams& p, cudaStream_t stream) {
+    constexpr int STAGES = STAGES_FOR(MB);
     const int stage = A_BYTES + MB * BK * 2;
     const int fin = TILE_F * (MB + 1) * 4;
     int smem = (STAGES * stage > fin ? STAGES * stage : fin) + 1024;
