@@ -65,7 +65,9 @@ def test_bfloat16_batch_of_32_in_one_chain_of_dependent_launches():
     kernel run between this project's own GEMMs (cluster reduce, rotation in the epilogue), every
     kernel launched while its predecessor still runs.  A kernel that wrote before its wait for the
     predecessor once corrupted a buffer still in use; so: no error, the same tokens twice, and the
-    same tokens as with eager steps."""
+    same tokens as with eager steps - except that a graph, laid out for its bucket's longest context,
+    may split the keys differently from an eager step, so a request may part from its eager run at a
+    token whose two best logits lie within bfloat16's reach of one another (checked), nowhere else."""
     from rvllm_b200 import SamplingParams
     wide = dict(MID, num_attention_heads=16, num_key_value_heads=8, head_dim=32, hidden_size=512)
     g = torch.Generator().manual_seed(2)
@@ -84,5 +86,18 @@ def test_bfloat16_batch_of_32_in_one_chain_of_dependent_launches():
     assert any(k[0] == 32 for k in llm.engine.runner._graphs), "the 32-row decode graph should have been used"
     b, _ = go()
     assert a == b
-    c, _ = go(enforce_eager=True)
-    assert a == c
+    c, eager = go(enforce_eager=True)
+    from rvllm_b200.engine import StepEntry
+    parted = 0
+    for prompt, ta, tc in zip(prompts, a, c):
+        j = next((i for i in range(len(ta)) if ta[i] != tc[i]), None)
+        if j is None:
+            continue
+        parted += 1
+        ids = list(prompt) + ta[:j]
+        logits = eager.engine.runner.step([StepEntry("margin", ids, [len(ids) - 1])])[0].float()
+        eager.engine.runner.finish("margin")
+        top = torch.topk(logits, 2)
+        assert {ta[j], tc[j]} == set(top.indices.tolist()), "the two runs chose the two best tokens"
+        assert float(top.values[0] - top.values[1]) / float(logits.abs().max()) < 2e-2, "and these lie within rounding"
+    assert parted <= 3
