@@ -12,6 +12,14 @@
 //   the draw is the first token, in vocabulary order, whose cumulated kept mass exceeds
 //   u * (kept mass), with u = Philox4x32-10(key = seed, counter = index of the output token).
 // The uniform depends on (seed, output index) only, never on the batch a row is sampled in.
+//
+// Rows with a top-k take two passes over the row (maximum + counts per bin of the top 12 bits of the
+// ordered bit pattern, then the candidates from the k-th token's bin upwards and the whole mass), rows
+// with a top-p alone three (arg-max, counts and fixed-point masses per bin, candidates); the at most
+// 2,048 candidates are sorted and cut exactly in the first CTA's shared memory.  Rows whose candidates
+// do not fit (a flat distribution under top-p alone, a k beyond 2,048) take the general search: eight
+// passes of four bits over the row.  All sums that decide anything are integers or are added in a fixed
+// order, so a token depends neither on the run nor on how many CTAs share the row.
 #include "common.cuh"
 
 #define SAMPLE_THREADS 1024
@@ -174,6 +182,383 @@ __device__ __forceinline__ void slice_scan(const float* row, int lo_s, int hi_s,
     upto = s_incl[tid];
 }
 
+// ---------------------------------------------------------------------------------------------
+// The short way to the top-k / top-p threshold: three passes over the row instead of eleven.
+//
+// Pass 1 (arg-max) has given the row's maximum m.  Pass 2 builds ONE histogram of the row over the top
+// 12 bits of the ordered bit pattern (sign, exponent, three bits of mantissa: 4,096 bins): tokens per bin
+// and their mass exp((v - m) / T) as a 40-bit fixed-point integer, added with integer atomics in shared
+// memory - so the sums do not depend on the order of the additions, on the number of CTAs that share the
+// row or on the run.  The CTAs of a row add their bins into the first CTA's histogram through distributed
+// shared memory.  From the top bin downwards the first CTA finds the bin in which the k-th token lies and
+// the bin in which the cumulated mass reaches top_p x (the whole mass); the threshold lies in the higher
+// of the two, and every token from that bin upwards is a candidate.  If there are at most FAST_CANDIDATES
+// of them (a peaked distribution, or a small k), pass 3 gathers them - ordered bit pattern and index, in
+// any order - into the first CTA's shared memory, where they are sorted (bitonic, by value then index:
+// a total order, so the result is the same whatever order they arrived in), cut exactly by count and by
+// cumulated mass, sorted back into vocabulary order and drawn from.  Otherwise (a flat distribution under
+// top-p alone, a huge k) the kernel goes on with the general search below.
+#define FAST_BINS 4096
+#define FAST_CANDIDATES 2048
+#define FAST_SCALE 1099511627776.0f      // 2^40
+
+__device__ __forceinline__ void sc_red_add(uint32_t addr, unsigned int v) { asm volatile("red.shared::cluster.add.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+__device__ __forceinline__ void sc_red_add(uint32_t addr, unsigned long long v) { asm volatile("red.shared::cluster.add.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory"); }
+__device__ __forceinline__ unsigned int sc_atom_add(uint32_t addr, unsigned int v) {
+    unsigned int old;
+    asm volatile("atom.shared::cluster.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
+    return old;
+}
+__device__ __forceinline__ void sc_store(uint32_t addr, unsigned long long v) { asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory"); }
+__device__ __forceinline__ float key_value(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+
+// Bitonic sort of n_pad (a power of two, <= 2 * SAMPLE_THREADS) 64-bit keys in shared memory, descending.
+__device__ void sort_desc(unsigned long long* a, int n_pad) {
+    for (int k = 2; k <= n_pad; k <<= 1)
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int t = threadIdx.x; t < n_pad / 2; t += SAMPLE_THREADS) {
+                const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1)), l = i | j;          // the pair (i, i + j)
+                const bool desc = (i & k) == 0;
+                const unsigned long long x = a[i], y = a[l];
+                if ((x < y) == desc) { a[i] = y; a[l] = x; }
+            }
+            __syncthreads();
+        }
+}
+
+// Inclusive sums of n (<= 2 * SAMPLE_THREADS) floats in shared memory, in place, in index order: thread t owns
+// elements 2t and 2t + 1; warp scans by shuffles, warp totals through s_scan.  The same order every time.
+__device__ void scan_inclusive(float* a, int n, float* s_scan) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float x0 = 2 * tid < n ? a[2 * tid] : 0.f, x1 = 2 * tid + 1 < n ? a[2 * tid + 1] : 0.f;
+    float incl = x0 + x1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    __syncthreads();
+    if (lane == 31) s_scan[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        float w = s_scan[lane], wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float v = __shfl_up_sync(0xffffffffu, wi, o);
+            if (lane >= o) wi += v;
+        }
+        s_scan[lane] = wi - w;
+    }
+    __syncthreads();
+    const float before = s_scan[warp] + incl - (x0 + x1);
+    if (2 * tid < n) a[2 * tid] = before + x0;
+    if (2 * tid + 1 < n) a[2 * tid + 1] = before + x0 + x1;
+    __syncthreads();
+}
+
+struct FastShared {
+    unsigned int n_cand;        // candidates gathered so far (in the first CTA)
+    int go;                     // 1: the short way serves the row; 0: the general search
+    int bin;                    // candidates are the tokens from this bin upwards
+    int kept, pick;
+    unsigned long long z_q;     // the row's whole mass, fixed point
+};
+
+// The first CTA's end of the short way: sort the gathered candidates, cut by count and by mass, draw.
+__device__ void short_way_finish(unsigned long long* cand, float* cmass, float m, float inv_t, int k, float pp, bool use_k, bool use_p,
+                                 unsigned long long seed, long long draw, int* out_token, float* s_scan, FastShared* fs) {
+    const int tid = threadIdx.x;
+    const int n = (int)min(fs->n_cand, (unsigned int)FAST_CANDIDATES);
+    int n_pad = 2;
+    while (n_pad < n) n_pad <<= 1;
+    for (int i = n + tid; i < n_pad; i += SAMPLE_THREADS) cand[i] = 0ull;       // sorts behind every candidate
+    __syncthreads();
+    sort_desc(cand, n_pad);
+    // masses in descending order of value and their running sums
+    for (int i = tid; i < n; i += SAMPLE_THREADS) cmass[i] = expf((key_value((uint32_t)(cand[i] >> 32)) - m) * inv_t);
+    __syncthreads();
+    scan_inclusive(cmass, n, s_scan);
+    // the threshold: the value of the k-th candidate, and of the first whose running sum reaches top_p x the whole mass
+    __shared__ unsigned int s_tau_k, s_tau_p;
+    if (tid == 0) {
+        s_tau_k = use_k ? (uint32_t)(cand[min(k, n) - 1] >> 32) : 0u;
+        s_tau_p = 0u;
+    }
+    __syncthreads();
+    if (use_p) {
+        const float target = pp * (float)((double)fs->z_q * (1.0 / (double)FAST_SCALE));
+        for (int i = tid; i < n; i += SAMPLE_THREADS)
+            if (cmass[i] >= target && (i == 0 || cmass[i - 1] < target)) s_tau_p = (uint32_t)(cand[i] >> 32);
+    }
+    __syncthreads();
+    const uint32_t tau = max(s_tau_k, s_tau_p);
+    // kept: the candidates whose value is at least the threshold - a prefix of the sorted list
+    for (int i = tid; i < n; i += SAMPLE_THREADS)
+        if ((uint32_t)(cand[i] >> 32) >= tau && (i + 1 == n || (uint32_t)(cand[i + 1] >> 32) < tau)) fs->kept = i + 1;
+    __syncthreads();
+    const int L = fs->kept;
+    // back into vocabulary order: (index, mass bits), ascending = descending of the complement
+    int l_pad = 2;
+    while (l_pad < L) l_pad <<= 1;
+    for (int i = tid; i < l_pad; i += SAMPLE_THREADS) {
+        unsigned long long w = 0ull;
+        if (i < L) {
+            const uint32_t key = (uint32_t)(cand[i] >> 32), inv_idx = (uint32_t)cand[i];
+            w = ((unsigned long long)inv_idx << 32) | (unsigned long long)__float_as_uint(expf((key_value(key) - m) * inv_t));
+        }
+        cand[i] = w;
+    }
+    __syncthreads();
+    sort_desc(cand, l_pad);                               // descending complemented index = ascending index; padding (0) last
+    for (int i = tid; i < L; i += SAMPLE_THREADS) cmass[i] = __uint_as_float((uint32_t)cand[i]);
+    __syncthreads();
+    scan_inclusive(cmass, L, s_scan);
+    uint32_t c4[4] = {(uint32_t)(draw & 0xffffffffll), (uint32_t)((unsigned long long)draw >> 32), 0u, 0u};
+    philox4x32_10(c4, (uint32_t)(seed & 0xffffffffull), (uint32_t)(seed >> 32));
+    const float u = (float)(c4[0] >> 8) * (1.0f / 16777216.0f);
+    const float t_draw = u * cmass[L - 1];
+    for (int i = tid; i < L; i += SAMPLE_THREADS)
+        if (cmass[i] > t_draw && (i == 0 || cmass[i - 1] <= t_draw)) fs->pick = i;
+    __syncthreads();
+    if (tid == 0) {
+        const int pick = fs->pick >= 0 ? fs->pick : L - 1;           // rounding put the target at the kept mass: the last kept token
+        *out_token = (int)(0xffffffffu - (uint32_t)(cand[pick] >> 32));
+    }
+}
+
+// Returns true if the row has been sampled (out[r] written by the first CTA); false: go on with the general search.
+__device__ bool sample_short_way(const float* __restrict__ row, int V, float m, float inv_t, int k, float pp, bool use_k, bool use_p,
+                                 unsigned long long seed, long long draw, int* out_token, unsigned char* s_dyn, float* s_scan,
+                                 FastShared* fs) {
+    const int CL = gridDim.x, rank = (int)sc_rank(), tid = threadIdx.x;
+    unsigned int* h_cnt = reinterpret_cast<unsigned int*>(s_dyn);                                   // [FAST_BINS]
+    unsigned long long* h_mass = reinterpret_cast<unsigned long long*>(s_dyn + FAST_BINS * 4);      // [FAST_BINS]
+    unsigned long long* cand = h_mass + FAST_BINS;                                                  // [FAST_CANDIDATES]
+    float* cmass = reinterpret_cast<float*>(cand + FAST_CANDIDATES);                                // [FAST_CANDIDATES]
+    for (int b = tid; b < FAST_BINS; b += SAMPLE_THREADS) { h_cnt[b] = 0u; h_mass[b] = 0ull; }
+    if (tid == 0) { fs->n_cand = 0u; fs->go = 0; fs->bin = 0; fs->kept = 0; fs->pick = -1; fs->z_q = 0ull; }
+    __syncthreads();
+    // this CTA's share of the row
+    const int per = (((V + CL - 1) / CL) + 3) & ~3;
+    const int lo = min(V, rank * per), hi = min(V, lo + per);
+    for (int i = lo + tid; i < hi; i += SAMPLE_THREADS) {
+        const float v = row[i];
+        if (v != v) continue;
+        const uint32_t bin = order_key(v) >> 20;
+        atomicAdd(&h_cnt[bin], 1u);
+        atomicAdd(&h_mass[bin], __float2ull_rz(expf((v - m) * inv_t) * FAST_SCALE));
+    }
+    sc_sync();                                            // every CTA's histogram is complete (and the first CTA's is no longer being zeroed)
+    if (rank != 0) {
+        for (int b = tid; b < FAST_BINS; b += SAMPLE_THREADS)
+            if (h_cnt[b]) { sc_red_add(sc_map(&h_cnt[b], 0), h_cnt[b]); sc_red_add(sc_map(&h_mass[b], 0), h_mass[b]); }
+    }
+    sc_sync();
+    if (rank == 0) {
+        // cumulated counts and masses from the top bin down: thread t owns the bins 4095 - 4t ... 4092 - 4t
+        const int lane = tid & 31, warp = tid >> 5;
+        unsigned int c_own = 0u;
+        unsigned long long m_own = 0ull;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { c_own += h_cnt[FAST_BINS - 1 - 4 * tid - j]; m_own += h_mass[FAST_BINS - 1 - 4 * tid - j]; }
+        unsigned int c_inc = c_own;
+        unsigned long long m_inc = m_own;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned int cv = __shfl_up_sync(0xffffffffu, c_inc, o);
+            const unsigned long long mv = __shfl_up_sync(0xffffffffu, m_inc, o);
+            if (lane >= o) { c_inc += cv; m_inc += mv; }
+        }
+        __shared__ unsigned int w_cnt[32];
+        __shared__ unsigned long long w_mass[32];
+        __shared__ int s_bk, s_bp;
+        if (lane == 31) { w_cnt[warp] = c_inc; w_mass[warp] = m_inc; }
+        if (tid == 0) { s_bk = -1; s_bp = -1; }
+        __syncthreads();
+        unsigned int c_before = 0u, c_total = 0u;
+        unsigned long long m_before = 0ull, m_total = 0ull;
+        for (int w = 0; w < 32; ++w) {
+            if (w < warp) { c_before += w_cnt[w]; m_before += w_mass[w]; }
+            c_total += w_cnt[w]; m_total += w_mass[w];
+        }
+        c_before += c_inc - c_own;
+        m_before += m_inc - m_own;
+        // the bin of the k-th token and the bin in which the mass reaches the target: exactly one thread finds each
+        const unsigned long long target = use_p ? (unsigned long long)((double)pp * (double)m_total) : 0ull;
+        unsigned int c_run = c_before;
+        unsigned long long m_run = m_before;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int b = FAST_BINS - 1 - 4 * tid - j;
+            const unsigned int c = h_cnt[b];
+            const unsigned long long mm = h_mass[b];
+            if (use_k && c_run < (unsigned int)k && c_run + c >= (unsigned int)k) s_bk = b;
+            if (use_p && target > 0ull && m_run < target && m_run + mm >= target) s_bp = b;
+            c_run += c; m_run += mm;
+        }
+        __syncthreads();
+        // (fewer than k tokens, or a mass that rounding keeps below the target: that filter keeps everything)
+        const bool k_on = use_k && s_bk >= 0, p_on = use_p && s_bp >= 0;
+        const int bin = max(k_on ? s_bk : 0, p_on ? s_bp : 0);
+        // tokens from `bin` upwards: one more pass over the cumulated counts
+        __shared__ unsigned int s_n;
+        if (tid == 0) s_n = 0u;
+        __syncthreads();
+        {
+            unsigned int mine = 0u;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const int b = FAST_BINS - 1 - 4 * tid - j; if (b >= bin) mine += h_cnt[b]; }
+            if (mine) atomicAdd(&s_n, mine);
+        }
+        __syncthreads();
+        const bool go = (k_on || p_on) && s_n > 0u && s_n <= FAST_CANDIDATES && c_total > 0u;
+        if (tid < CL) { sc_store(sc_map(&fs->go, tid), go ? 1 : 0); sc_store(sc_map(&fs->bin, tid), bin); }
+        if (tid == 0) fs->z_q = m_total;
+    }
+    sc_sync();
+    if (!fs->go) return false;
+    // ---- pass 3: the candidates go to the first CTA, (ordered bits, complemented index) in one word
+    {
+        const uint32_t bin = (uint32_t)fs->bin;
+        const uint32_t cnt_addr = sc_map(&fs->n_cand, 0), cand_addr = sc_map(cand, 0);
+        for (int i = lo + tid; i < hi; i += SAMPLE_THREADS) {
+            const float v = row[i];
+            if (v != v) continue;
+            const uint32_t key = order_key(v);
+            if ((key >> 20) >= bin) {
+                const unsigned int pos = sc_atom_add(cnt_addr, 1u);
+                if (pos < FAST_CANDIDATES) sc_store(cand_addr + pos * 8u, ((unsigned long long)key << 32) | (unsigned long long)(0xffffffffu - (uint32_t)i));
+            }
+        }
+    }
+    sc_sync();
+    if (rank != 0) return true;                           // the first CTA finishes the row; nobody's shared memory is touched from outside any more
+    short_way_finish(cand, cmass, m, inv_t, k, pp, use_k, use_p, seed, draw, out_token, s_scan, fs);
+    return true;
+}
+
+// The short way for rows with a top-k: TWO passes over the row.  Pass A finds the row's maximum (larger value, then
+// lower index - the same whatever the order) and counts the tokens per bin; no exponential, no mass: the bin of the
+// k-th token follows from the counts alone.  Pass B gathers the tokens from that bin upwards and adds up the row's
+// whole mass as 40-bit fixed-point integers in registers (needed only for a top-p cut, which then lies among the
+// candidates or below them all).  `m_out` / `best_out` carry the maximum on to the general search if there are too
+// many candidates (a k beyond FAST_CANDIDATES, a huge tie).
+__device__ bool sample_short_way_k(const float* __restrict__ row, int V, float inv_t, int k, float pp, bool use_p,
+                                   unsigned long long seed, long long draw, int* out_token, unsigned char* s_dyn, float* s_scan,
+                                   float* s_val, int* s_idx, FastShared* fs, float& m_out, int& best_out) {
+    const int CL = gridDim.x, rank = (int)sc_rank(), tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    unsigned int* h_cnt = reinterpret_cast<unsigned int*>(s_dyn);                                   // [FAST_BINS]
+    unsigned long long* h_mass = reinterpret_cast<unsigned long long*>(s_dyn + FAST_BINS * 4);      // (unused here; keeps the layout)
+    unsigned long long* cand = h_mass + FAST_BINS;                                                  // [FAST_CANDIDATES]
+    float* cmass = reinterpret_cast<float*>(cand + FAST_CANDIDATES);                                // [FAST_CANDIDATES]
+    __shared__ float x_val[8];
+    __shared__ int x_idx[8];
+    for (int b = tid; b < FAST_BINS; b += SAMPLE_THREADS) h_cnt[b] = 0u;
+    if (tid == 0) { fs->n_cand = 0u; fs->go = 0; fs->bin = 0; fs->kept = 0; fs->pick = -1; fs->z_q = 0ull; }
+    __syncthreads();
+    const int per = (((V + CL - 1) / CL) + 3) & ~3;
+    const int lo = min(V, rank * per), hi = min(V, lo + per);
+    // ---- pass A: maximum and counts
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lo + tid; i < hi; i += SAMPLE_THREADS) {
+        const float v = row[i];
+        if (v != v) continue;
+        if (v > bv) { bv = v; bi = i; }                   // indices rise within a thread: a strict comparison keeps the lowest
+        atomicAdd(&h_cnt[order_key(v) >> 20], 1u);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        argmax_combine(bv, bi, ov, oi);
+    }
+    if (lane == 0) { s_val[warp] = bv; s_idx[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        bv = s_val[lane]; bi = s_idx[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            argmax_combine(bv, bi, ov, oi);
+        }
+        if (lane < CL) { sc_store(sc_map(&x_val[rank], lane), bv); sc_store(sc_map(&x_idx[rank], lane), bi); }
+    }
+    sc_sync();                                            // maxima exchanged, every CTA's counts complete
+    float m = -INFINITY;
+    int best = 0x7fffffff;
+    for (int c = 0; c < CL; ++c) argmax_combine(m, best, x_val[c], x_idx[c]);
+    if (best == 0x7fffffff) best = 0;
+    m_out = m; best_out = best;
+    if (rank != 0) {
+        for (int b = tid; b < FAST_BINS; b += SAMPLE_THREADS)
+            if (h_cnt[b]) sc_red_add(sc_map(&h_cnt[b], 0), h_cnt[b]);
+    }
+    sc_sync();
+    if (rank == 0) {
+        // the bin of the k-th token, counted from the top bin down: thread t owns the bins 4095 - 4t ... 4092 - 4t
+        unsigned int c_own = 0u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c_own += h_cnt[FAST_BINS - 1 - 4 * tid - j];
+        unsigned int c_inc = c_own;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned int cv = __shfl_up_sync(0xffffffffu, c_inc, o);
+            if (lane >= o) c_inc += cv;
+        }
+        __shared__ unsigned int w_cnt[32];
+        __shared__ int s_bk;
+        __shared__ unsigned int s_n;
+        if (lane == 31) w_cnt[warp] = c_inc;
+        if (tid == 0) { s_bk = -1; s_n = 0u; }
+        __syncthreads();
+        unsigned int c_run = c_inc - c_own;
+        for (int w = 0; w < warp; ++w) c_run += w_cnt[w];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int b = FAST_BINS - 1 - 4 * tid - j;
+            const unsigned int c = h_cnt[b];
+            if (c_run < (unsigned int)k && c_run + c >= (unsigned int)k) { s_bk = b; s_n = c_run + c; }
+            c_run += c;
+        }
+        __syncthreads();
+        const bool go = s_bk >= 0 && s_n <= FAST_CANDIDATES;         // (fewer than k tokens in the row: the general search)
+        if (tid < CL) { sc_store(sc_map(&fs->go, tid), go ? 1 : 0); sc_store(sc_map(&fs->bin, tid), s_bk); }
+    }
+    sc_sync();
+    if (!fs->go) return false;
+    // ---- pass B: candidates to the first CTA; the whole mass, if a top-p cut wants it
+    {
+        const uint32_t bin = (uint32_t)fs->bin;
+        const uint32_t cnt_addr = sc_map(&fs->n_cand, 0), cand_addr = sc_map(cand, 0);
+        unsigned long long z = 0ull;
+        for (int i = lo + tid; i < hi; i += SAMPLE_THREADS) {
+            const float v = row[i];
+            if (v != v) continue;
+            const uint32_t key = order_key(v);
+            if (use_p) z += __float2ull_rz(expf((v - m) * inv_t) * FAST_SCALE);
+            if ((key >> 20) >= bin) {
+                const unsigned int pos = sc_atom_add(cnt_addr, 1u);
+                if (pos < FAST_CANDIDATES) sc_store(cand_addr + pos * 8u, ((unsigned long long)key << 32) | (unsigned long long)(0xffffffffu - (uint32_t)i));
+            }
+        }
+        if (use_p) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+            if (lane == 0) sc_red_add(sc_map(&fs->z_q, 0), z);
+        }
+    }
+    sc_sync();
+    if (rank != 0) return true;
+    short_way_finish(cand, cmass, m, inv_t, k, pp, true, use_p, seed, draw, out_token, s_scan, fs);
+    return true;
+}
+
+__device__ int g_sample_short_way = 1;      // 0: always the general search (tests compare the two)
+
 __global__ void __launch_bounds__(SAMPLE_THREADS, 1)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
@@ -189,6 +574,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     __shared__ int s_cnt[2][16];
     __shared__ float s_mass[2][16];
     __shared__ SampleExchange xch[2];
+    __shared__ FastShared fast_shared;
+    extern __shared__ __align__(16) unsigned char s_dyn_fast[];      // the dynamic shared memory, as the short way lays it out
     // gridDim.x CTAs (1, 2, 4 or 8: the cluster) share row blockIdx.y; this one owns the slices [first, first + per)
     const int CL = gridDim.x, rank = (int)sc_rank(), tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int per = SAMPLE_SLICES / CL, first = rank * per;
@@ -199,6 +586,21 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     int turn = 0;                                        // which copy of the exchange buffers is written next
     sc_sync();                                           // every CTA of the cluster runs before its memory is written
 
+    const int k_row = top_k ? top_k[r] : 0;
+    const float p_row = top_p ? top_p[r] : 1.0f;
+    const bool uk_row = k_row > 0 && k_row < V, up_row = p_row < 1.0f;
+    float m = -INFINITY;
+    int best = 0x7fffffff;
+    bool have_max = false;
+    if (T > 0.f && uk_row && g_sample_short_way) {
+        // top-k rows: maximum, counts and candidates in two passes; too many candidates: the maximum is kept, the search below goes on
+        if (sample_short_way_k(row, V, 1.0f / T, k_row, p_row, up_row, seeds[r], draw_index[r], out + r, s_dyn_fast, s_scan,
+                               s_val, s_idx, &fast_shared, m, best))
+            return;
+        have_max = true;
+        sc_sync();                                       // (the first CTA's shared memory is no longer written from outside)
+    }
+    if (!have_max) {
     // ---- arg-max of the row
     for (int sl = first; sl < first + per; ++sl) {
         const int lo_s = min(V, sl * S), n_s = min(V, lo_s + S) - lo_s;
@@ -211,16 +613,26 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
         }
     }
     sc_sync();
-    float m = -INFINITY;
-    int best = 0x7fffffff;
     for (int sl = 0; sl < SAMPLE_SLICES; ++sl) argmax_combine(m, best, xch[turn].val[sl], xch[turn].idx[sl]);   // larger value, then lower index
     if (best == 0x7fffffff) best = 0;
     turn ^= 1;
+    }
     if (!(T > 0.f)) {
         if (rank == 0 && tid == 0) out[r] = best;
         return;
     }
     const float inv_t = 1.0f / T;
+
+    // ---- top-k / top-p: the short way (one histogram, then the few candidates) where it serves the row
+    {
+        const int k_ = k_row;
+        const float p_ = p_row;
+        const bool uk = uk_row, up = up_row;
+        if (!uk && up && g_sample_short_way) {
+            if (sample_short_way(row, V, m, inv_t, k_, p_, uk, up, seeds[r], draw_index[r], out + r, s_dyn_fast, s_scan, &fast_shared))
+                return;
+        }
+    }
 
     // ---- mass of everything
     for (int sl = first; sl < first + per; ++sl) {
@@ -401,6 +813,11 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 static int g_sample_cluster = 0;
 // CTAs per row: 0 chosen by the number of rows, else 1, 2, 4 or 8 (for tests: the result is the same).
 RV_EXPORT void rv_sample_set_cluster(int ctas_per_row) { g_sample_cluster = ctas_per_row; }
+// 1 (default): top-k / top-p rows try the short way first; 0: always the general search.
+RV_EXPORT int rv_sample_set_short_way(int on) {
+    const int v = on ? 1 : 0;
+    return (int)cudaMemcpyToSymbol(g_sample_short_way, &v, sizeof(int));
+}
 
 // temperature, top_k, top_p may be null (greedy / disabled).  seeds and draw_index are read
 // only for rows with temperature > 0.

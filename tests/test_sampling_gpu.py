@@ -127,3 +127,41 @@ def test_the_token_does_not_depend_on_how_many_ctas_share_a_row(K, vocab):
     assert greedy[1] == 0 and greedy[2] == 0 and (vocab <= 20 or greedy[3] == 7)
     assert results[0][3][6] == greedy[6]                  # top-k of one: the most likely token
     assert results[0][1][4] == greedy[4]                  # temperature 0 among sampled rows
+
+
+@pytest.mark.parametrize("vocab,spread", [(128256, 8.0), (128256, 1.0), (5000, 3.0), (383, 0.2)])
+def test_the_short_way_and_the_general_search_draw_the_same_tokens(K, vocab, spread):
+    """Top-k / top-p rows first try one histogram and a sort of the few candidates; flat distributions
+    (too many candidates) fall back to the general digit-by-digit search.  Both must keep the same
+    set and draw the same token: compared row by row with the short way switched off, over peaked and
+    flat rows, k from 1 to beyond the candidate limit, p from 0.1 to 0.999, ties and NaN."""
+    from ctypes import c_int
+    torch.manual_seed(vocab + int(spread * 10))
+    R = 48
+    logits = torch.randn(R, vocab) * spread
+    logits[1, 5] = logits[1, vocab - 3] = logits[1].max() + 1.0          # a tie at the top
+    logits[2, ::7] = float("nan")
+    logits[3] = 1.5                                                       # all equal
+    temps = torch.tensor([0.5 + 0.03 * i for i in range(R)])
+    ks = torch.tensor([(0, 1, 2, 5, 50, 300, 2047, 2048, 5000, 100000)[i % 10] for i in range(R)], dtype=torch.int32)
+    ps = torch.tensor([(1.0, 0.1, 0.5, 0.9, 0.95, 0.999, 0.7)[i % 7] for i in range(R)])
+    seeds = torch.arange(900, 900 + R, dtype=torch.int64)
+    draws = torch.arange(R, dtype=torch.int64) * 5
+    lib = K._lib("sampling.cu")
+    g = logits.cuda()
+    try:
+        assert lib.rv_sample_set_short_way(c_int(0)) == 0
+        general = K.sample(g, temps.cuda(), ks.cuda(), ps.cuda(), seeds.cuda(), draws.cuda()).tolist()
+        general_k = K.sample(g, temps.cuda(), ks.cuda(), None, seeds.cuda(), draws.cuda()).tolist()
+    finally:
+        assert lib.rv_sample_set_short_way(c_int(1)) == 0
+    short = K.sample(g, temps.cuda(), ks.cuda(), ps.cuda(), seeds.cuda(), draws.cuda()).tolist()
+    short_k = K.sample(g, temps.cuda(), ks.cuda(), None, seeds.cuda(), draws.cuda()).tolist()
+    # the two ways add the masses up in different orders; a draw within rounding of a step of the CDF may differ
+    differ = [r for r in range(R) if short[r] != general[r]] + [r for r in range(R) if short_k[r] != general_k[r]]
+    for r in differ:
+        _, margin = P.sample(logits[r].nan_to_num(float("-inf")), float(temps[r]), int(seeds[r]), int(draws[r]),
+                             int(ks[r]) if 0 < int(ks[r]) < vocab else 0, float(ps[r]))
+        assert margin < 1e-4, f"row {r}: short way {short[r]}, general search {general[r]}, margin {margin:.2e}"
+    assert len(differ) <= 3
+    assert all(0 <= t < vocab for t in short + short_k)
