@@ -31,7 +31,11 @@ def _ids(text: str) -> List[int]:
 def _engine_options(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--model", default=os.environ.get("RVLLM_MODEL_DIR"),
                     help="folder with config.json and model.safetensors (default: $RVLLM_MODEL_DIR)")
+    ap.add_argument("--config", default=None, help="a config.json instead of a model folder, with --random-weights")
+    ap.add_argument("--random-weights", action="store_true",
+                    help="fill the model of --config with random weights on the device (N(0, 0.02), norms 1 + N(0, 0.1)) from --seed")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
+    ap.add_argument("--device", default="cuda", help="cuda (the only device: the engine has no CPU path)")
     ap.add_argument("--max-model-len", type=int, default=None)
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--max-num-seqs", type=int, default=64)
@@ -49,16 +53,26 @@ def _engine_options(ap: argparse.ArgumentParser) -> None:
 
 
 def _llm(args, **over):
-    from . import LLM
-    if not args.model:
-        raise SystemExit("no model: give --model DIR or set RVLLM_MODEL_DIR")
+    from . import LLM, config_from_dict
+    if not str(args.device).startswith("cuda"):
+        raise SystemExit(f"--device {args.device}: the engine runs its own CUDA kernels only and has no CPU path")
+    if args.config and not args.random_weights:
+        raise SystemExit("--config names no weights: add --random-weights, or give --model DIR")
+    if args.random_weights and not args.config:
+        raise SystemExit("--random-weights needs --config FILE (a config.json)")
+    if not args.model and not args.config:
+        raise SystemExit("no model: give --model DIR, set RVLLM_MODEL_DIR, or give --config FILE --random-weights")
     kw = dict(dtype=args.dtype, block_size=args.block_size, num_blocks=args.num_blocks,
               gpu_memory_utilization=args.gpu_memory_utilization, max_model_len=args.max_model_len,
               max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
               max_prefill_chunk=args.max_prefill_chunk, enforce_eager=args.enforce_eager, seed=args.seed,
               async_scheduling=not args.no_async_scheduling)
     kw.update(over)
-    llm = LLM(args.model, **kw)
+    if args.config:
+        with open(args.config) as f:
+            llm = LLM(config=config_from_dict(json.load(f), args.config), random_weights=True, **kw)
+    else:
+        llm = LLM(args.model, **kw)
     if getattr(args, "capture_graphs", False):
         llm.capture_graphs()
     return llm
@@ -165,7 +179,7 @@ def cmd_random_weights(args) -> int:
 def cmd_replay(args) -> int:
     from .engine.trace import build_engine, replay
     engine = build_engine(args.model, {"bf16": "bfloat16", "fp32": "float32"}.get(args.dtype, args.dtype),
-                          args.max_tokens, args.block_size)
+                          args.max_tokens, args.block_size, max_live=args.max_live, graphs=args.graphs)
     with (open(args.trace) if args.trace else sys.stdin) as f:
         replay(engine, f, args.out, sys.stdout)
     return 0
@@ -189,7 +203,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     g.add_argument("--ignore-eos", action="store_true")
     g.set_defaults(fn=cmd_generate)
 
-    b = sub.add_parser("benchmark", help="decode throughput per batch size")
+    b = sub.add_parser("benchmark", aliases=["bench"], help="decode throughput per batch size")
     _engine_options(b)
     b.add_argument("--n", default=None, help="batch sizes, e.g. 1,32,64 (default: $RVLLM_BATCH or 128)")
     b.add_argument("--input-len", type=int, default=int(os.environ.get("RVLLM_PREFILL_LEN", 16)))
@@ -217,6 +231,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     t.add_argument("--max-tokens", type=int, required=True)
     t.add_argument("--block-size", type=int, default=16)
     t.add_argument("--trace", default=None, help="file of JSON lines (default: standard input)")
+    t.add_argument("--max-live", type=int, default=4, help="most requests live at a time")
+    t.add_argument("--graphs", action="store_true", help="replay decode-only steps from CUDA graphs")
     t.set_defaults(fn=cmd_replay)
 
     args = ap.parse_args(argv)

@@ -40,6 +40,30 @@ def test_info_and_random_weights(tmp_path):
     assert p.returncode != 0 and "config.json" in p.stderr
 
 
+def test_generate_refuses_what_it_cannot_run(tmp_path):
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(tiny_configs.get("tiny_llama")))
+    p = run("generate", "--config", str(cfg), "--prompt-ids", "1,2")
+    assert p.returncode != 0 and "--random-weights" in p.stderr
+    p = run("generate", "--random-weights", "--prompt-ids", "1,2")
+    assert p.returncode != 0 and "--config" in p.stderr
+    p = run("generate", "--config", str(cfg), "--random-weights", "--device", "cpu", "--prompt-ids", "1,2")
+    assert p.returncode != 0 and "no CPU path" in p.stderr
+
+
+@pytest.mark.gpu
+def test_generate_from_a_configuration_with_random_weights(tmp_path):
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(tiny_configs.get("tiny_qwen2")))
+    outs = []
+    for seed in ("3", "3", "4"):
+        p = run("generate", "--config", str(cfg), "--random-weights", "--seed", seed, "--prompt-ids", "1,2,3",
+                "--max-tokens", "6", "--ignore-eos", "--num-blocks", "32", "--max-model-len", "128", "--dtype", "float32")
+        assert p.returncode == 0, p.stderr[-2000:]
+        outs.append(json.loads(p.stdout.splitlines()[0])["token_ids"])
+    assert outs[0] == outs[1] and len(outs[0]) == 6 and outs[0] != outs[2]
+
+
 @pytest.mark.gpu
 def test_generate_and_benchmark_on_the_gpu():
     folder = model_folder("tiny_llama")
