@@ -63,6 +63,8 @@ struct DecodeGemmParams {
     int cluster;             // 1: the CTAs of a tile are a thread-block cluster and add their partials in the
                              // cluster's shared memory (M <= 64, 2 <= splits <= 8); scratch and counters unused
     int cluster_rows;        // rows that each CTA of the cluster finishes: ceil(M / splits)
+    int k_rotate;            // != 0: tile t starts its K loop at k block (t * k_rotate) mod its count, so that the CTAs of a
+                             // wave ask for different blocks of the activations at a time, not all for the same lines of L2
     int l2_ahead;            // k blocks beyond the shared-memory stages whose weights are asked into L2 before the wait
     // rotary epilogue (q_out != nullptr): N = (nh + 2 nkv) * hd, 128 % hd == 0
     __nv_bfloat16* q_out;            // [M, nh * hd]
@@ -119,6 +121,12 @@ __device__ __forceinline__ float4 load_part(const float* src) {
     else
         asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(src) : "memory");
     return v;
+}
+
+// SiLU(g) * u.  For a bfloat16 result the hardware's approximations of 2^x and 1/x (two units in the last
+// place of a float, a 4000th of the result's own rounding step) save half of the epilogue's instructions.
+__device__ __forceinline__ float silu_gate(float g, float u, bool exact) {
+    return exact ? g / (1.0f + expf(-g)) * u : __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
 template <int MB, bool IN_SMEM>
@@ -291,6 +299,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int num_kb = (p.K + BK - 1) / BK;
     const int per = (num_kb + p.splits - 1) / p.splits;
     const int kb0 = split * per, kb1 = min(num_kb, kb0 + per);
+    const int n_kb = kb1 > kb0 ? kb1 - kb0 : 0;
+    const int rot = (p.k_rotate && n_kb > 1) ? (int)(((unsigned)tile * (unsigned)p.k_rotate) % (unsigned)n_kb) : 0;
+    // the i-th k block of this CTA's loop: its range, begun at `rot` and wrapped around
+    auto kb_at = [&](int i) { const int r = i + rot; return kb0 + (r >= n_kb ? r - n_kb : r); };
     const int half_n = p.N >> 1;
     // cluster reduction: [splits][cluster_rows][128 features] floats behind the stages (and gamma),
     // at the same offset in every CTA of the cluster
@@ -307,27 +319,28 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             // The weights are written by no kernel of a step: the first stages' weight tiles are
             // requested before waiting for the previous kernel, whose tail this overlaps.  The
             // activations follow after the wait; a stage's barrier completes when both have landed.
-            const int early = min(STAGES, kb1 - kb0);
+            const int early = min(STAGES, n_kb);
             for (int i = 0; i < early; ++i) {
                 const uint32_t a_dst = smem_u32(tiles + (size_t)i * STAGE_BYTES);
                 const uint32_t bar = full0 + 8 * i;
                 mbar_expect_tx(bar, STAGE_BYTES);
-                tma_load_2d(a_dst, &map_w, (kb0 + i) * BK, row_a, bar);
-                tma_load_2d(a_dst + A_BYTES / 2, &map_w, (kb0 + i) * BK, row_b, bar);
+                tma_load_2d(a_dst, &map_w, kb_at(i) * BK, row_a, bar);
+                tma_load_2d(a_dst + A_BYTES / 2, &map_w, kb_at(i) * BK, row_b, bar);
             }
             // ... and the weights of the k blocks after them are asked into L2: while this kernel waits
             // for its predecessor (a norm, the merge of the attention's key splits) the memory is idle
-            for (int kb = kb0 + early; kb < min(kb1, kb0 + early + p.l2_ahead); ++kb) {
-                tma_prefetch_2d(&map_w, kb * BK, row_a);
-                tma_prefetch_2d(&map_w, kb * BK, row_b);
+            for (int i = early; i < min(n_kb, early + p.l2_ahead); ++i) {
+                tma_prefetch_2d(&map_w, kb_at(i) * BK, row_a);
+                tma_prefetch_2d(&map_w, kb_at(i) * BK, row_b);
             }
             rv_pdl_wait();
             for (int i = 0; i < early; ++i)
-                tma_load_2d(smem_u32(tiles + (size_t)i * STAGE_BYTES) + A_BYTES, &map_x, (kb0 + i) * BK, 0, full0 + 8 * i);
+                tma_load_2d(smem_u32(tiles + (size_t)i * STAGE_BYTES) + A_BYTES, &map_x, kb_at(i) * BK, 0, full0 + 8 * i);
             issued = early;
             stage = early % STAGES;
             phase = early == STAGES ? 1 : 0;
-            for (int kb = kb0 + early; kb < kb1; ++kb) {
+            for (int i = early; i < n_kb; ++i) {
+                const int kb = kb_at(i);
                 if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, &abort_flag, 1)) { ok = false; break; }
                 const uint32_t a_dst = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
                 const uint32_t bar = full0 + 8 * stage;
@@ -355,14 +368,14 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int kb = kb0; kb < kb1; ++kb) {
+            for (int i = 0; i < n_kb; ++i) {
                 if (!mbar_wait((fused_norm ? normed0 : full0) + 8 * stage, phase, &abort_flag, 3)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t a_addr = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
                 const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
 #pragma unroll
                 for (int j = 0; j < BK / UMMA_K; ++j)
-                    tcgen05_mma_bf16(tmem_base, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (kb > kb0) || j != 0);
+                    tcgen05_mma_bf16(tmem_base, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, i > 0 || j != 0);
                 tcgen05_commit(empty0 + 8 * stage);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
@@ -423,7 +436,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const float r = row < p.M ? norm_rstd[row] : 0.f;
             int stage = 0;
             uint32_t phase = 0;
-            for (int kb = kb0; kb < kb1; ++kb) {
+            for (int i = 0; i < n_kb; ++i) {
+                const int kb = kb_at(i);
                 float g[8];
                 {
                     const float4 g0 = *reinterpret_cast<const float4*>(gam + (kb - kb0) * BK + lc * 8);
@@ -456,15 +470,19 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         epi_sync();
         const bool ok = abort_flag == 0;
         tcgen05_fence_after();
-        float* fin = reinterpret_cast<float*>(tiles);       // [128][MB + 1], the stages are free now
+        // [128 features][FS]: the stages are free now.  A feature's rows lie side by side and are moved four
+        // at a time (16-byte accesses; with a stride of MB + 4 floats the eight lanes of a quarter warp
+        // touch all 32 banks once), which also gives every thread four independent results to work on:
+        // with one warp per scheduler the epilogue is bound by the latency of dependent instructions.
+        constexpr int FS = MB + 4;
+        float* fin = reinterpret_cast<float*>(tiles);
         if (ok) {
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
             float* part = (p.splits > 1 && !p.cluster) ? p.scratch + ((size_t)(tile * p.splits + split) * MB) * TILE_F : nullptr;
             // row m goes to the CTA m / cluster_rows of the cluster, at [split][m % cluster_rows][feature]
             const uint32_t red_mine = smem_u32(red) + (uint32_t)((split * p.cluster_rows) * TILE_F + f) * 4u;
-#pragma unroll
-            for (int c = 0; c < MB; c += 16) {
-                uint32_t r[16];
+            // One loop per destination (a branch per element costs more than the element does here).
+            auto load16 = [&](int c, uint32_t (&r)[16]) {
                 if (have) {
                     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
                                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -476,17 +494,48 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                     for (int e = 0; e < 16; ++e) r[e] = 0u;    // this split got no k block: it adds zeros
                 }
-                int owner = c / p.cluster_rows, local = c - owner * p.cluster_rows;
+            };
+            if (p.cluster) {
+                // row m goes to CTA m / cluster_rows; the window of a CTA's shared memory is linear, so the
+                // address of the owner's buffer is mapped once per owner and the rows follow by offset
+                int owner = 0, local = 0;
+                uint32_t remote = cluster_map(red_mine, 0);
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    if (p.cluster) {
-                        if (c + e < p.M) st_cluster_f32(cluster_map(red_mine + (uint32_t)(local * TILE_F) * 4u, owner), __uint_as_float(r[e]));
-                        if (++local == p.cluster_rows) { local = 0; ++owner; }
-                    } else if (part) {
-                        if (c + e < p.M) part[(size_t)(c + e) * TILE_F + f] = __uint_as_float(r[e]);   // real rows only
-                    } else {
-                        fin[f * (MB + 1) + c + e] = __uint_as_float(r[e]);
+                for (int c = 0; c < MB; c += 16) {
+                    if (c >= p.M) break;
+                    uint32_t r[16];
+                    load16(c, r);
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        if (c + e < p.M) st_cluster_f32(remote + (uint32_t)(local * TILE_F) * 4u, __uint_as_float(r[e]));
+                        if (++local == p.cluster_rows) {
+                            local = 0;
+                            ++owner;
+                            if (c + e + 1 < p.M) remote = cluster_map(red_mine, owner);     // (a rank that exists)
+                        }
                     }
+                }
+            } else if (part) {
+#pragma unroll
+                for (int c = 0; c < MB; c += 16) {
+                    if (c >= p.M) break;
+                    uint32_t r[16];
+                    load16(c, r);
+#pragma unroll
+                    for (int e = 0; e < 16; ++e)
+                        if (c + e < p.M) part[(size_t)(c + e) * TILE_F + f] = __uint_as_float(r[e]);   // real rows only
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < MB; c += 16) {
+                    if (c >= p.M) break;                   // rows beyond M are never read below
+                    uint32_t r[16];
+                    load16(c, r);
+                    float4* dst = reinterpret_cast<float4*>(fin + f * FS + c);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        dst[e] = make_float4(__uint_as_float(r[4 * e]), __uint_as_float(r[4 * e + 1]),
+                                             __uint_as_float(r[4 * e + 2]), __uint_as_float(r[4 * e + 3]));
                 }
             }
             bool finish = true;
@@ -544,9 +593,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                                 for (int i = 0; i < 8; ++i) v[j] += t[j][i];
                         }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (m0 + j < p.M) fin[f * (MB + 1) + m0 + j] = v[j];
+                        *reinterpret_cast<float4*>(fin + f * FS + m0) = make_float4(v[0], v[1], v[2], v[3]);
                     }
                     if (et == 0) p.counters[tile] = 0;     // ready for the next launch
                 }
@@ -557,12 +604,28 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     // features 0..63 are gate rows, 64..127 the up rows of the same output columns
                     const int fo = et & 63;
                     const int n = tile * (TILE_F / 2) + fo;
-                    for (int m = et >> 6; m < p.M; m += 2) {
-                        if (n >= half_n) break;
-                        const float g = fin[fo * (MB + 1) + m], u = fin[(fo + 64) * (MB + 1) + m];
-                        const float v = g / (1.0f + expf(-g)) * u;
-                        if (p.out_f32) ((float*)p.out)[(size_t)m * half_n + n] = v;
-                        else ((__nv_bfloat16*)p.out)[(size_t)m * half_n + n] = __float2bfloat16_rn(v);
+                    // eight rows of an output column per pass: eight independent chains per thread
+                    for (int m0 = (et >> 6) * 8; m0 < p.M && n < half_n; m0 += 16) {
+                        const float4 ga = *reinterpret_cast<const float4*>(fin + fo * FS + m0);
+                        const float4 gb = *reinterpret_cast<const float4*>(fin + fo * FS + m0 + 4);
+                        const float4 ua = *reinterpret_cast<const float4*>(fin + (fo + 64) * FS + m0);
+                        const float4 ub = *reinterpret_cast<const float4*>(fin + (fo + 64) * FS + m0 + 4);
+                        const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+                        const float u[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+                        float v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = silu_gate(g[j], u[j], p.out_f32 != 0);
+                        if (p.out_f32) {
+                            float* o = (float*)p.out + (size_t)m0 * half_n + n;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (m0 + j < p.M) o[(size_t)j * half_n] = v[j];
+                        } else {
+                            __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m0 * half_n + n;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (m0 + j < p.M) o[(size_t)j * half_n] = __float2bfloat16_rn(v[j]);
+                        }
                     }
                 } else if (p.q_out) {
                     // positions and slots of the rows once per CTA, then four rows at a time so that
@@ -595,14 +658,17 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                                     sn[j] = __ldg(p.sin_t + (size_t)row_pos[m0 + j] * half + i);
                                 }
                             }
+                            const float4 own4 = *reinterpret_cast<const float4*>(fin + et * FS + m0);
+                            const float4 other4 = *reinterpret_cast<const float4*>(fin + pe * FS + m0);
+                            const float owns[4] = {own4.x, own4.y, own4.z, own4.w}, others[4] = {other4.x, other4.y, other4.z, other4.w};
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 const int m = m0 + j;
                                 if (m >= p.M) break;
-                                const float own = fin[et * (MB + 1) + m] + b;
+                                const float own = owns[j] + b;
                                 float v = own;
                                 if (is_q || is_k) {
-                                    const float other = fin[pe * (MB + 1) + m] + bp;
+                                    const float other = others[j] + bp;
                                     v = first ? own * c[j] - other * sn[j] : other * sn[j] + own * c[j];
                                 }
                                 if (is_q) {
@@ -627,11 +693,14 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                             for (int j = 0; j < 8; ++j)
                                 r8[j] = (p.residual && m0 + j < p.M) ? __bfloat162float(p.residual[(size_t)(m0 + j) * p.N + n]) : 0.f;
+                            const float4 lo4 = *reinterpret_cast<const float4*>(fin + et * FS + m0);
+                            const float4 hi4 = *reinterpret_cast<const float4*>(fin + et * FS + m0 + 4);
+                            const float acc8[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
                                 const int m = m0 + j;
                                 if (m >= p.M) break;
-                                const float v = fin[et * (MB + 1) + m] + b + r8[j];
+                                const float v = acc8[j] + b + r8[j];
                                 if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n] = v;
                                 else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
                             }
@@ -663,7 +732,7 @@ template <int MB>
 static int launch_decode(const CUtensorMap& mw, const CUtensorMap& mx, const DecodeGemmParams& p, cudaStream_t stream) {
     constexpr int STAGES = STAGES_FOR(MB);
     const int stage = A_BYTES + MB * BK * 2;
-    const int fin = TILE_F * (MB + 1) * 4;
+    const int fin = TILE_F * (MB + 4) * 4;
     int smem = (STAGES * stage > fin ? STAGES * stage : fin) + 1024;
     static RvPerDevice configured;
     if (int e = rv_configure_smem(configured, gemm_decode_kernel<MB>, smem + MAX_NORM_K * 4 + (64 + 8) * TILE_F * 4)) return e;
@@ -693,12 +762,16 @@ RV_EXPORT int rv_gemm_decode_tiles(int N, int gated) {
 }
 
 static int g_l2_ahead = 0;
+static int g_k_rotate = 0;
+// The K loop of tile t starts at k block (t * step) mod the CTA's count (0: every tile at its first block).
+RV_EXPORT void rv_gemm_decode_set_k_rotate(int step) { g_k_rotate = step < 0 ? 0 : step; }
 // How many k blocks of weights beyond its shared-memory stages a CTA asks into L2 before it waits for
 // the previous kernel (0: none).
 RV_EXPORT void rv_gemm_decode_set_l2_ahead(int k_blocks) { g_l2_ahead = k_blocks < 0 ? 0 : k_blocks; }
 
 static int run_decode(const void* x, const void* w, DecodeGemmParams p, cudaStream_t stream) {
     p.l2_ahead = g_l2_ahead;
+    p.k_rotate = g_k_rotate;
     if (p.M < 0 || p.N <= 0 || p.K <= 0 || p.splits < 1) return RV_ERR_BAD_SIZE;
     if (p.M > 128) return RV_ERR_UNSUPPORTED;
     if (p.K % 8) return RV_ERR_UNSUPPORTED;

@@ -79,6 +79,8 @@ class CudaKernels:
     DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
     DECODE_SPLIT_ROWS = 8   # ... when K has to be split over CTAs, only up to this many rows
     CLUSTER_REDUCE = True        # split-K partials of few rows are added up inside a thread-block cluster
+    DECODE_K_ROTATE = 13         # tile t of a decode GEMM starts its K loop at block (t * this) mod its count, so that the CTAs of a
+                                 # wave do not all read the same columns of the weights at a time (0: all start at the first block)
     DECODE_L2_AHEAD = 6          # k blocks of weights, beyond its stages, that a decode GEMM's CTA asks into L2 before its wait
     CLUSTER_MAX_ROWS = 32        # (with 64 rows one CTA fits an SM and the library's GEMM is faster)
     CLUSTER_TARGET_CTAS = 225    # of such a product, tiles x splits (measured best at 8B, 7B and 32B layer sizes)
@@ -118,6 +120,7 @@ class CudaKernels:
             lib.rv_set_pdl(c_int(1 if self.pdl else 0))
             if source == "gemm_tcgen05_decode.cu":
                 lib.rv_gemm_decode_set_l2_ahead(c_int(self.DECODE_L2_AHEAD if self.pdl else 0))
+                lib.rv_gemm_decode_set_k_rotate(c_int(self.DECODE_K_ROTATE))
             self._libs[key] = lib
         return lib
 
