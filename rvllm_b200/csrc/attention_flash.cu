@@ -479,6 +479,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FlashP
     const int n_tiles = t_end > t_begin ? t_end - t_begin : 0;
 
     if (tid == 0) {
+        tma_prefetch_descriptor(&map_kv);
         abort_flag = 0;
 #pragma unroll
         for (int s = 0; s < NST; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 4); }

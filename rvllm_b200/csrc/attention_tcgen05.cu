@@ -111,6 +111,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     rv_pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) { tma_prefetch_descriptor(&map_q); tma_prefetch_descriptor(&map_kv); }
     const uint32_t bar_q = smem_u32(&bars[0]), bar_k0 = smem_u32(&bars[1]);          // k full [2]
     const uint32_t bar_v0 = smem_u32(&bars[3]);                                      // v full [2]
     const uint32_t bar_vfree0 = smem_u32(&bars[5]);                                  // v free [2]

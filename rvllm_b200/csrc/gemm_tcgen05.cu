@@ -207,6 +207,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // pair: rank 0 issues the MMAs and owns the barriers that count both CTAs (full, tempty)
     const uint32_t rank = RV_PAIR ? pair_rank() : 0u;
     if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&map_a);
+        tma_prefetch_descriptor(&map_b);
         abort_flag = 0;
         // full: one arrival (the producer; in a pair the first CTA's, with the bytes of both CTAs);
         // empty, tfull: one arrival from the commit; tempty: the four epilogue warps (of both CTAs)

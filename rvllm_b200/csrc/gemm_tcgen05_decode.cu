@@ -279,12 +279,41 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const uint32_t normed0 = smem_u32(&bars[2 * STAGES + 1]);
     const bool fused_norm = p.norm_gamma != nullptr;
 
+    const int tile = blockIdx.x / p.splits, split = blockIdx.x - tile * p.splits;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const int per = (num_kb + p.splits - 1) / p.splits;
+    const int kb0 = split * per, kb1 = min(num_kb, kb0 + per);
+    const int n_kb = kb1 > kb0 ? kb1 - kb0 : 0;
+    const int rot = (p.k_rotate && n_kb > 1) ? (int)(((unsigned)tile * (unsigned)p.k_rotate) % (unsigned)n_kb) : 0;
+    // the i-th k block of this CTA's loop: its range, begun at `rot` and wrapped around
+    auto kb_at = [&](int i) { const int r = i + rot; return kb0 + (r >= n_kb ? r - n_kb : r); };
+    const int half_n = p.N >> 1;
+    // first weight row of the tile's (two) halves
+    const int row_a = p.gated ? tile * (TILE_F / 2) : tile * TILE_F;
+    const int row_b = p.gated ? half_n + tile * (TILE_F / 2) : tile * TILE_F + TILE_F / 2;
+    const int early = min(STAGES, n_kb);
+
     if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&map_w);
+        tma_prefetch_descriptor(&map_x);
         abort_flag = 0;
         is_last = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); mbar_init(normed0 + 8 * s, 4); }
         mbar_init(tfull, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // The weights are written by no kernel of a step: the first stages' weight tiles are requested
+        // at once, by the thread that has just set the barriers up - before the tensor memory is
+        // allocated, before the CTA's first barrier and before the wait for the previous kernel, whose
+        // tail this overlaps.  The activations follow after that wait; a stage's barrier completes when
+        // both have landed.
+        for (int i = 0; i < early; ++i) {
+            const uint32_t a_dst = smem_u32(tiles + (size_t)i * STAGE_BYTES);
+            const uint32_t bar = full0 + 8 * i;
+            mbar_expect_tx(bar, STAGE_BYTES);
+            tma_load_2d(a_dst, &map_w, kb_at(i) * BK, row_a, bar);
+            tma_load_2d(a_dst + A_BYTES / 2, &map_w, kb_at(i) * BK, row_b, bar);
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS));
@@ -295,39 +324,17 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
-    const int tile = blockIdx.x / p.splits, split = blockIdx.x - tile * p.splits;
-    const int num_kb = (p.K + BK - 1) / BK;
-    const int per = (num_kb + p.splits - 1) / p.splits;
-    const int kb0 = split * per, kb1 = min(num_kb, kb0 + per);
-    const int n_kb = kb1 > kb0 ? kb1 - kb0 : 0;
-    const int rot = (p.k_rotate && n_kb > 1) ? (int)(((unsigned)tile * (unsigned)p.k_rotate) % (unsigned)n_kb) : 0;
-    // the i-th k block of this CTA's loop: its range, begun at `rot` and wrapped around
-    auto kb_at = [&](int i) { const int r = i + rot; return kb0 + (r >= n_kb ? r - n_kb : r); };
-    const int half_n = p.N >> 1;
     // cluster reduction: [splits][cluster_rows][128 features] floats behind the stages (and gamma),
     // at the same offset in every CTA of the cluster
     float* red = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES + (fused_norm ? (size_t)per * BK * 4 : 0));
-    // first weight row of the tile's (two) halves
-    const int row_a = p.gated ? tile * (TILE_F / 2) : tile * TILE_F;
-    const int row_b = p.gated ? half_n + tile * (TILE_F / 2) : tile * TILE_F + TILE_F / 2;
 
     if (warp == 0) {
         if (lane == 0) {
             int stage = 0, issued = 0;
             uint32_t phase = 0;
             bool ok = true;
-            // The weights are written by no kernel of a step: the first stages' weight tiles are
-            // requested before waiting for the previous kernel, whose tail this overlaps.  The
-            // activations follow after the wait; a stage's barrier completes when both have landed.
-            const int early = min(STAGES, n_kb);
-            for (int i = 0; i < early; ++i) {
-                const uint32_t a_dst = smem_u32(tiles + (size_t)i * STAGE_BYTES);
-                const uint32_t bar = full0 + 8 * i;
-                mbar_expect_tx(bar, STAGE_BYTES);
-                tma_load_2d(a_dst, &map_w, kb_at(i) * BK, row_a, bar);
-                tma_load_2d(a_dst + A_BYTES / 2, &map_w, kb_at(i) * BK, row_b, bar);
-            }
-            // ... and the weights of the k blocks after them are asked into L2: while this kernel waits
+            // (the first stages' weights were requested during the set-up above) ... and the weights of
+            // the k blocks after them are asked into L2: while this kernel waits
             // for its predecessor (a norm, the merge of the attention's key splits) the memory is idle
             for (int i = early; i < min(n_kb, early + p.l2_ahead); ++i) {
                 tma_prefetch_2d(&map_w, kb_at(i) * BK, row_a);
