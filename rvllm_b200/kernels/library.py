@@ -82,7 +82,7 @@ class CudaKernels:
     DECODE_K_ROTATE = 13         # tile t of a decode GEMM starts its K loop at block (t * this) mod its count, so that the CTAs of a
                                  # wave do not all read the same columns of the weights at a time (0: all start at the first block)
     DECODE_L2_AHEAD = 6          # k blocks of weights, beyond its stages, that a decode GEMM's CTA asks into L2 before its wait
-    CLUSTER_MAX_ROWS = 32        # (with 64 rows one CTA fits an SM and the library's GEMM is faster)
+    CLUSTER_MAX_ROWS = 64        # ... of up to this many rows (the whole range of the weight-streaming GEMM)
     CLUSTER_TARGET_CTAS = 225    # of such a product, tiles x splits (measured best at 8B, 7B and 32B layer sizes)
     TMA_DECODE = True       # decode attention's tiles come by TMA (head sizes 64 / 128, pages of 8 keys or more) ...
     TMA_DECODE_EARLY = True   # ... and keys older than the step's own are requested before the wait for the kernel before
@@ -90,7 +90,7 @@ class CudaKernels:
     BALANCED_MIN_PAIRS = 256  # ... from this many (sequence, kv head) pairs on
     FUSED_QKV_PREFILL = True  # from TCGEN05_MIN_ROWS rows on the prefill GEMM rotates and writes the cache in its epilogue
     FUSED_NORM_MAX_ROWS = 0 # rows up to which an RMSNorm is applied inside the decode GEMM that consumes it
-    FUSED_QKV_MAX_ROWS = 32 # rows up to which q/k/v product, rotation and cache write are one kernel
+    FUSED_QKV_MAX_ROWS = 64 # rows up to which q/k/v product, rotation and cache write are one kernel
     pdl = os.environ.get("RVLLM_NO_PDL") != "1"   # programmatic dependent launch between kernels
     num_sms = 148           # SMs of the device; asked from the device when the library is made
 

@@ -38,7 +38,13 @@ def test_cluster_reduce_is_chosen_for_few_rows_and_caps_the_splits():
 def test_which_products_take_the_weight_streaming_gemm():
     k = _k()
     assert k._use_decode_gemm(8, 4096, 4096, False) and k._use_decode_gemm(32, 4096, 14336, False)
-    assert not k._use_decode_gemm(64, 4096, 4096, False)     # K would have to be split: the library there
+    assert k._use_decode_gemm(64, 4096, 4096, False)         # K split over a cluster, up to 64 rows
+    k.CLUSTER_REDUCE = False
+    try:
+        assert not k._use_decode_gemm(64, 4096, 4096, False) # without clusters K is split for at most 8 rows: the library there
+        assert k._use_decode_gemm(8, 4096, 4096, False)
+    finally:
+        del k.CLUSTER_REDUCE
     assert k._use_decode_gemm(64, 28672, 4096, True) and k._use_decode_gemm(64, 128256, 4096, False)
     assert not k._use_decode_gemm(65, 28672, 4096, True) and not k._use_decode_gemm(8, 4096, 4100, False)
     assert not k._use_decode_gemm(0, 4096, 4096, False)
