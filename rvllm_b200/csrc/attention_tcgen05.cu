@@ -1,7 +1,9 @@
 // Paged flash attention for prompt portions on the fifth-generation tensor cores (bfloat16).
 //
-// A CTA owns 128 rows - (token, query head) pairs of ONE key/value head, the G = nh / nkv heads of
-// a group packed side by side (128 / G tokens) - and walks the sequence's keys in tiles of 64:
+// A CTA owns up to 128 rows - (token, query head) pairs of ONE key/value head, the G = nh / nkv heads
+// of a group packed side by side: floor(128 / G) whole tokens, so 128 rows where G divides 128 and for
+// instance 126 (18 tokens) for G = 7; the rows left over are zeros that nothing reads back - and walks
+// the sequence's keys in tiles of 64:
 //   S = Q K^T        tcgen05.mma, Q [128 x hd] and K [64 x hd] K-major in shared memory (TMA,
 //                    128-byte swizzle), S [128 x 64] float in tensor memory;
 //   softmax          four warps, one thread per row: tcgen05.ld of the row, scale, causal / window
@@ -135,10 +137,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int q_start = p.cu_seqlens[seq];
     const int q_len = p.cu_seqlens[seq + 1] - q_start;
     const int rows_total = q_len * G;
-    const int row0 = tile_m * ROWS;
+    const int tile_rows = (ROWS / G) * G;                               // whole tokens only
+    const int row0 = tile_m * tile_rows;
     if (q_len <= 1 || ctx <= 0 || row0 >= rows_total) return;          // one-token sequences go to the decode kernel
 
-    const int last_row = min(rows_total, row0 + ROWS) - 1;
+    const int last_row = min(rows_total, row0 + tile_rows) - 1;
     const int pos_first = ctx - q_len + row0 / G, pos_last = ctx - q_len + last_row / G;
     const int key_lo = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
     const int key_hi = pos_last + 1;
@@ -164,6 +167,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // value tiles start as zeros: a page that is not loaded (beyond the context, or given back by
     // a window) must not meet a probability of zero with a NaN
     for (int i = tid; i < 2 * KV_BYTES / 16; i += NUM_THREADS) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+    // ... and so do the query rows that the box of whole tokens leaves over (a row is 128 bytes in
+    // each half of the head, whatever the swizzle does inside it)
+    for (int i = tid; i < (ROWS - tile_rows) * 8 * HALVES; i += NUM_THREADS) {
+        const int h = i / ((ROWS - tile_rows) * 8), j = i - h * ((ROWS - tile_rows) * 8);
+        reinterpret_cast<uint4*>(q_s + h * (ROWS * 128) + tile_rows * 128)[j] = make_uint4(0, 0, 0, 0);
+    }
     fence_async_smem();
     tcgen05_fence_before();
     __syncthreads();
@@ -201,9 +210,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             __syncwarp();
         };
-        // Q: one box of [64 hd, G heads, 128 / G tokens] per half of the head dimension
+        // Q: one box of [64 hd, G heads, floor(128 / G) tokens] per half of the head dimension
         if (lane == 0) {
-            mbar_expect_tx(bar_q, Q_BYTES);
+            mbar_expect_tx(bar_q, (uint32_t)tile_rows * HEAD_DIM * 2);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
                 tma_load_3d(smem_u32(q_s) + h * (ROWS * 128), &map_q, h * 64, kvh * G, q_start + row0 / G, bar_q);
@@ -267,7 +276,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     } else {
         // ------------------------------------------------------------ softmax warps: one thread per row
         const int r = row0 + warp * 32 + lane;               // packed row; TMEM lane = warp * 32 + lane
-        const bool in_range = r < rows_total;
+        const bool in_range = warp * 32 + lane < tile_rows && r < rows_total;
         const int tok_i = in_range ? r / G : 0;
         const int head = kvh * G + (in_range ? r - tok_i * G : 0);
         const int pos = in_range ? ctx - q_len + tok_i : -1;
@@ -434,7 +443,7 @@ RV_EXPORT int rv_attention_tcgen05_head_dim() { return HEAD_DIM; }
 
 // Attention of the sequences that bring more than one token to the step (the others are left to
 // the decode kernel).  Refuses (RV_ERR_UNSUPPORTED) what it is not built for: a head size other
-// than HEAD_DIM, a group size that does not divide 128, pages of fewer than 8 keys.
+// than HEAD_DIM, a group of more than 128 heads, pages of fewer than 8 keys.
 RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long num_pages, const int* block_tables,
                                    const int* cu_seqlens, const int* ctx_lens, void* out, int n_tokens, int num_seqs,
                                    int nh, int nkv, int hd, int page_size, int max_blocks, float scale, int window,
@@ -443,7 +452,7 @@ RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long n
     if (n_tokens < 0 || num_seqs < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_blocks <= 0 || max_q_len <= 0)
         return RV_ERR_BAD_SIZE;
     const int G = nh / nkv;
-    if (G > ROWS || ROWS % G) return RV_ERR_UNSUPPORTED;
+    if (G > ROWS) return RV_ERR_UNSUPPORTED;
     if ((page_size & (page_size - 1)) || page_size < 8) return RV_ERR_UNSUPPORTED;
     if (num_seqs > 65535 || nkv > 65535) return RV_ERR_BAD_SIZE;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) % 16)
@@ -464,7 +473,8 @@ RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long n
     const int smem = Q_BYTES + 4 * KV_BYTES + 256;
     static RvPerDevice configured;
     if (int e = rv_configure_smem(configured, attention_tcgen05_kernel, smem)) return e;
-    const dim3 grid(nkv, num_seqs, (max_q_len * G + ROWS - 1) / ROWS);
+    const int tile_tokens = ROWS / G;
+    const dim3 grid(nkv, num_seqs, (max_q_len + tile_tokens - 1) / tile_tokens);
     if (grid.y > 65535 || grid.z > 65535) return RV_ERR_UNSUPPORTED;
     RV_LAUNCH_ST = rv_launch(attention_tcgen05_kernel, grid, dim3(NUM_THREADS), smem, stream, map_q, map_kv, p);
     return rv_launch_status();

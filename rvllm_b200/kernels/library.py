@@ -267,7 +267,7 @@ class CudaKernels:
         out = torch.empty_like(q)
         group = num_heads // num_kv_heads
         if self.TCGEN05_ATTENTION and meta.max_q_len >= self.TCGEN05_ATTENTION_MIN_TOKENS and head_dim in (64, 128) \
-                and 128 % group == 0 and page >= 8:
+                and group <= 128 and page >= 8:
             self.attention_tcgen05(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window)
             if meta.num_decode:
                 if self._balanced_ok(meta, group, num_kv_heads):
@@ -381,7 +381,7 @@ class CudaKernels:
 
     def attention_tcgen05(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, status=None):
         """The tcgen05 flash-attention kernel for the sequences of a step that bring more than one
-        token (bfloat16, head size 64 or 128, group size dividing 128, pages of at least 8 keys)."""
+        token (bfloat16, head size 64 or 128, groups of up to 128 heads, pages of at least 8 keys)."""
         _need(q, "q", torch.bfloat16, 2); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
         lib = self._lib("attention_tcgen05.cu", (f"-DHEAD_DIM={head_dim}",))
         st = lib.rv_attention_tcgen05(

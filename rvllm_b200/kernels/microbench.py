@@ -3,7 +3,7 @@
     python -m rvllm_b200.kernels.microbench decode_gemm  --m 8 --n 28672 --k 4096 [--gated]
     python -m rvllm_b200.kernels.microbench prefill_gemm --m 2048 --n 6144 --k 4096 [--gated]
     python -m rvllm_b200.kernels.microbench decode_attention  --batch 32 --ctx 2048
-    python -m rvllm_b200.kernels.microbench prefill_attention --tokens 2048
+    python -m rvllm_b200.kernels.microbench prefill_attention --tokens 2048 [--past 2048]
     python -m rvllm_b200.kernels.microbench sampling --batch 8 --n 128256
 
 Used for timing a kernel in isolation (CUDA events, warm-up, inputs rotated so that L2 does not
@@ -41,6 +41,7 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--past", type=int, default=0, help="prefill_attention: keys already in the cache before the portion")
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
@@ -89,7 +90,7 @@ def main(argv=None) -> int:
         if args.kernel == "decode_attention":
             B, q_lens, ctx = args.batch, [1] * args.batch, args.ctx
         else:
-            B, q_lens, ctx = 1, [args.tokens], args.tokens
+            B, q_lens, ctx = 1, [args.tokens], args.tokens + args.past
         MB = (ctx + ps - 1) // ps
         # several copies of the cache in one layer, used in turn, so that L2 does not serve the keys
         kv_one = B * ctx * 2 * nkv * hd * 2
@@ -128,7 +129,7 @@ def main(argv=None) -> int:
         if args.kernel == "decode_attention":
             out.update(kv_gb_s=round(kv_bytes / ms / 1e6, 1), splits=args.splits or K.decode_splits(meta, nh, nkv))
         else:
-            out.update(tflops=round(4 * nh * hd * ctx * ctx / 2 / ms / 1e9, 1))
+            out.update(past=args.past, tflops=round(4 * nh * hd * (args.tokens * args.past + args.tokens * args.tokens / 2) / ms / 1e9, 1))
     print(json.dumps(out))
     return 0
 

@@ -578,6 +578,12 @@ TC_ATT_CASES = [
     (16, 1, 128, 64, [40, 50], [300, 50], 100),
     (32, 8, 128, 16, [333, 1, 64], [777, 100, 64], None),
     (8, 8, 128, 128, [17], [400], 256),
+    # groups that do not divide the 128 rows of a tile: 18 tokens of 7 heads, 25 of 5, 42 of 3, 21 of 6, one of 100
+    (28, 4, 128, 16, [300, 1, 19], [700, 50, 19], None),
+    (10, 2, 64, 16, [127, 26], [127, 400], 60),
+    (3, 1, 128, 32, [85, 43], [200, 43], None),
+    (12, 2, 64, 8, [64], [1000], None),
+    (100, 1, 64, 16, [5], [70], None),
 ]
 
 
