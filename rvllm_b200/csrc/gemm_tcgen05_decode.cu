@@ -256,7 +256,29 @@ __device__ __forceinline__ void finish_from_parts(const DecodeGemmParams& p, int
 template <int MB>
 __global__ void __launch_bounds__(NUM_THREADS, (MB <= 16 || MB == 64) ? 3 : 2)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                   const DecodeGemmParams p) {
+                   const DecodeGemmParams p_in) {
+    // More than 128 rows (MB = 128 only): blockIdx.y is a block of 128 rows, which this CTA treats as a
+    // product of its own - the rows' pointers moved on, M cut to the block.  The other widths see the
+    // parameters as they came.
+    DecodeGemmParams p_blk;
+    int x_row0 = 0;
+    if constexpr (MB == 128) {
+        p_blk = p_in;
+        x_row0 = (int)blockIdx.y * MB;
+        if (x_row0 > 0) {
+            const size_t r0 = (size_t)x_row0;
+            const size_t n_out = p_in.gated ? (size_t)(p_in.N >> 1) : (size_t)p_in.N;
+            p_blk.out = p_in.out_f32 ? (void*)((float*)p_in.out + r0 * n_out) : (void*)((__nv_bfloat16*)p_in.out + r0 * n_out);
+            if (p_in.residual) p_blk.residual = p_in.residual + r0 * p_in.N;
+            if (p_in.q_out) {
+                p_blk.q_out = p_in.q_out + r0 * p_in.nh * p_in.hd;
+                p_blk.positions = p_in.positions + r0;
+                p_blk.slot_mapping = p_in.slot_mapping + r0;
+            }
+        }
+        p_blk.M = min(MB, p_in.M - x_row0);
+    }
+    const DecodeGemmParams& p = (MB == 128) ? p_blk : p_in;
     constexpr int STAGES = STAGES_FOR(MB);
     constexpr int B_BYTES = MB * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -342,7 +364,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
             rv_pdl_wait();
             for (int i = 0; i < early; ++i)
-                tma_load_2d(smem_u32(tiles + (size_t)i * STAGE_BYTES) + A_BYTES, &map_x, kb_at(i) * BK, 0, full0 + 8 * i);
+                tma_load_2d(smem_u32(tiles + (size_t)i * STAGE_BYTES) + A_BYTES, &map_x, kb_at(i) * BK, x_row0, full0 + 8 * i);
             issued = early;
             stage = early % STAGES;
             phase = early == STAGES ? 1 : 0;
@@ -354,7 +376,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 mbar_expect_tx(bar, STAGE_BYTES);
                 tma_load_2d(a_dst, &map_w, kb * BK, row_a, bar);
                 tma_load_2d(a_dst + A_BYTES / 2, &map_w, kb * BK, row_b, bar);
-                tma_load_2d(a_dst + A_BYTES, &map_x, kb * BK, 0, bar);
+                tma_load_2d(a_dst + A_BYTES, &map_x, kb * BK, x_row0, bar);
                 ++issued;
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
@@ -750,11 +772,12 @@ static int launch_decode(const CUtensorMap& mw, const CUtensorMap& mx, const Dec
         if (p.cluster) smem += p.splits * p.cluster_rows * TILE_F * 4;              // the partials of this CTA's rows behind that
         if (smem < fin + 1024) smem = fin + 1024;
     }
+    const int row_blocks = MB == 128 ? (p.M + MB - 1) / MB : 1;
     if (p.cluster)
-        RV_LAUNCH_ST = rv_launch_cluster(gemm_decode_kernel<MB>, dim3(p.n_tiles * p.splits), dim3(NUM_THREADS), smem, stream,
+        RV_LAUNCH_ST = rv_launch_cluster(gemm_decode_kernel<MB>, dim3(p.n_tiles * p.splits, row_blocks), dim3(NUM_THREADS), smem, stream,
                                          (unsigned)p.splits, mw, mx, p);
     else
-        RV_LAUNCH_ST = rv_launch(gemm_decode_kernel<MB>, dim3(p.n_tiles * p.splits), dim3(NUM_THREADS), smem, stream, mw, mx, p);
+        RV_LAUNCH_ST = rv_launch(gemm_decode_kernel<MB>, dim3(p.n_tiles * p.splits, row_blocks), dim3(NUM_THREADS), smem, stream, mw, mx, p);
     return rv_launch_status();
 }
 
@@ -780,7 +803,9 @@ static int run_decode(const void* x, const void* w, DecodeGemmParams p, cudaStre
     p.l2_ahead = g_l2_ahead;
     p.k_rotate = g_k_rotate;
     if (p.M < 0 || p.N <= 0 || p.K <= 0 || p.splits < 1) return RV_ERR_BAD_SIZE;
-    if (p.M > 128) return RV_ERR_UNSUPPORTED;
+    if (p.M > 128 * 512) return RV_ERR_UNSUPPORTED;
+    // blocks of 128 rows share neither scratch nor counters: beyond 128 rows K is split inside a cluster, or not at all
+    if (p.M > 128 && p.splits > 1 && !(p.cluster && p.splits <= 8 && !p.gated && (!p.q_out || p.hd >= 8))) return RV_ERR_UNSUPPORTED;
     if (p.K % 8) return RV_ERR_UNSUPPORTED;
     if (p.norm_gamma && p.M > 16) return RV_ERR_UNSUPPORTED;       // the fused norm serves one 16-row tile
     if (p.norm_gamma && (p.K + BK - 1) / BK * BK > MAX_NORM_K) return RV_ERR_UNSUPPORTED;
@@ -791,8 +816,8 @@ static int run_decode(const void* x, const void* w, DecodeGemmParams p, cudaStre
     if (p.splits > num_kb) p.splits = num_kb;
     // few rows, few splits, an epilogue that adds partials four features at a time: the CTAs of a tile
     // form a cluster and add up in shared memory
-    p.cluster = (p.cluster && p.splits >= 2 && p.splits <= 8 && p.M <= 64 && !p.gated && (!p.q_out || p.hd >= 8)) ? 1 : 0;
-    p.cluster_rows = (p.M + p.splits - 1) / p.splits;
+    p.cluster = (p.cluster && p.splits >= 2 && p.splits <= 8 && !p.gated && (!p.q_out || p.hd >= 8)) ? 1 : 0;
+    p.cluster_rows = ((p.M < 128 ? p.M : 128) + p.splits - 1) / p.splits;
     if (p.splits > 1 && !p.cluster && (!p.scratch || !p.counters)) return RV_ERR_BAD_SIZE;
     const int mb = rv_gemm_decode_padded_rows(p.M);
     alignas(64) CUtensorMap mw, mx;

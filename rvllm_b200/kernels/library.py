@@ -78,6 +78,9 @@ class CudaKernels:
     TCGEN05_ATTENTION_MIN_TOKENS = 16  # ... from this many tokens in the longest portion of the step
     DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
     DECODE_SPLIT_ROWS = 8   # ... when K has to be split over CTAs, only up to this many rows
+    DECODE_BLOCK_MAX_ROWS = 256   # ... and, in blocks of 128 rows, for products of up to this many rows whose 128-feature
+                                  # tiles x row blocks do not fill the SMs (q/k/v, o, down of a short prompt: the 256-row
+                                  # tiles of the prefill GEMM would keep a fraction of the GPU busy)
     CLUSTER_REDUCE = True        # split-K partials of few rows are added up inside a thread-block cluster
     DECODE_K_ROTATE = 13         # tile t of a decode GEMM starts its K loop at block (t * this) mod its count, so that the CTAs of a
                                  # wave do not all read the same columns of the weights at a time (0: all start at the first block)
@@ -511,9 +514,12 @@ class CudaKernels:
         """Whether the weight-streaming tcgen05 GEMM serves this product: few rows, and either
         enough 128-feature tiles to fill the GPU without splitting K, or so few rows that the
         split reduction is cheap."""
-        if not (0 < M <= self.DECODE_MAX_ROWS) or K % 8:
+        if M <= 0 or K % 8:
             return False
         tiles = ((N // 2 + 63) // 64) if gated else (N + 127) // 128
+        if M > self.DECODE_MAX_ROWS:
+            return (not gated and self.CLUSTER_REDUCE and M <= self.DECODE_BLOCK_MAX_ROWS
+                    and tiles * ((M + 127) // 128) <= self.num_sms)
         split_rows = self.CLUSTER_MAX_ROWS if (self.CLUSTER_REDUCE and not gated) else self.DECODE_SPLIT_ROWS
         return M <= max(split_rows, self.DECODE_SPLIT_ROWS) or self.gemm_splits(tiles, K) == 1
 
@@ -546,6 +552,13 @@ class CudaKernels:
         gated are cut into at most 8 CTAs per tile, which add their partials up inside a cluster; where
         the caller left the cut open, about `CLUSTER_TARGET_CTAS` CTAs in all (measured: more CTAs
         than that delay the next kernel's first loads by more than they gain)."""
+        if M > self.DECODE_MAX_ROWS and not gated:
+            # blocks of 128 rows, one CTA per SM (four stages of 32 KB and the cluster's buffers fill one): K is
+            # split so that tiles x row blocks x splits stay within the SMs, inside a cluster or not at all
+            if not chosen:         # (clusters do not fill the last SMs of every GPC: an eighth of the SMs is left out of the count)
+                splits = (self.num_sms - self.num_sms // 8) // max(tiles * ((M + 127) // 128), 1)
+            splits = max(1, min(splits, 8, ((K + 63) // 64) // 4))
+            return splits, splits >= 2 and cluster is not False
         if cluster is None:
             cluster = self.CLUSTER_REDUCE and not gated and 0 < M <= self.CLUSTER_MAX_ROWS and splits >= 2
             if cluster:
@@ -556,7 +569,8 @@ class CudaKernels:
 
     def linear_decode(self, x, weight, bias=None, residual=None, out_dtype=None, gated=False, splits=None, status=None,
                       norm=None, cluster=None):
-        """The weight-streaming tcgen05 GEMM for at most 128 rows of bfloat16 activations.
+        """The weight-streaming tcgen05 GEMM for few rows of bfloat16 activations (beyond 128 rows:
+        in blocks of 128, K split inside a cluster or not at all).
         norm = (gamma, eps): RMSNorm applied to x inside the kernel (at most 16 rows)."""
         _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
         M, K = x.shape
@@ -571,7 +585,7 @@ class CudaKernels:
         splits = max(1, min(splits, (K + 63) // 64))
         splits, cluster = self._cluster_policy(M, gated, splits, cluster, tiles, K, chosen)
         scratch = None
-        if splits > 1:
+        if splits > 1 and not (cluster and M > self.DECODE_MAX_ROWS):
             if self._decode_counters is None or self._decode_counters.numel() < tiles:
                 self._decode_counters = torch.zeros((max(tiles, 4096),), dtype=torch.int32, device=x.device)
             mb = lib.rv_gemm_decode_padded_rows(c_int(M))
@@ -599,7 +613,8 @@ class CudaKernels:
         norm = (gamma, eps): x is normalised first (RMSNorm), inside the fused kernel where that runs."""
         M, K = x.shape
         full_rotation = cos is None or cos.shape[1] == head_dim // 2      # the rotary epilogues rotate whole heads
-        if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < M <= self.FUSED_QKV_MAX_ROWS and full_rotation
+        few = 0 < M <= self.FUSED_QKV_MAX_ROWS or (M > self.DECODE_MAX_ROWS and self._use_decode_gemm(M, weight.shape[0], K, False))
+        if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and few and full_rotation
                 and 128 % head_dim == 0 and K % 8 == 0 and weight.shape[0] == (num_heads + 2 * num_kv_heads) * head_dim):
             if norm is not None and not self._can_fuse_norm(x, norm):
                 x, norm = self.rmsnorm(x, *norm), None
@@ -670,7 +685,7 @@ class CudaKernels:
         splits = max(1, min(splits, (K + 63) // 64))
         splits, cluster = self._cluster_policy(M, False, splits, cluster, tiles, K, chosen)
         scratch = None
-        if splits > 1:
+        if splits > 1 and not (cluster and M > self.DECODE_MAX_ROWS):
             if self._decode_counters is None or self._decode_counters.numel() < tiles:
                 self._decode_counters = torch.zeros((max(tiles, 4096),), dtype=torch.int32, device=x.device)
             mb = lib.rv_gemm_decode_padded_rows(c_int(M))

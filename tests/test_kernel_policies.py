@@ -28,11 +28,16 @@ def test_cluster_reduce_is_chosen_for_few_rows_and_caps_the_splits():
     # given by the caller: kept, up to 8
     assert k._cluster_policy(8, False, 3, None, 32, 4096, True) == (3, True)
     assert k._cluster_policy(8, False, 12, None, 32, 4096, True) == (8, True)
-    # no cluster: one split, gated products, more rows than CLUSTER_MAX_ROWS, or when asked not to
+    # no cluster: one split, gated products, or when asked not to
     assert k._cluster_policy(8, False, 1, None, 1002, 4096, False) == (1, False)
     assert k._cluster_policy(8, True, 2, None, 224, 4096, False) == (2, False)
-    assert k._cluster_policy(k.CLUSTER_MAX_ROWS + 1, False, 9, None, 32, 4096, False) == (9, False)
     assert k._cluster_policy(8, False, 9, False, 32, 4096, False) == (9, False)
+    # beyond DECODE_MAX_ROWS, blocks of 128 rows: tiles x row blocks x splits within the SMs, four k blocks each at least
+    assert k._cluster_policy(65, False, 9, None, 32, 4096, False) == (4, True)
+    assert k._cluster_policy(128, False, 9, None, 48, 4096, False) == (2, True)
+    assert k._cluster_policy(256, False, 9, None, 32, 4096, False) == (2, True)
+    assert k._cluster_policy(300, False, 9, None, 48, 14336, False) == (1, False)
+    assert k._cluster_policy(100, False, 7, None, 5, 1032, True) == (4, True)        # given: kept up to 8 and to four k blocks each
 
 
 def test_which_products_take_the_weight_streaming_gemm():
@@ -47,6 +52,10 @@ def test_which_products_take_the_weight_streaming_gemm():
         del k.CLUSTER_REDUCE
     assert k._use_decode_gemm(64, 28672, 4096, True) and k._use_decode_gemm(64, 128256, 4096, False)
     assert not k._use_decode_gemm(65, 28672, 4096, True) and not k._use_decode_gemm(8, 4096, 4100, False)
+    # short prompts: q/k/v, o and down in blocks of 128 rows while tiles x row blocks leave SMs idle
+    assert k._use_decode_gemm(65, 4096, 4096, False) and k._use_decode_gemm(256, 4096, 14336, False)
+    assert k._use_decode_gemm(256, 6144, 4096, False) and not k._use_decode_gemm(256, 10240, 4096, False)
+    assert not k._use_decode_gemm(257, 4096, 4096, False) and not k._use_decode_gemm(128, 128256, 4096, False)
     assert not k._use_decode_gemm(0, 4096, 4096, False)
 
 

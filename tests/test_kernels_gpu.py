@@ -392,6 +392,89 @@ def test_split_k_added_up_inside_a_cluster(K, M, N, Kd):
         assert int(K._decode_counters.abs().sum().item()) == 0
 
 
+@pytest.mark.parametrize("M,N,Kd", [(100, 520, 1032), (128, 384, 4096), (129, 1000, 520), (300, 4096, 1024), (512, 256, 2048)])
+def test_decode_gemm_in_blocks_of_128_rows(K, M, N, Kd):
+    """More than 64 rows through the weight-streaming kernel: blocks of 128 rows (the last one cut), K whole or
+    split inside a cluster, every epilogue; a row's sums do not depend on the block it falls into or on what
+    else the batch holds."""
+    torch.manual_seed(21)
+    x = torch.randn(M, Kd, device="cuda").bfloat16()
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(N, device="cuda").bfloat16()
+    r = torch.randn(M, N, device="cuda").bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ref = x.double().cpu() @ w.double().cpu().t()
+    full = ref + b.double().cpu() + r.double().cpu()
+    for splits in (None, 1, 2, 4, 7):
+        if splits and splits > (Kd + 63) // 64:
+            continue
+        assert rel_err(K.linear_decode(x, w, splits=splits, status=status), ref) < BF16_TOL
+        assert rel_err(K.linear_decode(x, w, b, r, splits=splits, status=status), full) < BF16_TOL
+        got = K.linear_decode(x, w, b.float(), None, torch.float32, splits=splits, status=status)
+        assert rel_err(got, ref + b.double().cpu()) < 1e-5
+        if splits in (1, 2):
+            # the last rows alone, and the first, with K cut at the same places: the same bits as inside the batch
+            tail = K.linear_decode(x[-3:].contiguous(), w, b.float(), None, torch.float32, splits=splits, status=status)
+            head = K.linear_decode(x[:70].contiguous(), w, b.float(), None, torch.float32, splits=splits, status=status)
+            assert torch.equal(tail, got[-3:]) and torch.equal(head, got[:70])
+    g, u = ref[:, :N // 2], ref[:, N // 2:]
+    assert rel_err(K.linear_decode(x, w, gated=True, splits=1, status=status), g / (1 + torch.exp(-g)) * u) < BF16_TOL
+    assert int(status.item()) == 0, "a bounded wait inside the kernel gave up"
+    # the dispatch takes this kernel where tiles x row blocks leave SMs idle, and not beyond
+    assert K._use_decode_gemm(M, N, Kd, False) == (M <= K.DECODE_BLOCK_MAX_ROWS and -(-N // 128) * -(-M // 128) <= K.num_sms)
+    assert not K._use_decode_gemm(K.DECODE_BLOCK_MAX_ROWS + 1, N, Kd, False) and not K._use_decode_gemm(M, 2 * N, Kd, True)
+    assert torch.equal(K.linear(x, w, b, r), K.linear_decode(x, w, b, r)) or not K._use_decode_gemm(M, N, Kd, False)
+
+
+@pytest.mark.parametrize("M,nh,nkv,hd,Kd,page,bias", [(100, 6, 2, 64, 264, 16, True), (200, 8, 2, 128, 1024, 16, False),
+                                                      (384, 4, 4, 32, 520, 8, True)])
+def test_qkv_rotation_and_cache_write_in_blocks_of_128_rows(K, M, nh, nkv, hd, Kd, page, bias):
+    """The rotary epilogue for more than 64 rows: every block of 128 rows takes its own positions and slots."""
+    torch.manual_seed(22)
+    N = (nh + 2 * nkv) * hd
+    x = torch.randn(M, Kd, device="cuda").bfloat16()
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(N, device="cuda").bfloat16() if bias else None
+    positions = torch.randint(0, 500, (M,), device="cuda", dtype=torch.int32)
+    ang = torch.arange(512, dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))[None]
+    cos, sin = ang.cos().float().cuda(), ang.sin().float().cuda()
+    pages = 2 * M // page + 3
+    slots = torch.randperm(pages * page)[:M].to(torch.int32).cuda()
+    slots[M // 2] = -1
+    slots[M - 1] = -1
+    cache_a = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda").bfloat16()
+    cache_b = cache_a.clone()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for splits in (None, 1, 2, 3):
+        if splits and splits > (Kd + 63) // 64 // 4:
+            continue
+        cache_a.fill_(7.0)
+        cache_b.fill_(7.0)
+        qa = K._qkv_rope_fused(x, w, b, positions, cos, sin, slots, cache_a, nh, nkv, hd, splits=splits, status=status)
+        qkv = K.linear_decode(x, w, splits=splits, out_dtype=torch.float32)
+        qb = K.rope_cache_write(qkv, b, positions, cos, sin, slots, cache_b, nh, nkv, hd, out_dtype=torch.bfloat16)
+        assert same_up_to_an_ulp(qa, qb) and same_up_to_an_ulp(cache_a, cache_b)
+    assert int(status.item()) == 0
+    y = x.double().cpu() @ w.double().cpu().t()
+    if bias:
+        y = y + b.double().cpu()
+    y = y.view(M, nh + 2 * nkv, hd)
+    c, s_ = ang.cos()[positions.cpu().long()][:, None, :], ang.sin()[positions.cpu().long()][:, None, :]
+    rot = lambda t: torch.cat([t[..., :hd // 2] * c - t[..., hd // 2:] * s_, t[..., :hd // 2] * s_ + t[..., hd // 2:] * c], -1)
+    assert rounded_once(qa, rot(y[:, :nh]).reshape(M, nh * hd))
+    kref, vref = rot(y[:, nh:nh + nkv]), y[:, nh + nkv:]
+    for m in (0, 63, 64, 127, 128, M - 2):
+        if m >= M:
+            continue
+        sl = int(slots[m])
+        if sl >= 0:
+            assert rel_err(cache_a[sl // page, 0, :, sl % page], kref[m]) < BF16_TOL
+            assert rel_err(cache_a[sl // page, 1, :, sl % page], vref[m]) < BF16_TOL
+    # rows without a slot wrote nothing: as many untouched slots as the cache has beyond the written ones
+    written = int((slots >= 0).sum())
+    assert int((cache_a.float().permute(0, 3, 1, 2, 4).reshape(pages * page, -1) != 7.0).any(1).sum()) == written
+
+
 @pytest.mark.parametrize("M,nh,nkv,hd,Kd,page,bias", [(1, 32, 8, 128, 4096, 16, False), (5, 6, 2, 32, 96, 8, True),
                                                       (16, 5, 5, 16, 80, 16, True), (3, 4, 1, 64, 264, 4, False)])
 def test_qkv_product_with_rotation_and_cache_write_in_one_kernel(K, M, nh, nkv, hd, Kd, page, bias):
@@ -563,7 +646,9 @@ def test_qkv_product_with_rotation_and_cache_write_for_many_rows(K, M, nh, nkv, 
     cache_c = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda").bfloat16()
     before = COUNTERS["launches"]
     qc = K.qkv_rope_cache_write(x, w, b, positions, cos, sin, slots, cache_c, nh, nkv, hd)
-    if K._tcgen05_fills(M, N):
+    if K._use_decode_gemm(M, N, Kd, False):          # few tiles: the weight-streaming kernel in blocks of 128 rows
+        assert COUNTERS["launches"] == before + 1 and same_up_to_an_ulp(qc, qa) and same_up_to_an_ulp(cache_c, cache_a)
+    elif K._tcgen05_fills(M, N):
         assert COUNTERS["launches"] == before + 1 and torch.equal(qc, qa) and torch.equal(cache_c, cache_a)
     else:
         assert same_up_to_an_ulp(qc, qa) and same_up_to_an_ulp(cache_c, cache_a)
