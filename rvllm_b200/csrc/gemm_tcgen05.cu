@@ -44,7 +44,10 @@
 #define RV_PAIR 0
 #endif
 #define BM 128
-#define BN 256
+#ifndef BN
+#define BN 256          // columns of an output tile; -DBN=128 builds the narrow tiles for products that would not fill the SMs
+#endif
+static_assert(BN == 256 || BN == 128, "tiles of 256 or 128 columns");
 #define BK 64
 #define UMMA_K 16
 #define A_TILE_BYTES (BM * BK * 2)
@@ -511,6 +514,7 @@ RV_EXPORT int rv_gemm_tcgen05_qkv_rope(const void* x, const void* w, const void*
                                        int max_ctas, cudaStream_t stream) {
     if (M < 0 || K <= 0 || nh <= 0 || nkv <= 0 || page_size <= 0 || table_rows <= 0) return RV_ERR_BAD_SIZE;
     if (hd != 64 && hd != 128 && hd != 256) return RV_ERR_UNSUPPORTED;     // a head's halves are whole 32-column chunks of one tile
+    if (hd > BN) return RV_ERR_UNSUPPORTED;                                // (a narrow-tile build cannot hold a head of 256)
     if (K % 8) return RV_ERR_UNSUPPORTED;
     if ((cos_t == nullptr) != (sin_t == nullptr)) return RV_ERR_BAD_SIZE;
     if (!positions || !slot_mapping || !kv_cache || !q_out) return RV_ERR_BAD_SIZE;

@@ -73,6 +73,7 @@ class CudaKernels:
                             # (0: always.  With 0.8 the library's GEMM takes the partly filled shapes and is 20-140 %
                             # faster there, but its sums depend on the operands' addresses: the same request no longer
                             # gives the same bits in every run)
+    NARROW_TILES = True                # ... with tiles of 128 columns where those of 256 would occupy at most half of the SMs
     PAIR_GEMM = True                   # the tcgen05 GEMM runs on pairs of CTAs (cta_group::2) where the rows fill its 256-row tiles
     TCGEN05_ATTENTION = True           # prompt portions go to the tcgen05 attention kernel when it fits
     TCGEN05_ATTENTION_MIN_TOKENS = 16  # ... from this many tokens in the longest portion of the step
@@ -484,12 +485,20 @@ class CudaKernels:
         rounds = -(-tiles // workers)
         return tiles >= self.TCGEN05_MIN_FILL * rounds * workers
 
-    def _prefill_gemm_lib(self, M: int, pair=None):
+    def _prefill_gemm_lib(self, M: int, pair=None, N: int = 0, gated: bool = False, head_dim: int = 0):
         """The tcgen05 GEMM library for M rows: built for pairs of CTAs (tiles of 256 rows) unless the
-        last tile's second half would be empty, or for one CTA per tile (tiles of 128 rows)."""
+        last tile's second half would be empty, or for one CTA per tile (tiles of 128 rows); with
+        tiles of 128 columns instead of 256 where the wide ones would leave half of the workers without
+        a tile (N given: a few hundred rows of a product with few weight rows)."""
         if pair is None:
             pair = self.PAIR_GEMM and (M % 256 == 0 or M % 256 > 128)
-        return self._lib("gemm_tcgen05.cu", ("-DRV_PAIR=1",) if pair else ())
+        defines = ("-DRV_PAIR=1",) if pair else ()
+        if N and self.NARROW_TILES and head_dim <= 128:        # (a head's rotation pairs lie in one tile)
+            rows, workers = (256, self.num_sms // 2) if pair else (128, self.num_sms)
+            tiles = -(-M // rows) * (-(-(N // 2) // 128) if gated else -(-N // 256))
+            if 2 * tiles <= workers + workers // 8:
+                defines = defines + ("-DBN=128",)
+        return self._lib("gemm_tcgen05.cu", defines)
 
     def linear_tcgen05(self, x, weight, residual=None, out_dtype=None, gated=False, status=None, max_ctas=0, pair=None):
         """The tcgen05 / TMEM / TMA GEMM for bfloat16 (any M; K a multiple of 8).  gated: weight rows
@@ -504,7 +513,7 @@ class CudaKernels:
         if residual is not None:
             _need(residual, "residual", torch.bfloat16, 2)
         epilogue = 2 if gated else (1 if residual is not None else 0)
-        st = self._prefill_gemm_lib(M, pair).rv_gemm_tcgen05_bf16(
+        st = self._prefill_gemm_lib(M, pair, N, gated).rv_gemm_tcgen05_bf16(
             _ptr(x), _ptr(weight), _ptr(residual), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0),
             c_int(M), c_int(N), c_int(K), c_int(epilogue), _ptr(status if status is not None else self._status), c_int(max_ctas), self._stream())
         _check("gemm_tcgen05", st)
@@ -651,7 +660,7 @@ class CudaKernels:
         if bias is not None:
             _need(bias, "bias", dims=1)
         q = torch.empty((M, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
-        st = self._prefill_gemm_lib(M, pair).rv_gemm_tcgen05_qkv_rope(
+        st = self._prefill_gemm_lib(M, pair, weight.shape[0], head_dim=head_dim).rv_gemm_tcgen05_qkv_rope(
             _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0),
             _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(cache_layer), _ptr(q), c_int(M), c_int(K),
             c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]),

@@ -19,7 +19,8 @@ def all_variants() -> List[Tuple[str, Sequence[str]]]:
         elif src == "attention_tcgen05.cu":
             out.extend((src, (f"-DHEAD_DIM={hd}",)) for hd in (64, 128))
         elif src == "gemm_tcgen05.cu":
-            out.extend([(src, ()), (src, ("-DRV_PAIR=1",))])         # one CTA per tile, and pairs of CTAs
+            # one CTA per tile and pairs of CTAs, each with tiles of 256 and of 128 columns
+            out.extend([(src, ()), (src, ("-DRV_PAIR=1",)), (src, ("-DBN=128",)), (src, ("-DRV_PAIR=1", "-DBN=128"))])
         else:
             out.append((src, ()))
     return out

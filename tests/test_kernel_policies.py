@@ -76,6 +76,12 @@ def test_the_prefill_gemm_and_its_build_are_chosen_by_rows():
         k._prefill_gemm_lib(rows)
     assert [bool(d) for _, d in picked] == [True, False, True, True, False, False]
     assert all(src == "gemm_tcgen05.cu" for src, _ in picked)
+    # tiles of 128 columns where the 256-column ones would give at most half of the workers a tile
+    picked.clear()
+    for rows, n, gated, hd in ((384, 4096, False, 0), (512, 4096, False, 0), (2048, 4096, False, 0), (512, 28672, True, 0),
+                               (384, 6144, False, 128), (384, 1536, False, 256)):
+        k._prefill_gemm_lib(rows, None, n, gated, hd)
+    assert [("-DBN=128" in d) for _, d in picked] == [True, True, False, False, True, False]
 
 
 def test_key_splits_of_decode_attention_follow_the_wave_model():
