@@ -1005,6 +1005,315 @@ flash_decode_balanced_kernel(const BalancedParams p) {
     }
 }
 
+#ifdef RV_HAVE_TMA_DECODE
+// The evenly cut kernel fed by TMA: the tile list, the pieces and the arithmetic of the kernel above (so the same
+// bits), the tiles brought by a fifth warp as in flash_decode_tma_kernel.  The producer walks the CTA's run of
+// tiles on its own, across the pieces' borders: while the four consumer warps merge a piece and load the next
+// piece's queries, the next piece's first tiles are already on their way.  The merge buffer lies behind the ring
+// (the ring is never idle), sized for the group's rows.
+// Sequences per step: with 240 the kernel's static shared memory stays within 1 KB, and three CTAs (two stages of
+// keys and values, the merge buffer of a group of four heads) just fit an SM.
+#define BAL_TMA_MAX_SEQS 240
+template <int NST>
+__global__ void __launch_bounds__(TMA_THREADS, TMA_MIN_CTAS)
+flash_decode_balanced_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const BalancedParams p, int* status) {
+    rv_pdl_launch_dependents();
+    constexpr int HD = HEAD_DIM;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* k_s = smem;                                   // [NST][TMA_TILE_BYTES]
+    unsigned char* v_s = smem + NST * TMA_TILE_BYTES;            // [NST][TMA_TILE_BYTES]
+    float* mo = reinterpret_cast<float*>(smem + 2 * NST * TMA_TILE_BYTES);       // [4 warps][G][HD], then [4][G][2]
+    __shared__ __align__(8) uint64_t bars[2 * NST];
+    __shared__ volatile int abort_flag;
+    __shared__ int s_first[BAL_TMA_MAX_SEQS + 1];      // tiles of the sequences before this one (a sequence's first key
+                                                       // tile under a window is worked out again where it is needed)
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int quad = lane >> 2, tq = lane & 3;
+    const int G = p.nh / p.nkv;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[NST]);
+
+    // ---- the list of tiles (step metadata: read before the wait for the previous kernel)
+    for (int s = tid; s < p.num_seqs; s += TMA_THREADS) {
+        const int ctx = p.ctx_lens[s];
+        const int q_len = p.cu_seqlens[s + 1] - p.cu_seqlens[s];
+        int lo = 0, n = 0;
+        if (q_len == 1 && ctx > 0) {
+            const int pos = ctx - 1;
+            const int key_lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+            lo = key_lo / KV_TILE;
+            n = (ctx + KV_TILE - 1) / KV_TILE - lo;
+        }
+        s_first[s + 1] = n;
+    }
+    if (tid == 0) {
+        tma_prefetch_descriptor(&map_kv);
+        abort_flag = 0;
+#pragma unroll
+        for (int s = 0; s < NST; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // value stages start as zeros (keys of a tile that are not requested meet a probability of zero)
+    for (int i = tid; i < NST * TMA_TILE_BYTES / 16; i += TMA_THREADS) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        s_first[0] = 0;
+        for (int s = 0; s < p.num_seqs; ++s) { run += s_first[s + 1]; s_first[s + 1] = run; }
+    }
+    __syncthreads();
+    const int total = s_first[p.num_seqs] * p.nkv;
+    const int ctas = gridDim.x, cta = blockIdx.x;
+    const int W = total > 0 ? (total + ctas - 1) / ctas : 1;
+    const int u0 = cta * W;
+    const int u_end = min(total, u0 + W);
+    // first sequence of the run: the last one whose tiles start at or before u0 (both roles walk on from it)
+    int seq0 = 0;
+    if (u0 < u_end) {
+        int lo = 0, hi = p.num_seqs - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (s_first[mid] * p.nkv <= u0) lo = mid; else hi = mid - 1;
+        }
+        seq0 = lo;
+    }
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ producer warp
+        const int box_keys = p.page_size < KV_TILE ? p.page_size : KV_TILE;
+        const int boxes = KV_TILE / box_keys;
+        bool waited = false, ok = true;
+        int issued = 0, seq = seq0;
+        for (int u = u0; u < u_end && ok; ++u, ++issued) {
+            while (s_first[seq + 1] * p.nkv <= u) ++seq;
+            const int n_seq = s_first[seq + 1] - s_first[seq];
+            const int in_seq = u - s_first[seq] * p.nkv;
+            const int kvh = in_seq / n_seq;
+            const int stage = issued % NST, use = issued / NST;
+            if (use > 0) {
+                int ok_l = 1;
+                if (lane == 0) ok_l = mbar_wait(empty0 + 8 * stage, (use - 1) & 1, &abort_flag, 1) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok_l, 0) != 0;
+                if (!ok) break;
+            }
+            const int ctx = p.ctx_lens[seq];
+            const int key_lo = (p.window > 0 && ctx - p.window > 0) ? ctx - p.window : 0;
+            const int t = key_lo / KV_TILE + (in_seq - kvh * n_seq);
+            // the newest key of a sequence was written by the kernel before this one
+            if (!waited && (t + 1) * KV_TILE >= ctx) { rv_pdl_wait(); waited = true; }
+            const int* table = p.block_tables + (size_t)seq * p.max_blocks;
+            const int key = t * KV_TILE + lane * box_keys;
+            int page = -1;
+            if (lane < boxes && key < ctx && key + box_keys > key_lo) page = __ldg(table + (key >> p.page_shift));
+            const unsigned mask = __ballot_sync(0xffffffffu, page >= 0);
+            const uint32_t bar = full0 + 8 * stage;
+            if (lane == 0) mbar_expect_tx(bar, (uint32_t)__popc(mask) * 2u * TMA_HALVES * (uint32_t)box_keys * 128u);
+            __syncwarp();
+            if (page >= 0) {
+                const int row_k = ((page * 2) * p.nkv + kvh) * p.page_size + (key & (p.page_size - 1));
+                const int row_v = row_k + p.nkv * p.page_size;
+                const uint32_t dk = smem_u32(k_s) + (uint32_t)stage * TMA_TILE_BYTES + (uint32_t)lane * box_keys * 128;
+                const uint32_t dv = smem_u32(v_s) + (uint32_t)stage * TMA_TILE_BYTES + (uint32_t)lane * box_keys * 128;
+#pragma unroll
+                for (int h = 0; h < TMA_HALVES; ++h) {
+                    tma_load_2d(dk + h * TMA_SLAB, &map_kv, h * 64, row_k, bar);
+                    tma_load_2d(dv + h * TMA_SLAB, &map_kv, h * 64, row_v, bar);
+                }
+            }
+            __syncwarp();
+        }
+        if (!waited) rv_pdl_wait();
+        if (!ok || abort_flag != 0) {
+            // something gave up: wait (bounded) for the copies still in flight before this CTA's shared memory is given up
+            if (lane == 0) {
+                volatile int ignore = 0;
+                for (int i = max(0, issued - NST); i < issued; ++i)
+                    mbar_wait(full0 + 8 * (i % NST), (i / NST) & 1, &ignore, 0);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ consumer warps
+        const int warp_n = warp;
+        // Nothing is written before this wait (see the kernel above).
+        rv_pdl_wait();
+        for (int pair = cta * 128 + tid; pair < p.num_seqs * p.nkv; pair += ctas * 128) {
+            const int s = pair / p.nkv, kvh = pair - s * p.nkv;
+            const int n = s_first[s + 1] - s_first[s];
+            int count = 0;
+            if (n > 0) {
+                const int u_pair = s_first[s] * p.nkv + kvh * n;
+                count = (u_pair + n - 1) / W - u_pair / W + 1;
+            }
+            p.piece_count[pair] = count;
+        }
+        const size_t rows_all = (size_t)p.n_tokens * p.nh;
+        float* mml = mo + 4 * G * HD;
+        int consumed = 0, seq = seq0;
+        bool ok = true;
+        int u = u0;
+        while (u < u_end && ok) {
+            while (s_first[seq + 1] * p.nkv <= u) ++seq;
+            const int n_seq = s_first[seq + 1] - s_first[seq];
+            const int in_seq = u - s_first[seq] * p.nkv;
+            const int kvh = in_seq / n_seq;
+            const int t_rel = in_seq - kvh * n_seq;
+            const int n_here = min(n_seq - t_rel, u_end - u);              // tiles of this piece
+            const int u_pair = u - t_rel;
+            const int piece = u / W - u_pair / W;                           // its place among the pair's pieces
+            const int ctx = p.ctx_lens[seq];
+            const int pos = ctx - 1;
+            const int key_lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+            const int t_begin = key_lo / KV_TILE + t_rel, t_end = t_begin + n_here;
+            const int tok = p.cu_seqlens[seq];
+            bool valid[2];
+            int head[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = quad + 8 * i;
+                valid[i] = r < G;
+                head[i] = kvh * G + (r < G ? r : 0);
+            }
+            uint32_t qa[HD / 16][4];
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const __nv_bfloat16* qp = p.q + ((size_t)tok * p.nh + head[i]) * HD + ks * 16 + tq * 2;
+                    qa[ks][i] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp) : 0u;
+                    qa[ks][i + 2] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp + 8) : 0u;
+                }
+            }
+            float o[HD / 8][4];
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+            float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+            for (int t = t_begin; t < t_end; ++t, ++consumed) {
+                const int stage = consumed % NST;
+                if (!mbar_wait(full0 + 8 * stage, (consumed / NST) & 1, &abort_flag, 2)) { ok = false; break; }
+                const unsigned char* ks = k_s + (size_t)stage * TMA_TILE_BYTES;
+                const unsigned char* vs = v_s + (size_t)stage * TMA_TILE_BYTES;
+                float s[2][4];
+#pragma unroll
+                for (int n = 0; n < 2; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    uint32_t b[4];
+                    const int key_row = warp_n * 16 + (lane >> 4) * 8 + (lane & 7);
+                    const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+                    ldmatrix_x4(b, ks + tma_swz(key_row, col));
+                    mma_bf16(s[0], qa[kk], b[0], b[1]);
+                    mma_bf16(s[1], qa[kk], b[2], b[3]);
+                }
+                const int key0 = t * KV_TILE + warp_n * 16 + tq * 2;
+                float m_tile[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int n = 0; n < 2; ++n) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + n * 8 + (e & 1);
+                        const bool see = key <= pos && key >= key_lo;
+                        const float v = see ? s[n][e] * p.scale_log2e : -INFINITY;
+                        s[n][e] = v;
+                        m_tile[e >> 1] = fmaxf(m_tile[e >> 1], v);
+                    }
+                }
+                float alpha[2], m_safe[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    m_tile[i] = fmaxf(m_tile[i], __shfl_xor_sync(0xffffffffu, m_tile[i], 1));
+                    m_tile[i] = fmaxf(m_tile[i], __shfl_xor_sync(0xffffffffu, m_tile[i], 2));
+                    const float m_new = fmaxf(m_run[i], m_tile[i]);
+                    m_safe[i] = m_new == -INFINITY ? 0.f : m_new;
+                    alpha[i] = exp2f(m_run[i] - m_safe[i]);
+                    m_run[i] = m_new;
+                }
+                float l_tile[2] = {0.f, 0.f};
+#pragma unroll
+                for (int n = 0; n < 2; ++n) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float pv = exp2f(s[n][e] - m_safe[e >> 1]);
+                        s[n][e] = pv;
+                        l_tile[e >> 1] += pv;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * alpha[i] + l_tile[i];
+#pragma unroll
+                for (int n = 0; n < HD / 8; ++n) {
+                    o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+                    o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+                }
+                uint32_t pa[4];
+                pa[0] = pack_bf16(s[0][0], s[0][1]);
+                pa[1] = pack_bf16(s[0][2], s[0][3]);
+                pa[2] = pack_bf16(s[1][0], s[1][1]);
+                pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+                for (int n2 = 0; n2 < HD / 16; ++n2) {
+                    uint32_t b[4];
+                    const int key_row = warp_n * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                    const int col = n2 * 16 + (lane >> 4) * 8;
+                    ldmatrix_x4_trans(b, vs + tma_swz(key_row, col));
+                    mma_bf16(o[2 * n2], pa, b[0], b[1]);
+                    mma_bf16(o[2 * n2 + 1], pa, b[2], b[3]);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + 8 * stage);      // this warp has read the stage for the last time
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+                l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+            }
+            // ---- merge the four warps (their buffer lies behind the ring) and write the piece's partial result;
+            // after a wait that gave up nothing is written, but every consumer still comes to both barriers
+            consumer_sync();                                   // the merge of the piece before has been read
+            const bool good = abort_flag == 0 && ok;
+            if (good) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int row = quad + 8 * i;
+                    if (row >= G) continue;
+#pragma unroll
+                    for (int n = 0; n < HD / 8; ++n) {
+                        float* dst = mo + ((size_t)warp_n * G + row) * HD + n * 8 + tq * 2;
+                        dst[0] = o[n][2 * i]; dst[1] = o[n][2 * i + 1];
+                    }
+                    if (tq == 0) {
+                        mml[(warp_n * G + row) * 2] = m_run[i];
+                        mml[(warp_n * G + row) * 2 + 1] = l_run[i];
+                    }
+                }
+            }
+            consumer_sync();
+            if (abort_flag != 0 || !ok) { ok = false; break; }
+            for (int idx = tid; idx < G * HD; idx += 128) {
+                const int row = idx / HD, d = idx - row * HD;
+                float m_all = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) m_all = fmaxf(m_all, mml[(w * G + row) * 2]);
+                const float m_s = m_all == -INFINITY ? 0.f : m_all;
+                float l_all = 0.f, acc = 0.f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const float f = exp2f(mml[(w * G + row) * 2] - m_s);
+                    l_all += mml[(w * G + row) * 2 + 1] * f;
+                    acc += mo[((size_t)w * G + row) * HD + d] * f;
+                }
+                const size_t prow = (size_t)piece * rows_all + (size_t)tok * p.nh + kvh * G + row;
+                p.part_o[prow * HD + d] = acc;
+                if (d == 0) { p.part_ml[prow * 2] = m_all; p.part_ml[prow * 2 + 1] = l_all; }
+            }
+            u += n_here;
+        }
+    }
+    __syncthreads();
+    if (tid == 0 && abort_flag != 0 && status) atomicCAS(status, 0, abort_flag);
+}
+#endif   // RV_HAVE_TMA_DECODE
+
 // Merge of the balanced kernel's pieces: one block per (sequence, query head).
 __global__ void flash_balanced_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               const int* __restrict__ piece_count, const int* __restrict__ cu_seqlens,
@@ -1181,6 +1490,78 @@ RV_EXPORT int rv_flash_decode_tma(const void* q, const void* cache, long long nu
         return rv_launch_status();
     }
     return RV_OK;
+#else
+    return RV_ERR_UNSUPPORTED;
+#endif
+}
+
+// The evenly cut decode kernel fed by TMA (head sizes 64 and 128, pages of at least 8 keys; else
+// RV_ERR_UNSUPPORTED and the caller takes rv_flash_decode_balanced).  Same arguments, plus the number of pages
+// of the cache layer (for the tensor map) and the status word of the bounded waits.  ctas <= 0: as many as
+// stay resident, which rv_flash_balanced_tma_ctas tells the caller, who sizes scratch by it.
+#ifdef RV_HAVE_TMA_DECODE
+static int balanced_tma_smem(int G) { return 2 * TMA_STAGES * TMA_TILE_BYTES + 4 * G * (HEAD_DIM + 2) * 4 + 1024; }
+#endif
+RV_EXPORT int rv_flash_balanced_tma_ctas(int nh, int nkv) {
+#ifdef RV_HAVE_TMA_DECODE
+    if (nh <= 0 || nkv <= 0 || nh % nkv || nh / nkv > 16) return 0;
+    const int smem = balanced_tma_smem(nh / nkv);
+    static RvPerDevice configured;
+    if (rv_configure_smem(configured, flash_decode_balanced_tma_kernel<TMA_STAGES>, balanced_tma_smem(16))) return 0;
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, flash_decode_balanced_tma_kernel<TMA_STAGES>, TMA_THREADS, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return per_sm * rv_sm_count();
+#else
+    return 0;
+#endif
+}
+RV_EXPORT int rv_flash_decode_balanced_tma(const void* q, const void* cache, long long num_pages, const int* block_tables,
+                                           const int* cu_seqlens, const int* ctx_lens, void* out, float* scratch,
+                                           int* piece_count, int max_pieces, int n_tokens, int num_seqs, int nh, int nkv,
+                                           int hd, int page_size, int max_blocks, float scale, int window, int ctas,
+                                           int* status, cudaStream_t stream) {
+#ifdef RV_HAVE_TMA_DECODE
+    if (hd != HEAD_DIM) return RV_ERR_UNSUPPORTED;
+    if (n_tokens < 0 || num_seqs < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_blocks <= 0 || max_pieces < 1 ||
+        num_pages <= 0)
+        return RV_ERR_BAD_SIZE;
+    if ((page_size & (page_size - 1)) || page_size < 8) return RV_ERR_UNSUPPORTED;
+    if (nh / nkv > 16 || num_seqs > BAL_TMA_MAX_SEQS) return RV_ERR_UNSUPPORTED;
+    if (n_tokens == 0 || num_seqs == 0) return RV_OK;
+    if (!scratch || !piece_count) return RV_ERR_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) % 16)
+        return RV_ERR_ALIGNMENT;
+    alignas(64) CUtensorMap map_kv;
+    int st = rv_make_bf16_map(&map_kv, cache, num_pages * 2 * nkv * page_size, HEAD_DIM, page_size < KV_TILE ? page_size : KV_TILE);
+    if (st != RV_OK) return st;
+    if (ctas <= 0) ctas = rv_flash_balanced_tma_ctas(nh, nkv);
+    if (ctas <= 0) return RV_ERR_UNSUPPORTED;
+    BalancedParams p;
+    p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache;
+    p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.ctx_lens = ctx_lens;
+    p.out = (__nv_bfloat16*)out;
+    p.part_o = scratch;
+    p.part_ml = scratch + (size_t)max_pieces * n_tokens * nh * HEAD_DIM;
+    p.piece_count = piece_count;
+    p.n_tokens = n_tokens; p.num_seqs = num_seqs; p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.max_blocks = max_blocks;
+    p.max_pieces = max_pieces;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.scale_log2e = scale * 1.4426950408889634f;
+    p.window = window;
+    const int smem = balanced_tma_smem(nh / nkv);
+    static RvPerDevice configured;
+    if (int e = rv_configure_smem(configured, flash_decode_balanced_tma_kernel<TMA_STAGES>, balanced_tma_smem(16))) return e;
+    RV_LAUNCH_ST = rv_launch(flash_decode_balanced_tma_kernel<TMA_STAGES>, dim3(ctas), dim3(TMA_THREADS), smem, stream, map_kv, p, status);
+    st = rv_launch_status();
+    if (st != RV_OK) return st;
+    RV_LAUNCH_ST = rv_launch(flash_balanced_combine_kernel, dim3(num_seqs * nh), dim3((HEAD_DIM + 31) / 32 * 32), 0, stream,
+                             (const float*)p.part_o, (const float*)p.part_ml, (const int*)piece_count, cu_seqlens, p.out,
+                             n_tokens, nh, nkv);
+    return rv_launch_status();
 #else
     return RV_ERR_UNSUPPORTED;
 #endif

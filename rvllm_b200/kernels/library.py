@@ -341,6 +341,14 @@ class CudaKernels:
                 best, best_t = s, t
         return best
 
+    def _balanced_tma_ctas(self, lib, num_heads: int, num_kv_heads: int) -> int:
+        """CTAs of the TMA-fed evenly cut kernel that stay resident (asked from the device once per shape)."""
+        key = (id(lib), num_heads, num_kv_heads)
+        cache = self.__dict__.setdefault("_balanced_ctas", {})
+        if key not in cache:
+            cache[key] = int(lib.rv_flash_balanced_tma_ctas(c_int(num_heads), c_int(num_kv_heads)))
+        return cache[key]
+
     def _balanced_ok(self, meta, group: int, num_kv_heads: int) -> bool:
         """The evenly cut decode kernel serves batches whose (sequence, kv head) pairs alone fill more
         than half of the resident CTAs: there the split kernel leaves waves half empty, and sequences
@@ -348,13 +356,31 @@ class CudaKernels:
         return (self.BALANCED_DECODE and group <= 16 and meta.num_seqs <= 256
                 and meta.num_decode * num_kv_heads >= self.BALANCED_MIN_PAIRS)
 
-    def flash_decode_balanced(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, ctas=0):
+    def flash_decode_balanced(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, ctas=0,
+                              tma=None, status=None):
         """Decode attention for the sequences of the step that bring one token, the 64-key tiles of
         all (sequence, kv head) pairs cut evenly over a fixed number of resident CTAs; sequences
-        with more tokens are left alone."""
+        with more tokens are left alone.  The tiles come by TMA where the kernel is built for the
+        sizes (head size 64 or 128, pages of 8 keys or more, up to 240 sequences), by cp.async
+        otherwise; both give the same bits."""
         _need(q, "q", torch.bfloat16, 2); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
         lib = self._lib("attention_flash.cu", (f"-DHEAD_DIM={head_dim}",))
         T = q.shape[0]
+        tma = self.TMA_DECODE if tma is None else tma
+        if tma and head_dim in (64, 128) and cache_layer.shape[3] >= 8 and meta.num_seqs <= 240:
+            grid = ctas or self._balanced_tma_ctas(lib, num_heads, num_kv_heads)
+            if grid > 0:
+                pieces = lib.rv_flash_balanced_max_pieces(c_int(meta.max_ctx_len), c_int(num_kv_heads), c_int(grid))
+                scratch = torch.empty((pieces * T * num_heads * (head_dim + 2),), dtype=torch.float32, device=q.device)
+                counts = torch.empty((meta.num_seqs * num_kv_heads,), dtype=torch.int32, device=q.device)
+                st = lib.rv_flash_decode_balanced_tma(
+                    _ptr(q), _ptr(cache_layer), ctypes.c_longlong(cache_layer.shape[0]), _ptr(meta.block_tables),
+                    _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens), _ptr(out), _ptr(scratch), _ptr(counts), c_int(pieces), c_int(T),
+                    c_int(meta.num_seqs), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]),
+                    c_int(meta.max_blocks), c_float(scale), c_int(window or 0), c_int(grid),
+                    _ptr(status if status is not None else self._status), self._stream())
+                _check("flash_decode_balanced_tma", st)
+                return out
         grid = ctas or 3 * self.num_sms
         pieces = lib.rv_flash_balanced_max_pieces(c_int(meta.max_ctx_len), c_int(num_kv_heads), c_int(grid))
         scratch = torch.empty((pieces * T * num_heads * (head_dim + 2),), dtype=torch.float32, device=q.device)

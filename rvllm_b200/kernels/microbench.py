@@ -48,7 +48,7 @@ def main(argv=None) -> int:
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--splits", type=int, default=0, help="key splits of the decode attention (0: the library's choice)")
-    ap.add_argument("--variant", default="", help="decode_attention: tma | cpasync | balanced (default: the library's choice)")
+    ap.add_argument("--variant", default="", help="decode_attention: tma | cpasync | balanced | balanced_cpasync (default: the library's choice)")
     args = ap.parse_args(argv)
     K = get_library("cuda:0")
     torch.manual_seed(0)
@@ -110,6 +110,8 @@ def main(argv=None) -> int:
             splits = args.splits or K.decode_splits(meta, nh, nkv)
             if args.variant == "balanced":
                 fn = lambda m: K.flash_decode_balanced(q, cache, m, o, nh, nkv, hd, hd ** -0.5, None)
+            elif args.variant == "balanced_cpasync":
+                fn = lambda m: K.flash_decode_balanced(q, cache, m, o, nh, nkv, hd, hd ** -0.5, None, tma=False)
             else:
                 fn = lambda m: K.decode_attention(q, cache, m, o, nh, nkv, hd, hd ** -0.5, None, num_splits=splits,
                                                   tma=args.variant != "cpasync")

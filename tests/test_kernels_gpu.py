@@ -199,7 +199,12 @@ def test_flash_attention_kernel(K, case):
         # the kernel that cuts all tiles evenly over a fixed number of CTAs: rows of one-token sequences
         for ctas in (0, 1, 3, 7, 64):
             o3 = torch.full_like(q, 9.0)
-            K.flash_decode_balanced(q, cache, meta, o3, nh, nkv, hd, scale, window, ctas=ctas)
+            status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            K.flash_decode_balanced(q, cache, meta, o3, nh, nkv, hd, scale, window, ctas=ctas, status=status)
+            assert int(status.item()) == 0, "a bounded wait inside the kernel gave up"
+            o4 = torch.full_like(q, 9.0)           # tiles by cp.async instead of TMA (where the sizes allow TMA): the same bits
+            K.flash_decode_balanced(q, cache, meta, o4, nh, nkv, hd, scale, window, ctas=ctas, tma=False)
+            assert torch.equal(o3, o4)
             row = 0
             for n in q_lens:
                 if n == 1:
