@@ -137,3 +137,44 @@ def test_contexts_cross_the_graph_buckets(tmp_path, dtype):
     TT.run_trace_tool(folder, dtype, t, str(tmp_path), extra=("--graphs",))
     got = TT.read_logits(str(tmp_path), t, VOCAB)
     check(got, ref, rounded, dtype, f"{name}/graph context buckets/{dtype}")
+
+
+# One layer at the widths of other checkpoints of the two architectures (vocabulary cut): head size 64, groups of
+# 4, 5, 6, 7 and 8 query heads a key/value head, hidden sizes whose products have 7, 12, 16, 40 and 64 tiles of 128
+# features, tied embeddings.  Each meets another side of the kernels' dispatch: how K is split, which tile the
+# attention packs, which epilogue rotates.
+OTHER_WIDTHS = {
+    "llama32_1b": dict(arch="LlamaForCausalLM", hidden=2048, heads=32, kv=8, hd=64, inter=8192, tie=True, theta=500000.0, eps=1e-5),
+    "qwen25_05b": dict(arch="Qwen2ForCausalLM", hidden=896, heads=14, kv=2, hd=64, inter=4864, tie=True, theta=1000000.0, eps=1e-6),
+    "qwen25_15b": dict(arch="Qwen2ForCausalLM", hidden=1536, heads=12, kv=2, hd=128, inter=8960, tie=True, theta=1000000.0, eps=1e-6),
+    "qwen25_14b": dict(arch="Qwen2ForCausalLM", hidden=5120, heads=40, kv=8, hd=128, inter=13824, tie=False, theta=1000000.0, eps=1e-6),
+    "llama31_70b": dict(arch="LlamaForCausalLM", hidden=8192, heads=64, kv=8, hd=128, inter=28672, tie=False, theta=500000.0, eps=1e-5),
+}
+OTHER_VOCAB = 4099
+
+
+def other_config(w):
+    cfg = {"architectures": [w["arch"]], "hidden_size": w["hidden"], "num_hidden_layers": 1, "num_attention_heads": w["heads"],
+           "num_key_value_heads": w["kv"], "head_dim": w["hd"], "intermediate_size": w["inter"], "vocab_size": OTHER_VOCAB,
+           "max_position_embeddings": 2048, "rms_norm_eps": w["eps"], "rope_theta": w["theta"], "tie_word_embeddings": w["tie"],
+           "hidden_act": "silu", "torch_dtype": "bfloat16"}
+    if w["arch"] == "Qwen2ForCausalLM":
+        cfg["use_sliding_window"] = False
+    else:
+        cfg["attention_bias"] = False
+    return cfg
+
+
+@pytest.mark.parametrize("name", sorted(OTHER_WIDTHS))
+def test_one_layer_at_the_widths_of_other_checkpoints(tmp_path, name):
+    """bfloat16, prompts of 150 / 33 / 260 / 70 / 400 tokens whole (the short-prompt products in blocks of 128 rows,
+    the narrow prefill tiles) and in mixed portions beside decoded tokens, against the plain implementation."""
+    folder = folder_for(other_config(OTHER_WIDTHS[name]), seed=12)
+    reqs = random_requests(OTHER_VOCAB, (150, 33, 260, 70, 400), seed=31)
+    ref, rounded = plain_logits(folder, reqs, device="cuda", rounded=True)
+    for schedule, trace in (("whole", TT.schedule_whole(reqs)),
+                            ("mixed", TT.schedule_mixed(reqs, seed=5, portions=(2, 40, 130, 200)))):
+        out = tmp_path / schedule
+        TT.run_trace_tool(folder, "bfloat16", trace, str(out))
+        got = TT.read_logits(str(out), trace, OTHER_VOCAB)
+        TT.compare_bfloat16(got, ref, rounded, f"{name}/{schedule}")
