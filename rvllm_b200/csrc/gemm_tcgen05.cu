@@ -79,7 +79,11 @@ struct GemmParams {
     int M, N, K;
     int out_f32;
     int epilogue;
-    int m_tiles, n_tiles;   // tiles of TILE_ROWS rows x 256 columns
+    int m_tiles, n_tiles;   // tiles of TILE_ROWS rows x BN columns
+    // K cut into `splits` parts (1, 2 or 4; the build on single CTAs only): the CTAs of a tile are a thread-block
+    // cluster, every CTA keeps BN / splits columns of the tile, gets the other CTAs' partials of those columns into
+    // its shared memory (where its stages were) and adds them in the order of the parts.  Not for EPI_GATED.
+    int splits;
     // EPI_ROPE: W rows are [q heads | k heads | v heads] of hd (64, 128 or 256) features
     const void* bias;                // [N] or nullptr
     int bias_dtype;
@@ -94,6 +98,17 @@ struct GemmParams {
 
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+// a cluster of CTAs that share a tile's K (the build on single CTAs)
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f4(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 
 // EPI_ROPE: columns d .. d + 31 (a) and d + hd/2 .. d + hd/2 + 31 (b) of one head of row m.
 __device__ __forceinline__ void store_rope_pair(const GemmParams& p, int m, int head, int d, const uint32_t (&ra)[32],
@@ -233,8 +248,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int num_tiles = p.m_tiles * p.n_tiles;
     // the persistent workers: CTAs, or pairs of CTAs
-    const int worker = RV_PAIR ? blockIdx.x >> 1 : blockIdx.x, num_workers = RV_PAIR ? gridDim.x >> 1 : gridDim.x;
+    const int S = (!RV_PAIR && p.splits > 1) ? p.splits : 1;          // CTAs of a cluster that share a tile's K
+    const int split = S > 1 ? (int)blockIdx.x % S : 0;                 // (the rank in the cluster)
+    const int worker = RV_PAIR ? blockIdx.x >> 1 : blockIdx.x / S, num_workers = RV_PAIR ? gridDim.x >> 1 : gridDim.x / S;
     const int num_kb = (p.K + BK - 1) / BK;
+    const int kb_per = (num_kb + S - 1) / S;
+    const int kb_first = split * kb_per, kb_last = min(num_kb, kb_first + kb_per);     // this CTA's k blocks
     const bool gated = p.epilogue == EPI_GATED;
     const int half_n = p.N >> 1;
 
@@ -248,7 +267,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
                 const int m0 = (tile % p.m_tiles) * TILE_ROWS + (int)rank * BM;      // this CTA's 128 rows
                 const int nt = tile / p.m_tiles;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb_first; kb < kb_last; ++kb) {
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, &abort_flag, 1)) { ok = false; break; }
                     const uint32_t a_dst = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
                     const uint32_t b_dst = a_dst + A_TILE_BYTES;
@@ -291,6 +310,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             }
         }
+        // (the producer's and the issuer's warps take part in the cluster's two barriers after their work)
+        if (S > 1) { cluster_arrive(); cluster_wait(); cluster_arrive(); cluster_wait(); }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && rank == 0) {
@@ -305,7 +326,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (!mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, &abort_flag, 2)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t tmem_c = tmem_base + (uint32_t)buf * BN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb_first; kb < kb_last; ++kb) {
                     if (!mbar_wait(full0 + 8 * stage, phase, &abort_flag, 3)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
@@ -313,7 +334,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < BK / UMMA_K; ++j) {
                         // 16 k = 32 bytes further along the 128-byte row: +2 in 16-byte units
-                        mma_issue(tmem_c, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (kb | j) != 0);
+                        mma_issue(tmem_c, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, kb > kb_first || j != 0);
                     }
                     mma_commit(empty0 + 8 * stage);         // the stage is free (in both CTAs) once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -321,6 +342,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (ok) mma_commit(tfull0 + 8 * buf);       // accumulator complete (in both CTAs)
             }
         }
+        if (S > 1) { cluster_arrive(); cluster_wait(); cluster_arrive(); cluster_wait(); }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const int quarter = warp & 3;                       // the TMEM lanes this warp may read
@@ -329,11 +351,67 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int tile = worker; tile < num_tiles && ok; tile += num_workers, ++local) {
             const int buf = local & 1;
             const uint32_t use = (uint32_t)(local >> 1);
-            if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_flag, 4)) { ok = false; break; }
+            if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_flag, 4)) {
+                ok = false;
+                if (S > 1) { cluster_arrive(); cluster_wait(); cluster_arrive(); cluster_wait(); }     // the others still count on both barriers
+                break;
+            }
             tcgen05_fence_after();
             const int m = (tile % p.m_tiles) * TILE_ROWS + (int)rank * BM + quarter * 32 + lane;
             const int nt = tile / p.m_tiles;
             const uint32_t taddr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(quarter * 32) << 16);
+            // ---- K in parts over a cluster: every CTA keeps cols_per columns of the tile.  After the cluster's first
+            // barrier (every CTA's products are done, so its stages are free) each thread sends its row's partial of
+            // the other CTAs' columns into their shared memory - [part][row][cols_per + 4] floats where the stages
+            // were - and after the second barrier adds the parts of its own columns in the order of the parts.
+            const int cols_per = BN / S, RS = cols_per + 4;
+            const int c_begin = S > 1 ? split * cols_per : 0, c_end = S > 1 ? c_begin + cols_per : BN;
+            const float* red_row = reinterpret_cast<const float*>(tiles) + (size_t)(quarter * 32 + lane) * RS;
+            if (S > 1) {
+                cluster_arrive();
+                cluster_wait();
+                if (abort_flag == 0) {
+                    const uint32_t mine = smem_u32(tiles) + (uint32_t)(((split * BM) + quarter * 32 + lane) * RS) * 4u;
+                    for (int c = 0; c < BN; c += 32) {
+                        const int owner = c / cols_per;
+                        uint32_t r[32];
+                        if (kb_first < kb_last) {
+                            tmem_ld_32x32(taddr + c, r);
+                            tmem_ld_wait();
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) r[e] = 0u;        // a part without a k block (a short K) adds zeros
+                        }
+                        const uint32_t dst = cluster_map(mine + (uint32_t)(c - owner * cols_per) * 4u, (uint32_t)owner);
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            st_cluster_f4(dst + 16u * v, __uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                          __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                    }
+                }
+                cluster_arrive();
+                cluster_wait();
+            }
+            // 32 accumulator columns of this thread's row: from tensor memory, or the parts' partials added in part order
+            auto load_acc = [&](int col, uint32_t (&r)[32]) {
+                if (S == 1) {
+                    tmem_ld_32x32(taddr + col, r);
+                    tmem_ld_wait();
+                    return;
+                }
+                float acc[32];
+                for (int sp = 0; sp < S; ++sp) {
+                    const float4* src = reinterpret_cast<const float4*>(red_row + (size_t)sp * BM * RS + (col - c_begin));
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        const float4 t = src[v];
+                        if (sp == 0) { acc[4 * v] = t.x; acc[4 * v + 1] = t.y; acc[4 * v + 2] = t.z; acc[4 * v + 3] = t.w; }
+                        else { acc[4 * v] += t.x; acc[4 * v + 1] += t.y; acc[4 * v + 2] += t.z; acc[4 * v + 3] += t.w; }
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(acc[e]);
+            };
             if (gated) {
                 const int n_out0 = nt * (BN / 2);
                 for (int c = 0; c < BN / 2; c += 32) {
@@ -377,24 +455,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     pos = pos < 0 ? 0 : (pos >= p.table_rows ? p.table_rows - 1 : pos);
                     slot = p.slot_mapping[m];
                 }
-                for (int hb = 0; hb < BN; hb += p.hd) {            // the heads of this tile
+                for (int hb = c_begin; hb < c_end; hb += p.hd) {   // the heads of this tile (of this CTA's columns of it)
                     if (n0 + hb >= p.N) break;                      // uniform over the warp
                     const int head = (n0 + hb) / p.hd;
                     for (int c = 0; c < half; c += 32) {
                         uint32_t ra[32], rb[32];
-                        tmem_ld_32x32(taddr + hb + c, ra);
-                        tmem_ld_32x32(taddr + hb + half + c, rb);
-                        tmem_ld_wait();
+                        load_acc(hb + c, ra);
+                        load_acc(hb + half + c, rb);
                         if (m < p.M) store_rope_pair(p, m, head, c, ra, rb, pos, slot);
                     }
                 }
             } else {
                 const int n0 = nt * BN;
-                for (int c = 0; c < BN; c += 32) {
+                for (int c = c_begin; c < c_end; c += 32) {
                     if (n0 + c >= p.N) break;              // uniform over the warp
                     uint32_t r[32];
-                    tmem_ld_32x32(taddr + c, r);
-                    tmem_ld_wait();
+                    load_acc(c, r);
                     if (m < p.M) {
                         const int n = n0 + c;
                         const bool vec = n + 32 <= p.N && (p.N & 7) == 0;
@@ -462,6 +538,13 @@ static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const
     static RvPerDevice configured;
     if (int e = rv_configure_smem(configured, gemm_tcgen05_kernel, smem)) return e;
     int workers = p.m_tiles * p.n_tiles;
+#if !RV_PAIR
+    if (p.splits > 1) {      // one cluster of `splits` CTAs per tile
+        RV_LAUNCH_ST = rv_launch_cluster(gemm_tcgen05_kernel, dim3(workers * p.splits), dim3(NUM_THREADS), smem, stream,
+                                         (unsigned)p.splits, map_a, map_b, p);
+        return rv_launch_status();
+    }
+#endif
     const int limit = (max_ctas > 0 ? max_ctas : rv_sm_count()) / (RV_PAIR ? 2 : 1);
     if (workers > limit) workers = limit;
     if (workers < 1) workers = 1;
@@ -478,10 +561,21 @@ RV_EXPORT int rv_gemm_tcgen05_is_pair() { return RV_PAIR; }
 
 // epilogue: 0 plain, 1 + residual (bf16 [M, N]), 2 gated (W rows [gate | up], out has N/2 columns).
 // status: optional device int that receives a non-zero code if a wait inside the kernel gave up.
+// splits (both entry points): 1, or 2 / 4 on the build for single CTAs: the CTAs of a tile share its K as a cluster
+// (see GemmParams); not with the gated epilogue, and with the rotary one only while a CTA's columns hold whole heads.
+static int check_splits(int splits, int K, int epilogue, int hd) {
+    if (splits == 1) return RV_OK;
+    if (RV_PAIR || (splits != 2 && splits != 4) || epilogue == EPI_GATED) return RV_ERR_UNSUPPORTED;
+    if ((K + BK - 1) / BK < splits) return RV_ERR_UNSUPPORTED;
+    if (epilogue == EPI_ROPE && (BN / splits) % hd) return RV_ERR_UNSUPPORTED;
+    return RV_OK;
+}
+
 RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* residual, void* out, int out_f32,
-                                   int M, int N, int K, int epilogue, int* status, int max_ctas,
+                                   int M, int N, int K, int epilogue, int* status, int max_ctas, int splits,
                                    cudaStream_t stream) {
     if (M < 0 || N <= 0 || K <= 0) return RV_ERR_BAD_SIZE;
+    if (int e = check_splits(splits, K, epilogue, 0)) return e;
     if (K % 8) return RV_ERR_UNSUPPORTED;                          // rows must start on 16-byte boundaries
     if (epilogue == EPI_GATED && (N & 1)) return RV_ERR_BAD_SIZE;
     if (epilogue == EPI_RESIDUAL && (!residual || out_f32)) return RV_ERR_BAD_SIZE;
@@ -497,6 +591,7 @@ RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* res
     GemmParams p = {};
     p.out = out; p.residual = epilogue == EPI_RESIDUAL ? (const __nv_bfloat16*)residual : nullptr;
     p.status = status; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.epilogue = epilogue;
+    p.splits = splits;
     p.m_tiles = (M + TILE_ROWS - 1) / TILE_ROWS;
     // gated: a tile is 128 gate rows and the 128 up rows of the same output columns; gate rows past
     // N/2 read up rows, whose products the epilogue never stores
@@ -511,8 +606,9 @@ RV_EXPORT int rv_gemm_tcgen05_qkv_rope(const void* x, const void* w, const void*
                                        const int* positions, const float* cos_t, const float* sin_t,
                                        const int* slot_mapping, void* kv_cache, void* q_out, int M, int K,
                                        int nh, int nkv, int hd, int page_size, int table_rows, int* status,
-                                       int max_ctas, cudaStream_t stream) {
+                                       int max_ctas, int splits, cudaStream_t stream) {
     if (M < 0 || K <= 0 || nh <= 0 || nkv <= 0 || page_size <= 0 || table_rows <= 0) return RV_ERR_BAD_SIZE;
+    if (int e = check_splits(splits, K, EPI_ROPE, hd)) return e;
     if (hd != 64 && hd != 128 && hd != 256) return RV_ERR_UNSUPPORTED;     // a head's halves are whole 32-column chunks of one tile
     if (hd > BN) return RV_ERR_UNSUPPORTED;                                // (a narrow-tile build cannot hold a head of 256)
     if (K % 8) return RV_ERR_UNSUPPORTED;
@@ -530,6 +626,7 @@ RV_EXPORT int rv_gemm_tcgen05_qkv_rope(const void* x, const void* w, const void*
     if (st != RV_OK) return st;
     GemmParams p = {};
     p.status = status; p.M = M; p.N = N; p.K = K; p.epilogue = EPI_ROPE;
+    p.splits = splits;
     p.m_tiles = (M + TILE_ROWS - 1) / TILE_ROWS;
     p.n_tiles = (N + BN - 1) / BN;
     p.bias = bias; p.bias_dtype = bias_dtype;

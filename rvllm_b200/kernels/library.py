@@ -73,6 +73,7 @@ class CudaKernels:
                             # (0: always.  With 0.8 the library's GEMM takes the partly filled shapes and is 20-140 %
                             # faster there, but its sums depend on the operands' addresses: the same request no longer
                             # gives the same bits in every run)
+    PREFILL_SPLIT_K = True             # ... or, where 2 or 4 CTAs per tile still fit the SMs, with K cut over a cluster of CTAs per tile
     NARROW_TILES = True                # ... with tiles of 128 columns where those of 256 would occupy at most half of the SMs
     PAIR_GEMM = True                   # the tcgen05 GEMM runs on pairs of CTAs (cta_group::2) where the rows fill its 256-row tiles
     TCGEN05_ATTENTION = True           # prompt portions go to the tcgen05 attention kernel when it fits
@@ -511,6 +512,19 @@ class CudaKernels:
         rounds = -(-tiles // workers)
         return tiles >= self.TCGEN05_MIN_FILL * rounds * workers
 
+    def _prefill_splits(self, M: int, N: int, K: int, gated: bool = False, head_dim: int = 0) -> int:
+        """Into how many parts (1, 2 or 4) the prefill GEMM cuts K over a cluster of CTAs per tile of 128 rows x 256
+        columns: as many as keep all CTAs within the SMs, with 32 k blocks each at least (the exchange of the partials
+        through the cluster's shared memory costs about 7 us, as much as 16 k blocks); with the rotary epilogue only
+        while a CTA's share of the columns holds whole heads."""
+        if gated or not self.PREFILL_SPLIT_K or M < self.TCGEN05_MIN_ROWS:
+            return 1
+        tiles = -(-M // 128) * -(-N // 256)
+        for s in (4, 2):
+            if tiles * s <= self.num_sms and ((K + 63) // 64) // s >= 32 and (head_dim == 0 or (256 // s) % head_dim == 0):
+                return s
+        return 1
+
     def _prefill_gemm_lib(self, M: int, pair=None, N: int = 0, gated: bool = False, head_dim: int = 0):
         """The tcgen05 GEMM library for M rows: built for pairs of CTAs (tiles of 256 rows) unless the
         last tile's second half would be empty, or for one CTA per tile (tiles of 128 rows); with
@@ -526,7 +540,8 @@ class CudaKernels:
                 defines = defines + ("-DBN=128",)
         return self._lib("gemm_tcgen05.cu", defines)
 
-    def linear_tcgen05(self, x, weight, residual=None, out_dtype=None, gated=False, status=None, max_ctas=0, pair=None):
+    def linear_tcgen05(self, x, weight, residual=None, out_dtype=None, gated=False, status=None, max_ctas=0, pair=None,
+                       splits=None):
         """The tcgen05 / TMEM / TMA GEMM for bfloat16 (any M; K a multiple of 8).  gated: weight rows
         are [gate | up] and the result is silu(x gate^T) * (x up^T).  `status`: optional int32 device
         tensor that receives a non-zero code if a bounded wait inside the kernel gave up.  `pair`:
@@ -539,9 +554,16 @@ class CudaKernels:
         if residual is not None:
             _need(residual, "residual", torch.bfloat16, 2)
         epilogue = 2 if gated else (1 if residual is not None else 0)
-        st = self._prefill_gemm_lib(M, pair, N, gated).rv_gemm_tcgen05_bf16(
+        if splits is None:
+            splits = self._prefill_splits(M, N, K, gated) if (max_ctas == 0 and pair is None) else 1
+        if splits > 1:
+            lib = self._lib("gemm_tcgen05.cu", ())          # K over a cluster: the build on single CTAs, wide tiles
+        else:
+            lib = self._prefill_gemm_lib(M, pair, N, gated)
+        st = lib.rv_gemm_tcgen05_bf16(
             _ptr(x), _ptr(weight), _ptr(residual), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0),
-            c_int(M), c_int(N), c_int(K), c_int(epilogue), _ptr(status if status is not None else self._status), c_int(max_ctas), self._stream())
+            c_int(M), c_int(N), c_int(K), c_int(epilogue), _ptr(status if status is not None else self._status), c_int(max_ctas),
+            c_int(splits), self._stream())
         _check("gemm_tcgen05", st)
         return out
 
@@ -668,7 +690,7 @@ class CudaKernels:
                                      num_heads, num_kv_heads, head_dim, out_dtype=x.dtype)
 
     def _qkv_rope_tcgen05(self, x, weight, bias, positions, cos, sin, slot_mapping, cache_layer,
-                          num_heads, num_kv_heads, head_dim, status=None, max_ctas=0, pair=None):
+                          num_heads, num_kv_heads, head_dim, status=None, max_ctas=0, pair=None, splits=None):
         """The prefill tcgen05 GEMM with the rotary epilogue (many rows, head sizes 64 / 128 / 256)."""
         _need(x, "x", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
         _need(positions, "positions", torch.int32, 1); _need(slot_mapping, "slot_mapping", torch.int32, 1)
@@ -686,11 +708,18 @@ class CudaKernels:
         if bias is not None:
             _need(bias, "bias", dims=1)
         q = torch.empty((M, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
-        st = self._prefill_gemm_lib(M, pair, weight.shape[0], head_dim=head_dim).rv_gemm_tcgen05_qkv_rope(
+        if splits is None:
+            splits = self._prefill_splits(M, weight.shape[0], K, False, head_dim) if (max_ctas == 0 and pair is None) else 1
+        if splits > 1:
+            lib = self._lib("gemm_tcgen05.cu", ())
+        else:
+            lib = self._prefill_gemm_lib(M, pair, weight.shape[0], head_dim=head_dim)
+        st = lib.rv_gemm_tcgen05_qkv_rope(
             _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0),
             _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(cache_layer), _ptr(q), c_int(M), c_int(K),
             c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]),
-            c_int(cos.shape[0] if cos is not None else 1), _ptr(status if status is not None else self._status), c_int(max_ctas), self._stream())
+            c_int(cos.shape[0] if cos is not None else 1), _ptr(status if status is not None else self._status), c_int(max_ctas),
+            c_int(splits), self._stream())
         _check("gemm_tcgen05_qkv_rope", st)
         return q
 

@@ -84,6 +84,16 @@ def test_the_prefill_gemm_and_its_build_are_chosen_by_rows():
     assert [("-DBN=128" in d) for _, d in picked] == [True, True, False, False, True, False]
 
 
+def test_k_of_the_prefill_gemm_is_cut_over_a_cluster_where_the_tiles_leave_sms_idle():
+    k = _k()
+    assert k._prefill_splits(512, 4096, 14336) == 2 and k._prefill_splits(384, 4096, 14336) == 2       # down: 64 / 48 tiles
+    assert k._prefill_splits(300, 4096, 14336) == 2 and k._prefill_splits(2048, 4096, 14336) == 1
+    assert k._prefill_splits(512, 4096, 4096) == 2 and k._prefill_splits(512, 6144, 4096) == 1         # 64 tiles; 96 tiles
+    assert k._prefill_splits(384, 6144, 4096, False, 128) == 2 and k._prefill_splits(384, 1536, 4096, False, 256) == 1
+    assert k._prefill_splits(512, 28672, 4096, True) == 1 and k._prefill_splits(100, 4096, 14336) == 1  # gated; too few rows
+    assert k._prefill_splits(512, 4096, 2048) == 1                                                   # 32 k blocks a part at least
+
+
 def test_key_splits_of_decode_attention_follow_the_wave_model():
     meta = lambda seqs, ctx: SimpleNamespace(num_seqs=seqs, max_ctx_len=ctx)
     assert _k().decode_splits(meta(8, 2088), 32, 8) == 6           # 384 CTAs: one wave of 444

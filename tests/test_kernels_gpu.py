@@ -321,6 +321,15 @@ def test_gemm_tcgen05_bf16(K, M, N, Kd):
             assert rel_err(K.linear_tcgen05(x, w, gated=True, status=status, pair=pair), want) < BF16_TOL
             assert rel_err(K.linear_tcgen05(x, w, None, torch.float32, gated=True, status=status, max_ctas=2, pair=pair), want) < 1e-5
     assert torch.equal(K.linear_tcgen05(x, w, r, pair=True), K.linear_tcgen05(x, w, r, pair=False))    # the same sums
+    # K cut over a cluster of 2 or 4 CTAs per tile (partials through the cluster's shared memory, added in part order):
+    # the same bits in every run, every epilogue but the gated one
+    for splits in (2, 4):
+        if splits > (Kd + 63) // 64:
+            continue
+        outs = [K.linear_tcgen05(x, w, r, status=status, splits=splits) for _ in range(3)]
+        assert all(torch.equal(outs[0], o) for o in outs[1:]) and rel_err(outs[0], ref + r.double().cpu()) < BF16_TOL
+        assert rel_err(K.linear_tcgen05(x, w, None, torch.float32, status=status, splits=splits), ref) < 1e-5
+        assert rel_err(K.linear_tcgen05(x, w, status=status, splits=splits), ref) < BF16_TOL
     assert int(status.item()) == 0, "a bounded wait inside the kernel gave up"
     # the product path picks it where its tiles fill the GPU, and the library's GEMM elsewhere
     if K._tcgen05_fills(M, N):
@@ -621,9 +630,12 @@ def test_qkv_product_with_rotation_and_cache_write_for_many_rows(K, M, nh, nkv, 
     cache_b = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda").bfloat16()
     qb = K.rope_cache_write(K.linear_tcgen05(x, w, out_dtype=torch.float32), b, positions, cos, sin, slots, cache_b, nh, nkv, hd,
                             out_dtype=torch.bfloat16)
-    for ctas, pair in ((0, False), (2, False), (0, True), (4, True)):
+    for ctas, pair, splits in ((0, False, 1), (2, False, 1), (0, True, 1), (4, True, 1), (0, False, 2), (0, False, 4), (0, None, None)):
+        if splits and splits > 1 and ((256 // splits) % hd or (Kd + 63) // 64 < splits):
+            continue
         cache_a = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda").bfloat16()
-        qa = K._qkv_rope_tcgen05(x, w, b, positions, cos, sin, slots, cache_a, nh, nkv, hd, status=status, max_ctas=ctas, pair=pair)
+        qa = K._qkv_rope_tcgen05(x, w, b, positions, cos, sin, slots, cache_a, nh, nkv, hd, status=status, max_ctas=ctas, pair=pair,
+                                 splits=splits)
         assert same_up_to_an_ulp(qa, qb) and same_up_to_an_ulp(cache_a, cache_b)         # nearly every element bit-equal
     assert int(status.item()) == 0
     y = x.double().cpu() @ w.double().cpu().t()
