@@ -93,14 +93,19 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
     return r;
 }
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
 }
+// One bulk copy from this CTA's shared memory into another CTA's of the cluster; its bytes are counted on a barrier
+// of the receiving CTA (both given as addresses in the cluster's shared window).
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst, uint32_t src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "r"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -285,7 +290,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     constexpr int TMEM_COLS = MB < 32 ? 32 : MB;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t bars[3 * STAGES + 1];     // full, empty, accumulator ready, normalised
+    __shared__ __align__(8) uint64_t bars[3 * STAGES + 2];     // full, empty, accumulator ready, normalised, partials arrived
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
     __shared__ int is_last;
@@ -293,12 +298,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __shared__ float norm_red[4][16], norm_rstd[16];
 
     rv_pdl_launch_dependents();
-    // A CTA's shared memory may be written from another CTA of the cluster only once it runs: every
-    // thread arrives here, and waits before the partials are stored (warps 0 and 1 at the end).
-    if (p.cluster) cluster_arrive();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), tfull = smem_u32(&bars[2 * STAGES]);
     const uint32_t normed0 = smem_u32(&bars[2 * STAGES + 1]);
+    const uint32_t xbar = smem_u32(&bars[3 * STAGES + 1]);     // the other CTAs' partials of this CTA's rows have arrived
     const bool fused_norm = p.norm_gamma != nullptr;
 
     const int tile = blockIdx.x / p.splits, split = blockIdx.x - tile * p.splits;
@@ -322,6 +325,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         is_last = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); mbar_init(normed0 + 8 * s, 4); }
         mbar_init(tfull, 1);
+        mbar_init(xbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         // The weights are written by no kernel of a step: the first stages' weight tiles are requested
@@ -345,6 +349,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    // A CTA's shared memory and its barrier may be written from another CTA of the cluster only once it runs and
+    // has set them up: every thread arrives here; the epilogue warps wait before partials are sent, the others at the end.
+    if (p.cluster) cluster_arrive();
 
     // cluster reduction: [splits][cluster_rows][128 features] floats behind the stages (and gamma),
     // at the same offset in every CTA of the cluster
@@ -492,7 +499,12 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
-        if (p.cluster) cluster_wait();                      // all CTAs of the cluster have started
+        // rows of the tile that this CTA finishes, and the bytes that all CTAs of the cluster (itself among them) send for them
+        const int my_rows = p.cluster ? max(0, min(p.M, (split + 1) * p.cluster_rows) - split * p.cluster_rows) : 0;
+        if (p.cluster) {
+            cluster_wait();                                 // all CTAs of the cluster have started and set their barriers up
+            if (et == 0 && my_rows > 0) mbar_expect_tx(xbar, (uint32_t)(p.splits * my_rows * TILE_F * 4));
+        }
         if (have) mbar_wait(tfull, 0, &abort_flag, 4);
         // every epilogue thread comes here in bounded time; after the barrier they all see the same
         // abort flag, so the named barriers below are never reached by only some of them
@@ -508,8 +520,6 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (ok) {
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
             float* part = (p.splits > 1 && !p.cluster) ? p.scratch + ((size_t)(tile * p.splits + split) * MB) * TILE_F : nullptr;
-            // row m goes to the CTA m / cluster_rows of the cluster, at [split][m % cluster_rows][feature]
-            const uint32_t red_mine = smem_u32(red) + (uint32_t)((split * p.cluster_rows) * TILE_F + f) * 4u;
             // One loop per destination (a branch per element costs more than the element does here).
             auto load16 = [&](int c, uint32_t (&r)[16]) {
                 if (have) {
@@ -525,24 +535,31 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 }
             };
             if (p.cluster) {
-                // row m goes to CTA m / cluster_rows; the window of a CTA's shared memory is linear, so the
-                // address of the owner's buffer is mapped once per owner and the rows follow by offset
-                int owner = 0, local = 0;
-                uint32_t remote = cluster_map(red_mine, 0);
+                // The partial goes row by row ([row][128 features] floats) into this CTA's shared memory, where its
+                // stages were; the rows of CTA o (o * cluster_rows onwards) are one piece of it, which one bulk copy
+                // takes to that CTA's buffer at [this split][its rows] and counts on its barrier.  (Stores into another
+                // CTA's shared memory, one thread per feature and row, left an SM at about 20 GB/s.)
+                float* stage_rows = reinterpret_cast<float*>(tiles);
 #pragma unroll
                 for (int c = 0; c < MB; c += 16) {
                     if (c >= p.M) break;
                     uint32_t r[16];
                     load16(c, r);
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        if (c + e < p.M) st_cluster_f32(remote + (uint32_t)(local * TILE_F) * 4u, __uint_as_float(r[e]));
-                        if (++local == p.cluster_rows) {
-                            local = 0;
-                            ++owner;
-                            if (c + e + 1 < p.M) remote = cluster_map(red_mine, owner);     // (a rank that exists)
-                        }
+                    for (int e = 0; e < 16; ++e)
+                        if (c + e < p.M) stage_rows[(c + e) * TILE_F + f] = __uint_as_float(r[e]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                epi_sync();
+                if (et == 0) {
+                    for (int o = 0; o < p.splits; ++o) {
+                        const int r0 = o * p.cluster_rows, rows = min(p.M, r0 + p.cluster_rows) - r0;
+                        if (rows <= 0) break;
+                        bulk_copy_to_cluster(cluster_map(smem_u32(red) + (uint32_t)(split * p.cluster_rows * TILE_F) * 4u, (uint32_t)o),
+                                             smem_u32(stage_rows) + (uint32_t)(r0 * TILE_F) * 4u, (uint32_t)(rows * TILE_F) * 4u,
+                                             cluster_map(xbar, (uint32_t)o));
                     }
+                    bulk_commit();
                 }
             } else if (part) {
 #pragma unroll
@@ -575,9 +592,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 bool from_parts = false;
                 const float* parts = nullptr;
                 if (p.cluster) {
-                    cluster_arrive();                      // releases the stores above
-                    cluster_wait();
-                    from_parts = split * p.cluster_rows < p.M;      // (the rank in the cluster is the split)
+                    // every CTA's piece for this CTA's rows has arrived (a CTA without rows waits for nothing)
+                    from_parts = my_rows > 0 && mbar_wait(xbar, 0, &abort_flag, 6);
                     parts = red;
                     finish = false;
                 } else {
@@ -737,17 +753,17 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     }
                 }
             }
-        } else if (p.cluster) {
-            cluster_arrive();                              // gave up: the cluster's hand-over still takes place
-            cluster_wait();
+        } else if (p.cluster && my_rows > 0) {
+            // gave up: what the other CTAs send still lands in this CTA's shared memory, which must not be given up before
+            volatile int ignore = 0;
+            mbar_wait(xbar, 0, &ignore, 0);
         }
+        if (p.cluster && et == 0) bulk_wait_read();         // the copies have read this CTA's rows: its shared memory may go
     }
 
-    // The cluster's barrier has two phases, and every thread of the cluster takes part in both: the
-    // start (arrive at the top; wait before the partials are stored) and the hand-over of the
-    // partials (arrive after the stores, then wait).  Warps 0 and 1 store nothing: they arrive for the
-    // hand-over here and wait at the very end.
-    if (p.cluster && warp < 2) { cluster_wait(); cluster_arrive(); }
+    // The cluster's barrier has one phase (every CTA runs and has set its barriers up): the epilogue warps waited for it
+    // before they sent anything, warps 0 and 1 do so at the very end.  The hand-over of the partials is counted on
+    // the receiving CTA's own barrier.
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {
