@@ -99,6 +99,7 @@ struct GemmParams {
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
 // a cluster of CTAs that share a tile's K (the build on single CTAs)
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }     // the four epilogue warps
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 __device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
@@ -106,9 +107,14 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
     return r;
 }
-__device__ __forceinline__ void st_cluster_f4(uint32_t addr, float a, float b, float c, float d) {
-    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+// One bulk copy from this CTA's shared memory into another CTA's of the cluster; its bytes are counted on a barrier
+// of the receiving CTA (both given as addresses in the cluster's shared window).
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst, uint32_t src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "r"(src), "r"(bytes), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
 // EPI_ROPE: columns d .. d + 31 (a) and d + hd/2 .. d + hd/2 + 31 (b) of one head of row m.
 __device__ __forceinline__ void store_rope_pair(const GemmParams& p, int m, int head, int d, const uint32_t (&ra)[32],
@@ -213,7 +219,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 5];     // full, empty, accumulator full / empty [2], partials arrived
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
 
@@ -221,6 +227,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
     const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
+    const uint32_t xbar = smem_u32(&bars[2 * STAGES + 4]);     // K over a cluster: the other CTAs' partials of this CTA's columns
 
     // pair: rank 0 issues the MMAs and owns the barriers that count both CTAs (full, tempty)
     const uint32_t rank = RV_PAIR ? pair_rank() : 0u;
@@ -232,6 +239,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // empty, tfull: one arrival from the commit; tempty: the four epilogue warps (of both CTAs)
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, RV_PAIR ? 8 : 4); }
+        mbar_init(xbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -310,8 +318,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             }
         }
-        // (the producer's and the issuer's warps take part in the cluster's two barriers after their work)
-        if (S > 1) { cluster_arrive(); cluster_wait(); cluster_arrive(); cluster_wait(); }
+        // (the producer's and the issuer's warps take part in the cluster's barrier after their work)
+        if (S > 1) { cluster_arrive(); cluster_wait(); }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && rank == 0) {
@@ -342,7 +350,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (ok) mma_commit(tfull0 + 8 * buf);       // accumulator complete (in both CTAs)
             }
         }
-        if (S > 1) { cluster_arrive(); cluster_wait(); cluster_arrive(); cluster_wait(); }
+        if (S > 1) { cluster_arrive(); cluster_wait(); }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const int quarter = warp & 3;                       // the TMEM lanes this warp may read
@@ -353,27 +361,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t use = (uint32_t)(local >> 1);
             if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_flag, 4)) {
                 ok = false;
-                if (S > 1) { cluster_arrive(); cluster_wait(); cluster_arrive(); cluster_wait(); }     // the others still count on both barriers
+                if (S > 1) {     // the others still count on the barrier, and send what this CTA's shared memory has to outlive
+                    if (warp == 2 && lane == 0) mbar_expect_tx(xbar, (uint32_t)(S - 1) * (uint32_t)(BM * (BN / S + 4)) * 4u);
+                    cluster_arrive();
+                    cluster_wait();
+                    volatile int ignore = 0;
+                    mbar_wait(xbar, 0, &ignore, 0);
+                }
                 break;
             }
             tcgen05_fence_after();
             const int m = (tile % p.m_tiles) * TILE_ROWS + (int)rank * BM + quarter * 32 + lane;
             const int nt = tile / p.m_tiles;
             const uint32_t taddr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(quarter * 32) << 16);
-            // ---- K in parts over a cluster: every CTA keeps cols_per columns of the tile.  After the cluster's first
-            // barrier (every CTA's products are done, so its stages are free) each thread sends its row's partial of
-            // the other CTAs' columns into their shared memory - [part][row][cols_per + 4] floats where the stages
-            // were - and after the second barrier adds the parts of its own columns in the order of the parts.
+            // ---- K in parts over a cluster: every CTA keeps cols_per columns of the tile.  After the cluster's barrier
+            // (every CTA's products are done, so its stages are free) each thread writes its row's partial of the OTHER
+            // CTAs' columns into this CTA's shared memory, one piece of [128 rows][cols_per + 4] floats per receiving
+            // CTA, and one bulk copy per piece takes it into that CTA's shared memory, counted on that CTA's barrier.
+            // Then the parts of the CTA's own columns are added in the order of the parts, its own from tensor memory.
+            // (Per-row stores straight into the other CTAs' shared memory left an SM at 15 GB/s: 6.4 us for this.)
             const int cols_per = BN / S, RS = cols_per + 4;
             const int c_begin = S > 1 ? split * cols_per : 0, c_end = S > 1 ? c_begin + cols_per : BN;
-            const float* red_row = reinterpret_cast<const float*>(tiles) + (size_t)(quarter * 32 + lane) * RS;
+            const uint32_t piece_bytes = (uint32_t)(BM * RS) * 4u;
+            // [0, S - 1): pieces received (from part sp, at index sp or sp - 1 past this CTA); [S - 1, 2 S - 2): pieces to send
+            float* pieces = reinterpret_cast<float*>(tiles);
             if (S > 1) {
+                if (warp == 2 && lane == 0) mbar_expect_tx(xbar, (uint32_t)(S - 1) * piece_bytes);
                 cluster_arrive();
                 cluster_wait();
                 if (abort_flag == 0) {
-                    const uint32_t mine = smem_u32(tiles) + (uint32_t)(((split * BM) + quarter * 32 + lane) * RS) * 4u;
                     for (int c = 0; c < BN; c += 32) {
                         const int owner = c / cols_per;
+                        if (owner == split) continue;
                         uint32_t r[32];
                         if (kb_first < kb_last) {
                             tmem_ld_32x32(taddr + c, r);
@@ -382,26 +401,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                             for (int e = 0; e < 32; ++e) r[e] = 0u;        // a part without a k block (a short K) adds zeros
                         }
-                        const uint32_t dst = cluster_map(mine + (uint32_t)(c - owner * cols_per) * 4u, (uint32_t)owner);
+                        const int slot = S - 1 + (owner < split ? owner : owner - 1);
+                        float4* dst = reinterpret_cast<float4*>(pieces + ((size_t)slot * BM + quarter * 32 + lane) * RS + (c - owner * cols_per));
 #pragma unroll
                         for (int v = 0; v < 8; ++v)
-                            st_cluster_f4(dst + 16u * v, __uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                          __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                            dst[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                 __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    epi_sync();
+                    if (warp == 2 && lane == 0) {
+                        for (int owner = 0; owner < S; ++owner) {
+                            if (owner == split) continue;
+                            const int slot = S - 1 + (owner < split ? owner : owner - 1);     // here
+                            const int there = split < owner ? split : split - 1;              // this part's place in the receiving CTA
+                            bulk_copy_to_cluster(cluster_map(smem_u32(pieces) + (uint32_t)there * piece_bytes, (uint32_t)owner),
+                                                 smem_u32(pieces) + (uint32_t)slot * piece_bytes, piece_bytes, cluster_map(xbar, (uint32_t)owner));
+                        }
+                        bulk_commit();
                     }
                 }
-                cluster_arrive();
-                cluster_wait();
+                // the other parts' pieces have arrived (bounded; after a wait that gave up the flag says so)
+                mbar_wait(xbar, 0, &abort_flag, 5);
             }
             // 32 accumulator columns of this thread's row: from tensor memory, or the parts' partials added in part order
             auto load_acc = [&](int col, uint32_t (&r)[32]) {
-                if (S == 1) {
-                    tmem_ld_32x32(taddr + col, r);
-                    tmem_ld_wait();
-                    return;
+                tmem_ld_32x32(taddr + col, r);
+                tmem_ld_wait();
+                if (S == 1) return;
+                if (kb_first >= kb_last) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) r[e] = 0u;
                 }
                 float acc[32];
                 for (int sp = 0; sp < S; ++sp) {
-                    const float4* src = reinterpret_cast<const float4*>(red_row + (size_t)sp * BM * RS + (col - c_begin));
+                    if (sp == split) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) acc[e] = sp == 0 ? __uint_as_float(r[e]) : acc[e] + __uint_as_float(r[e]);
+                        continue;
+                    }
+                    const int slot = sp < split ? sp : sp - 1;
+                    const float4* src = reinterpret_cast<const float4*>(pieces + ((size_t)slot * BM + quarter * 32 + lane) * RS + (col - c_begin));
 #pragma unroll
                     for (int v = 0; v < 8; ++v) {
                         const float4 t = src[v];
@@ -511,6 +551,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             }
+            if (S > 1 && warp == 2 && lane == 0) bulk_wait_read();     // the copies have read this CTA's pieces
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -535,12 +576,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // One CTA per tile and SM, or (RV_PAIR) one cluster of two CTAs per tile and pair of SMs.
 static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, int max_ctas, cudaStream_t stream) {
     const int smem = STAGES * STAGE_BYTES + 1024;
+    // (the largest a launch may ask for: the pieces of an exchange between four CTAs)
+    const int most_pieces = 2 * 3 * BM * (BN / 4 + 4) * 4 + 1024;
     static RvPerDevice configured;
-    if (int e = rv_configure_smem(configured, gemm_tcgen05_kernel, smem)) return e;
+    if (int e = rv_configure_smem(configured, gemm_tcgen05_kernel, most_pieces > smem ? most_pieces : smem)) return e;
     int workers = p.m_tiles * p.n_tiles;
 #if !RV_PAIR
-    if (p.splits > 1) {      // one cluster of `splits` CTAs per tile
-        RV_LAUNCH_ST = rv_launch_cluster(gemm_tcgen05_kernel, dim3(workers * p.splits), dim3(NUM_THREADS), smem, stream,
+    if (p.splits > 1) {      // one cluster of `splits` CTAs per tile; the pieces of the exchange lie where the stages were
+        const int pieces = 2 * (p.splits - 1) * BM * (BN / p.splits + 4) * 4 + 1024;
+        const int split_smem = pieces > smem ? pieces : smem;
+        RV_LAUNCH_ST = rv_launch_cluster(gemm_tcgen05_kernel, dim3(workers * p.splits), dim3(NUM_THREADS), split_smem, stream,
                                          (unsigned)p.splits, map_a, map_b, p);
         return rv_launch_status();
     }

@@ -73,6 +73,7 @@ class CudaKernels:
                             # (0: always.  With 0.8 the library's GEMM takes the partly filled shapes and is 20-140 %
                             # faster there, but its sums depend on the operands' addresses: the same request no longer
                             # gives the same bits in every run)
+    PREFILL_SPLIT_MIN_KB = 32          # ... k blocks that a part keeps at least
     PREFILL_SPLIT_K = True             # ... or, where 2 or 4 CTAs per tile still fit the SMs, with K cut over a cluster of CTAs per tile
     NARROW_TILES = True                # ... with tiles of 128 columns where those of 256 would occupy at most half of the SMs
     PAIR_GEMM = True                   # the tcgen05 GEMM runs on pairs of CTAs (cta_group::2) where the rows fill its 256-row tiles
@@ -521,7 +522,7 @@ class CudaKernels:
             return 1
         tiles = -(-M // 128) * -(-N // 256)
         for s in (4, 2):
-            if tiles * s <= self.num_sms and ((K + 63) // 64) // s >= 32 and (head_dim == 0 or (256 // s) % head_dim == 0):
+            if tiles * s <= self.num_sms and ((K + 63) // 64) // s >= self.PREFILL_SPLIT_MIN_KB and (head_dim == 0 or (256 // s) % head_dim == 0):
                 return s
         return 1
 
