@@ -1148,7 +1148,7 @@ flash_decode_balanced_tma_kernel(const __grid_constant__ CUtensorMap map_kv, con
             p.piece_count[pair] = count;
         }
         const size_t rows_all = (size_t)p.n_tokens * p.nh;
-        float* mml = mo + 4 * G * HD;
+        float* mml = mo + 4 * G * (HD / (G <= 4 ? 1 : (G <= 8 ? 2 : 4)));
         int consumed = 0, seq = seq0;
         bool ok = true;
         int u = u0;
@@ -1269,43 +1269,51 @@ flash_decode_balanced_tma_kernel(const __grid_constant__ CUtensorMap map_kv, con
             }
             // ---- merge the four warps (their buffer lies behind the ring) and write the piece's partial result;
             // after a wait that gave up nothing is written, but every consumer still comes to both barriers
-            consumer_sync();                                   // the merge of the piece before has been read
-            const bool good = abort_flag == 0 && ok;
-            if (good) {
+            // The buffer holds HD / passes columns of the group's rows at a time (one pass for up to four heads a
+            // group, two up to eight, four beyond): so that three CTAs still fit an SM.
+            const int passes = G <= 4 ? 1 : (G <= 8 ? 2 : 4), HDP = HD / passes;
+            bool gave_up = false;
+            for (int ps = 0; ps < passes; ++ps) {
+                consumer_sync();                               // the merge before (of the piece before, of the pass before) has been read
+                const bool good = abort_flag == 0 && ok;
+                if (good) {
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int row = quad + 8 * i;
-                    if (row >= G) continue;
+                    for (int i = 0; i < 2; ++i) {
+                        const int row = quad + 8 * i;
+                        if (row >= G) continue;
 #pragma unroll
-                    for (int n = 0; n < HD / 8; ++n) {
-                        float* dst = mo + ((size_t)warp_n * G + row) * HD + n * 8 + tq * 2;
-                        dst[0] = o[n][2 * i]; dst[1] = o[n][2 * i + 1];
-                    }
-                    if (tq == 0) {
-                        mml[(warp_n * G + row) * 2] = m_run[i];
-                        mml[(warp_n * G + row) * 2 + 1] = l_run[i];
+                        for (int n = 0; n < HD / 8; ++n) {
+                            if (n * 8 < ps * HDP || n * 8 >= (ps + 1) * HDP) continue;
+                            float* dst = mo + ((size_t)warp_n * G + row) * HDP + (n * 8 - ps * HDP) + tq * 2;
+                            dst[0] = o[n][2 * i]; dst[1] = o[n][2 * i + 1];
+                        }
+                        if (ps == 0 && tq == 0) {
+                            mml[(warp_n * G + row) * 2] = m_run[i];
+                            mml[(warp_n * G + row) * 2 + 1] = l_run[i];
+                        }
                     }
                 }
-            }
-            consumer_sync();
-            if (abort_flag != 0 || !ok) { ok = false; break; }
-            for (int idx = tid; idx < G * HD; idx += 128) {
-                const int row = idx / HD, d = idx - row * HD;
-                float m_all = -INFINITY;
+                consumer_sync();
+                if (abort_flag != 0 || !ok) { gave_up = true; break; }
+                for (int idx = tid; idx < G * HDP; idx += 128) {
+                    const int row = idx / HDP, dd = idx - row * HDP, d = ps * HDP + dd;
+                    float m_all = -INFINITY;
 #pragma unroll
-                for (int w = 0; w < 4; ++w) m_all = fmaxf(m_all, mml[(w * G + row) * 2]);
-                const float m_s = m_all == -INFINITY ? 0.f : m_all;
-                float l_all = 0.f, acc = 0.f;
+                    for (int w = 0; w < 4; ++w) m_all = fmaxf(m_all, mml[(w * G + row) * 2]);
+                    const float m_s = m_all == -INFINITY ? 0.f : m_all;
+                    float l_all = 0.f, acc = 0.f;
 #pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const float f = exp2f(mml[(w * G + row) * 2] - m_s);
-                    l_all += mml[(w * G + row) * 2 + 1] * f;
-                    acc += mo[((size_t)w * G + row) * HD + d] * f;
+                    for (int w = 0; w < 4; ++w) {
+                        const float f = exp2f(mml[(w * G + row) * 2] - m_s);
+                        l_all += mml[(w * G + row) * 2 + 1] * f;
+                        acc += mo[((size_t)w * G + row) * HDP + dd] * f;
+                    }
+                    const size_t prow = (size_t)piece * rows_all + (size_t)tok * p.nh + kvh * G + row;
+                    p.part_o[prow * HD + d] = acc;
+                    if (d == 0) { p.part_ml[prow * 2] = m_all; p.part_ml[prow * 2 + 1] = l_all; }
                 }
-                const size_t prow = (size_t)piece * rows_all + (size_t)tok * p.nh + kvh * G + row;
-                p.part_o[prow * HD + d] = acc;
-                if (d == 0) { p.part_ml[prow * 2] = m_all; p.part_ml[prow * 2 + 1] = l_all; }
             }
+            if (gave_up) { ok = false; break; }
             u += n_here;
         }
     }
@@ -1500,7 +1508,10 @@ RV_EXPORT int rv_flash_decode_tma(const void* q, const void* cache, long long nu
 // of the cache layer (for the tensor map) and the status word of the bounded waits.  ctas <= 0: as many as
 // stay resident, which rv_flash_balanced_tma_ctas tells the caller, who sizes scratch by it.
 #ifdef RV_HAVE_TMA_DECODE
-static int balanced_tma_smem(int G) { return 2 * TMA_STAGES * TMA_TILE_BYTES + 4 * G * (HEAD_DIM + 2) * 4 + 1024; }
+static int balanced_tma_smem(int G) {       // the ring, the merge buffer (HEAD_DIM / passes columns of G rows of four warps) and its maxima and sums
+    const int passes = G <= 4 ? 1 : (G <= 8 ? 2 : 4);
+    return 2 * TMA_STAGES * TMA_TILE_BYTES + 4 * G * (HEAD_DIM / passes + 2) * 4 + 1024;
+}
 #endif
 RV_EXPORT int rv_flash_balanced_tma_ctas(int nh, int nkv) {
 #ifdef RV_HAVE_TMA_DECODE
