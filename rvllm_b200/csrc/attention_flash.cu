@@ -393,15 +393,58 @@ __device__ __forceinline__ float merge_splits(const float* __restrict__ part_o, 
     return acc * (l_run > 0.f ? 1.f / l_run : 0.f);
 }
 
-// Merge the partial results of the key splits: one block per (token, head), one thread per
-// element of the head.
+// The same for four neighbouring elements d .. d + 3 (d a multiple of 4), every split's loads in flight together.
+__device__ __forceinline__ float4 merge_splits4(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                size_t row, size_t rows, int num_splits, int d) {
+    float m_run = -INFINITY, l_run = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < num_splits; s0 += 8) {
+        float m[8], l[8];
+        float4 o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const bool have = s0 + i < num_splits;
+            const size_t r = (size_t)(have ? s0 + i : s0) * rows + row;
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + r);
+            m[i] = have ? ml.x : -INFINITY;
+            l[i] = have ? ml.y : 0.f;
+            o[i] = __ldcg(reinterpret_cast<const float4*>(part_o + r * HEAD_DIM + d));
+        }
+        float m_new = m_run;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m_new = fmaxf(m_new, m[i]);
+        const float m_s = m_new == -INFINITY ? 0.f : m_new;
+        const float keep = exp2f(m_run - m_s);          // 0 while nothing has been seen
+        l_run *= keep;
+        acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float f = exp2f(m[i] - m_s);           // 0 for an empty or absent split
+            l_run += l[i] * f;
+            if (f > 0.f) { acc.x += o[i].x * f; acc.y += o[i].y * f; acc.z += o[i].z * f; acc.w += o[i].w * f; }
+        }
+        m_run = m_new;
+    }
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    return make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+}
+
+// Merge the partial results of the key splits: HEAD_DIM / 4 threads per (token, head) row, four neighbouring
+// elements each (16-byte reads of the partials, an 8-byte store); a block of 128 threads takes several rows.
+#define COMBINE_TPR (HEAD_DIM / 4)                 // threads per row
+#define COMBINE_ROWS (128 / COMBINE_TPR)           // rows per block
 __global__ void flash_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                      __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
-    const int d = threadIdx.x;
-    if (d >= HEAD_DIM) return;
-    out[(size_t)blockIdx.x * HEAD_DIM + d] = __float2bfloat16_rn(merge_splits(part_o, part_ml, blockIdx.x, rows, num_splits, d));
+    const int r = threadIdx.x / COMBINE_TPR, d = (threadIdx.x - r * COMBINE_TPR) * 4;
+    const int row = blockIdx.x * COMBINE_ROWS + r;
+    if (r >= COMBINE_ROWS || row >= rows) return;
+    const float4 v = merge_splits4(part_o, part_ml, (size_t)row, (size_t)rows, num_splits, d);
+    uint2 o2;
+    o2.x = pack_bf16(v.x, v.y);
+    o2.y = pack_bf16(v.z, v.w);
+    *reinterpret_cast<uint2*>(out + (size_t)row * HEAD_DIM + d) = o2;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1325,17 +1368,24 @@ flash_decode_balanced_tma_kernel(const __grid_constant__ CUtensorMap map_kv, con
 // Merge of the balanced kernel's pieces: one block per (sequence, query head).
 __global__ void flash_balanced_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               const int* __restrict__ piece_count, const int* __restrict__ cu_seqlens,
-                                              __nv_bfloat16* __restrict__ out, int n_tokens, int nh, int nkv) {
+                                              __nv_bfloat16* __restrict__ out, int n_tokens, int nh, int nkv, int num_seqs) {
     rv_pdl_launch_dependents();
-    const int seq = blockIdx.x / nh, head = blockIdx.x - seq * nh;
-    const int d = threadIdx.x;
+    const int r = threadIdx.x / COMBINE_TPR, d = (threadIdx.x - r * COMBINE_TPR) * 4;
+    const int item = blockIdx.x * COMBINE_ROWS + r;          // (sequence, query head)
+    const bool live = r < COMBINE_ROWS && item < num_seqs * nh;
+    const int seq = live ? item / nh : 0, head = live ? item - seq * nh : 0;
     const int tok = cu_seqlens[seq];
     const bool decode = cu_seqlens[seq + 1] - tok == 1;       // metadata of the step: read before the wait
     rv_pdl_wait();
-    if (!decode || d >= HEAD_DIM) return;
+    if (!live || !decode) return;
     const int pieces = piece_count[seq * nkv + head / (nh / nkv)];
     const size_t row = (size_t)tok * nh + head;
-    out[row * HEAD_DIM + d] = __float2bfloat16_rn(pieces > 0 ? merge_splits(part_o, part_ml, row, (size_t)n_tokens * nh, pieces, d) : 0.f);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (pieces > 0) v = merge_splits4(part_o, part_ml, row, (size_t)n_tokens * nh, pieces, d);
+    uint2 o2;
+    o2.x = pack_bf16(v.x, v.y);
+    o2.y = pack_bf16(v.z, v.w);
+    *reinterpret_cast<uint2*>(out + row * HEAD_DIM + d) = o2;
 }
 
 // The most pieces a (sequence, kv head) pair can be cut into by `ctas` CTAs when no sequence has more
@@ -1383,9 +1433,9 @@ RV_EXPORT int rv_flash_decode_balanced(const void* q, const void* cache, const i
     RV_LAUNCH_ST = rv_launch(flash_decode_balanced_kernel<DECODE_STAGES>, dim3(ctas), dim3(128), smem, stream, p);
     int st = rv_launch_status();
     if (st != RV_OK) return st;
-    RV_LAUNCH_ST = rv_launch(flash_balanced_combine_kernel, dim3(num_seqs * nh), dim3((HEAD_DIM + 31) / 32 * 32), 0, stream,
+    RV_LAUNCH_ST = rv_launch(flash_balanced_combine_kernel, dim3((num_seqs * nh + COMBINE_ROWS - 1) / COMBINE_ROWS), dim3(128), 0, stream,
                              (const float*)p.part_o, (const float*)p.part_ml, (const int*)piece_count, cu_seqlens, p.out,
-                             n_tokens, nh, nkv);
+                             n_tokens, nh, nkv, num_seqs);
     return rv_launch_status();
 }
 
@@ -1441,7 +1491,7 @@ RV_EXPORT int rv_flash_attention(const void* q, const void* cache, const int* bl
     int st = mode == 1 ? launch_flash<1, 4, DECODE_STAGES>(p, num_seqs, stream) : launch_flash<4, 1, 2>(p, num_seqs, stream);
     if (st != RV_OK) return st;
     if (num_splits > 1) {
-        RV_LAUNCH_ST = rv_launch(flash_combine_kernel, dim3(n_tokens * nh), dim3((HEAD_DIM + 31) / 32 * 32), 0, stream,
+        RV_LAUNCH_ST = rv_launch(flash_combine_kernel, dim3((n_tokens * nh + COMBINE_ROWS - 1) / COMBINE_ROWS), dim3(128), 0, stream,
                                  p.part_o, p.part_ml, p.out, n_tokens * nh, num_splits);
         return rv_launch_status();
     }
@@ -1493,7 +1543,7 @@ RV_EXPORT int rv_flash_decode_tma(const void* q, const void* cache, long long nu
     st = rv_launch_status();
     if (st != RV_OK) return st;
     if (num_splits > 1) {
-        RV_LAUNCH_ST = rv_launch(flash_combine_kernel, dim3(n_tokens * nh), dim3((HEAD_DIM + 31) / 32 * 32), 0, stream,
+        RV_LAUNCH_ST = rv_launch(flash_combine_kernel, dim3((n_tokens * nh + COMBINE_ROWS - 1) / COMBINE_ROWS), dim3(128), 0, stream,
                                  p.part_o, p.part_ml, p.out, n_tokens * nh, num_splits);
         return rv_launch_status();
     }
@@ -1569,9 +1619,9 @@ RV_EXPORT int rv_flash_decode_balanced_tma(const void* q, const void* cache, lon
     RV_LAUNCH_ST = rv_launch(flash_decode_balanced_tma_kernel<TMA_STAGES>, dim3(ctas), dim3(TMA_THREADS), smem, stream, map_kv, p, status);
     st = rv_launch_status();
     if (st != RV_OK) return st;
-    RV_LAUNCH_ST = rv_launch(flash_balanced_combine_kernel, dim3(num_seqs * nh), dim3((HEAD_DIM + 31) / 32 * 32), 0, stream,
+    RV_LAUNCH_ST = rv_launch(flash_balanced_combine_kernel, dim3((num_seqs * nh + COMBINE_ROWS - 1) / COMBINE_ROWS), dim3(128), 0, stream,
                              (const float*)p.part_o, (const float*)p.part_ml, (const int*)piece_count, cu_seqlens, p.out,
-                             n_tokens, nh, nkv);
+                             n_tokens, nh, nkv, num_seqs);
     return rv_launch_status();
 #else
     return RV_ERR_UNSUPPORTED;
