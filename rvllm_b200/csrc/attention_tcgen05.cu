@@ -15,12 +15,18 @@
 //                    float accumulated in tensor memory.
 // P never passes through shared memory, and because P(i) lives in S buffer i mod 2, the softmax of
 // tile i + 1 does not have to wait for the P V product of tile i: softmax and tensor core run side
-// by side, the products ordered among themselves by the order in which the one thread issues them.
-// The reference maximum of a row is only raised when the true maximum has grown by more than 2^8
-// (then O is rescaled in tensor memory), so most tiles need no pass over O; the final division
-// by the row sum uses the same reference.  One thread issues all TMA loads and MMAs; pages are
-// fetched one TMA box per (page, half of hd) through the block table.  Two CTAs fit an SM, so
-// the softmax of one overlaps the MMAs of the other.  Every mbarrier wait is bounded.
+// by side.  The reference maximum of a row is only raised when the true maximum has grown by more
+// than 2^8 (then O is rescaled in tensor memory), so most tiles need no pass over O; the final
+// division by the row sum uses the same reference.
+//
+// Eight warps, every one a chain of waits and a little work per tile, so that none of them is
+// slower than the softmax: four softmax warps (one warpgroup); a loader of Q and the keys and a
+// loader of the values (one TMA box per (page, half of hd) through the block table, whose entries
+// are read a tile ahead; rings of NK and NV stages); a warp whose one thread issues S = Q K^T and
+// one that issues O += P V (S(i) overwrites P(i - 2), so the first follows the second's o_full
+// barrier).  The second warpgroup hands most of its registers to the softmax warps (setmaxnreg).
+// Two CTAs fit an SM, so the softmax of one overlaps that of the other.  Every mbarrier wait is
+// bounded.
 //
 // Rule as in attention_flash.cu (v3/kernels/paged_attention_sm89.cu:277-308 of the reference):
 // token i of the step's q_len tokens sits at p = ctx_len - q_len + i and sees keys (p - window, p].
@@ -35,13 +41,36 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "this kernel is built for head 
 
 #define ROWS 128
 #define KV_TILE 64
+#define SOFTMAX_WARPS 4
+#define LOADER_WARP SOFTMAX_WARPS               // Q and the keys (and the tensor memory's allocation)
+#define VLOADER_WARP (SOFTMAX_WARPS + 1)       // the values
+#define QK_WARP (SOFTMAX_WARPS + 2)            // issues S = Q K^T
+#define PV_WARP (SOFTMAX_WARPS + 3)            // issues O += P V
 #define HALVES (HEAD_DIM / 64)                 // 64-element (128-byte) slabs of the head dimension
 #define Q_BYTES (ROWS * HEAD_DIM * 2)
 #define KV_BYTES (KV_TILE * HEAD_DIM * 2)      // one of K or V for a tile
-#define NUM_THREADS 192               // 4 softmax warps, 1 loader warp, 1 MMA warp
+#define NUM_THREADS (32 * (SOFTMAX_WARPS + 4)) // two warpgroups: the softmax warps; 2 loader warps and 2 MMA warps
+// Two CTAs fit an SM, so a thread starts with 128 registers; the four warps that load and issue give
+// most of theirs back and the softmax warps take them (setmaxnreg works on whole warpgroups).
+#define REGS_SOFTMAX 200
+#define REGS_OTHERS 56
 #define TMEM_COLS 256
-#define S_COL 0                   // two S buffers: columns 0-63 and 64-127; P (bf16 pairs) reuses the first 32 columns of each
+#define S_COL 0                   // two S buffers of 64 columns; P (bf16 pairs) reuses the first 32 columns of each
 #define O_COL 128
+// Stages of the key ring and of the value ring: what fits beside Q with two CTAs on an SM.
+#define NK (HEAD_DIM == 128 ? 3 : 4)
+#define NV (HEAD_DIM == 128 ? 2 : 4)
+// mbarriers, by their index
+#define B_Q 0
+#define B_K 1                      // keys of a stage have landed [NK]
+#define B_KFREE (B_K + NK)         // the S product that read a stage has finished [NK]
+#define B_V (B_KFREE + NK)         // values of a stage have landed [NV]
+#define B_VFREE (B_V + NV)         // the P V product that read a stage has finished [NV]
+#define B_SFULL (B_VFREE + NV)     // [2] each from here on
+#define B_OFULL (B_SFULL + 2)
+#define B_PFULL (B_OFULL + 2)
+#define NUM_BARS (B_PFULL + 2)
+static_assert(NUM_BARS <= 30, "the barriers, the tensor-memory address and the abort flag share 256 bytes");
 #define RESCALE_LOG2 8.0f
 
 struct AttnParams {
@@ -75,6 +104,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// the largest of three in one instruction
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows in the 128 lanes, 16 bf16 of K in 8 columns) from tensor memory
 __device__ __forceinline__ void tcgen05_mma_bf16_ts(uint32_t tmem_c, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
@@ -105,26 +140,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // boundary the 128-byte swizzle needs without a pad, and two CTAs fit an SM.
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* q_s = smem_raw;                           // [HALVES][128 rows x 128 B]
-    unsigned char* k_s = q_s + Q_BYTES;                      // [2 stages][HALVES][64 keys x 128 B]
-    unsigned char* v_s = k_s + 2 * KV_BYTES;                 // [2 stages][HALVES][64 keys x 128 B]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * KV_BYTES);  // 15 barriers
-    uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 15);
-    volatile int& abort_flag = *reinterpret_cast<volatile int*>(bars + 16);
+    unsigned char* k_s = q_s + Q_BYTES;                      // [NK stages][HALVES][KV_TILE keys x 128 B]
+    unsigned char* v_s = k_s + NK * KV_BYTES;                // [NV stages][HALVES][KV_TILE keys x 128 B]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + NV * KV_BYTES);
+    uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 30);
+    volatile int& abort_flag = *reinterpret_cast<volatile int*>(bars + 31);
 
     rv_pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) { tma_prefetch_descriptor(&map_q); tma_prefetch_descriptor(&map_kv); }
-    const uint32_t bar_q = smem_u32(&bars[0]), bar_k0 = smem_u32(&bars[1]);          // k full [2]
-    const uint32_t bar_v0 = smem_u32(&bars[3]);                                      // v full [2]
-    const uint32_t bar_vfree0 = smem_u32(&bars[5]);                                  // v free [2]
-    const uint32_t bar_s_full0 = smem_u32(&bars[7]), bar_s_free0 = smem_u32(&bars[9]);   // [2] each
-    // The P V product of tile i reports on o_full[i mod 2]: a thread that follows every phase of both barriers
-    // in order, and looks at product i - 2 before it lets product i start, is never more than one phase behind
-    // either of them (with one barrier a warp that ran late could not tell phase i - 1 from phase i + 1).
-    // P of tile i is announced on p_full[i mod 2] as well: a softmax warp may run one tile ahead of the
-    // slowest one (it no longer waits for the product of the tile before), and its arrival for tile i + 1
-    // must not be counted among the four of tile i.
-    const uint32_t bar_o_full0 = smem_u32(&bars[11]), bar_p_full0 = smem_u32(&bars[13]);      // o full [2], p full [2]
+    const uint32_t bar_q = smem_u32(&bars[B_Q]), bar_k0 = smem_u32(&bars[B_K]);
+    const uint32_t bar_kfree0 = smem_u32(&bars[B_KFREE]), bar_v0 = smem_u32(&bars[B_V]);
+    const uint32_t bar_vfree0 = smem_u32(&bars[B_VFREE]);
+    const uint32_t bar_s_full0 = smem_u32(&bars[B_SFULL]);
+    // The P V product of tile i reports on o_full[i mod 2], P of tile i on p_full[i mod 2]: two barriers each,
+    // because a waiter may be a tile behind the one that arrives (with one barrier it could not tell phase
+    // i - 1 from phase i + 1; a softmax warp may also run one tile ahead of the slowest, and its arrival for
+    // tile i + 1 must not be counted among the four of tile i).
+    const uint32_t bar_o_full0 = smem_u32(&bars[B_OFULL]), bar_p_full0 = smem_u32(&bars[B_PFULL]);
 
     // Row tiles late in the prompt see the most keys.  CTAs are handed out in the order of their
     // linear index (x fastest), so the row tile is the slowest index, counted down: all heads' and
@@ -151,22 +184,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (tid == 0) {
         abort_flag = 0;
         mbar_init(bar_q, 1);
-        mbar_init(bar_k0, 1); mbar_init(bar_k0 + 8, 1);
-        mbar_init(bar_v0, 1); mbar_init(bar_v0 + 8, 1);
-        mbar_init(bar_vfree0, 1); mbar_init(bar_vfree0 + 8, 1);
+        for (int i = 0; i < NK; ++i) { mbar_init(bar_k0 + 8 * i, 1); mbar_init(bar_kfree0 + 8 * i, 1); }
+        for (int i = 0; i < NV; ++i) { mbar_init(bar_v0 + 8 * i, 1); mbar_init(bar_vfree0 + 8 * i, 1); }
         mbar_init(bar_s_full0, 1); mbar_init(bar_s_full0 + 8, 1);
         // the softmax warps arrive once per warp (after a warp barrier), not once per thread
-        mbar_init(bar_s_free0, 4); mbar_init(bar_s_free0 + 8, 4);
-        mbar_init(bar_p_full0, 4); mbar_init(bar_p_full0 + 8, 4); mbar_init(bar_o_full0, 1); mbar_init(bar_o_full0 + 8, 1);
+        mbar_init(bar_p_full0, SOFTMAX_WARPS); mbar_init(bar_p_full0 + 8, SOFTMAX_WARPS);
+        mbar_init(bar_o_full0, 1); mbar_init(bar_o_full0 + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == LOADER_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     // value tiles start as zeros: a page that is not loaded (beyond the context, or given back by
     // a window) must not meet a probability of zero with a NaN
-    for (int i = tid; i < 2 * KV_BYTES / 16; i += NUM_THREADS) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < NV * KV_BYTES / 16; i += NUM_THREADS) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
     // ... and so do the query rows that the box of whole tokens leaves over (a row is 128 bytes in
     // each half of the head, whatever the swizzle does inside it)
     for (int i = tid; i < (ROWS - tile_rows) * 8 * HALVES; i += NUM_THREADS) {
@@ -183,22 +215,32 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int boxes = KV_TILE / box_keys;
 
     const int n_it = t_end - t_begin;
-    if (warp == 4) {
-        // ------------------------------------------------------------ loader warp: TMA
+    if (warp == LOADER_WARP || warp == VLOADER_WARP) {
+        // ------------------------------------------------------------ loader warps: TMA, one for keys, one for values
         // Lane 0 waits on barriers (the result is broadcast); the lanes share the TMA boxes of a tile,
-        // one (page, both halves of hd) each.  Keys of tile it + 2 follow the product that read the
-        // buffer (tile it); values of tile it + 1 follow the P V product of tile it - 1.
+        // one (page, both halves of hd) each.  The tile that follows a stage's tile (NK or NV tiles on)
+        // is loaded when the product that read the stage has finished; each stage reports on a barrier
+        // of its own, so that a product can never be two phases ahead of its loader.  The block-table
+        // entries of a load are read a turn before it is issued: a loader is one chain of waits and
+        // loads, and has to stay ahead of the products.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_OTHERS));
+        const int which = warp == LOADER_WARP ? 0 : 1;
+        const int stages = which == 0 ? NK : NV;
+        const uint32_t bar_full0 = which == 0 ? bar_k0 : bar_v0, bar_free0 = which == 0 ? bar_kfree0 : bar_vfree0;
+        const uint32_t ring = smem_u32(which == 0 ? k_s : v_s);
         auto wait_all = [&](uint32_t bar, uint32_t parity, int code) -> bool {
             int ok_l = 1;
             if (lane == 0) ok_l = mbar_wait(bar, parity, &abort_flag, code) ? 1 : 0;
             return __shfl_sync(0xffffffffu, ok_l, 0) != 0;
         };
-        auto load_tile = [&](int t, int which, int stage) {
-            const uint32_t bar = (which == 0 ? bar_k0 : bar_v0) + 8 * stage;
-            const uint32_t dst0 = smem_u32(which == 0 ? k_s : v_s) + (uint32_t)stage * KV_BYTES;
+        auto lookup = [&](int t) -> int {               // this lane's page of tile t, or -1
             const int key = t * KV_TILE + lane * box_keys;
-            int page = -1;
-            if (lane < boxes && key < key_hi && key + box_keys > key_lo) page = __ldg(table + (key >> p.page_shift));
+            return (lane < boxes && key < key_hi && key + box_keys > key_lo) ? __ldg(table + (key >> p.page_shift)) : -1;
+        };
+        auto issue = [&](int t, int stage, int page) {
+            const uint32_t bar = bar_full0 + 8 * stage;
+            const uint32_t dst0 = ring + (uint32_t)stage * KV_BYTES;
+            const int key = t * KV_TILE + lane * box_keys;
             const unsigned mask = __ballot_sync(0xffffffffu, page >= 0);
             if (lane == 0) mbar_expect_tx(bar, (uint32_t)__popc(mask) * HALVES * (uint32_t)box_keys * 128u);
             __syncwarp();
@@ -211,72 +253,120 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             __syncwarp();
         };
         // Q: one box of [64 hd, G heads, floor(128 / G) tokens] per half of the head dimension
-        if (lane == 0) {
+        if (which == 0 && lane == 0) {
             mbar_expect_tx(bar_q, (uint32_t)tile_rows * HEAD_DIM * 2);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
                 tma_load_3d(smem_u32(q_s) + h * (ROWS * 128), &map_q, h * 64, kvh * G, q_start + row0 / G, bar_q);
         }
-        load_tile(t_begin, 0, 0);
-        load_tile(t_begin, 1, 0);
-        if (n_it > 1) load_tile(t_begin + 1, 0, 1);
-        for (int it = 0; it < n_it; ++it) {
-            const int t = t_begin + it;
-            if (it + 2 < n_it) {
-                if (!wait_all(bar_s_full0 + 8 * (it & 1), (it >> 1) & 1, 3)) break;
-                load_tile(t + 2, 0, it & 1);
-            }
-            if (it + 1 < n_it) {
-                if (it >= 1 && !wait_all(bar_vfree0 + 8 * ((it + 1) & 1), ((it - 1) >> 1) & 1, 4)) break;
-                load_tile(t + 1, 1, (it + 1) & 1);
-            }
+        for (int i = 0; i < stages && i < n_it; ++i) issue(t_begin + i, i, lookup(t_begin + i));
+        int page = stages < n_it ? lookup(t_begin + stages) : -1;
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int e = 0; e + stages < n_it; ++e) {
+            const int next = e + 1 + stages < n_it ? lookup(t_begin + e + 1 + stages) : -1;
+#ifdef ATTN_TRACE
+            const bool trl = p.status && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && e < 24 && lane == 0;
+            if (trl) p.status[8 + 800 + 800 * which + e * 5 + 0] = (int)clock64();
+#endif
+            if (!wait_all(bar_free0 + 8 * stage, phase, 3 + which)) break;
+#ifdef ATTN_TRACE
+            if (trl) p.status[8 + 800 + 800 * which + e * 5 + 1] = (int)clock64();
+#endif
+            issue(t_begin + e + stages, stage, page);
+#ifdef ATTN_TRACE
+            if (trl) p.status[8 + 800 + 800 * which + e * 5 + 2] = (int)clock64();
+#endif
+            page = next;
+            if (++stage == stages) { stage = 0; phase ^= 1; }
         }
-    } else if (warp == 5) {
-        // ------------------------------------------------------------ MMA warp: one thread issues
+    } else if (warp == QK_WARP) {
+        // ------------------------------------------------------------ first MMA warp: S = Q K^T, one thread issues
+        // S(i) goes into buffer i mod 2, over P(i - 2): the product that read P(i - 2) must have finished
+        // (o_full, which this thread follows phase by phase).  The two kinds of product have a warp each
+        // because a thread that waits on four barriers and issues twelve products a tile is, by itself,
+        // slower than the softmax warps.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_OTHERS));
         if (lane == 0) {
             const uint32_t idesc_s = umma_idesc_bf16(ROWS, KV_TILE);
-            const uint32_t idesc_o = umma_idesc_bf16(ROWS, HEAD_DIM) | (1u << 16);       // B is MN-major
-            auto mma_s = [&](int buf) {          // S[buf] = Q K[buf]^T over the head dimension
+            bool ok = mbar_wait(bar_q, 0, &abort_flag, 1);
+            int k_stage = 0;
+            uint32_t k_phase = 0;
+            for (int i = 0; i < n_it && ok; ++i) {
+                const int buf = i & 1;
+#ifdef ATTN_TRACE
+                const bool trm = p.status && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 24;
+                if (trm) p.status[8 + 400 + i * 5 + 0] = (int)clock64();
+#endif
+                if (!(ok = mbar_wait(bar_k0 + 8 * k_stage, k_phase, &abort_flag, 5))) break;
+#ifdef ATTN_TRACE
+                if (trm) p.status[8 + 400 + i * 5 + 1] = (int)clock64();
+#endif
+                if (i >= 2 && !(ok = mbar_wait(bar_o_full0 + 8 * buf, ((i - 2) >> 1) & 1, &abort_flag, 6))) break;
                 tcgen05_fence_after();
+#ifdef ATTN_TRACE
+                if (trm) p.status[8 + 400 + i * 5 + 2] = (int)clock64();
+#endif
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) {
                     const uint64_t dq = umma_desc(smem_u32(q_s) + h * (ROWS * 128));
-                    const uint64_t dk = umma_desc(smem_u32(k_s) + buf * KV_BYTES + h * (KV_TILE * 128));
+                    const uint64_t dk = umma_desc(smem_u32(k_s) + k_stage * KV_BYTES + h * (KV_TILE * 128));
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
                         tcgen05_mma_bf16(tmem_base + S_COL + buf * KV_TILE, dq + (uint64_t)(2 * j), dk + (uint64_t)(2 * j),
                                          idesc_s, (h | j) != 0);
                 }
                 tcgen05_commit(bar_s_full0 + 8 * buf);
-            };
-            bool ok = mbar_wait(bar_q, 0, &abort_flag, 1) && mbar_wait(bar_k0, 0, &abort_flag, 2);
-            if (ok) mma_s(0);
+                tcgen05_commit(bar_kfree0 + 8 * k_stage);
+#ifdef ATTN_TRACE
+                if (trm) p.status[8 + 400 + i * 5 + 3] = (int)clock64();
+#endif
+                if (++k_stage == NK) { k_stage = 0; k_phase ^= 1; }
+            }
+        }
+    } else if (warp == PV_WARP) {
+        // ------------------------------------------------------------ second MMA warp: O += P V
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_OTHERS));
+        if (lane == 0) {
+            const uint32_t idesc_o = umma_idesc_bf16(ROWS, HEAD_DIM) | (1u << 16);       // B is MN-major
+            bool ok = true;
+            int v_stage = 0;
+            uint32_t v_phase = 0;
             for (int it = 0; it < n_it && ok; ++it) {
                 const int b = it & 1;
-                if (it + 1 < n_it) {
-                    // S(it + 1) is produced while the softmax warps work on S(it); its buffer was read by
-                    // the softmax of tile it - 1
-                    if (!(ok = mbar_wait(bar_k0 + 8 * (b ^ 1), ((it + 1) >> 1) & 1, &abort_flag, 5))) break;
-                    if (it >= 1 && !(ok = mbar_wait(bar_s_free0 + 8 * (b ^ 1), (((it + 1) >> 1) - 1) & 1, &abort_flag, 6))) break;
-                    mma_s(b ^ 1);
-                }
-                if (!(ok = mbar_wait(bar_v0 + 8 * b, (it >> 1) & 1, &abort_flag, 7))) break;
-                // O += P V once the softmax warps have written P (and rescaled O if they had to)
+#ifdef ATTN_TRACE
+                const bool trm = p.status && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && it < 24;
+                if (trm) p.status[8 + 2400 + it * 5 + 0] = (int)clock64();
+#endif
+                if (!(ok = mbar_wait(bar_v0 + 8 * v_stage, v_phase, &abort_flag, 7))) break;
+#ifdef ATTN_TRACE
+                if (trm) p.status[8 + 2400 + it * 5 + 1] = (int)clock64();
+#endif
+                // once the softmax warps have written P (and rescaled O if they had to)
                 if (!(ok = mbar_wait(bar_p_full0 + 8 * b, (it >> 1) & 1, &abort_flag, 8))) break;
                 tcgen05_fence_after();
-                const uint32_t tp = tmem_base + S_COL + b * KV_TILE;     // P(it): bf16 pairs in the first 32 columns of S buffer b
-                const uint64_t dv = umma_desc_mn(smem_u32(v_s) + b * KV_BYTES, KV_TILE * 128);
+#ifdef ATTN_TRACE
+                if (trm) p.status[8 + 2400 + it * 5 + 2] = (int)clock64();
+#endif
+                const uint32_t tp = tmem_base + S_COL + b * KV_TILE;     // P(it): bf16 pairs in the first half of S buffer b
+                const uint64_t dv = umma_desc_mn(smem_u32(v_s) + v_stage * KV_BYTES, KV_TILE * 128);
 #pragma unroll
                 for (int j = 0; j < KV_TILE / 16; ++j)   // 16 keys per MMA: 8 columns along P's rows, 2048 bytes down V
                     tcgen05_mma_bf16_ts(tmem_base + O_COL, tp + 8 * j, dv + (uint64_t)(128 * j), idesc_o, (it | j) != 0);
-                tcgen05_commit(bar_vfree0 + 8 * b);
+                tcgen05_commit(bar_vfree0 + 8 * v_stage);
                 tcgen05_commit(bar_o_full0 + 8 * b);
+#ifdef ATTN_TRACE
+                if (trm) p.status[8 + 2400 + it * 5 + 3] = (int)clock64();
+#endif
+                if (++v_stage == NV) { v_stage = 0; v_phase ^= 1; }
             }
         }
     } else {
         // ------------------------------------------------------------ softmax warps: one thread per row
-        const int r = row0 + warp * 32 + lane;               // packed row; TMEM lane = warp * 32 + lane
-        const bool in_range = warp * 32 + lane < tile_rows && r < rows_total;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
+        const int row_l = warp * 32 + lane;                  // row of the tile = TMEM lane
+        const int r = row0 + row_l;                          // packed row
+        const bool in_range = row_l < tile_rows && r < rows_total;
         const int tok_i = in_range ? r / G : 0;
         const int head = kvh * G + (in_range ? r - tok_i * G : 0);
         const int pos = in_range ? ctx - q_len + tok_i : -1;
@@ -284,7 +374,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
         float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
-        bool prev_waited = false;    // whether this iteration's rescale has already waited for the product of the tile before
         for (int t = t_begin; t < t_end; ++t) {
             const int it = t - t_begin;
             const int sb = it & 1;
@@ -303,24 +392,26 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tmem_ld_wait();
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_s_free0 + 8 * sb);   // this S buffer may be overwritten two tiles on
             const int key0 = t * KV_TILE;
             // Scores stay raw in the registers; scale and reference maximum are applied in one FMA
             // before the exponential.  Only tiles that cross the row's visible range need masks.
-            float m_raw = -INFINITY;
-            if (key0 + KV_TILE - 1 <= pos && key0 >= lo) {
-#pragma unroll
-                for (int e = 0; e < 32; ++e)
-                    m_raw = fmaxf(m_raw, fmaxf(__uint_as_float(s0[e]), __uint_as_float(s1[e])));
-            } else {
+            if (!(key0 + KV_TILE - 1 <= pos && key0 >= lo)) {
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
                     const int ka = key0 + e, kb = key0 + 32 + e;
                     if (!(ka <= pos && ka >= lo)) s0[e] = 0xff800000u;        // -inf
                     if (!(kb <= pos && kb >= lo)) s1[e] = 0xff800000u;
-                    m_raw = fmaxf(m_raw, fmaxf(__uint_as_float(s0[e]), __uint_as_float(s1[e])));
                 }
             }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains: one would be a chain of latencies
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+                mx[0] = max3(mx[0], __uint_as_float(s0[e]), __uint_as_float(s0[e + 1]));
+                mx[1] = max3(mx[1], __uint_as_float(s0[e + 2]), __uint_as_float(s0[e + 3]));
+                mx[2] = max3(mx[2], __uint_as_float(s1[e]), __uint_as_float(s1[e + 1]));
+                mx[3] = max3(mx[3], __uint_as_float(s1[e + 2]), __uint_as_float(s1[e + 3]));
+            }
+            const float m_raw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
             const float m_tile = m_raw * p.scale_log2e;       // the scale is positive: the maximum commutes
             // raise the reference maximum only when it is far behind: O then needs a pass
             const bool first_data = m_ref == -INFINITY && m_tile > -INFINITY;
@@ -336,16 +427,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #ifdef ATTN_TRACE
             if (tr) p.status[8 + it * 5 + 2] = (int)clock64();
 #endif
-            // product it - 2 (finished before S(it) was produced) is looked at before product it may start,
-            // unless the rescale of the tile before has looked at it already
-            if (it >= 2 && !prev_waited &&
-                !mbar_wait(bar_o_full0 + 8 * (it & 1), ((it - 2) >> 1) & 1, &abort_flag, 12)) { ok = false; break; }
-            prev_waited = false;
             const bool any_raise = __any_sync(0xffffffffu, raise && it > 0);
             if (any_raise) {
-                // O is rescaled: the product of the tile before must have finished
+                // O is rescaled: the product of the tile before must have finished.  The one before that
+                // has (S(it - 1) was only issued after it), and the one after cannot have started (it needs
+                // this warp's P), so the parity of o_full[(it - 1) mod 2] cannot be mistaken.
                 if (!mbar_wait(bar_o_full0 + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1, &abort_flag, 11)) { ok = false; break; }
-                prev_waited = true;
                 tcgen05_fence_after();
 #pragma unroll
                 for (int c = 0; c < HEAD_DIM; c += 32) {
@@ -419,7 +506,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == LOADER_WARP) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
     }
     if (tid == 0 && abort_flag != 0 && p.status) atomicCAS(p.status, 0, abort_flag);
@@ -470,7 +557,7 @@ RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long n
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.window = window;
-    const int smem = Q_BYTES + 4 * KV_BYTES + 256;
+    const int smem = Q_BYTES + (NK + NV) * KV_BYTES + 256;
     static RvPerDevice configured;
     if (int e = rv_configure_smem(configured, attention_tcgen05_kernel, smem)) return e;
     const int tile_tokens = ROWS / G;
