@@ -215,6 +215,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int boxes = KV_TILE / box_keys;
 
     const int n_it = t_end - t_begin;
+#ifdef ATTN_TRACE
+    const int tr0 = p.status ? p.status[1] : 0, tr_z = p.status ? p.status[2] : 0;
+    if (p.status && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && (int)blockIdx.z == tr_z) { p.status[4] = (int)clock64(); p.status[6] = n_it; unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); p.status[3] = (int)(unsigned)g; }
+#endif
     if (warp == LOADER_WARP || warp == VLOADER_WARP) {
         // ------------------------------------------------------------ loader warps: TMA, one for keys, one for values
         // Lane 0 waits on barriers (the result is broadcast); the lanes share the TMA boxes of a tile,
@@ -266,16 +270,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int e = 0; e + stages < n_it; ++e) {
             const int next = e + 1 + stages < n_it ? lookup(t_begin + e + 1 + stages) : -1;
 #ifdef ATTN_TRACE
-            const bool trl = p.status && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && e < 24 && lane == 0;
-            if (trl) p.status[8 + 800 + 800 * which + e * 5 + 0] = (int)clock64();
+            const bool trl = p.status && blockIdx.x == 0 && blockIdx.y == 0 && (int)blockIdx.z == tr_z && e >= tr0 && e < tr0 + 24 && lane == 0;
+            if (trl) p.status[8 + 800 + 800 * which + (e - tr0) * 5 + 0] = (int)clock64();
 #endif
             if (!wait_all(bar_free0 + 8 * stage, phase, 3 + which)) break;
 #ifdef ATTN_TRACE
-            if (trl) p.status[8 + 800 + 800 * which + e * 5 + 1] = (int)clock64();
+            if (trl) p.status[8 + 800 + 800 * which + (e - tr0) * 5 + 1] = (int)clock64();
 #endif
             issue(t_begin + e + stages, stage, page);
 #ifdef ATTN_TRACE
-            if (trl) p.status[8 + 800 + 800 * which + e * 5 + 2] = (int)clock64();
+            if (trl) p.status[8 + 800 + 800 * which + (e - tr0) * 5 + 2] = (int)clock64();
 #endif
             page = next;
             if (++stage == stages) { stage = 0; phase ^= 1; }
@@ -295,17 +299,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int i = 0; i < n_it && ok; ++i) {
                 const int buf = i & 1;
 #ifdef ATTN_TRACE
-                const bool trm = p.status && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 24;
-                if (trm) p.status[8 + 400 + i * 5 + 0] = (int)clock64();
+                const bool trm = p.status && blockIdx.x == 0 && blockIdx.y == 0 && (int)blockIdx.z == tr_z && i >= tr0 && i < tr0 + 24;
+                if (trm) p.status[8 + 400 + (i - tr0) * 5 + 0] = (int)clock64();
 #endif
                 if (!(ok = mbar_wait(bar_k0 + 8 * k_stage, k_phase, &abort_flag, 5))) break;
 #ifdef ATTN_TRACE
-                if (trm) p.status[8 + 400 + i * 5 + 1] = (int)clock64();
+                if (trm) p.status[8 + 400 + (i - tr0) * 5 + 1] = (int)clock64();
 #endif
                 if (i >= 2 && !(ok = mbar_wait(bar_o_full0 + 8 * buf, ((i - 2) >> 1) & 1, &abort_flag, 6))) break;
                 tcgen05_fence_after();
 #ifdef ATTN_TRACE
-                if (trm) p.status[8 + 400 + i * 5 + 2] = (int)clock64();
+                if (trm) p.status[8 + 400 + (i - tr0) * 5 + 2] = (int)clock64();
 #endif
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) {
@@ -319,7 +323,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tcgen05_commit(bar_s_full0 + 8 * buf);
                 tcgen05_commit(bar_kfree0 + 8 * k_stage);
 #ifdef ATTN_TRACE
-                if (trm) p.status[8 + 400 + i * 5 + 3] = (int)clock64();
+                if (trm) p.status[8 + 400 + (i - tr0) * 5 + 3] = (int)clock64();
 #endif
                 if (++k_stage == NK) { k_stage = 0; k_phase ^= 1; }
             }
@@ -335,18 +339,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int it = 0; it < n_it && ok; ++it) {
                 const int b = it & 1;
 #ifdef ATTN_TRACE
-                const bool trm = p.status && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && it < 24;
-                if (trm) p.status[8 + 2400 + it * 5 + 0] = (int)clock64();
+                const bool trm = p.status && blockIdx.x == 0 && blockIdx.y == 0 && (int)blockIdx.z == tr_z && it >= tr0 && it < tr0 + 24;
+                if (trm) p.status[8 + 2400 + (it - tr0) * 5 + 0] = (int)clock64();
 #endif
                 if (!(ok = mbar_wait(bar_v0 + 8 * v_stage, v_phase, &abort_flag, 7))) break;
 #ifdef ATTN_TRACE
-                if (trm) p.status[8 + 2400 + it * 5 + 1] = (int)clock64();
+                if (trm) p.status[8 + 2400 + (it - tr0) * 5 + 1] = (int)clock64();
 #endif
                 // once the softmax warps have written P (and rescaled O if they had to)
                 if (!(ok = mbar_wait(bar_p_full0 + 8 * b, (it >> 1) & 1, &abort_flag, 8))) break;
                 tcgen05_fence_after();
 #ifdef ATTN_TRACE
-                if (trm) p.status[8 + 2400 + it * 5 + 2] = (int)clock64();
+                if (trm) p.status[8 + 2400 + (it - tr0) * 5 + 2] = (int)clock64();
 #endif
                 const uint32_t tp = tmem_base + S_COL + b * KV_TILE;     // P(it): bf16 pairs in the first half of S buffer b
                 const uint64_t dv = umma_desc_mn(smem_u32(v_s) + v_stage * KV_BYTES, KV_TILE * 128);
@@ -356,7 +360,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tcgen05_commit(bar_vfree0 + 8 * v_stage);
                 tcgen05_commit(bar_o_full0 + 8 * b);
 #ifdef ATTN_TRACE
-                if (trm) p.status[8 + 2400 + it * 5 + 3] = (int)clock64();
+                if (trm) p.status[8 + 2400 + (it - tr0) * 5 + 3] = (int)clock64();
 #endif
                 if (++v_stage == NV) { v_stage = 0; v_phase ^= 1; }
             }
@@ -378,12 +382,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const int it = t - t_begin;
             const int sb = it & 1;
 #ifdef ATTN_TRACE
-            const bool tr = p.status && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0 && it < 24;
-            if (tr) p.status[8 + it * 5 + 0] = (int)clock64();
+            const bool tr = p.status && blockIdx.x == 0 && blockIdx.y == 0 && (int)blockIdx.z == tr_z && tid == 0 && it >= tr0 && it < tr0 + 24;
+            if (tr) p.status[8 + (it - tr0) * 5 + 0] = (int)clock64();
 #endif
             if (!mbar_wait(bar_s_full0 + 8 * sb, (it >> 1) & 1, &abort_flag, 9)) { ok = false; break; }
 #ifdef ATTN_TRACE
-            if (tr) p.status[8 + it * 5 + 1] = (int)clock64();
+            if (tr) p.status[8 + (it - tr0) * 5 + 1] = (int)clock64();
 #endif
             tcgen05_fence_after();
             uint32_t s0[32], s1[32];
@@ -425,7 +429,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             // P(it) goes into S buffer sb, which no product reads any more (P(it - 2) was consumed before
             // S(it) was produced), so only a rescale of O has to wait for the P V product of the tile before.
 #ifdef ATTN_TRACE
-            if (tr) p.status[8 + it * 5 + 2] = (int)clock64();
+            if (tr) p.status[8 + (it - tr0) * 5 + 2] = (int)clock64();
 #endif
             const bool any_raise = __any_sync(0xffffffffu, raise && it > 0);
             if (any_raise) {
@@ -447,7 +451,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tcgen05_fence_before();
             }
 #ifdef ATTN_TRACE
-            if (tr) p.status[8 + it * 5 + 3] = (int)clock64();
+            if (tr) p.status[8 + (it - tr0) * 5 + 3] = (int)clock64();
 #endif
             const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
             float l_tile = 0.f, l_tile2 = 0.f;
@@ -470,7 +474,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_p_full0 + 8 * sb);
 #ifdef ATTN_TRACE
-            if (tr) p.status[8 + it * 5 + 4] = (int)clock64();
+            if (tr) p.status[8 + (it - tr0) * 5 + 4] = (int)clock64();
 #endif
         }
         if (ok) {
@@ -506,6 +510,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     tcgen05_fence_before();
     __syncthreads();
+#ifdef ATTN_TRACE
+    if (p.status && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && (int)blockIdx.z == tr_z) { p.status[5] = (int)clock64(); unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); p.status[7] = (int)(unsigned)g; }
+#endif
     if (warp == LOADER_WARP) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
     }
