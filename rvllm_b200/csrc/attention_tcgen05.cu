@@ -219,6 +219,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int tr0 = p.status ? p.status[1] : 0, tr_z = p.status ? p.status[2] : 0;
     if (p.status && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && (int)blockIdx.z == tr_z) { p.status[4] = (int)clock64(); p.status[6] = n_it; unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); p.status[3] = (int)(unsigned)g; }
 #endif
+    int tiles_issued = 0;             // by this warp, if it is a loader
     if (warp == LOADER_WARP || warp == VLOADER_WARP) {
         // ------------------------------------------------------------ loader warps: TMA, one for keys, one for values
         // Lane 0 waits on barriers (the result is broadcast); the lanes share the TMA boxes of a tile,
@@ -263,7 +264,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int h = 0; h < HALVES; ++h)
                 tma_load_3d(smem_u32(q_s) + h * (ROWS * 128), &map_q, h * 64, kvh * G, q_start + row0 / G, bar_q);
         }
-        for (int i = 0; i < stages && i < n_it; ++i) issue(t_begin + i, i, lookup(t_begin + i));
+        for (int i = 0; i < stages && i < n_it; ++i, ++tiles_issued) issue(t_begin + i, i, lookup(t_begin + i));
         int page = stages < n_it ? lookup(t_begin + stages) : -1;
         int stage = 0;
         uint32_t phase = 0;
@@ -278,6 +279,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (trl) p.status[8 + 800 + 800 * which + (e - tr0) * 5 + 1] = (int)clock64();
 #endif
             issue(t_begin + e + stages, stage, page);
+            ++tiles_issued;
 #ifdef ATTN_TRACE
             if (trl) p.status[8 + 800 + 800 * which + (e - tr0) * 5 + 2] = (int)clock64();
 #endif
@@ -510,6 +512,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     tcgen05_fence_before();
     __syncthreads();
+    if (abort_flag != 0) {
+        // A wait gave up somewhere: tiles may still be on their way into this CTA's shared memory with nobody
+        // left to wait for them.  Their loaders do (bounded, without touching the flag) before the CTA ends.
+        if ((warp == LOADER_WARP || warp == VLOADER_WARP) && lane == 0) {
+            volatile int ignore = 0;
+            const int stages = warp == LOADER_WARP ? NK : NV;
+            const uint32_t full0 = warp == LOADER_WARP ? bar_k0 : bar_v0;
+            if (warp == LOADER_WARP) mbar_wait(bar_q, 0, &ignore, 0);
+            for (int i = max(0, tiles_issued - stages); i < tiles_issued; ++i)
+                mbar_wait(full0 + 8 * (i % stages), (i / stages) & 1, &ignore, 0);
+        }
+        __syncthreads();
+    }
 #ifdef ATTN_TRACE
     if (p.status && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && (int)blockIdx.z == tr_z) { p.status[5] = (int)clock64(); unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); p.status[7] = (int)(unsigned)g; }
 #endif
