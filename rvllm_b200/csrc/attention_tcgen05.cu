@@ -110,6 +110,15 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
+// two multiply-adds, two additions in one instruction each (packed pairs of floats)
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}" : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1) {
+    asm("{\n\t.reg .b64 ra, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rd, {%0, %1};\n\tadd.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "+f"(d0), "+f"(d1) : "f"(a0), "f"(a1));
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows in the 128 lanes, 16 bf16 of K in 8 columns) from tensor memory
 __device__ __forceinline__ void tcgen05_mma_bf16_ts(uint32_t tmem_c, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
@@ -461,10 +470,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
             for (int j = 0; j < 32; ++j) {                   // keys 2j and 2j + 1 of the tile: one column of P
                 const int e = 2 * j;
-                const float x0 = fast_exp2(fmaf(__uint_as_float(e < 32 ? s0[e] : s1[e - 32]), p.scale_log2e, neg_m));
-                const float x1 = fast_exp2(fmaf(__uint_as_float(e + 1 < 32 ? s0[e + 1] : s1[e + 1 - 32]), p.scale_log2e, neg_m));
-                l_tile += x0;
-                l_tile2 += x1;
+                float a0, a1;
+                fma2(a0, a1, __uint_as_float(e < 32 ? s0[e] : s1[e - 32]), __uint_as_float(e + 1 < 32 ? s0[e + 1] : s1[e + 1 - 32]),
+                     p.scale_log2e, neg_m);
+                const float x0 = fast_exp2(a0), x1 = fast_exp2(a1);
+                add2(l_tile, l_tile2, x0, x1);
                 __nv_bfloat162 h2 = __floats2bfloat162_rn(x0, x1);
                 pk[j] = *reinterpret_cast<uint32_t*>(&h2);
             }
